@@ -1,0 +1,184 @@
+/*
+ * pa_b200.h - C ABI of the B200 (sm_100a) PagedAttention operator.
+ *
+ * The entry points below are what an OpenVINO `ov::op::Op::evaluate()` shim (or the
+ * ModelRunner itself) binds in place of the PagedAttentionExtension operator that the
+ * reference inserts with ov::pass::SDPAToPagedAttention
+ * (src/cpp/src/continuous_batching/pipeline_impl.cpp:73-92) and runs inside
+ * ov::InferRequest::infer() (src/cpp/src/continuous_batching/model_runner.hpp:953).
+ * Argument names and meaning follow the model-level tensors that ModelRunner::forward
+ * fills (model_runner.hpp:505-522, 802-853, 1420-1509).
+ *
+ * Conventions
+ *  - Plain C: pointers, sizes, integer status codes.  No exceptions cross this boundary.
+ *  - The caller owns every buffer it passes.  The handle owns only its own scratch.
+ *  - Device kernels never trap and never spin without a bound: a bad block index or a
+ *    non-monotonic prefix sum sets a bit in a device status word and the offending row is
+ *    skipped; pa_b200_last_device_status() reads the word.
+ *  - One handle serves one engine thread (ContinuousBatchingImpl::step() is single
+ *    threaded, pipeline_impl.cpp:378-533).  Calls on one handle are ordered on the
+ *    handle's stream (or the stream passed in the args).
+ */
+#ifndef PA_B200_H
+#define PA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PA_B200_ABI_VERSION 1
+
+typedef enum pa_status {
+    PA_OK = 0,
+    PA_ERR_INVALID_ARG = 1,  /* NULL pointer, negative size, struct_size mismatch         */
+    PA_ERR_UNSUPPORTED = 2,  /* sliding_window / alibi / unsupported head size or dtype   */
+    PA_ERR_CUDA = 3,         /* a CUDA runtime call failed; see pa_b200_last_error()      */
+    PA_ERR_BAD_INDEX = 4,    /* device status word reported an out-of-range block index   */
+    PA_ERR_NO_DEVICE = 5,    /* no sm_100 device / library built without a usable kernel  */
+    PA_ERR_TOO_LARGE = 6     /* request exceeds a stated fixed capacity                   */
+} pa_status;
+
+typedef enum pa_dtype {
+    PA_DTYPE_F32 = 0,
+    PA_DTYPE_F16 = 1,
+    PA_DTYPE_BF16 = 2,
+    PA_DTYPE_U8 = 3 /* cache only: by-token asymmetric u8, one (scale, zero-point) f32 pair per token per head */
+} pa_dtype;
+
+/* Bits of the device status word. */
+#define PA_DEV_BAD_BLOCK_INDEX 0x1u   /* block_indices[i] outside [0, num_blocks)           */
+#define PA_DEV_BAD_BEGINS 0x2u        /* subsequence_begins / block_indices_begins invalid  */
+#define PA_DEV_BAD_PAST_LEN 0x4u      /* past_lens < 0 or block table too short             */
+#define PA_DEV_BAD_ROTATION 0x8u      /* rotated block id or LUT row out of range           */
+
+/* Static attributes of one attention layer.  Replaces what KVCacheManager reads from the
+ * compiled model's key_cache.N / value_cache.N ports
+ * (src/cpp/src/continuous_batching/cache/kv_cache_manager.hpp:56-113). */
+typedef struct pa_model_desc {
+    uint32_t struct_size; /* sizeof(pa_model_desc) */
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t head_size;   /* 64 or 128 */
+    int32_t block_size;  /* tokens per physical block: 16 or 32 */
+    int32_t act_dtype;   /* pa_dtype of query/key/value/output: F16, BF16 or F32 */
+    int32_t cache_dtype; /* pa_dtype of key_cache/value_cache: F16, BF16 or U8   */
+} pa_model_desc;
+
+/* What the caller's cache allocator must honour.  genai treats the cache as opaque bytes and
+ * only copies whole blocks (kv_cache_manager.hpp:278-335), so the element order inside a block
+ * is this library's choice:
+ *   f16/bf16  key   [num_blocks][Hkv][block_size][D]
+ *             value [num_blocks][Hkv][block_size][D]
+ *   u8        key   [num_blocks][Hkv]{ u8 data[block_size][D], f32 scale[block_size], f32 zp[block_size] }
+ *             value [num_blocks][Hkv]{ u8 data[D][block_size], f32 scale[block_size], f32 zp[block_size] }
+ *             (value data is token-minor so that P.V contracts over contiguous bytes)
+ * The declared 4-D shape for u8 is [num_blocks, Hkv, block_size, D + 8], same byte count. */
+typedef struct pa_cache_layout {
+    uint32_t struct_size;
+    int32_t elem_dtype;          /* element type to declare on the port (F16, BF16, U8) */
+    int64_t key_shape[4];        /* [0 (= any number of blocks), Hkv, block_size, D or D+8] */
+    int64_t value_shape[4];
+    int64_t key_block_bytes;     /* bytes of one physical block, all heads */
+    int64_t value_block_bytes;
+    int32_t base_alignment;      /* required alignment of the cache base pointers, bytes */
+} pa_cache_layout;
+
+/* One operator invocation (one layer, one step).  Field names = the reference's tensor names. */
+typedef struct pa_forward_args {
+    uint32_t struct_size; /* sizeof(pa_forward_args) */
+
+    /* Activations, row-major [num_tokens, H*D], element type = pa_model_desc.act_dtype. */
+    const void* query;  /* [num_tokens, Hq*D]  */
+    const void* key;    /* [num_tokens, Hkv*D] new keys, written to the cache by this call   */
+    const void* value;  /* [num_tokens, Hkv*D] new values                                    */
+    void* output;       /* [num_tokens, Hq*D]  */
+    int32_t num_tokens;
+
+    /* Paged cache, device memory, layout per pa_b200_query_cache_layout(). */
+    void* key_cache;
+    void* value_cache;
+    int32_t num_blocks; /* physical blocks in each cache tensor */
+
+    /* Scheduler metadata (model_runner.hpp:509-516).  i32. */
+    const int32_t* past_lens;            /* [num_sequences]     */
+    const int32_t* subsequence_begins;   /* [num_sequences + 1] */
+    const int32_t* block_indices;        /* [num_block_indices] */
+    const int32_t* block_indices_begins; /* [num_sequences + 1] */
+    int32_t num_sequences;
+    int32_t num_block_indices;
+    int32_t max_context_len;             /* max over sequences of past_len + new tokens */
+
+    float scale;                         /* 0 => 1/sqrt(head_size) */
+    int32_t sliding_window;              /* must be 0 (PA_ERR_UNSUPPORTED otherwise) */
+    const float* alibi_slopes;           /* must be NULL */
+
+    /* Eviction support (model_runner.hpp:838-848, 1483-1568).  All optional. */
+    const int32_t* score_aggregation_window; /* [num_sequences] or NULL                       */
+    float* scores;                           /* [sum_s (past_len_s + new_s)] or NULL          */
+    int64_t scores_len;
+    const int32_t* rotated_block_indices;    /* [num_rotated_blocks] physical ids or NULL     */
+    const int32_t* rotation_deltas;          /* [num_rotated_blocks, 1] rows of the trig LUT  */
+    int32_t num_rotated_blocks;
+    const float* rotation_trig_lut;          /* [rotation_lut_rows, head_size] cos | -sin     */
+    int32_t rotation_lut_rows;
+
+    void* stream; /* cudaStream_t, NULL => the handle's stream */
+} pa_forward_args;
+
+typedef struct pa_handle pa_handle;
+
+/* Library / device probing. */
+int pa_b200_abi_version(void);
+const char* pa_b200_last_error(void); /* thread-local text of the last PA_ERR_CUDA / INVALID_ARG */
+
+/* Cache layout query: what KVCacheManager would read from the model ports
+ * (kv_cache_manager.hpp:74-113). */
+int pa_b200_query_cache_layout(const pa_model_desc* desc, pa_cache_layout* out);
+
+/* Handle life cycle.  `device` is a CUDA ordinal.  The handle allocates its scratch with
+ * cudaMalloc at creation and when a later call needs more (never inside a kernel). */
+int pa_b200_create(const pa_model_desc* desc, int device, pa_handle** out);
+int pa_b200_destroy(pa_handle* h);
+
+/* Scratch bytes a forward call of this shape needs (split-K partials, score partials,
+ * device copies of host metadata).  pa_b200_reserve() grows the handle's scratch to it so that
+ * later calls of that shape do not allocate. */
+int64_t pa_b200_workspace_bytes(const pa_handle* h, int32_t num_tokens, int32_t num_sequences,
+                                int32_t max_context_len, int64_t scores_len);
+int pa_b200_reserve(pa_handle* h, int32_t num_tokens, int32_t num_sequences, int32_t max_context_len,
+                    int64_t scores_len, int32_t num_block_indices);
+
+/* The operator: every pointer in `args` is DEVICE memory.  Asynchronous on the stream.
+ * Replaces the PagedAttentionExtension node executed by infer() (model_runner.hpp:953). */
+int pa_b200_forward(pa_handle* h, const pa_forward_args* args);
+
+/* Same operator for a caller that holds HOST tensors, as ModelRunner does for everything
+ * except the cache (model_runner.hpp:505-522 fills host ov::Tensors): query/key/value/output,
+ * the metadata, the rotation inputs and `scores` are HOST pointers; key_cache/value_cache stay
+ * device pointers.  Copies in, runs, copies out, synchronises, and returns PA_ERR_BAD_INDEX if
+ * the device status word is non-zero. */
+int pa_b200_forward_host(pa_handle* h, const pa_forward_args* args);
+
+/* Reads (and clears) the device status word; synchronises the handle's stream. */
+int pa_b200_last_device_status(pa_handle* h, uint32_t* status_bits);
+
+/* Number of kernels this handle has launched since creation (for launch accounting). */
+int64_t pa_b200_launch_count(const pa_handle* h);
+
+/* Stand-alone cache operations used by the operator and by the cache manager.
+ *  - write: scatter `num_tokens` new K/V rows into their slots (quantising for u8).
+ *  - rotate: re-rotate the keys of the listed blocks in place (pipeline_impl.cpp:810-882).
+ *  - copy_blocks: copy-on-write block copies (kv_cache_manager.hpp:278-335);
+ *    src_dst_pairs is [num_pairs][2] i32 in device memory. */
+int pa_b200_write_kv(pa_handle* h, const pa_forward_args* args);
+int pa_b200_rotate_blocks(pa_handle* h, const pa_forward_args* args);
+int pa_b200_copy_blocks(pa_handle* h, void* key_cache, void* value_cache, int32_t num_blocks,
+                        const int32_t* src_dst_pairs, int32_t num_pairs, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PA_B200_H */

@@ -1,0 +1,234 @@
+// Cache maintenance kernels of the PagedAttention operator: writing a chunk's new keys / values
+// into their paged slots (with by-token u8 quantisation), re-rotating the keys of listed blocks,
+// and block copies for copy-on-write.  All three are HBM-bound byte movers; one warp owns one
+// (token, kv head) row so the min/max for the quantiser is a warp shuffle.
+#include "pa_common.cuh"
+#include "pa_kernels.h"
+
+namespace pa {
+
+namespace {
+
+// Locates the sequence that owns flattened token `t` by binary search in subsequence_begins.
+__device__ __forceinline__ int find_sequence(const int32_t* begins, int num_seq, int t) {
+    int lo = 0, hi = num_seq;  // begins[lo] <= t < begins[hi]
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (begins[mid] <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// One warp per (token, kv head).  Lane l owns dims {l + 32*i}.
+template <int D>
+__global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
+    constexpr int PER = D / 32;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total = a.num_tokens * a.g.Hkv;
+    if (warp >= total) return;
+    const int t = warp / a.g.Hkv, h = warp % a.g.Hkv;
+    const int s = find_sequence(a.subsequence_begins, a.num_sequences, t);
+    const int t0 = a.subsequence_begins[s];
+    const int n = a.subsequence_begins[s + 1] - t0;
+    const int past = a.past_lens[s];
+    const int tb = a.block_indices_begins[s];
+    const int nb = a.block_indices_begins[s + 1] - tb;
+    const int pos = past + (t - t0);
+    if (past < 0 || n <= 0 || pos / a.g.bs >= nb) {
+        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
+        return;
+    }
+    const int block = a.block_indices[tb + pos / a.g.bs];
+    if (block < 0 || block >= a.num_blocks) {
+        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
+        return;
+    }
+    const int slot = pos % a.g.bs;
+    const long long src = ((long long)t * a.g.Hkv + h) * D;
+    const long long rec = (long long)block * a.g.block_bytes + (long long)h * a.g.head_bytes;
+    float k[PER], v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        k[i] = load_act(a.key, src + lane + 32 * i, a.g.act);
+        v[i] = load_act(a.value, src + lane + 32 * i, a.g.act);
+    }
+    if (a.g.cache == PA_DTYPE_U8) {
+        uint8_t* kr = (uint8_t*)a.key_cache + rec;
+        uint8_t* vr = (uint8_t*)a.value_cache + rec;
+        float kmn = k[0], kmx = k[0], vmn = v[0], vmx = v[0];
+#pragma unroll
+        for (int i = 1; i < PER; ++i) {
+            kmn = fminf(kmn, k[i]); kmx = fmaxf(kmx, k[i]);
+            vmn = fminf(vmn, v[i]); vmx = fmaxf(vmx, v[i]);
+        }
+        kmn = warp_min(kmn); kmx = warp_max(kmx); vmn = warp_min(vmn); vmx = warp_max(vmx);
+        float ks, kz, ki, vs, vz, vi;
+        quant_params(kmn, kmx, ks, kz, ki);
+        quant_params(vmn, vmx, vs, vz, vi);
+        float* kp = (float*)(kr + (long long)a.g.bs * D);
+        float* vp = (float*)(vr + (long long)a.g.bs * D);
+        if (lane == 0) {
+            kp[slot] = ks; kp[a.g.bs + slot] = kz;
+            vp[slot] = vs; vp[a.g.bs + slot] = vz;
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + 32 * i;
+            kr[(long long)slot * D + d] = (uint8_t)quant_one(k[i], ki, kz);   // key data   [bs][D]
+            vr[(long long)d * a.g.bs + slot] = (uint8_t)quant_one(v[i], vi, vz);  // value data [D][bs]
+        }
+    } else {
+        uint16_t* kr = (uint16_t*)((uint8_t*)a.key_cache + rec) + (long long)slot * D;
+        uint16_t* vr = (uint16_t*)((uint8_t*)a.value_cache + rec) + (long long)slot * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + 32 * i;
+            if (a.g.cache == PA_DTYPE_F16) {
+                kr[d] = __half_as_ushort(__float2half_rn(k[i]));
+                vr[d] = __half_as_ushort(__float2half_rn(v[i]));
+            } else {
+                kr[d] = __bfloat16_as_ushort(__float2bfloat16_rn(k[i]));
+                vr[d] = __bfloat16_as_ushort(__float2bfloat16_rn(v[i]));
+            }
+        }
+    }
+}
+
+// One warp per (rotated block, kv head, token).  Lane l owns the pairs (j, j + D/2) for
+// j in {l + 32*i}.  k'[j] = fma(-k[j+D/2], s, k[j]*c);  k'[j+D/2] = fma(k[j], s, k[j+D/2]*c)
+// with c = lut[row][j], s = lut[row][D/2 + j].
+template <int D>
+__global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
+    constexpr int HALF = D / 2;
+    constexpr int PER = HALF / 32;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long total = (long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs;
+    if (warp >= total) return;
+    const int tok = (int)(warp % a.g.bs);
+    const int h = (int)((warp / a.g.bs) % a.g.Hkv);
+    const int r = (int)(warp / ((long long)a.g.bs * a.g.Hkv));
+    const int block = a.rotated_block_indices[r];
+    const int row = a.rotation_deltas[r];
+    if (block < 0 || block >= a.num_blocks || row < 0 || row >= a.rotation_lut_rows) {
+        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_ROTATION);
+        return;
+    }
+    const float* lut = a.rotation_trig_lut + (long long)row * D;
+    uint8_t* rec = (uint8_t*)a.key_cache + (long long)block * a.g.block_bytes + (long long)h * a.g.head_bytes;
+    float lo[PER], hi[PER];
+    float* params = (float*)(rec + (long long)a.g.bs * D);
+    if (a.g.cache == PA_DTYPE_U8) {
+        const float sc = params[tok], zp = params[a.g.bs + tok];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = lane + 32 * i;
+            lo[i] = dequant_one(rec[(long long)tok * D + j], sc, zp);
+            hi[i] = dequant_one(rec[(long long)tok * D + HALF + j], sc, zp);
+        }
+    } else {
+        const uint16_t* p = (const uint16_t*)rec + (long long)tok * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = lane + 32 * i;
+            if (a.g.cache == PA_DTYPE_F16) {
+                lo[i] = __half2float(__ushort_as_half(p[j]));
+                hi[i] = __half2float(__ushort_as_half(p[HALF + j]));
+            } else {
+                lo[i] = __bfloat162float(__ushort_as_bfloat16(p[j]));
+                hi[i] = __bfloat162float(__ushort_as_bfloat16(p[HALF + j]));
+            }
+        }
+    }
+    float nlo[PER], nhi[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int j = lane + 32 * i;
+        const float c = lut[j], s = lut[HALF + j];
+        nlo[i] = __fmaf_rn(-hi[i], s, __fmul_rn(lo[i], c));
+        nhi[i] = __fmaf_rn(lo[i], s, __fmul_rn(hi[i], c));
+    }
+    if (a.g.cache == PA_DTYPE_U8) {
+        float mn = fminf(nlo[0], nhi[0]), mx = fmaxf(nlo[0], nhi[0]);
+#pragma unroll
+        for (int i = 1; i < PER; ++i) {
+            mn = fminf(mn, fminf(nlo[i], nhi[i]));
+            mx = fmaxf(mx, fmaxf(nlo[i], nhi[i]));
+        }
+        mn = warp_min(mn); mx = warp_max(mx);
+        float sc, zp, inv;
+        quant_params(mn, mx, sc, zp, inv);
+        __syncwarp();
+        if (lane == 0) { params[tok] = sc; params[a.g.bs + tok] = zp; }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = lane + 32 * i;
+            rec[(long long)tok * D + j] = (uint8_t)quant_one(nlo[i], inv, zp);
+            rec[(long long)tok * D + HALF + j] = (uint8_t)quant_one(nhi[i], inv, zp);
+        }
+    } else {
+        uint16_t* p = (uint16_t*)rec + (long long)tok * D;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = lane + 32 * i;
+            if (a.g.cache == PA_DTYPE_F16) {
+                p[j] = __half_as_ushort(__float2half_rn(nlo[i]));
+                p[HALF + j] = __half_as_ushort(__float2half_rn(nhi[i]));
+            } else {
+                p[j] = __bfloat16_as_ushort(__float2bfloat16_rn(nlo[i]));
+                p[HALF + j] = __bfloat16_as_ushort(__float2bfloat16_rn(nhi[i]));
+            }
+        }
+    }
+}
+
+// Block copies: grid.x = pair, grid.y = slice of the block.  16-byte vectors.
+__global__ void __launch_bounds__(256) copy_blocks_kernel(uint8_t* key_cache, uint8_t* value_cache, long long block_bytes,
+                                                          int num_blocks, const int32_t* pairs, uint32_t* status) {
+    const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+    if (src < 0 || src >= num_blocks || dst < 0 || dst >= num_blocks) {
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, PA_DEV_BAD_BLOCK_INDEX);
+        return;
+    }
+    if (src == dst) return;
+    const long long vecs = block_bytes / 16;
+    const uint4* ks = (const uint4*)(key_cache + (long long)src * block_bytes);
+    uint4* kd = (uint4*)(key_cache + (long long)dst * block_bytes);
+    const uint4* vs = (const uint4*)(value_cache + (long long)src * block_bytes);
+    uint4* vd = (uint4*)(value_cache + (long long)dst * block_bytes);
+    for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < vecs; i += (long long)gridDim.y * blockDim.x) {
+        kd[i] = ks[i];
+        vd[i] = vs[i];
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream) {
+    if (a.num_tokens <= 0) return cudaSuccess;
+    const long long warps = (long long)a.num_tokens * a.g.Hkv;
+    const int grid = (int)((warps * 32 + 255) / 256);
+    if (a.g.D == 128) write_kv_kernel<128><<<grid, 256, 0, stream>>>(a);
+    else write_kv_kernel<64><<<grid, 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rotate(const KernelArgs& a, cudaStream_t stream) {
+    if (a.num_rotated_blocks <= 0) return cudaSuccess;
+    const long long warps = (long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs;
+    const int grid = (int)((warps * 32 + 255) / 256);
+    if (a.g.D == 128) rotate_kernel<128><<<grid, 256, 0, stream>>>(a);
+    else rotate_kernel<64><<<grid, 256, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_copy_blocks(void* key_cache, void* value_cache, long long block_bytes, int num_blocks,
+                               const int32_t* pairs, int num_pairs, uint32_t* status, cudaStream_t stream) {
+    if (num_pairs <= 0) return cudaSuccess;
+    dim3 grid(num_pairs, 8);
+    copy_blocks_kernel<<<grid, 256, 0, stream>>>((uint8_t*)key_cache, (uint8_t*)value_cache, block_bytes, num_blocks, pairs, status);
+    return cudaGetLastError();
+}
+
+}  // namespace pa

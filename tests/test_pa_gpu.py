@@ -1,0 +1,144 @@
+"""Parity of the CUDA PagedAttention path (through the C ABI) with the CPU oracle.
+
+Tolerances are the ones the operator is specified to: attention output within 2e-3 relative for
+f16/bf16 caches and 1e-2 for the u8 cache (relative to the largest reference magnitude);
+cache bytes written by the kernels must equal the oracle's bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from tests import pa_harness as H
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"f16": 2e-3, "bf16": 2e-3, "u8": 1e-2}
+
+
+def _check(res, cache, act=None):
+    assert res["status"] == 0, f"device status {res['status']:#x}"
+    assert np.array_equal(res["kc_gpu"], res["kc_ref"]), "key cache bytes differ from the oracle"
+    assert np.array_equal(res["vc_gpu"], res["vc_ref"]), "value cache bytes differ from the oracle"
+    tol = TOL[cache]
+    if act == torch.bfloat16:
+        tol = max(tol, 8e-3)  # the output itself is rounded to bf16 (8 significant bits)
+    err = H.rel_err(res["out_gpu"], res["out_ref"])
+    assert err < tol, f"attention output rel err {err:.3e} >= {tol}"
+
+
+@pytest.mark.parametrize("cache", ["f16", "bf16", "u8"])
+@pytest.mark.parametrize("d,bs", [(64, 32), (128, 32), (128, 16), (64, 16)])
+def test_decode_parity(cache, d, bs):
+    act = torch.float16 if cache == "f16" else torch.bfloat16
+    wl = H.small_workload(hq=8, hkv=2, d=d, bs=bs, act=act, cache=cache, past=[0, 1, 31, 32, 33, 100, 517, 1500],
+                          new=[1] * 8, seed=20 + d + bs)
+    _check(H.run_both(wl), cache, act)
+
+
+@pytest.mark.parametrize("hq,hkv", [(4, 4), (28, 4), (32, 4), (16, 1), (40, 2)])
+def test_decode_group_sizes(hq, hkv):
+    wl = H.small_workload(hq=hq, hkv=hkv, d=128, bs=32, act=torch.float16, cache="u8", past=[77, 300, 1024], new=[1, 1, 1], seed=hq)
+    _check(H.run_both(wl), "u8")
+
+
+def test_decode_config1_tinyllama_shape():
+    from openvino_genai_b200 import workloads
+    wl = workloads.config_tinyllama_decode()
+    _check(H.run_both(wl), "f16")
+
+
+def test_decode_long_context_many_splits(monkeypatch):
+    monkeypatch.setenv("PA_B200_SPLIT_TOKENS", "256")
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[5000, 255, 256, 257], new=[1] * 4, seed=31)
+    _check(H.run_both(wl), "u8", torch.bfloat16)
+
+
+def test_decode_f32_activations():
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.float32, cache="u8", past=[200, 64], new=[1, 1], seed=33)
+    _check(H.run_both(wl), "u8")
+
+
+@pytest.mark.parametrize("cache", ["f16", "bf16", "u8"])
+def test_prefill_and_mixed_parity(cache):
+    act = torch.float16 if cache == "f16" else torch.bfloat16
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache=cache, past=[0, 40, 300, 0, 65], new=[37, 1, 64, 1, 130], seed=41)
+    _check(H.run_both(wl), cache, act)
+
+
+def test_host_entry_point_matches():
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[0, 40, 300], new=[20, 1, 1], seed=43)
+    _check(H.run_both(wl, host_entry=True), "u8", torch.bfloat16)
+
+
+@pytest.mark.parametrize("cache", ["f16", "u8"])
+def test_scores_parity(cache):
+    act = torch.float16
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache=cache, past=[0, 40, 300, 90], new=[37, 1, 1, 16], seed=47)
+    wl.score_aggregation_window = np.array([8, 1, 0, 40], np.int32)
+    res = H.run_both(wl)
+    _check(res, cache, act)
+    ref, got = res["scores_ref"], res["scores_gpu"]
+    assert not np.isnan(got).any()
+    assert np.abs(got - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+    off = int(wl.past_lens[0] + wl.new_lens[0] + wl.past_lens[1] + wl.new_lens[1])
+    assert np.all(got[off:off + 301] == 0), "window 0 must write zeros"
+
+
+@pytest.mark.parametrize("cache", ["f16", "bf16", "u8"])
+def test_rotation_is_bit_exact(cache):
+    from openvino_genai_b200 import workloads
+    act = torch.float16 if cache == "f16" else torch.bfloat16
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache=cache, past=[200, 96], new=[1, 1], seed=53)
+    wl.rotated_block_indices = np.concatenate([wl.block_indices[1:4], wl.block_indices[8:9]]).astype(np.int32)
+    wl.rotation_deltas = np.array([1, 7, 2, 5], np.int32)
+    wl.rotation_trig_lut = workloads.rotation_trig_lut(9, 32, 128, 1e6)
+    _check(H.run_both(wl), cache, act)
+
+
+def test_bad_block_index_sets_status_and_does_not_fault():
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[100, 50], new=[1, 1], seed=59)
+    data = H.make_host_data(wl)
+    good = wl.block_indices.copy()
+    op = H.make_op(wl)
+    res = H.run_gpu(wl, data, op=op)
+    assert res["status"] == 0
+    wl.block_indices = good.copy()
+    wl.block_indices[1] = wl.num_blocks + 7
+    res = H.run_gpu(wl, data, op=op)
+    from openvino_genai_b200 import _abi
+    assert res["status"] & _abi.PA_DEV_BAD_BLOCK_INDEX
+    wl.block_indices = good
+    assert H.run_gpu(wl, data, op=op)["status"] == 0  # the context is still usable
+
+
+def test_unsupported_inputs_are_rejected(pkg):
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[10], new=[1], seed=61)
+    op = H.make_op(wl)
+    dev = torch.device("cuda", 0)
+    q, k, v = (x.to(dev) for x in H.workloads.random_activations(wl))
+    kc, vc = op.allocate_cache(wl.num_blocks)
+    t = lambda a: torch.from_numpy(a).to(dev)
+    common = dict(query=q, key=k, value=v, key_cache=kc, value_cache=vc, past_lens=t(wl.past_lens),
+                  subsequence_begins=t(wl.subsequence_begins), block_indices=t(wl.block_indices),
+                  block_indices_begins=t(wl.block_indices_begins), max_context_len=wl.max_context_len)
+    with pytest.raises(pkg.GenaiB200Error):
+        op.evaluate(dict(common, sliding_window=128), {"output": torch.empty_like(q)})
+    with pytest.raises(pkg.GenaiB200Error):
+        op.evaluate(dict(common, alibi_slopes=torch.zeros(8, device=dev)), {"output": torch.empty_like(q)})
+
+
+def test_copy_blocks():
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[100], new=[1], seed=67, pool=12)
+    res = H.run_both(wl)
+    op = res["op"]
+    dev = torch.device("cuda", 0)
+    kc = torch.from_numpy(res["kc_gpu"]).to(dev)
+    vc = torch.from_numpy(res["vc_gpu"]).to(dev)
+    src = int(wl.block_indices[0])
+    free = [b for b in range(wl.num_blocks) if b not in set(wl.block_indices.tolist())][:2]
+    pairs = torch.tensor([[src, free[0]], [src, free[1]]], dtype=torch.int32, device=dev)
+    op.copy_blocks(kc, vc, pairs)
+    torch.cuda.synchronize()
+    bb = H.block_bytes(wl)
+    k = kc.cpu().numpy()
+    for f in free:
+        assert np.array_equal(k[f * bb:(f + 1) * bb], k[src * bb:(src + 1) * bb])
