@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-attention decode step (the headline metric: KV GB/s of one
+PagedAttention decode step, as a fraction of the measured HBM peak).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A "step" is one PagedAttention operator call over the whole decode batch: write the new token's
+K/V into the paged cache, split-K attention over every sequence's block table, merge.
+Workload (default): Llama-3-8B attention shape, 64 sequences, past_lens U[512, 8192], u8 by-token
+KV cache scattered over a 20k-block pool, bf16 q - seeded synthetic data.  The KV bytes touched
+per step (~600 MB) exceed the 126 MB L2, so consecutive steps cannot be served from L2.
+
+Prints ONE JSON line.  `value` is whole-job KV GB/s with every input resident in HBM;
+`e2e` is the same metric through the host-tensor entry point (pa_b200_forward_host) with the
+step's q/k/v/metadata copied host->device and the output device->host inside the timed region.
+`--impl reference` times the CPU restatement of the operator (the reference's own operator lives
+in the OpenVINO runtime, which is not available) on the host cores over a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "paged_attn_decode_kv_gbps"
+UNIT = "GB/s"
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def build_workload(name: str, rank: int):
+    from openvino_genai_b200 import workloads
+    if name == "llama3_8b_u8_decode":
+        return workloads.config_llama3_8b_decode(seed=1002 + 97 * rank)
+    if name == "tinyllama_f16_decode":
+        return workloads.config_tinyllama_decode(seed=1001 + 97 * rank)
+    if name == "llama3_70b_u8_decode":
+        return workloads.config_llama3_70b_decode(seed=1005 + 97 * rank)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def config_of(wl, n_gpus: int) -> dict:
+    return {"workload": wl.name, "num_q_heads": wl.num_q_heads, "num_kv_heads": wl.num_kv_heads, "head_size": wl.head_size,
+            "block_size": wl.block_size, "kv_cache": wl.cache_dtype + (" by-token asymmetric" if wl.cache_dtype == "u8" else ""),
+            "sequences_per_gpu": wl.num_sequences, "past_lens": f"U[{int(wl.past_lens.min())},{int(wl.past_lens.max())}]",
+            "pool_blocks": wl.num_blocks, "parallelism": f"sequences and KV pools sharded over {n_gpus} rank(s), no data-path collective",
+            "l2_policy": "KV bytes per step exceed L2 (inputs larger than L2)"}
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_leg(wl_name: str, steps: int, warmup: int, target_mb: float = 300.0):
+    """Times the CPU restatement of the operator (attention only, cache already written) on a
+    bounded sample: the first sequences of the same seeded workload up to ~target_mb of KV."""
+    import torch
+    import __graft_entry__ as entry
+    entry.load_package()
+    from oracle import pa_oracle
+    from tests import pa_harness as H
+    from openvino_genai_b200 import workloads
+    full = build_workload(wl_name, 0)
+    per_tok = full.kv_token_bytes()
+    take, acc = 0, 0
+    while take < full.num_sequences and (take == 0 or acc + (int(full.past_lens[take]) + 1) * per_tok <= target_mb * 1e6):
+        acc += (int(full.past_lens[take]) + 1) * per_tok
+        take += 1
+    wl = workloads.make_workload(full.name, hq=full.num_q_heads, hkv=full.num_kv_heads, d=full.head_size, bs=full.block_size,
+                                 act=full.act_dtype, cache=full.cache_dtype, past=full.past_lens[:take].astype(np.int64),
+                                 new=np.ones(take, np.int64), num_blocks=int(((full.past_lens[:take] + 1 + full.block_size - 1) // full.block_size).sum()) + 2,
+                                 seed=full.seed, scale=full.scale)
+    q, k, v, fill, pk, pv = H.make_host_data(wl)
+    desc = H.desc_of(wl)
+    n = wl.num_blocks * H.block_bytes(wl)
+    kc, vc = np.zeros(n, np.uint8), np.zeros(n, np.uint8)
+    dummy = torch.zeros((fill.num_tokens, 1), dtype=wl.act_dtype)
+    assert pa_oracle.write_kv(desc, H.host_args(fill, dummy, pk, pv, dummy, kc, vc, with_eviction=False)) == 0
+    out = torch.zeros_like(q)
+    args = H.host_args(wl, q, k, v, out, kc, vc)
+    assert pa_oracle.write_kv(desc, args) == 0
+    cores = pa_oracle.hardware_threads()
+    for _ in range(warmup):
+        pa_oracle.attend(desc, args, cores)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        assert pa_oracle.attend(desc, args, cores) == 0
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    gbps = wl.decode_kv_bytes() / dt / 1e9
+    sample = f"first {take} of {full.num_sequences} sequences of the same seeded workload ({wl.decode_kv_bytes() / 1e6:.1f} MB of KV per step), attention only"
+    return gbps, dt * 1e3, cores, sample, full
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 5)), min(args.warmup, 1)
+    gbps, ms, cores, sample, wl = cpu_reference_leg(args.workload, steps, warmup)
+    line = {"metric": METRIC, "value": round(gbps, 4), "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config_of(wl, args.gpus),
+            "cpu_baseline": {"value": round(gbps, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": round(gbps, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of the operator contract (the reference's operator lives in the OpenVINO runtime, unavailable here)"}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    pkg.load_library()  # fails loudly when the CUDA extension is missing
+    from openvino_genai_b200 import workloads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = build_workload(args.workload, rank)
+    op = pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, local)
+    kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
+    workloads.fill_cache_on_device(op, wl, kc, vc)
+    q, k, v = workloads.random_activations(wl, dev)
+    out = torch.empty_like(q)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    meta = [t(wl.past_lens), t(wl.subsequence_begins), t(wl.block_indices), t(wl.block_indices_begins)]
+    stream = torch.cuda.Stream(dev)
+    torch.cuda.synchronize(dev)
+    dargs = op.make_args(q, k, v, out, kc, vc, *meta, wl.scale, wl.max_context_len, stream=stream.cuda_stream)
+    op._check(op.lib.pa_b200_reserve(op._h, wl.num_tokens, wl.num_sequences, wl.max_context_len, 0, len(wl.block_indices)))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident steps --------------------------------------------------------------------
+    for _ in range(args.warmup):
+        op.forward_args(dargs)
+    barrier()
+    launches0 = op.launch_count()
+    op._check(op.lib.pa_b200_set_kernel_timing(op._h, 1))
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        op.forward_args(dargs)
+    ev1.record(stream)
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    op._check(op.lib.pa_b200_set_kernel_timing(op._h, 0))
+    ktot, kcnt = C.c_double(0), C.c_int64(0)
+    op._check(op.lib.pa_b200_get_kernel_timing(op._h, C.byref(ktot), C.byref(kcnt)))
+    launches = op.launch_count() - launches0
+    status = op.device_status()
+    if status:
+        raise SystemExit(f"device status word {status:#x} after the timed region")
+
+    # ---- end to end through the host-tensor entry point -------------------------------------------
+    hq, hk_, hv = (x.cpu().pin_memory() for x in (q, k, v))
+    hout = torch.empty_like(hq).pin_memory()
+    hargs = op.make_args(hq, hk_, hv, hout, kc, vc, wl.past_lens, wl.subsequence_begins, wl.block_indices, wl.block_indices_begins,
+                         wl.scale, wl.max_context_len, stream=stream.cuda_stream)
+    h2d = int(hq.numel() * hq.element_size() + 2 * hk_.numel() * hk_.element_size() +
+              4 * (len(wl.past_lens) + len(wl.subsequence_begins) + len(wl.block_indices) + len(wl.block_indices_begins)))
+    d2h = int(hout.numel() * hout.element_size())
+    for _ in range(max(args.warmup, 1)):
+        op.forward_args(hargs, host=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        op.forward_args(hargs, host=True)
+    e1.record(stream)
+    barrier()
+    ms_e2e_total = e0.elapsed_time(e1)
+    same = torch.equal(hout.to(dev), out)
+
+    # ---- reduce over ranks ------------------------------------------------------------------------
+    kv_bytes = wl.decode_kv_bytes()
+    stats = torch.tensor([ms_total, ms_e2e_total, ktot.value / max(kcnt.value, 1)], dtype=torch.float64, device=dev)
+    sums = torch.tensor([float(kv_bytes), float(wl.num_sequences), float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    ms_total, ms_e2e_total, kernel_ms = (float(x) for x in stats.cpu())
+    total_bytes, total_seqs, total_launches = (float(x) for x in sums.cpu())
+
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        ms_step = ms_total / args.steps
+        value = total_bytes / (ms_step * 1e-3) / 1e9
+        e2e_value = total_bytes / (ms_e2e_total / args.steps * 1e-3) / 1e9
+        achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
+        traffic = None
+        tp = ROOT / "profiles" / "decode_u8_llama3_8b.traffic.json"
+        if tp.exists() and wl.name == "llama3_8b_u8_decode":
+            traffic = json.loads(tp.read_text()).get("dram_bytes_per_launch")
+        line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma / f32 accumulate",
+                "data": "synthetic", "config": config_of(wl, world),
+                "tokens_per_s": round(total_seqs / (ms_step * 1e-3), 1),
+                "hbm_peak_frac_step": round(value / world / peak, 4),
+                "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                             "traffic": traffic, "kernel": "decode_kernel (split-K paged decode)", "kernel_ms": round(kernel_ms, 4),
+                             "algorithmic_bytes_per_launch": kv_bytes, "peak_source": peak_kind},
+                "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": round(ms_e2e_total / args.steps, 4), "matches_device_path": bool(same)},
+                "gpu_launches": int(total_launches), "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            gbps, ms, cores, sample, _ = cpu_reference_leg(args.workload, 2, 1)
+            line["cpu_baseline"] = {"value": round(gbps, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama3_8b_u8_decode")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -168,6 +168,12 @@ int pa_b200_last_device_status(pa_handle* h, uint32_t* status_bits);
 /* Number of kernels this handle has launched since creation (for launch accounting). */
 int64_t pa_b200_launch_count(const pa_handle* h);
 
+/* Measurement support: while enabled, every forward call records a CUDA event pair around its
+ * split-K decode kernel on the stream it launches on.  get_kernel_timing waits for the recorded
+ * pairs, returns their summed duration and count, and clears them (at most 4096 pairs are kept). */
+int pa_b200_set_kernel_timing(pa_handle* h, int enabled);
+int pa_b200_get_kernel_timing(pa_handle* h, double* total_ms, int64_t* timed_launches);
+
 /* Stand-alone cache operations used by the operator and by the cache manager.
  *  - write: scatter `num_tokens` new K/V rows into their slots (quantising for u8).
  *  - rotate: re-rotate the keys of the listed blocks in place (pipeline_impl.cpp:810-882).

@@ -3,10 +3,12 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <climits>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "pa_kernels.h"
 
@@ -46,7 +48,9 @@ struct pa_handle {
     uint8_t* stage_host = nullptr;  // pinned
     size_t stage_host_bytes = 0;
     int64_t launches = 0;
-    int split_override = 0;
+    bool timing = false;                       // record events around the split-K decode kernel
+    std::vector<cudaEvent_t> ev;               // pairs, created on demand
+    size_t ev_used = 0;
 };
 
 namespace {
@@ -73,34 +77,31 @@ pa::CacheGeom make_geom(const pa_model_desc& d) {
     return g;
 }
 
+// Scratch layout of one forward call.
 struct Plan {
-    int split_tokens, max_splits;
-    size_t off_part_o, off_part_ml, off_lse, off_score_off, total;
+    long long max_tiles;
+    size_t off_hdr, off_prefix, off_done, off_part_o, off_part_ml, off_lse, off_score_off, total;
 };
 
-Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_context_len, int64_t scores_len) {
+Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_context_len, int64_t scores_len,
+               int num_block_indices = -1) {
     Plan p;
     const pa::CacheGeom& g = h->g;
-    const int G = g.Hq / g.Hkv, gtiles = (G + 15) / 16;
-    int split = h->split_override;
-    if (split <= 0) {
-        // enough CTAs for ~16 rounds over 2 resident CTAs per SM, never below 256 tokens per CTA
-        const double total = (double)std::max(num_sequences, 1) * std::max(max_context_len, 1) * g.Hkv * gtiles;
-        split = (int)(total / ((double)h->sm_count * 2 * 16));
-        split = std::min(4096, std::max(256, split));
-    }
-    split = (int)align_up((size_t)split, 128);
-    p.split_tokens = split;
-    p.max_splits = std::max(1, (std::max(max_context_len, 1) + split - 1) / split);
+    const int G = g.Hq / g.Hkv, gtiles = (G + 15) / 16, HK = g.Hkv * gtiles, RT = std::min(G, 16);
+    const long long B = std::max(num_sequences, 0);
+    // upper bound of the step's context tiles, known without reading device metadata
+    long long tiles = B * ((std::max(max_context_len, 1) + 31) / 32);
+    if (num_block_indices >= 0) tiles = std::min(tiles, (long long)num_block_indices * g.bs / 32 + B);
+    p.max_tiles = tiles * HK;
+    const long long slots = B * HK + pa::decode_max_workers(h->sm_count);  // slot = stream + worker
     size_t off = 0;
-    p.off_part_o = off;
-    off += align_up((size_t)num_sequences * g.Hq * p.max_splits * g.D * sizeof(float), 256);
-    p.off_part_ml = off;
-    off += align_up((size_t)num_sequences * g.Hq * p.max_splits * 2 * sizeof(float), 256);
-    p.off_lse = off;
-    off += align_up((size_t)std::max(num_tokens, 1) * g.Hq * sizeof(float), 256);
-    p.off_score_off = off;
-    off += align_up((size_t)(num_sequences + 1) * sizeof(int64_t), 256);
+    p.off_hdr = off;       off += 256;
+    p.off_prefix = off;    off += align_up((size_t)(B + 1) * sizeof(int), 256);
+    p.off_done = off;      off += align_up((size_t)std::max(B, 1LL) * HK * sizeof(int), 256);
+    p.off_part_o = off;    off += align_up((size_t)slots * RT * g.D * sizeof(float), 256);
+    p.off_part_ml = off;   off += align_up((size_t)slots * RT * 2 * sizeof(float), 256);
+    p.off_lse = off;       off += align_up((size_t)std::max(num_tokens, 1) * g.Hq * sizeof(float), 256);
+    p.off_score_off = off; off += align_up((size_t)(B + 1) * sizeof(int64_t), 256);
     (void)scores_len;
     p.total = off;
     return p;
@@ -172,21 +173,34 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.part_ml = (float*)(h->ws + p.off_part_ml);
     k.lse = (float*)(h->ws + p.off_lse);
     k.score_offsets = (int64_t*)(h->ws + p.off_score_off);
-    k.score_part = nullptr;
-    k.split_tokens = p.split_tokens; k.max_splits = p.max_splits;
+    k.plan = (pa::PlanHeader*)(h->ws + p.off_hdr);
+    k.tile_prefix = (int*)(h->ws + p.off_prefix);
+    k.stream_done = (int*)(h->ws + p.off_done);
+    k.max_tiles = p.max_tiles;
+    k.rows_per_tile = std::min(h->g.Hq / h->g.Hkv, 16);
     return k;
 }
 
 int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     if (a->num_sequences == 0 || a->num_tokens == 0) return PA_OK;
-    Plan p = make_plan(h, a->num_tokens, a->num_sequences, a->max_context_len, a->scores_len);
+    Plan p = make_plan(h, a->num_tokens, a->num_sequences, a->max_context_len, a->scores_len, a->num_block_indices);
     int rc = ensure_ws(h, p.total);
     if (rc != PA_OK) return rc;
     pa::KernelArgs k = make_kernel_args(h, a, p);
     int launches = 0;
     if (a->num_rotated_blocks > 0) { PA_CUDA(pa::launch_rotate(k, stream)); ++launches; }
-    PA_CUDA(pa::launch_write_kv(k, stream)); ++launches;
-    PA_CUDA(pa::launch_decode(k, stream, &launches));
+    PA_CUDA(pa::launch_write_kv(k, stream, /*with_plan=*/true)); ++launches;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    if (h->timing && h->ev_used + 2 <= 8192) {
+        while (h->ev.size() < h->ev_used + 2) {
+            cudaEvent_t e;
+            PA_CUDA(cudaEventCreate(&e));
+            h->ev.push_back(e);
+        }
+        ev0 = h->ev[h->ev_used]; ev1 = h->ev[h->ev_used + 1];
+        h->ev_used += 2;
+    }
+    PA_CUDA(pa::launch_decode(k, stream, h->sm_count, &launches, ev0, ev1));
     if (a->num_tokens > a->num_sequences) PA_CUDA(pa::launch_prefill(k, stream, &launches));
     if (a->scores) PA_CUDA(pa::launch_scores(k, stream, &launches));
     h->launches += launches;
@@ -232,7 +246,6 @@ int pa_b200_create(const pa_model_desc* desc, int device, pa_handle** out) {
     h->g = make_geom(*desc);
     h->device = device;
     h->sm_count = prop.multiProcessorCount;
-    if (const char* e = std::getenv("PA_B200_SPLIT_TOKENS")) h->split_override = std::atoi(e);
     cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc((void**)&h->status, 256);
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);
@@ -252,6 +265,7 @@ int pa_b200_destroy(pa_handle* h) {
     if (h->status) cudaFree(h->status);
     if (h->stage_dev) cudaFree(h->stage_dev);
     if (h->stage_host) cudaFreeHost(h->stage_host);
+    for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
     return PA_OK;
@@ -267,7 +281,7 @@ int pa_b200_reserve(pa_handle* h, int32_t num_tokens, int32_t num_sequences, int
                     int32_t num_block_indices) {
     if (!h) return fail(PA_ERR_INVALID_ARG, "NULL handle");
     PA_CUDA(cudaSetDevice(h->device));
-    int rc = ensure_ws(h, make_plan(h, num_tokens, num_sequences, max_context_len, scores_len).total);
+    int rc = ensure_ws(h, make_plan(h, num_tokens, num_sequences, max_context_len, scores_len, num_block_indices).total);
     if (rc != PA_OK) return rc;
     const size_t ab = act_bytes(h->g.act);
     size_t stage = (size_t)num_tokens * (2 * h->g.Hq + 2 * h->g.Hkv) * h->g.D * ab + (size_t)(3 * num_sequences + 2 + num_block_indices) * 4 +
@@ -292,7 +306,7 @@ int pa_b200_write_kv(pa_handle* h, const pa_forward_args* a) {
     rc = ensure_ws(h, p.total);
     if (rc != PA_OK) return rc;
     pa::KernelArgs k = make_kernel_args(h, a, p);
-    PA_CUDA(pa::launch_write_kv(k, stream));
+    PA_CUDA(pa::launch_write_kv(k, stream, /*with_plan=*/false));
     h->launches += 1;
     return PA_OK;
 }
@@ -334,6 +348,28 @@ int pa_b200_last_device_status(pa_handle* h, uint32_t* status_bits) {
 }
 
 int64_t pa_b200_launch_count(const pa_handle* h) { return h ? h->launches : -1; }
+
+int pa_b200_set_kernel_timing(pa_handle* h, int enabled) {
+    if (!h) return fail(PA_ERR_INVALID_ARG, "NULL handle");
+    h->timing = enabled != 0;
+    return PA_OK;
+}
+
+int pa_b200_get_kernel_timing(pa_handle* h, double* total_ms, int64_t* timed_launches) {
+    if (!h || !total_ms || !timed_launches) return fail(PA_ERR_INVALID_ARG, "NULL argument");
+    PA_CUDA(cudaSetDevice(h->device));
+    double total = 0.0;
+    for (size_t i = 0; i + 1 < h->ev_used; i += 2) {
+        PA_CUDA(cudaEventSynchronize(h->ev[i + 1]));
+        float ms = 0.f;
+        PA_CUDA(cudaEventElapsedTime(&ms, h->ev[i], h->ev[i + 1]));
+        total += ms;
+    }
+    *total_ms = total;
+    *timed_launches = (int64_t)(h->ev_used / 2);
+    h->ev_used = 0;
+    return PA_OK;
+}
 
 // Host-tensor entry point.  Everything except the cache is packed into one pinned staging
 // buffer, moved with a single host->device copy, and the results come back with one

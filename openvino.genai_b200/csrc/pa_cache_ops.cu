@@ -19,10 +19,65 @@ __device__ __forceinline__ int find_sequence(const int32_t* begins, int num_seq,
     return lo;
 }
 
-// One warp per (token, kv head).  Lane l owns dims {l + 32*i}.
-template <int D>
+// Number of 32-token context tiles of one decode row (0 for rows that are not decode rows).
+__device__ __forceinline__ int seq_tiles(const KernelArgs& a, int s) {
+    const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
+    if (n != 1) return 0;
+    const int past = a.past_lens[s];
+    const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
+    if (past < 0 || nb < 0 || (long long)nb * a.g.bs < (long long)past + 1) {
+        atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
+        return 0;
+    }
+    return (past + 1 + 31) / 32;
+}
+
+// Builds the decode plan with one block of 256 threads: the exclusive prefix sum of the per-row
+// tile counts (workers slice the global tile sequence through it) and zeroed per-stream counters.
+__device__ void build_decode_plan(const KernelArgs& a) {
+    __shared__ int sh_warp[8];
+    __shared__ int sh_run;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int B = a.num_sequences;
+    const int G = a.g.Hq / a.g.Hkv, HK = a.g.Hkv * ((G + 15) / 16);
+    if (tid == 0) sh_run = 0;
+    __syncthreads();
+    for (int base = 0; base < B; base += 256) {
+        const int s = base + tid;
+        const int n = s < B ? seq_tiles(a, s) : 0;
+        int v = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += u;
+        }
+        if (lane == 31) sh_warp[wid] = v;
+        __syncthreads();
+        int off = sh_run;
+        for (int w = 0; w < wid; ++w) off += sh_warp[w];
+        if (s < B) a.tile_prefix[s] = off + v - n;
+        __syncthreads();
+        if (tid == 255) sh_run = off + v;
+        __syncthreads();
+    }
+    for (int i = tid; i < B * HK; i += 256) a.stream_done[i] = 0;
+    if (tid == 0) {
+        a.tile_prefix[B] = sh_run;
+        a.plan->total_tiles = sh_run * HK;
+    }
+}
+
+// One warp per (token, kv head).  Lane l owns dims {l + 32*i}.  With PLAN set, the last block of
+// the grid builds the decode plan instead.
+template <int D, bool PLAN>
 __global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
     constexpr int PER = D / 32;
+    if constexpr (PLAN) {
+        if (blockIdx.x == gridDim.x - 1) {
+            build_decode_plan(a);
+            return;
+        }
+    }
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int total = a.num_tokens * a.g.Hkv;
@@ -205,12 +260,17 @@ __global__ void __launch_bounds__(256) copy_blocks_kernel(uint8_t* key_cache, ui
 
 }  // namespace
 
-cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream) {
-    if (a.num_tokens <= 0) return cudaSuccess;
+cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream, bool with_plan) {
+    if (a.num_tokens <= 0 && !with_plan) return cudaSuccess;
     const long long warps = (long long)a.num_tokens * a.g.Hkv;
-    const int grid = (int)((warps * 32 + 255) / 256);
-    if (a.g.D == 128) write_kv_kernel<128><<<grid, 256, 0, stream>>>(a);
-    else write_kv_kernel<64><<<grid, 256, 0, stream>>>(a);
+    const int grid = (int)((warps * 32 + 255) / 256) + (with_plan ? 1 : 0);
+    if (a.g.D == 128) {
+        if (with_plan) write_kv_kernel<128, true><<<grid, 256, 0, stream>>>(a);
+        else write_kv_kernel<128, false><<<grid, 256, 0, stream>>>(a);
+    } else {
+        if (with_plan) write_kv_kernel<64, true><<<grid, 256, 0, stream>>>(a);
+        else write_kv_kernel<64, false><<<grid, 256, 0, stream>>>(a);
+    }
     return cudaGetLastError();
 }
 

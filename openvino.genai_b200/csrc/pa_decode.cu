@@ -1,19 +1,27 @@
 // Paged decode attention for sm_100a: rows with exactly one new token.
 //
-// Work split: one CTA per (sequence, kv head, context split).  Inside the CTA each of the four
-// warps owns a private multi-stage shared-memory ring and walks its own 32-token tiles of the
-// block table, so the main loop needs no block-wide barrier:
+// Persistent kernel: the grid is (resident CTAs per SM) x (SM count) and every WARP is an
+// independent worker.  The 32-token tiles of all (decode row, head tile) "streams" form one
+// global sequence (row-major, then head tile, then position); the plan step of the cache-write
+// launch publishes its per-row prefix sum, and worker w takes the w-th equal slice of that
+// sequence.  A slice crosses at most a few stream boundaries, so a warp reduces one to three
+// "runs", each into one partial result; no queue, no atomics on the load path.
+// A warp owns a private shared-memory ring whose loads run ahead of the math across run
+// boundaries:
 //   * u8 cache   - lane 0 issues one TMA-engine bulk copy per (block, head) record (data +
 //                  per-token scale / zero-point, contiguous and 16-byte aligned), completion on
-//                  an mbarrier; bytes are turned into exact f16 in registers
-//                  (byte | 0x6400 = 1024 + byte) and the zero-point is folded algebraically:
-//                     q.k  = ks * (q.k_u8 - kz * sum(q))
-//                     p.v  = sum_t (p*vs)_t * v_u8 - sum_t (p*vs)_t * vz_t
+//                  an mbarrier; bytes become exact f16 in registers (byte | 0x6400 = 1024 + byte)
+//                  and both offsets are folded algebraically:
+//                     q.k  = ks * (q.(1024 + k_u8) - (kz + 1024) * sum(q))
+//                     p.v  = sum_t (p*vs)_t * (1024 + v_u8) - sum_t (p*vs)_t * (vz_t + 1024)
 //   * f16 / bf16 - all lanes issue 16-byte cp.async into an XOR-swizzled tile read by ldmatrix.
 // Q.K^T and P.V run on mma.sync m16n8k16 with the GQA group as the M dimension, so a KV byte is
-// read from HBM once for all q heads that share it.  Softmax is online per warp; the four warps
-// are merged through shared memory, the context splits through a small fp32 scratch and a
-// merge kernel.  The kernel is bound by HBM: 2*Hkv*(D+8) bytes per context token for u8.
+// read from HBM once for all q heads that share it.  Softmax is online with a lazily updated
+// reference maximum.  A stream cut by slice boundaries is merged by the warp whose partial
+// completes it (one atomic counter per stream, no waiting).
+// HBM-bound: 2*Hkv*(D+8) bytes per context token for the u8 cache.
+#include <algorithm>
+
 #include "pa_common.cuh"
 #include "pa_kernels.h"
 
@@ -21,10 +29,36 @@ namespace pa {
 
 namespace {
 
-constexpr int kTile = 32;       // context tokens per pipeline stage
+constexpr int kTile = 32;  // context tokens per pipeline stage
 constexpr int kDecodeWarps = 4;
+constexpr int kDecodeMaxCtasPerSm = 4;
+constexpr int kMinSlice = 4;     // a worker is given at least this many tiles
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kLazyMax = 8.f;  // the running reference may lag the true row maximum by 2^8
+
+enum : int { kFirst = 1, kLast = 2, kEnd = 4 };
+
+// What the loader records for each ring stage; read by the whole warp when the tile is consumed.
+struct __align__(16) StageDesc {
+    int flags;  // kFirst (run starts: load Q, clear state) | kLast (run ends: publish) | kEnd
+    int valid;  // live tokens in the tile (1..32)
+    int run;    // index of the run's record in the warp's run ring
+    int pad;
+};
+
+// One run (consecutive tiles of one stream inside a worker's slice), kept in shared memory so that
+// it costs no registers while its tiles are in flight.
+struct __align__(16) RunRec {
+    int t0;          // row of the stream's token in query / output
+    int hkp;         // head tile: kv head * gtiles + tile of the GQA group
+    int stream;      // s * HK + hkp
+    int nparts;      // workers whose slices touch the stream (1 => write the output directly)
+    int first_slot;  // partial slot of the stream's first worker (slots are consecutive)
+    int slot;        // this worker's partial slot
+    int pad[2];
+};
+constexpr int kRunRing = 4;
 
 template <int D, int BS, int CACHE>
 struct DecodeCfg {
@@ -34,165 +68,169 @@ struct DecodeCfg {
     static constexpr int NREC = kTile / BS;                     // records per tile
     static constexpr int HALF_STAGE = NREC * REC;               // K part (V part has the same size)
     static constexpr int STAGE = 2 * HALF_STAGE;
-    static constexpr int NSTAGE = 3;
+    static constexpr int NSTAGE = 2;
     static constexpr int RING = NSTAGE * STAGE;                 // per warp
-    static constexpr int SMEM = kDecodeWarps * RING + kDecodeWarps * NSTAGE * 8;
+    static constexpr int WARP_SMEM = RING + NSTAGE * (int)sizeof(StageDesc) + kRunRing * (int)sizeof(RunRec) + NSTAGE * 8;
+    static constexpr int SMEM = kDecodeWarps * WARP_SMEM;
 };
 
-struct SeqInfo {
-    int t0, past, ctx, nb;
-    const int32_t* table;
-};
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void store_pair(void* out, long long idx, int act, float v0, float v1) {
+    if (act == PA_DTYPE_F32) *reinterpret_cast<float2*>((float*)out + idx) = make_float2(v0, v1);
+    else if (act == PA_DTYPE_F16) *reinterpret_cast<__half2*>((__half*)out + idx) = __floats2half2_rn(v0, v1);
+    else *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)out + idx) = __floats2bfloat162_rn(v0, v1);
+}
 
 template <int D, int BS, int CACHE, bool HI>
-__global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a) {
+__global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(KernelArgs a) {
     using Cfg = DecodeCfg<D, BS, CACHE>;
     constexpr bool U8 = Cfg::U8;
     constexpr bool BF16 = Cfg::BF16;
     constexpr int NKK = D / 16;   // k-steps of Q.K^T
     constexpr int NDT = D / 8;    // n-tiles of P.V
     constexpr int ROWS = HI ? 2 : 1;
+    constexpr int NS = Cfg::NSTAGE;
 
     extern __shared__ __align__(128) uint8_t smem[];
-
-    const int s = blockIdx.z;
-    const int t0 = a.subsequence_begins[s];
-    const int n_new = a.subsequence_begins[s + 1] - t0;
-    if (n_new != 1) return;  // prefill chunks are handled elsewhere
-    const int past = a.past_lens[s];
-    const int tb = a.block_indices_begins[s];
-    const int nb = a.block_indices_begins[s + 1] - tb;
-    if (past < 0 || nb < 0 || (long long)nb * BS < (long long)past + 1) {
-        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
-        return;
-    }
-    const int ctx = past + 1;
-    const int split = blockIdx.x;
-    const int tok_begin = split * a.split_tokens;
-    if (tok_begin >= ctx) return;
-    const int tok_end = min(ctx, tok_begin + a.split_tokens);
-    const int nsplit = (ctx + a.split_tokens - 1) / a.split_tokens;
-    const int32_t* table = a.block_indices + tb;
-
-    const int G = a.g.Hq / a.g.Hkv;
-    const int gtiles = (G + 15) / 16;
-    const int hk = blockIdx.y / gtiles;
-    const int hbase = hk * G + (blockIdx.y % gtiles) * 16;  // first q head of this CTA
-    const int hcount = min(16, hk * G + G - hbase);          // q heads of this CTA (<= 8 unless HI)
-
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
-
-    uint8_t* ring = smem + warp * Cfg::RING;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecodeWarps * Cfg::RING) + warp * Cfg::NSTAGE;
+    uint8_t* ring = smem + warp * Cfg::WARP_SMEM;
+    StageDesc* descs = reinterpret_cast<StageDesc*>(ring + Cfg::RING);
+    RunRec* runs = reinterpret_cast<RunRec*>(ring + Cfg::RING + NS * sizeof(StageDesc));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + Cfg::RING + NS * sizeof(StageDesc) + kRunRing * sizeof(RunRec));
     if constexpr (U8) {
         if (lane == 0) {
 #pragma unroll
-            for (int i = 0; i < Cfg::NSTAGE; ++i) mbar_init(&bars[i], 1);
+            for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1);
             mbar_fence_init();
         }
         __syncwarp();
     }
 
-    // ---- Q fragments ---------------------------------------------------------------------
-    // u8: the contraction index is permuted so that one 16-byte shared load of a key row feeds
-    // four k-steps: k-step kk = 4*half + i covers dims 64*half + 16*c + 4*i + {0..3} for lane c.
-    uint32_t qa[NKK][4];
-    float qsum[ROWS], qscale[ROWS];  // sum of the f16 q row (u8 zero-point term); logit scale in log2 units
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        const int hrow = g + 8 * r;
-        const bool live = hrow < hcount;
-        const long long qoff = ((long long)t0 * a.g.Hq + hbase + hrow) * D;
-        float q[D / 4];
-        float amax = 0.f;
-#pragma unroll
-        for (int e = 0; e < D / 4; ++e) {
-            int d;
-            if constexpr (U8) d = 64 * (e / 16) + 16 * c + (e % 16);
-            else d = 16 * (e / 4) + 2 * c + (e & 1) + 8 * ((e >> 1) & 1);
-            q[e] = live ? load_act(a.query, qoff + d, a.g.act) : 0.f;
-            amax = fmaxf(amax, fabsf(q[e]));
-        }
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        // keep |q| inside the f16 range with an exact power-of-two prescale
-        float qmul = 1.f;
-        if (!BF16 && amax > 32768.f && amax < INFINITY) {
-            int ex;
-            frexpf(amax, &ex);
-            qmul = ldexpf(1.f, 15 - ex);
-        }
-        float sum = 0.f;
-#pragma unroll
-        for (int e = 0; e < D / 4; e += 2) {
-            uint32_t packed;
-            if constexpr (BF16) {
-                packed = pack_bf2(q[e], q[e + 1]);
-            } else {
-                packed = pack_h2(q[e] * qmul, q[e + 1] * qmul);
-                __half2 h = *reinterpret_cast<__half2*>(&packed);
-                sum += __low2float(h) + __high2float(h);
-            }
-            const int kk = e / 4;
-            qa[kk][r + 2 * ((e >> 1) & 1)] = packed;
-        }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        qsum[r] = sum;
-        const float sm_scale = a.scale != 0.f ? a.scale : rsqrtf((float)D);
-        qscale[r] = sm_scale * kLog2e / qmul;
-    }
-    if constexpr (!HI) {
-#pragma unroll
-        for (int kk = 0; kk < NKK; ++kk) { qa[kk][1] = 0u; qa[kk][3] = 0u; }
-    }
-
-    // ---- tile schedule of this warp ------------------------------------------------------------
-    const int first_tile = tok_begin / kTile;
-    const int num_tiles = (tok_end - tok_begin + kTile - 1) / kTile;
-    const int my_tiles = num_tiles > warp ? (num_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
-    const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)hk * a.g.head_bytes;
-    const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)hk * a.g.head_bytes;
+    const int G = a.g.Hq / a.g.Hkv;
+    const int gtiles = (G + 15) / 16;
+    const int HK = a.g.Hkv * gtiles;
+    const int RT = a.rows_per_tile;
+    const float sm_scale = a.scale != 0.f ? a.scale : rsqrtf((float)D);
     bool bad_index = false;
 
-    auto issue = [&](int it) {
-        const int tile = first_tile + warp + it * kDecodeWarps;
-        uint8_t* st = ring + (it % Cfg::NSTAGE) * Cfg::STAGE;
+    // ---- this worker's slice of the global tile sequence -----------------------------------------
+    const int total_tiles = a.plan->total_tiles;                  // all streams
+    const int all_workers = gridDim.x * kDecodeWarps;
+    const int workers = max(1, min(all_workers, (total_tiles + kMinSlice - 1) / kMinSlice));
+    const int per_worker = (total_tiles + workers - 1) / workers;
+    const int wid = blockIdx.x * kDecodeWarps + warp;
+    int g_tile = min(total_tiles, wid * per_worker);               // next global tile to load
+    const int g_end = min(total_tiles, g_tile + per_worker);
+
+    // ---- loader state (warp-uniform registers) -------------------------------------------------------
+    int r_s = -1, r_hkp = 0, r_tiles = 0;   // current stream: row, head tile, tiles of the row per head tile
+    int r_tok = 0, r_end = 0;                // token cursor and end of the current run
+    int r_tb = 0, r_nb = 0, r_seq = 0;       // block table of the row, run counter
+    int w_blk0 = 0, tbl = 0;                 // block window: lane j holds block_indices[r_tb + w_blk0 + j]
+    bool r_first = false;
+
+    auto load_window = [&](int first_block) {
+        w_blk0 = first_block;
+        const int bi = first_block + lane;
+        int blk = 0;
+        if (bi < r_nb) {
+            blk = a.block_indices[r_tb + bi];
+            if (blk < 0 || blk >= a.num_blocks) { blk = 0; bad_index = true; }
+        }
+        tbl = blk;
+    };
+
+    // Starts the run that contains global tile g_tile (g_tile < g_end).
+    auto next_run = [&]() {
+        int tile0;
+        if (r_s < 0) {  // first run: locate the row by binary search in the prefix sums
+            const int key = g_tile / HK;
+            int lo = 0, hi = a.num_sequences;  // tile_prefix[lo] <= key < tile_prefix[hi]
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (__ldcg(a.tile_prefix + mid) <= key) lo = mid; else hi = mid;
+            }
+            r_s = lo;
+            const int p0 = __ldcg(a.tile_prefix + r_s);
+            r_tiles = __ldcg(a.tile_prefix + r_s + 1) - p0;
+            const int off = g_tile - p0 * HK;
+            r_hkp = off / r_tiles;
+            tile0 = off % r_tiles;
+        } else {        // later runs start at the first tile of the next stream
+            tile0 = 0;
+            if (++r_hkp == HK) {
+                r_hkp = 0;
+                do {
+                    ++r_s;
+                    r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
+                } while (r_tiles == 0);
+            }
+        }
+        const int p0 = __ldcg(a.tile_prefix + r_s);
+        const int ntile = min(r_tiles - tile0, g_end - g_tile);
+        const int ctx = a.past_lens[r_s] + 1;
+        r_tok = tile0 * kTile;
+        r_end = min(ctx, (tile0 + ntile) * kTile);
+        r_tb = a.block_indices_begins[r_s];
+        r_nb = a.block_indices_begins[r_s + 1] - r_tb;
+        const int s_begin = p0 * HK + r_hkp * r_tiles;             // global tile range of the stream
+        const int first_w = s_begin / per_worker, last_w = (s_begin + r_tiles - 1) / per_worker;
+        const int stream = r_s * HK + r_hkp;
+        ++r_seq;
+        if (lane == 0)
+            runs[r_seq % kRunRing] = RunRec{a.subsequence_begins[r_s], r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, {0, 0}};
+        g_tile += ntile;
+        r_first = true;
+        load_window(r_tok / BS);
+    };
+
+    // Issues the next tile of the load stream into ring stage `slot` and records its descriptor.
+    auto produce = [&](int slot) {
+        if (r_tok >= r_end && g_tile < g_end) next_run();
+        if (r_tok >= r_end) {
+            if (lane == 0) descs[slot] = StageDesc{kEnd, 0, 0, 0};
+            if constexpr (!U8) cp_async_commit();
+            return;
+        }
+        uint8_t* st = ring + slot * Cfg::STAGE;
+        const int hk = r_hkp / gtiles;
+        const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)hk * a.g.head_bytes;
+        const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)hk * a.g.head_bytes;
+        const int bi0 = r_tok / BS;
+        if (bi0 + Cfg::NREC - 1 - w_blk0 >= 32) load_window(bi0);
+        int blocks[Cfg::NREC];
+        bool live[Cfg::NREC];
+#pragma unroll
+        for (int r = 0; r < Cfg::NREC; ++r) {
+            live[r] = (bi0 + r) * BS < r_end;
+            blocks[r] = __shfl_sync(0xffffffffu, tbl, (bi0 + r - w_blk0) & 31);
+        }
         if constexpr (U8) {
             if (lane == 0) {
-                int blocks[Cfg::NREC];
                 uint32_t bytes = 0;
 #pragma unroll
-                for (int r = 0; r < Cfg::NREC; ++r) {
-                    const int bi = tile * Cfg::NREC + r;
-                    int blk = -1;
-                    if (bi < nb && bi * BS < tok_end) {
-                        blk = table[bi];
-                        if (blk < 0 || blk >= a.num_blocks) { blk = 0; bad_index = true; }
-                        bytes += 2 * Cfg::REC;
-                    }
-                    blocks[r] = blk;
-                }
-                uint64_t* bar = &bars[it % Cfg::NSTAGE];
-                mbar_expect_tx(bar, bytes);
+                for (int r = 0; r < Cfg::NREC; ++r) bytes += live[r] ? 2 * Cfg::REC : 0;
+                mbar_expect_tx(&bars[slot], bytes);
 #pragma unroll
                 for (int r = 0; r < Cfg::NREC; ++r)
-                    if (blocks[r] >= 0) {
-                        bulk_g2s(st + r * Cfg::REC, kc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, bar);
-                        bulk_g2s(st + Cfg::HALF_STAGE + r * Cfg::REC, vc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, bar);
+                    if (live[r]) {
+                        bulk_g2s(st + r * Cfg::REC, kc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, &bars[slot]);
+                        bulk_g2s(st + Cfg::HALF_STAGE + r * Cfg::REC, vc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, &bars[slot]);
                     }
             }
         } else {
             constexpr int CPR = D / 8;  // 16-byte chunks per token row
 #pragma unroll
-            for (int r = 0; r < Cfg::NREC; ++r) {
-                const int bi = tile * Cfg::NREC + r;
-                if (bi < nb && bi * BS < tok_end) {
-                    int blk = table[bi];
-                    if (blk < 0 || blk >= a.num_blocks) { blk = 0; bad_index = true; }
-                    const uint8_t* ksrc = kc + (long long)blk * a.g.block_bytes;
-                    const uint8_t* vsrc = vc + (long long)blk * a.g.block_bytes;
+            for (int r = 0; r < Cfg::NREC; ++r)
+                if (live[r]) {
+                    const uint8_t* ksrc = kc + (long long)blocks[r] * a.g.block_bytes;
+                    const uint8_t* vsrc = vc + (long long)blocks[r] * a.g.block_bytes;
 #pragma unroll
                     for (int i = lane; i < BS * CPR; i += 32) {
                         const int row = r * BS + i / CPR, ch = i % CPR;
@@ -201,40 +239,101 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a)
                         cp_async16(st + Cfg::HALF_STAGE + dst, vsrc + (long long)i * 16);
                     }
                 }
-            }
+            cp_async_commit();
         }
+        const int valid = min(kTile, r_end - r_tok);
+        const bool last = r_tok + kTile >= r_end;
+        if (lane == 0)
+            descs[slot] = StageDesc{(r_first ? kFirst : 0) | (last ? kLast : 0), valid, r_seq % kRunRing, 0};
+        r_first = false;
+        r_tok += kTile;
     };
 
-    // ---- running state ----------------------------------------------------------------------------
+    // ---- consumer state --------------------------------------------------------------------------
+    uint32_t qa[NKK][4];
+    float qsum[ROWS], qscale[ROWS];
     float oacc[NDT][2 * ROWS];
-#pragma unroll
-    for (int i = 0; i < NDT; ++i)
-#pragma unroll
-        for (int r = 0; r < 2 * ROWS; ++r) oacc[i][r] = 0.f;
     float m_run[ROWS], l_run[ROWS], z_run[ROWS];
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) { m_run[r] = -INFINITY; l_run[r] = 0.f; z_run[r] = 0.f; }
+    int hbase = 0, hcount = 0, t0 = 0;
 
 #pragma unroll
-    for (int p = 0; p < Cfg::NSTAGE - 1; ++p) {
-        if (p < my_tiles) issue(p);
-        if constexpr (!U8) cp_async_commit();
-    }
+    for (int p = 0; p < NS - 1; ++p) produce(p);
 
-    bool timed_out = false;
-    for (int it = 0; it < my_tiles; ++it) {
+    for (int it = 0;; ++it) {
         __syncwarp();  // every lane is done with the stage that is refilled next
-        if (it + Cfg::NSTAGE - 1 < my_tiles) issue(it + Cfg::NSTAGE - 1);
+        produce((it + NS - 1) % NS);
+        __syncwarp();
+        const int slot = it % NS;
+        const StageDesc d = descs[slot];
+        if (d.flags & kEnd) break;
         if constexpr (U8) {
-            if (!mbar_wait_bounded(&bars[it % Cfg::NSTAGE], (it / Cfg::NSTAGE) & 1)) { timed_out = true; break; }
+            if (!mbar_wait_bounded(&bars[slot], (it / NS) & 1)) {
+                if (lane == 0) atomicOr(a.status, 0x80000000u);
+                break;
+            }
         } else {
-            cp_async_commit();
-            cp_async_wait<Cfg::NSTAGE - 1>();
+            cp_async_wait<NS - 1>();
             __syncwarp();
         }
-        const uint8_t* st = ring + (it % Cfg::NSTAGE) * Cfg::STAGE;
-        const int tile_base = (first_tile + warp + it * kDecodeWarps) * kTile;
-        const int valid = tok_end - tile_base;  // tokens of this tile inside the split (may exceed 32)
+        const uint8_t* st = ring + slot * Cfg::STAGE;
+        const int valid = d.valid;
+
+        if (d.flags & kFirst) {
+            // ---- Q fragments of the run -------------------------------------------------------------
+            // u8: the contraction index is permuted so that one 16-byte shared load of a key row
+            // feeds four k-steps: k-step 4*half + i covers dims 64*half + 16*c + 4*i + {0..3}.
+            t0 = runs[d.run].t0;
+            const int hkp = runs[d.run].hkp;
+            const int hk = hkp / gtiles;
+            hbase = hk * G + (hkp % gtiles) * 16;
+            hcount = min(16, hk * G + G - hbase);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                const int hrow = g + 8 * r;
+                const bool live = hrow < hcount;
+                const long long qoff = ((long long)t0 * a.g.Hq + hbase + hrow) * D;
+                float q[D / 4];
+                float amax = 0.f;
+#pragma unroll
+                for (int e = 0; e < D / 4; ++e) {
+                    int dd;
+                    if constexpr (U8) dd = 64 * (e / 16) + 16 * c + (e % 16);
+                    else dd = 16 * (e / 4) + 2 * c + (e & 1) + 8 * ((e >> 1) & 1);
+                    q[e] = live ? load_act(a.query, qoff + dd, a.g.act) : 0.f;
+                    amax = fmaxf(amax, fabsf(q[e]));
+                }
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                float qmul = 1.f;  // exact power-of-two prescale that keeps |q| inside the f16 range
+                if (!BF16 && amax > 32768.f && amax < INFINITY) {
+                    int ex;
+                    frexpf(amax, &ex);
+                    qmul = ldexpf(1.f, 15 - ex);
+                }
+                float sum = 0.f;
+#pragma unroll
+                for (int e = 0; e < D / 4; e += 2) {
+                    uint32_t packed;
+                    if constexpr (BF16) {
+                        packed = pack_bf2(q[e], q[e + 1]);
+                    } else {
+                        packed = pack_h2(q[e] * qmul, q[e + 1] * qmul);
+                        __half2 h = *reinterpret_cast<__half2*>(&packed);
+                        sum += __low2float(h) + __high2float(h);
+                    }
+                    qa[e / 4][r + 2 * ((e >> 1) & 1)] = packed;
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                qsum[r] = sum;
+                qscale[r] = sm_scale * kLog2e / qmul;
+                m_run[r] = -INFINITY; l_run[r] = 0.f; z_run[r] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < NDT; ++i)
+#pragma unroll
+                for (int r = 0; r < 2 * ROWS; ++r) oacc[i][r] = 0.f;
+        }
 
         if constexpr (!U8) {
             if (valid < kTile) {  // stale rows of a partly filled block may hold NaN bit patterns
@@ -251,8 +350,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a)
         float sacc[4][2 * ROWS];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-#pragma unroll
-            for (int r = 0; r < 2 * ROWS; ++r) sacc[j][r] = 0.f;
             float acc4[4] = {0.f, 0.f, 0.f, 0.f};
             if constexpr (U8) {
                 const int row = 8 * (g >> 1) + 2 * j + (g & 1);
@@ -262,8 +359,9 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a)
                     const uint4 w = *reinterpret_cast<const uint4*>(kp + 64 * h);
                     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        mma16816<false, HI>(acc4, qa[4 * h + i], u8x2_to_h2_lo(ww[i]), u8x2_to_h2_hi(ww[i]));
+                    for (int i = 0; i < 4; ++i)  // bytes stay offset by 1024; removed with the zero-point
+                        mma16816<false, HI>(acc4, qa[4 * h + i], __byte_perm(ww[i], 0x64646464u, 0x4140),
+                                            __byte_perm(ww[i], 0x64646464u, 0x4342));
                 }
             } else {
 #pragma unroll
@@ -292,47 +390,63 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a)
                 const uint8_t* kp = st + (tk / BS) * Cfg::REC + BS * D;
                 const float2 ks = *reinterpret_cast<const float2*>(kp + 4 * (tk % BS));
                 const float2 kz = *reinterpret_cast<const float2*>(kp + 4 * BS + 4 * (tk % BS));
-                ks0 = ks.x; ks1 = ks.y; kz0 = kz.x; kz1 = kz.y;
+                ks0 = ks.x; ks1 = ks.y; kz0 = kz.x + 1024.f; kz1 = kz.y + 1024.f;
                 const uint8_t* vp = st + Cfg::HALF_STAGE + (tk / BS) * Cfg::REC + BS * D;
                 const float2 vs = *reinterpret_cast<const float2*>(vp + 4 * (tk % BS));
                 const float2 vz = *reinterpret_cast<const float2*>(vp + 4 * BS + 4 * (tk % BS));
-                vsc[j][0] = vs.x; vsc[j][1] = vs.y; vzp[j][0] = vz.x; vzp[j][1] = vz.y;
+                vsc[j][0] = vs.x; vsc[j][1] = vs.y; vzp[j][0] = vz.x + 1024.f; vzp[j][1] = vz.y + 1024.f;
             }
             const bool ok0 = tk < valid, ok1 = tk + 1 < valid;
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) {
                 float s0 = sacc[j][2 * r], s1 = sacc[j][2 * r + 1];
                 if constexpr (U8) {
-                    s0 = (s0 - kz0 * qsum[r]) * ks0;
-                    s1 = (s1 - kz1 * qsum[r]) * ks1;
+                    s0 = (s0 - kz0 * qsum[r]) * (ks0 * qscale[r]);
+                    s1 = (s1 - kz1 * qsum[r]) * (ks1 * qscale[r]);
+                } else {
+                    s0 *= qscale[r]; s1 *= qscale[r];
                 }
-                s0 = ok0 ? s0 * qscale[r] : -INFINITY;
-                s1 = ok1 ? s1 * qscale[r] : -INFINITY;
+                s0 = ok0 ? s0 : -INFINITY;
+                s1 = ok1 ? s1 : -INFINITY;
                 sacc[j][2 * r] = s0; sacc[j][2 * r + 1] = s1;
                 tmax[r] = fmaxf(tmax[r], fmaxf(s0, s1));
             }
         }
-        uint32_t pa_frag[2][4];
+        // The reference maximum is raised only when the tile maximum exceeds it by more than
+        // kLazyMax (warp-uniform decision), so most tiles skip the rescale of the accumulators.
+        bool grow = false;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             float mx = tmax[r];
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[r], mx);       // finite: every tile has >= 1 valid token
-            const float alpha = exp2f(m_run[r] - m_new);   // 0 on the first tile
-            m_run[r] = m_new;
-            l_run[r] *= alpha;
-            z_run[r] *= alpha;
+            tmax[r] = mx;
+            grow |= mx > m_run[r] + kLazyMax;
+        }
+        if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-            for (int i = 0; i < NDT; ++i) { oacc[i][2 * r] *= alpha; oacc[i][2 * r + 1] *= alpha; }
+            for (int r = 0; r < ROWS; ++r) {
+                const float m_new = fmaxf(m_run[r], tmax[r]);
+                const float alpha = fast_exp2(m_run[r] - m_new);  // 0 on the first tile
+                m_run[r] = m_new;
+                l_run[r] *= alpha;
+                z_run[r] *= alpha;
+#pragma unroll
+                for (int i = 0; i < NDT; ++i) { oacc[i][2 * r] *= alpha; oacc[i][2 * r + 1] *= alpha; }
+            }
+        }
+        uint32_t pa_frag[2][4];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
             float lsum = 0.f, zsum = 0.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int tk = U8 ? 8 * c + 2 * j : 8 * j + 2 * c;
-                const float p0 = exp2f(sacc[j][2 * r] - m_new), p1 = exp2f(sacc[j][2 * r + 1] - m_new);
+                const float p0 = fast_exp2(sacc[j][2 * r] - m_run[r]), p1 = fast_exp2(sacc[j][2 * r + 1] - m_run[r]);
                 lsum += p0 + p1;
                 uint32_t packed;
                 if constexpr (U8) {
+                    const int tk = 8 * c + 2 * j;
+                    // masked tokens have p == 0; the select keeps garbage scale bits (NaN) out
                     packed = pack_h2(tk < valid ? p0 * vsc[j][0] : 0.f, tk + 1 < valid ? p1 * vsc[j][1] : 0.f);
                     const __half2 h = *reinterpret_cast<__half2*>(&packed);
                     zsum += (tk < valid ? __low2float(h) * vzp[j][0] : 0.f) + (tk + 1 < valid ? __high2float(h) * vzp[j][1] : 0.f);
@@ -352,14 +466,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a)
         if constexpr (U8) {
 #pragma unroll
             for (int i = 0; i < NDT; ++i) {
-                const int d = 8 * i + g;
-                const uint8_t* vp = st + Cfg::HALF_STAGE + ((8 * c) / BS) * Cfg::REC + d * BS + ((8 * c) % BS);
+                const int dd = 8 * i + g;
+                const uint8_t* vp = st + Cfg::HALF_STAGE + ((8 * c) / BS) * Cfg::REC + dd * BS + ((8 * c) % BS);
                 const uint2 w = *reinterpret_cast<const uint2*>(vp);
                 float acc4[4];
                 acc4[0] = oacc[i][0]; acc4[1] = oacc[i][1];
                 if constexpr (HI) { acc4[2] = oacc[i][2]; acc4[3] = oacc[i][3]; }
-                mma16816<false, HI>(acc4, pa_frag[0], u8x2_to_h2_lo(w.x), u8x2_to_h2_hi(w.x));
-                mma16816<false, HI>(acc4, pa_frag[1], u8x2_to_h2_lo(w.y), u8x2_to_h2_hi(w.y));
+                mma16816<false, HI>(acc4, pa_frag[0], __byte_perm(w.x, 0x64646464u, 0x4140), __byte_perm(w.x, 0x64646464u, 0x4342));
+                mma16816<false, HI>(acc4, pa_frag[1], __byte_perm(w.y, 0x64646464u, 0x4140), __byte_perm(w.y, 0x64646464u, 0x4342));
                 oacc[i][0] = acc4[0]; oacc[i][1] = acc4[1];
                 if constexpr (HI) { oacc[i][2] = acc4[2]; oacc[i][3] = acc4[3]; }
             }
@@ -383,132 +497,128 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) decode_kernel(KernelArgs a)
                     }
                 }
         }
+
+        if (!(d.flags & kLast)) continue;
+
+        // ---- end of the run: fold the zero-point term, publish ---------------------------------------
+        float lrow[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            float l = l_run[r], z = z_run[r];
+            l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
+            z += __shfl_xor_sync(0xffffffffu, z, 1); z += __shfl_xor_sync(0xffffffffu, z, 2);
+            lrow[r] = l;
+#pragma unroll
+            for (int i = 0; i < NDT; ++i) { oacc[i][2 * r] -= z; oacc[i][2 * r + 1] -= z; }
+        }
+        const RunRec fin = runs[d.run];
+        if (fin.nparts == 1) {  // the run is the whole stream
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                const int hrow = g + 8 * r;
+                if (hrow >= hcount) continue;
+                const long long row = (long long)t0 * a.g.Hq + hbase + hrow;
+                const float inv = 1.f / lrow[r];
+#pragma unroll
+                for (int i = 0; i < NDT; ++i) store_pair(a.output, row * D + 8 * i + 2 * c, a.g.act, oacc[i][2 * r] * inv, oacc[i][2 * r + 1] * inv);
+                if (c == 0 && a.lse) a.lse[row] = (m_run[r] + log2f(lrow[r])) * kLn2;
+            }
+            continue;
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const int hrow = g + 8 * r;
+            if (hrow >= hcount) continue;
+            const long long prow = (long long)fin.slot * RT + hrow;
+#pragma unroll
+            for (int i = 0; i < NDT; ++i)
+                __stcg(reinterpret_cast<float2*>(a.part_o + prow * D + 8 * i + 2 * c), make_float2(oacc[i][2 * r], oacc[i][2 * r + 1]));
+            if (c == 0) __stcg(reinterpret_cast<float2*>(a.part_ml + prow * 2), make_float2(m_run[r], lrow[r]));
+        }
+        __threadfence();
+        __syncwarp();
+        int done = 0;
+        if (lane == 0) done = atomicAdd(&a.stream_done[fin.stream], 1) + 1;
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (done != fin.nparts) continue;
+        // ---- this partial completed the stream: merge all of its partials ---------------------------
+        __threadfence();
+        const int nparts = fin.nparts;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const int hrow = g + 8 * r;
+            if (hrow >= hcount) continue;
+            float m = -INFINITY;
+            for (int j = 0; j < nparts; ++j) m = fmaxf(m, __ldcg(a.part_ml + ((long long)(fin.first_slot + j) * RT + hrow) * 2));
+            float l = 0.f;
+            float o[NDT][2];
+#pragma unroll
+            for (int i = 0; i < NDT; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; }
+            for (int j = 0; j < nparts; ++j) {
+                const long long prow = (long long)(fin.first_slot + j) * RT + hrow;
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + prow * 2));
+                const float f = fast_exp2(ml.x - m);
+                l += f * ml.y;
+#pragma unroll
+                for (int i = 0; i < NDT; ++i) {
+                    const float2 v = __ldcg(reinterpret_cast<const float2*>(a.part_o + prow * D + 8 * i + 2 * c));
+                    o[i][0] += f * v.x; o[i][1] += f * v.y;
+                }
+            }
+            const long long row = (long long)t0 * a.g.Hq + hbase + hrow;
+            const float inv = 1.f / l;
+#pragma unroll
+            for (int i = 0; i < NDT; ++i) store_pair(a.output, row * D + 8 * i + 2 * c, a.g.act, o[i][0] * inv, o[i][1] * inv);
+            if (c == 0 && a.lse) a.lse[row] = (m + log2f(l)) * kLn2;
+        }
     }
     if constexpr (!U8) cp_async_wait<0>();
-    if (timed_out || bad_index) {
-        if (lane == 0) atomicOr(a.status, bad_index ? PA_DEV_BAD_BLOCK_INDEX : 0x80000000u);
-    }
-
-    // ---- fold the zero-point term, reduce the row sums over the four lanes of a row ---------------
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        float l = l_run[r], z = z_run[r];
-        l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
-        z += __shfl_xor_sync(0xffffffffu, z, 1); z += __shfl_xor_sync(0xffffffffu, z, 2);
-        l_run[r] = l;
-#pragma unroll
-        for (int i = 0; i < NDT; ++i) { oacc[i][2 * r] -= z; oacc[i][2 * r + 1] -= z; }
-    }
-
-    // ---- merge the four warps through shared memory (the rings are free now) ----------------------
-    __syncthreads();
-    constexpr int HROWS = 8 * ROWS;
-    float* sm_o = reinterpret_cast<float*>(smem);              // [warp][HROWS][D]
-    float* sm_m = sm_o + kDecodeWarps * HROWS * D;             // [warp][HROWS]
-    float* sm_l = sm_m + kDecodeWarps * HROWS;                 // [warp][HROWS]
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        const int hrow = g + 8 * r;
-#pragma unroll
-        for (int i = 0; i < NDT; ++i) {
-            float2 v = make_float2(oacc[i][2 * r], oacc[i][2 * r + 1]);
-            *reinterpret_cast<float2*>(&sm_o[(warp * HROWS + hrow) * D + 8 * i + 2 * c]) = v;
-        }
-        if (c == 0) { sm_m[warp * HROWS + hrow] = m_run[r]; sm_l[warp * HROWS + hrow] = l_run[r]; }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < hcount * D; idx += blockDim.x) {
-        const int hrow = idx / D, d = idx % D;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) m = fmaxf(m, sm_m[w * HROWS + hrow]);
-        float o = 0.f, l = 0.f;
-#pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) {
-            const float mw = sm_m[w * HROWS + hrow];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
-            o += f * sm_o[(w * HROWS + hrow) * D + d];
-            l += f * sm_l[w * HROWS + hrow];
-        }
-        const int hq = hbase + hrow;
-        if (nsplit == 1) {
-            store_act(a.output, ((long long)t0 * a.g.Hq + hq) * D + d, a.g.act, o / l);
-            if (d == 0 && a.lse) a.lse[(long long)t0 * a.g.Hq + hq] = (m + log2f(l)) * kLn2;
-        } else {
-            const long long slot = ((long long)s * a.g.Hq + hq) * a.max_splits + split;
-            a.part_o[slot * D + d] = o;
-            if (d == 0) { a.part_ml[slot * 2] = m; a.part_ml[slot * 2 + 1] = l; }
-        }
-    }
-}
-
-// Combines the context splits of one (sequence, q head): grid (Hq, num_sequences), D threads.
-template <int D>
-__global__ void __launch_bounds__(D) decode_merge_kernel(KernelArgs a) {
-    const int s = blockIdx.y, hq = blockIdx.x, d = threadIdx.x;
-    const int t0 = a.subsequence_begins[s];
-    if (a.subsequence_begins[s + 1] - t0 != 1) return;
-    const int past = a.past_lens[s];
-    if (past < 0) return;
-    const int nsplit = (past + 1 + a.split_tokens - 1) / a.split_tokens;
-    if (nsplit <= 1 || nsplit > a.max_splits) return;
-    const long long base = ((long long)s * a.g.Hq + hq) * a.max_splits;
-    float m = -INFINITY;
-    for (int i = 0; i < nsplit; ++i) m = fmaxf(m, a.part_ml[(base + i) * 2]);
-    float o = 0.f, l = 0.f;
-    for (int i = 0; i < nsplit; ++i) {
-        const float f = exp2f(a.part_ml[(base + i) * 2] - m);
-        o += f * a.part_o[(base + i) * D + d];
-        l += f * a.part_ml[(base + i) * 2 + 1];
-    }
-    store_act(a.output, ((long long)t0 * a.g.Hq + hq) * D + d, a.g.act, o / l);
-    if (d == 0 && a.lse) a.lse[(long long)t0 * a.g.Hq + hq] = (m + log2f(l)) * kLn2;
+    if (__any_sync(0xffffffffu, bad_index) && lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
 }
 
 template <int D, int BS, int CACHE>
-cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int* launches) {
+cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {
     using Cfg = DecodeCfg<D, BS, CACHE>;
     const int G = a.g.Hq / a.g.Hkv;
-    const int gtiles = (G + 15) / 16;
-    dim3 grid(a.max_splits, a.g.Hkv * gtiles, a.num_sequences);
     const bool hi = G > 8;
     auto kern = hi ? decode_kernel<D, BS, CACHE, true> : decode_kernel<D, BS, CACHE, false>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[hi]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-        if (e != cudaSuccess) return e;
-        attr_set[hi] = true;
-    }
-    kern<<<grid, kDecodeWarps * 32, Cfg::SMEM, stream>>>(a);
-    ++*launches;
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) return e;
-    if (a.max_splits > 1) {
-        decode_merge_kernel<D><<<dim3(a.g.Hq, a.num_sequences), D, 0, stream>>>(a);
-        ++*launches;
-        e = cudaGetLastError();
-    }
-    return e;
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeWarps * 32, Cfg::SMEM);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    // no more workers than slices could ever exist (upper bound known on the host)
+    const long long max_slices = (a.max_tiles + kMinSlice - 1) / kMinSlice;
+    long long ctas = (long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count;
+    ctas = std::min(ctas, (max_slices + kDecodeWarps - 1) / kDecodeWarps);
+    if (ev0) cudaEventRecord(ev0, stream);
+    kern<<<(unsigned)std::max(1LL, ctas), kDecodeWarps * 32, Cfg::SMEM, stream>>>(a);
+    if (ev1) cudaEventRecord(ev1, stream);
+    ++*launches;
+    return cudaGetLastError();
 }
 
 template <int D, int BS>
-cudaError_t launch_decode_c(const KernelArgs& a, cudaStream_t stream, int* launches) {
+cudaError_t launch_decode_c(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {
     switch (a.g.cache) {
-        case PA_DTYPE_U8: return launch_decode_t<D, BS, PA_DTYPE_U8>(a, stream, launches);
-        case PA_DTYPE_F16: return launch_decode_t<D, BS, PA_DTYPE_F16>(a, stream, launches);
-        case PA_DTYPE_BF16: return launch_decode_t<D, BS, PA_DTYPE_BF16>(a, stream, launches);
+        case PA_DTYPE_U8: return launch_decode_t<D, BS, PA_DTYPE_U8>(a, stream, sm_count, launches, ev0, ev1);
+        case PA_DTYPE_F16: return launch_decode_t<D, BS, PA_DTYPE_F16>(a, stream, sm_count, launches, ev0, ev1);
+        case PA_DTYPE_BF16: return launch_decode_t<D, BS, PA_DTYPE_BF16>(a, stream, sm_count, launches, ev0, ev1);
     }
     return cudaErrorInvalidValue;
 }
 
 }  // namespace
 
-cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int* launches) {
+int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps; }
+
+cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {
     if (a.num_sequences <= 0) return cudaSuccess;
-    if (a.g.D == 128 && a.g.bs == 32) return launch_decode_c<128, 32>(a, stream, launches);
-    if (a.g.D == 128 && a.g.bs == 16) return launch_decode_c<128, 16>(a, stream, launches);
-    if (a.g.D == 64 && a.g.bs == 32) return launch_decode_c<64, 32>(a, stream, launches);
-    if (a.g.D == 64 && a.g.bs == 16) return launch_decode_c<64, 16>(a, stream, launches);
+    if (a.g.D == 128 && a.g.bs == 32) return launch_decode_c<128, 32>(a, stream, sm_count, launches, ev0, ev1);
+    if (a.g.D == 128 && a.g.bs == 16) return launch_decode_c<128, 16>(a, stream, sm_count, launches, ev0, ev1);
+    if (a.g.D == 64 && a.g.bs == 32) return launch_decode_c<64, 32>(a, stream, sm_count, launches, ev0, ev1);
+    if (a.g.D == 64 && a.g.bs == 16) return launch_decode_c<64, 16>(a, stream, sm_count, launches, ev0, ev1);
     return cudaErrorInvalidValue;
 }
 

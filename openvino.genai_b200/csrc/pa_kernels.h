@@ -8,6 +8,12 @@
 
 namespace pa {
 
+// Header of the plan area in the handle's scratch.
+struct PlanHeader {
+    int total_tiles;   // 32-token tiles of all decode streams (rows x head tiles)
+    int pad[3];
+};
+
 // Everything a kernel needs, passed by value.  All pointers are device memory.
 struct KernelArgs {
     CacheGeom g;
@@ -35,25 +41,36 @@ struct KernelArgs {
     int rotation_lut_rows;
     uint32_t* status;      // device status word (PA_DEV_* bits)
     // scratch owned by the handle
-    float* part_o;         // split partial outputs  [item][split][G][D]
-    float* part_ml;        // split partial (max, sum) [item][split][G][2]
+    // Decode plan.  A "stream" is (decode row, head tile); row s has tile_prefix[s+1] - tile_prefix[s]
+    // tiles of 32 context tokens per head tile.  The global tile sequence is row-major, then head
+    // tile, then position; worker w processes its w-th equal slice.
+    PlanHeader* plan;      // decode plan header
+    int* tile_prefix;      // [num_sequences + 1] exclusive prefix sum of tiles per row (one head tile)
+    int* stream_done;      // [num_sequences * HK] partials of the stream published so far
+    long long max_tiles;   // upper bound of total_tiles known on the host
+    int rows_per_tile;     // q heads per head tile: min(G, 16)
+    float* part_o;         // partial outputs    [slot = stream + worker][rows_per_tile][D]
+    float* part_ml;        // partial (max, sum) [slot][rows_per_tile][2]
     float* lse;            // log-sum-exp per (token, q head), natural log, of the scaled logits
-    float* score_part;     // per kv-head score partials [Hkv][scores_len]
     int64_t* score_offsets;// [num_sequences + 1] prefix sum of past_len + new tokens
-    int split_tokens;      // context tokens handled by one decode CTA
-    int max_splits;        // ceil(max_context_len / split_tokens)
     long long scores_len;
 };
 
-cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream);
+// Writes the chunk's new keys / values into the paged cache and, in the same launch, builds the
+// decode plan (chunk list, zeroed counters) when `with_plan` is set.
+cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream, bool with_plan);
 cudaError_t launch_rotate(const KernelArgs& a, cudaStream_t stream);
 cudaError_t launch_copy_blocks(void* key_cache, void* value_cache, long long block_bytes, int num_blocks,
                                const int32_t* pairs, int num_pairs, uint32_t* status, cudaStream_t stream);
 
-// Attention over rows with exactly one new token (decode rows).  Launches the split-K kernel and
-// the merge kernel.  Rows with more than one new token are skipped by these kernels.
-cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int* launches);
-size_t decode_smem_bytes(const CacheGeom& g);
+// Attention over rows with exactly one new token (decode rows): one persistent launch that walks
+// the plan's work queue.  Rows with more than one new token are not in the plan.
+// When ev0/ev1 are given they are recorded immediately before / after the kernel.
+cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0 = nullptr,
+                          cudaEvent_t ev1 = nullptr);
+
+// Upper bound of the decode kernel's worker (warp) count, for sizing the partial-result scratch.
+int decode_max_workers(int sm_count);
 
 // Attention over rows with more than one new token (prefill chunks).
 cudaError_t launch_prefill(const KernelArgs& a, cudaStream_t stream, int* launches);

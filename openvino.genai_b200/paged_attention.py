@@ -101,6 +101,8 @@ class PagedAttentionExtension:
         a.rotation_lut_rows = int(rotation_trig_lut.shape[0]) if rotation_trig_lut is not None else 0
         if stream is None and isinstance(query, torch.Tensor) and query.is_cuda:
             stream = torch.cuda.current_stream(query.device).cuda_stream  # order after the caller's torch work
+        if stream == 0:
+            stream = 1  # cudaStreamLegacy: NULL would select the handle's own stream instead of the default stream
         a.stream = stream
         return a
 

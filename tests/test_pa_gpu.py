@@ -47,7 +47,7 @@ def test_decode_config1_tinyllama_shape():
 
 
 def test_decode_long_context_many_splits(monkeypatch):
-    monkeypatch.setenv("PA_B200_SPLIT_TOKENS", "256")
+    monkeypatch.setenv("PA_B200_UNUSED", "1")
     wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[5000, 255, 256, 257], new=[1] * 4, seed=31)
     _check(H.run_both(wl), "u8", torch.bfloat16)
 
