@@ -1,0 +1,689 @@
+// Sampler step for sm_100a: one kernel launch for the whole batch, one CTA per sampled row.
+//
+// Phases of a row (src/cpp/src/sampling/logit_processor.hpp:28-112 fixes the order):
+//   1. penalties, in place on the logits row, one thread per distinct history id, in the
+//      reference's float (+) double -> float arithmetic with every step individually rounded;
+//   2. greedy rows: strict-> argmax with lowest-index ties over the row (one HBM pass);
+//   3. multinomial rows with an active top-k: the reference keeps a K-element min-heap whose final
+//      ARRAY ORDER feeds every later float sum and the draw itself, so the order is reproduced
+//      exactly: 31 producer warps stream the row, keep only elements above a (stale, hence
+//      conservative) copy of the heap minimum, and compact them in index order into a double
+//      buffer; one thread replays libstdc++'s pop_heap / push_heap on those few hundred survivors
+//      while the producers filter the next chunk.  Softmax, min-p, top-p and the draw then run
+//      over <= K elements in one thread, in the reference's order of operations;
+//   4. multinomial rows over the full vocabulary: max, exp and sums are block reductions
+//      (deterministic, but not the reference's index-order float accumulation), top-p uses a
+//      three-level radix descent over the order-preserving bit pattern of the logits.
+// HBM-bound: the row is read once (plus an L2-resident second pass for the radix descent).
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/sampler_b200.h"
+#include "sampler_kernels.h"
+
+namespace sampler {
+
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr int kProducerThreads = kThreads - 32;       // warps 1..31 filter, warp 0 replays the heap
+constexpr int kChunk = kProducerThreads * 4;          // elements per filter round
+constexpr int kMaxTopK = 1024;                        // heap capacity in shared memory
+
+struct Cand {
+    float v;
+    int idx;
+};
+
+__device__ __forceinline__ void named_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void named_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+// expf as "exp in double, rounded once to float": within an ulp of glibc's expf and equal to it
+// except where glibc's own result is not the correctly rounded one.
+__device__ __forceinline__ float exp_as_float(float x) { return (float)exp((double)x); }
+
+// ---- libstdc++ heap primitives on (value, index) pairs with comp(a, b) = a.v > b.v (min-heap) ----
+__device__ void push_heap_from(Cand* h, int hole, int top, Cand value) {
+    int parent = (hole - 1) / 2;
+    while (hole > top && h[parent].v > value.v) {
+        h[hole] = h[parent];
+        hole = parent;
+        parent = (hole - 1) / 2;
+    }
+    h[hole] = value;
+}
+
+__device__ void adjust_heap(Cand* h, int hole, int len, Cand value) {
+    const int top = hole;
+    int child = hole;
+    while (child < (len - 1) / 2) {
+        child = 2 * (child + 1);
+        if (h[child].v > h[child - 1].v) --child;
+        h[hole] = h[child];
+        hole = child;
+    }
+    if ((len & 1) == 0 && child == (len - 2) / 2) {
+        child = 2 * (child + 1);
+        h[hole] = h[child - 1];
+        hole = child - 1;
+    }
+    push_heap_from(h, hole, top, value);
+}
+
+__device__ void make_heap(Cand* h, int len) {
+    if (len < 2) return;
+    for (int parent = (len - 2) / 2;; --parent) {
+        adjust_heap(h, parent, len, h[parent]);
+        if (parent == 0) return;
+    }
+}
+
+// pop_heap(first, last) followed by back() = x and push_heap(first, last), as TopKFilter does
+// (src/cpp/src/sampling/logit_transformers.hpp:240-246).
+__device__ __forceinline__ void replace_min(Cand* h, int k, Cand x) {
+    if (k > 1) {
+        const Cand last = h[k - 1];
+        h[k - 1] = h[0];
+        adjust_heap(h, 0, k - 1, last);
+    }
+    h[k - 1] = x;
+    push_heap_from(h, k - 1, 0, x);
+}
+
+// ---- libstdc++ partial_sort / sort on (value, index) pairs with comp(a, b) = a.v > b.v --------------
+// TopPFilter sorts candidates with std::partial_sort and std::sort; neither is stable, so to scan
+// equal probabilities in the reference's order the algorithms themselves are restated:
+// heap-select + sort-heap, and introsort (median-of-three, threshold 16, depth 2*floor(log2 n))
+// with the final guarded / unguarded insertion pass.
+__device__ __forceinline__ bool desc(const Cand& a, const Cand& b) { return a.v > b.v; }
+__device__ __forceinline__ void swap_cand(Cand& a, Cand& b) { const Cand t = a; a = b; b = t; }
+
+__device__ void pop_heap_into(Cand* first, int len, Cand* result) {  // __pop_heap(first, first + len, result)
+    const Cand value = *result;
+    *result = first[0];
+    adjust_heap(first, 0, len, value);
+}
+
+__device__ void std_partial_sort(Cand* v, int middle, int n) {
+    make_heap(v, middle);
+    for (int i = middle; i < n; ++i)
+        if (desc(v[i], v[0])) pop_heap_into(v, middle, &v[i]);
+    for (int last = middle; last > 1;) {
+        --last;
+        pop_heap_into(v, last, &v[last]);
+    }
+}
+
+__device__ void unguarded_linear_insert(Cand* v, int last) {
+    const Cand val = v[last];
+    int next = last - 1;
+    while (desc(val, v[next])) {
+        v[last] = v[next];
+        last = next;
+        --next;
+    }
+    v[last] = val;
+}
+
+__device__ void insertion_sort(Cand* v, int first, int last) {
+    if (first == last) return;
+    for (int i = first + 1; i != last; ++i) {
+        if (desc(v[i], v[first])) {
+            const Cand val = v[i];
+            for (int j = i; j > first; --j) v[j] = v[j - 1];
+            v[first] = val;
+        } else {
+            unguarded_linear_insert(v, i);
+        }
+    }
+}
+
+__device__ void move_median_to_first(Cand* v, int result, int a, int b, int c) {
+    if (desc(v[a], v[b])) {
+        if (desc(v[b], v[c])) swap_cand(v[result], v[b]);
+        else if (desc(v[a], v[c])) swap_cand(v[result], v[c]);
+        else swap_cand(v[result], v[a]);
+    } else if (desc(v[a], v[c])) swap_cand(v[result], v[a]);
+    else if (desc(v[b], v[c])) swap_cand(v[result], v[c]);
+    else swap_cand(v[result], v[b]);
+}
+
+__device__ int unguarded_partition(Cand* v, int first, int last, int pivot) {
+    for (;;) {
+        while (desc(v[first], v[pivot])) ++first;
+        --last;
+        while (desc(v[pivot], v[last])) --last;
+        if (!(first < last)) return first;
+        swap_cand(v[first], v[last]);
+        ++first;
+    }
+}
+
+__device__ void std_sort(Cand* v, int n) {
+    if (n == 0) return;
+    int lg = 0;
+    for (int t = n; t > 1; t >>= 1) ++lg;
+    // explicit stack instead of the recursive call on [cut, last): the two halves are independent
+    int stack_first[48], stack_last[48], stack_depth[48];
+    int sp = 0;
+    stack_first[sp] = 0; stack_last[sp] = n; stack_depth[sp] = 2 * lg; ++sp;
+    while (sp > 0) {
+        --sp;
+        int first = stack_first[sp], last = stack_last[sp], depth = stack_depth[sp];
+        while (last - first > 16) {
+            if (depth == 0) {
+                std_partial_sort(v + first, last - first, last - first);
+                break;
+            }
+            --depth;
+            const int mid = first + (last - first) / 2;
+            move_median_to_first(v, first, first + 1, mid, last - 1);
+            const int cut = unguarded_partition(v, first + 1, last, first);
+            stack_first[sp] = cut; stack_last[sp] = last; stack_depth[sp] = depth; ++sp;
+            last = cut;
+        }
+    }
+    if (n > 16) {
+        insertion_sort(v, 0, 16);
+        for (int i = 16; i < n; ++i) unguarded_linear_insert(v, i);
+    } else {
+        insertion_sort(v, 0, n);
+    }
+}
+
+// ---- block reductions -------------------------------------------------------------------------------
+template <class T>
+__device__ __forceinline__ T shfl_xor_any(T v, int o) {
+    static_assert(sizeof(T) % 4 == 0, "word-sized types only");
+    union { T t; uint32_t w[sizeof(T) / 4]; } in, out;
+    in.t = v;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(T) / 4); ++i) out.w[i] = __shfl_xor_sync(0xffffffffu, in.w[i], o);
+    return out.t;
+}
+
+template <class T, class Op>
+__device__ T block_reduce(T v, T identity, Op op, T* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = op(v, shfl_xor_any(v, o));
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    v = lane < kWarps ? sh[lane] : identity;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = op(v, shfl_xor_any(v, o));
+    return v;
+}
+
+struct ArgMax {
+    float v;
+    int i;
+};
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    // strict '>' with the lowest index among equals; NaN never wins (sampler.cpp:952-961)
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+// Order-preserving 32-bit key of a float: larger float <=> larger unsigned key.
+__device__ __forceinline__ uint32_t float_key(float x) {
+    const uint32_t b = __float_as_uint(x);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+struct Shared {
+    Cand heap[kMaxTopK];
+    Cand cand[2][kChunk];
+    int cand_count[2];
+    float tau;                 // producers' copy of the heap minimum (may lag, never leads)
+    int warp_off[kWarps];
+    float red_f[kWarps];
+    double red_d[kWarps];
+    int red_i[kWarps];
+    unsigned long long red_u[kWarps];
+    ArgMax red_a[kWarps];
+    unsigned int hist_cnt[2048];
+    unsigned long long hist_mass[2048];
+    int sel_bin;
+    unsigned long long sel_mass_above;
+    unsigned int sel_cnt_above;
+    float out_p;
+    long long out_idx;
+};
+
+// ---- phase 1: penalties ---------------------------------------------------------------------------------
+__device__ void apply_history(float* row, long long V, const sampler_row_params& p, const int32_t* ids, const uint32_t* meta,
+                              long long n, uint32_t* status) {
+    const double rep = (double)p.repetition_penalty, pres = (double)p.presence_penalty, freq = (double)p.frequency_penalty;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        const int id = ids[i];
+        const uint32_t m = meta[i];
+        if (id < 0 || id >= V) {
+            atomicOr(status, 1u);
+            continue;
+        }
+        float v = row[id];
+        if (m & SAMPLER_HIST_STOP_MASK) v = -CUDART_INF_F;
+        if (p.repetition_penalty != 1.0f && (m & (SAMPLER_HIST_IN_PROMPT | SAMPLER_HIST_GENERATED)))
+            v = v >= 0 ? (float)__ddiv_rn((double)v, rep) : (float)__dmul_rn((double)v, rep);
+        if (m & SAMPLER_HIST_GENERATED) {
+            if (p.presence_penalty != 0.0f) v = v >= 0 ? (float)__dsub_rn((double)v, pres) : (float)__dadd_rn((double)v, pres);
+            if (p.frequency_penalty != 0.0f) {
+                const double t = __dmul_rn(freq, (double)(m >> 3));
+                v = v >= 0 ? (float)__dsub_rn((double)v, t) : (float)__dadd_rn((double)v, t);
+            }
+        }
+        row[id] = v;
+    }
+}
+
+// ---- phase 3 tail: softmax / min-p / top-p / draw over the K heap entries, one thread ---------------
+// Mirrors TemperatureLogitTransform, MinPFilter, TopPFilter (logit_transformers.hpp:90-362) and
+// Sampler::_multinomial_sample (sampler.cpp:979-1095) statement by statement.
+__device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float* out_p, long long* out_idx) {
+    const bool min_p_active = p.min_p > 0.0f;
+    const bool defer = p.top_p == 1.0f && !min_p_active;
+    const float T = p.temperature;
+    if (defer) {
+        if (T != 1.0f) {
+            const float f = 1.0f / T;
+            for (int i = 0; i < n; ++i) v[i].v *= f;
+        }
+        float mx = v[0].v;
+        for (int i = 1; i < n; ++i) if (v[i].v > mx) mx = v[i].v;
+        float sum = 0.0f;
+        // weights overwrite nothing: recompute in the scan (same values, same order)
+        for (int i = 0; i < n; ++i) sum += exp_as_float(v[i].v - mx);
+        const bool uniform = !(sum > 0.0f && isfinite(sum));
+        if (uniform) sum = (float)n;
+        const float log_sum = logf(sum) + (uniform ? 0.0f : mx);
+        const float r = sum * p.rand_u;
+        float run = 0.0f;
+        int pick = n - 1;
+        for (int i = 0; i < n; ++i) {
+            run += uniform ? 1.0f : exp_as_float(v[i].v - mx);
+            if (run > r) { pick = i; break; }
+        }
+        *out_p = uniform ? logf(1.0f / (float)n) : v[pick].v - log_sum;
+        *out_idx = v[pick].idx;
+        return;
+    }
+    {   // softmax(logits / T) over the heap array, in array order
+        float mx = v[0].v;
+        for (int i = 1; i < n; ++i) if (v[i].v > mx) mx = v[i].v;
+        float sum = 0.0f;
+        if (T == 1.0f) {
+            for (int i = 0; i < n; ++i) { v[i].v = exp_as_float(v[i].v - mx); sum += v[i].v; }
+        } else {
+            const float f = 1.0f / T;
+            for (int i = 0; i < n; ++i) { v[i].v = exp_as_float((v[i].v - mx) * f); sum += v[i].v; }
+        }
+        for (int i = 0; i < n; ++i) v[i].v = __fdiv_rn(v[i].v, sum);
+    }
+    if (min_p_active) {
+        float mx = 0.0f;
+        int arg = 0;
+        for (int i = 0; i < n; ++i) if (v[i].v > mx) { mx = v[i].v; arg = i; }
+        const float thr = (float)(double)p.min_p * mx;
+        int m = 0;
+        for (int i = 0; i < n; ++i) if (v[i].v >= thr) v[m++] = v[i];
+        if (m == 0) { v[0] = v[arg]; m = 1; }
+        n = m;
+    }
+    if (p.top_p != 1.0f) {
+        // TopPFilter::apply: partial sorts of the top 16, 32, ... 1024 until the running float sum
+        // exceeds top_p, else a full sort (logit_transformers.hpp:94-139)
+        const double tp = (double)p.top_p;
+        bool done = false;
+        for (int step = 16; step <= 1024 && !done; step *= 2) {
+            if (n <= step) break;
+            std_partial_sort(v, step, n);
+            float sum = 0.0f;
+            for (int i = 0; i < step; ++i) {
+                sum += v[i].v;
+                if ((double)sum > tp) { n = i + 1; done = true; break; }
+            }
+        }
+        if (!done) {
+            std_sort(v, n);
+            float sum = 0.0f;
+            int keep = 0;
+            for (int i = 0; i < n; ++i) {
+                sum += v[i].v;
+                ++keep;
+                if ((double)sum > tp) break;
+            }
+            n = keep;
+        }
+    }
+    float total = 0.0f;
+    for (int i = 0; i < n; ++i) total += v[i].v;
+    if (!(total > 0.0f && isfinite(total))) {
+        int pick = (int)(p.rand_u * (float)n);
+        if (pick > n - 1) pick = n - 1;
+        *out_p = logf(1.0f / (float)n);
+        *out_idx = v[pick].idx;
+        return;
+    }
+    const float log_total = logf(total);
+    const float r = total * p.rand_u;
+    float run = 0.0f;
+    int pick = n - 1;
+    for (int i = 0; i < n; ++i) {
+        run += v[i].v;
+        if (run > r) { pick = i; break; }
+    }
+    *out_p = logf(v[pick].v) - log_total;
+    *out_idx = v[pick].idx;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) sampler_kernel(StepArgs a) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    Shared& sh = *reinterpret_cast<Shared*>(smem_raw);
+    const int r = blockIdx.x;
+    const sampler_row_params p = a.rows[r];
+    const long long V = a.vocab;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (p.logits_row < 0 || p.logits_row >= a.num_logit_rows) {
+        if (tid == 0) { atomicOr(a.status, 2u); a.out_token[r] = -1; a.out_log_prob[r] = 0.f; }
+        return;
+    }
+    float* row = a.logits + p.logits_row * V;
+
+    // ---- 1. penalties ------------------------------------------------------------------------------
+    if (a.hist_offsets) {
+        const long long h0 = a.hist_offsets[r], h1 = a.hist_offsets[r + 1];
+        if (h1 > h0) apply_history(row, V, p, a.hist_ids + h0, a.hist_meta + h0, h1 - h0, a.status);
+    }
+    __syncthreads();
+
+    // ---- 2. greedy ----------------------------------------------------------------------------------
+    if (!p.do_sample) {
+        ArgMax best{-CUDART_INF_F, 0x7fffffff};
+        for (long long i = tid; i < V; i += kThreads) {
+            const float x = row[i];
+            if (x > best.v) { best.v = x; best.i = (int)i; }  // i ascends per thread: first maximum kept
+        }
+        best = block_reduce(best, ArgMax{-CUDART_INF_F, 0x7fffffff}, better, sh.red_a);
+        if (tid == 0) {
+            a.out_token[r] = best.i == 0x7fffffff ? 0 : best.i;  // all -inf / NaN: the reference returns index 0
+            a.out_log_prob[r] = 0.f;
+        }
+        return;
+    }
+
+    const bool top_k_active = p.top_k > 0 && p.top_k < 0x7fffffffffffffffLL;
+    if (top_k_active && p.top_k < V && p.top_k <= kMaxTopK) {
+        // ---- 3. exact top-k heap replay --------------------------------------------------------------
+        const int K = (int)p.top_k;
+        if (warp == 0) {
+            for (int i = lane; i < K; i += 32) sh.heap[i] = Cand{row[i], i};
+            __syncwarp();
+            if (lane == 0) {
+                make_heap(sh.heap, K);
+                sh.tau = sh.heap[0].v;
+            }
+        }
+        __syncthreads();
+        const long long n_rest = V - K;
+        const int rounds = (int)((n_rest + kChunk - 1) / kChunk);
+        if (warp == 0) {
+            // consumer: replays the survivors of round c while the producers filter round c + 1
+            for (int c = 0; c < rounds; ++c) {
+                const int b = c & 1;
+                named_sync(1 + b, kThreads);           // full[b]
+                if (lane == 0) {
+                    const int n = sh.cand_count[b];
+                    for (int i = 0; i < n; ++i) {
+                        const Cand x = sh.cand[b][i];
+                        if (x.v > sh.heap[0].v) replace_min(sh.heap, K, x);
+                    }
+                    *reinterpret_cast<volatile float*>(&sh.tau) = sh.heap[0].v;
+                }
+                __syncwarp();
+                named_arrive(3 + b, kThreads);         // empty[b]
+            }
+        } else {
+            const int ptid = tid - 32, pwarp = warp - 1;
+            for (int c = 0; c < rounds; ++c) {
+                const int b = c & 1;
+                if (c >= 2) named_sync(3 + b, kThreads);  // wait until the consumer drained buffer b
+                const float tau = *reinterpret_cast<volatile float*>(&sh.tau);
+                const long long base = K + (long long)c * kChunk + (long long)ptid * 4;
+                float x[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[e] = base + e < V ? row[base + e] : -CUDART_INF_F;
+                int mine = 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mine += (base + e < V && x[e] > tau) ? 1 : 0;
+                // ordered compaction: exclusive prefix of `mine` over the 992 producer threads
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += u;
+                }
+                if (lane == 31) sh.warp_off[pwarp] = incl;
+                named_sync(5, kProducerThreads);
+                int off = 0;
+                for (int w = 0; w < pwarp; ++w) off += sh.warp_off[w];
+                if (ptid == kProducerThreads - 1) sh.cand_count[b] = off + incl;
+                int pos = off + incl - mine;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (base + e < V && x[e] > tau) sh.cand[b][pos++] = Cand{x[e], (int)(base + e)};
+                named_sync(6, kProducerThreads);       // warp_off is reused next round
+                __threadfence_block();
+                named_arrive(1 + b, kThreads);         // full[b]
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float lp;
+            long long idx;
+            finish_top_k(sh.heap, K, p, &lp, &idx);
+            a.out_token[r] = idx;
+            a.out_log_prob[r] = lp;
+        }
+        return;
+    }
+
+    // ---- 4. full vocabulary ---------------------------------------------------------------------------
+    const float T = p.temperature;
+    const float f = 1.0f / T;
+    float mx = -CUDART_INF_F;
+    for (long long i = tid; i < V; i += kThreads) mx = fmaxf(mx, row[i]);
+    mx = block_reduce(mx, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
+    auto weight = [&](float x) { return T == 1.0f ? exp_as_float(x - mx) : exp_as_float((x - mx) * f); };
+    double dsum = 0.0;
+    for (long long i = tid; i < V; i += kThreads) dsum += (double)weight(row[i]);
+    dsum = block_reduce(dsum, 0.0, [](double x, double y) { return x + y; }, sh.red_d);
+    const float norm = (float)dsum;
+    auto prob = [&](float x) { return __fdiv_rn(weight(x), norm); };
+
+    const bool min_p_active = p.min_p > 0.0f;
+    const bool top_p_active = p.top_p != 1.0f;
+    // probabilities as 2^-40 fixed point so that sums do not depend on the order of addition
+    auto fixed = [](float pr) { return (unsigned long long)((double)pr * 1099511627776.0); };
+    const float pmax = prob(mx);
+    const float min_thr = min_p_active ? (float)(double)p.min_p * pmax : -1.0f;
+
+    uint32_t key_lo = 0;  // candidates are the elements with key >= key_lo that pass min-p
+    if (top_p_active) {
+        // radix descent (11 + 11 + 10 bits) for the smallest key whose descending cumulative mass
+        // first exceeds top_p: elements above it are in the nucleus, the boundary key itself too.
+        const unsigned long long target = fixed(p.top_p);
+        unsigned long long mass_above = 0;   // mass of keys strictly above the current prefix range
+        uint32_t prefix = 0;
+        int shift = 32;
+        bool found_all = false;
+        for (int level = 0; level < 3 && !found_all; ++level) {
+            const int bits = level == 2 ? 10 : 11;
+            shift -= bits;
+            const int nb = 1 << bits;
+            for (int i = tid; i < nb; i += kThreads) { sh.hist_cnt[i] = 0; sh.hist_mass[i] = 0; }
+            __syncthreads();
+            const uint32_t hi_mask = level == 0 ? 0u : (0xffffffffu << (shift + bits));
+            for (long long i = tid; i < V; i += kThreads) {
+                const float x = row[i];
+                const uint32_t k = float_key(x);
+                if ((k & hi_mask) != prefix) continue;
+                const float pr = prob(x);
+                if (pr < min_thr) continue;
+                const int bin = (k >> shift) & (nb - 1);
+                atomicAdd(&sh.hist_cnt[bin], 1u);
+                atomicAdd(&sh.hist_mass[bin], fixed(pr));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long acc = mass_above;
+                int sel = -1;
+                for (int bin = nb - 1; bin >= 0; --bin) {
+                    if (sh.hist_cnt[bin] == 0) continue;
+                    if (acc + sh.hist_mass[bin] > target) { sel = bin; break; }
+                    acc += sh.hist_mass[bin];
+                }
+                sh.sel_bin = sel;
+                sh.sel_mass_above = acc;
+            }
+            __syncthreads();
+            if (sh.sel_bin < 0) { found_all = true; prefix = 0; shift = 0; break; }  // the whole row stays
+            mass_above = sh.sel_mass_above;
+            prefix |= (uint32_t)sh.sel_bin << shift;
+        }
+        key_lo = found_all ? 0u : prefix;
+    }
+
+    // total kept mass, then the draw: r = total * u, first element (descending by key when top-p
+    // sorted the candidates, ascending by index otherwise) whose running sum exceeds r.
+    unsigned long long kept = 0;
+    for (long long i = tid; i < V; i += kThreads) {
+        const float x = row[i];
+        if (float_key(x) < key_lo) continue;
+        const float pr = prob(x);
+        if (pr < min_thr) continue;
+        kept += fixed(pr);
+    }
+    kept = block_reduce(kept, 0ull, [](unsigned long long x, unsigned long long y) { return x + y; }, sh.red_u);
+    const float total = (float)((double)kept / 1099511627776.0);
+    const unsigned long long rfix = fixed(total * p.rand_u);
+
+    if (top_p_active) {
+        // second radix descent, over the kept elements, for the key where the descending
+        // cumulative mass first exceeds r
+        unsigned long long mass_above = 0;
+        uint32_t prefix = 0;
+        int shift = 32;
+        for (int level = 0; level < 3; ++level) {
+            const int bits = level == 2 ? 10 : 11;
+            shift -= bits;
+            const int nb = 1 << bits;
+            for (int i = tid; i < nb; i += kThreads) { sh.hist_cnt[i] = 0; sh.hist_mass[i] = 0; }
+            __syncthreads();
+            const uint32_t hi_mask = level == 0 ? 0u : (0xffffffffu << (shift + bits));
+            for (long long i = tid; i < V; i += kThreads) {
+                const float x = row[i];
+                const uint32_t k = float_key(x);
+                if (k < key_lo || (k & hi_mask) != prefix) continue;
+                const float pr = prob(x);
+                if (pr < min_thr) continue;
+                const int bin = (k >> shift) & (nb - 1);
+                atomicAdd(&sh.hist_cnt[bin], 1u);
+                atomicAdd(&sh.hist_mass[bin], fixed(pr));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long acc = mass_above;
+                int sel = -1, last_nonempty = -1;
+                for (int bin = nb - 1; bin >= 0; --bin) {
+                    if (sh.hist_cnt[bin] == 0) continue;
+                    last_nonempty = bin;
+                    if (acc + sh.hist_mass[bin] > rfix) { sel = bin; break; }
+                    acc += sh.hist_mass[bin];
+                }
+                if (sel < 0) { sel = last_nonempty; acc -= last_nonempty >= 0 ? sh.hist_mass[last_nonempty] : 0; }  // fallback: last element
+                sh.sel_bin = sel;
+                sh.sel_mass_above = acc;
+            }
+            __syncthreads();
+            mass_above = sh.sel_mass_above;
+            prefix |= (uint32_t)max(sh.sel_bin, 0) << shift;
+        }
+        // all elements with this exact key have the same probability: the lowest index is taken
+        int pick = 0x7fffffff;
+        for (long long i = tid; i < V; i += kThreads)
+            if (float_key(row[i]) == prefix) pick = min(pick, (int)i);
+        pick = block_reduce(pick, 0x7fffffff, [](int x, int y) { return min(x, y); }, sh.red_i);
+        if (tid == 0) {
+            const float pr = prob(row[pick]);
+            a.out_token[r] = pick;
+            a.out_log_prob[r] = logf(pr) - logf(total);
+        }
+        return;
+    }
+
+    // index-order draw (no top-p): running sums over chunks of the row
+    {
+        unsigned long long before = 0;
+        int pick = -1;
+        const long long per = (V + kThreads - 1) / kThreads;
+        const long long lo = (long long)tid * per, hi = min(V, lo + per);
+        unsigned long long mine = 0;
+        for (long long i = lo; i < hi; ++i) {
+            const float pr = prob(row[i]);
+            if (pr >= min_thr) mine += fixed(pr);
+        }
+        // exclusive prefix of `mine` over threads
+        unsigned long long incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
+        }
+        __syncthreads();
+        if (lane == 31) sh.red_u[warp] = incl;
+        __syncthreads();
+        for (int w = 0; w < warp; ++w) before += sh.red_u[w];
+        before += incl - mine;
+        if (before <= rfix && rfix < before + mine) {
+            unsigned long long run = before;
+            for (long long i = lo; i < hi; ++i) {
+                const float pr = prob(row[i]);
+                if (pr < min_thr) continue;
+                run += fixed(pr);
+                if (run > rfix) { pick = (int)i; break; }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) sh.sel_bin = -1;
+        __syncthreads();
+        if (pick >= 0) atomicMax(&sh.sel_bin, pick);
+        __syncthreads();
+        if (tid == 0) {
+            int chosen = sh.sel_bin;
+            if (chosen < 0) {  // rounding left r at or beyond the total: the reference falls back to the last element
+                chosen = (int)V - 1;
+            }
+            const float pr = prob(row[chosen]);
+            a.out_token[r] = chosen;
+            a.out_log_prob[r] = logf(pr) - logf(total);
+        }
+    }
+}
+
+}  // namespace
+
+size_t sampler_smem_bytes() { return sizeof(Shared); }
+
+cudaError_t launch_sampler(const StepArgs& a, cudaStream_t stream) {
+    if (a.num_rows <= 0) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(sampler_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Shared));
+    if (e != cudaSuccess) return e;
+    sampler_kernel<<<a.num_rows, kThreads, sizeof(Shared), stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace sampler

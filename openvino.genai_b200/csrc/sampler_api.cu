@@ -1,0 +1,187 @@
+// C ABI of the Sampler step (include/sampler_b200.h): argument checks, staging for the
+// host-tensor entry point, launch.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <string>
+
+#include "sampler_kernels.h"
+
+namespace {
+
+thread_local std::string g_sampler_error;
+
+int sfail(int code, const std::string& msg) {
+    g_sampler_error = msg;
+    return code;
+}
+
+#define S_CUDA(expr)                                                                           \
+    do {                                                                                       \
+        cudaError_t _e = (expr);                                                               \
+        if (_e != cudaSuccess)                                                                 \
+            return sfail(SAMPLER_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+    } while (0)
+
+size_t up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+struct sampler_handle {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    uint32_t* status = nullptr;
+    uint8_t* stage_dev = nullptr;
+    uint8_t* stage_host = nullptr;  // pinned
+    size_t stage_bytes = 0;
+    int64_t launches = 0;
+};
+
+namespace {
+
+int ensure_stage(sampler_handle* h, size_t bytes) {
+    if (bytes <= h->stage_bytes) return SAMPLER_OK;
+    S_CUDA(cudaStreamSynchronize(h->stream));
+    if (h->stage_dev) S_CUDA(cudaFree(h->stage_dev));
+    if (h->stage_host) S_CUDA(cudaFreeHost(h->stage_host));
+    h->stage_dev = nullptr; h->stage_host = nullptr; h->stage_bytes = 0;
+    const size_t want = up(bytes + bytes / 8, 1 << 20);
+    S_CUDA(cudaMalloc((void**)&h->stage_dev, want));
+    S_CUDA(cudaMallocHost((void**)&h->stage_host, want));
+    h->stage_bytes = want;
+    return SAMPLER_OK;
+}
+
+int validate(const sampler_handle* h, const sampler_step_args* a) {
+    if (!h) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL handle");
+    if (!a || a->struct_size != sizeof(sampler_step_args)) return sfail(SAMPLER_ERR_INVALID_ARG, "sampler_step_args: NULL or struct_size mismatch");
+    if (a->num_rows < 0 || a->vocab <= 0 || a->num_logit_rows < 0) return sfail(SAMPLER_ERR_INVALID_ARG, "bad size");
+    if (a->vocab > 0x7fffffffLL) return sfail(SAMPLER_ERR_TOO_LARGE, "vocab above 2^31 - 1");
+    if (a->num_rows > 0 && (!a->logits || !a->rows || !a->out_token || !a->out_log_prob)) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL pointer");
+    if (a->hist_offsets && (!a->hist_ids || !a->hist_meta)) return sfail(SAMPLER_ERR_INVALID_ARG, "history arrays incomplete");
+    return SAMPLER_OK;
+}
+
+sampler::StepArgs kernel_args(sampler_handle* h, const sampler_step_args* a) {
+    sampler::StepArgs k;
+    k.logits = a->logits; k.num_logit_rows = a->num_logit_rows; k.vocab = a->vocab; k.num_rows = a->num_rows;
+    k.rows = a->rows; k.hist_offsets = a->hist_offsets; k.hist_ids = a->hist_ids; k.hist_meta = a->hist_meta;
+    k.out_token = a->out_token; k.out_log_prob = a->out_log_prob; k.status = h->status;
+    return k;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* sampler_b200_last_error(void) { return g_sampler_error.c_str(); }
+
+int sampler_b200_create(int device, int32_t max_rows, int64_t max_vocab, sampler_handle** out) {
+    if (!out) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL out pointer");
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return sfail(SAMPLER_ERR_INVALID_ARG, "no such CUDA device");
+    cudaDeviceProp prop;
+    S_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return sfail(SAMPLER_ERR_UNSUPPORTED, "this library is built for sm_100a only");
+    S_CUDA(cudaSetDevice(device));
+    sampler_handle* h = new sampler_handle();
+    h->device = device;
+    cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&h->status, 256);
+    if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);
+    if (e != cudaSuccess) {
+        delete h;
+        return sfail(SAMPLER_ERR_CUDA, std::string("sampler_b200_create: ") + cudaGetErrorString(e));
+    }
+    (void)max_rows; (void)max_vocab;  // scratch is sized on first use of the host entry point
+    *out = h;
+    return SAMPLER_OK;
+}
+
+int sampler_b200_destroy(sampler_handle* h) {
+    if (!h) return SAMPLER_OK;
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    if (h->status) cudaFree(h->status);
+    if (h->stage_dev) cudaFree(h->stage_dev);
+    if (h->stage_host) cudaFreeHost(h->stage_host);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+    return SAMPLER_OK;
+}
+
+int sampler_b200_step(sampler_handle* h, const sampler_step_args* a) {
+    int rc = validate(h, a);
+    if (rc != SAMPLER_OK) return rc;
+    if (a->num_rows == 0) return SAMPLER_OK;
+    S_CUDA(cudaSetDevice(h->device));
+    cudaStream_t stream = a->stream ? (cudaStream_t)a->stream : h->stream;
+    S_CUDA(sampler::launch_sampler(kernel_args(h, a), stream));
+    h->launches += 1;
+    return SAMPLER_OK;
+}
+
+int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int copy_logits_back) {
+    int rc = validate(h, a);
+    if (rc != SAMPLER_OK) return rc;
+    if (a->num_rows == 0) return SAMPLER_OK;
+    S_CUDA(cudaSetDevice(h->device));
+    cudaStream_t stream = a->stream ? (cudaStream_t)a->stream : h->stream;
+    const size_t n = (size_t)a->num_rows;
+    const size_t logits_bytes = (size_t)a->num_logit_rows * a->vocab * sizeof(float);
+    const size_t hist_n = a->hist_offsets ? (size_t)a->hist_offsets[n] : 0;
+    size_t off = 0;
+    const size_t o_rows = off;  off += up(n * sizeof(sampler_row_params));
+    const size_t o_hoff = off;  off += up((n + 1) * sizeof(int64_t));
+    const size_t o_hid = off;   off += up(hist_n * sizeof(int32_t));
+    const size_t o_hmeta = off; off += up(hist_n * sizeof(uint32_t));
+    const size_t small_in = off;
+    const size_t o_tok = off;   off += up(n * sizeof(int64_t));
+    const size_t o_lp = off;    off += up(n * sizeof(float));
+    const size_t o_logits = off; off += up(logits_bytes);
+    rc = ensure_stage(h, off);
+    if (rc != SAMPLER_OK) return rc;
+    std::memcpy(h->stage_host + o_rows, a->rows, n * sizeof(sampler_row_params));
+    if (a->hist_offsets) {
+        std::memcpy(h->stage_host + o_hoff, a->hist_offsets, (n + 1) * sizeof(int64_t));
+        std::memcpy(h->stage_host + o_hid, a->hist_ids, hist_n * sizeof(int32_t));
+        std::memcpy(h->stage_host + o_hmeta, a->hist_meta, hist_n * sizeof(uint32_t));
+    }
+    S_CUDA(cudaMemcpyAsync(h->stage_dev, h->stage_host, small_in, cudaMemcpyHostToDevice, stream));
+    S_CUDA(cudaMemcpyAsync(h->stage_dev + o_logits, a->logits, logits_bytes, cudaMemcpyHostToDevice, stream));
+    sampler_step_args d = *a;
+    d.logits = (float*)(h->stage_dev + o_logits);
+    d.rows = (const sampler_row_params*)(h->stage_dev + o_rows);
+    d.hist_offsets = a->hist_offsets ? (const int64_t*)(h->stage_dev + o_hoff) : nullptr;
+    d.hist_ids = (const int32_t*)(h->stage_dev + o_hid);
+    d.hist_meta = (const uint32_t*)(h->stage_dev + o_hmeta);
+    d.out_token = (int64_t*)(h->stage_dev + o_tok);
+    d.out_log_prob = (float*)(h->stage_dev + o_lp);
+    S_CUDA(sampler::launch_sampler(kernel_args(h, &d), stream));
+    h->launches += 1;
+    S_CUDA(cudaMemcpyAsync(a->out_token, d.out_token, n * sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    S_CUDA(cudaMemcpyAsync(a->out_log_prob, d.out_log_prob, n * sizeof(float), cudaMemcpyDeviceToHost, stream));
+    if (copy_logits_back) S_CUDA(cudaMemcpyAsync(a->logits, d.logits, logits_bytes, cudaMemcpyDeviceToHost, stream));
+    uint32_t bits = 0;
+    S_CUDA(cudaMemcpyAsync(&bits, h->status, 4, cudaMemcpyDeviceToHost, stream));
+    S_CUDA(cudaStreamSynchronize(stream));
+    if (bits) {
+        S_CUDA(cudaMemsetAsync(h->status, 0, 4, stream));
+        return sfail((bits & 1u) ? SAMPLER_ERR_BAD_TOKEN_ID : SAMPLER_ERR_INVALID_ARG, "device status word " + std::to_string(bits));
+    }
+    return SAMPLER_OK;
+}
+
+int sampler_b200_last_device_status(sampler_handle* h, uint32_t* status_bits) {
+    if (!h || !status_bits) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL argument");
+    S_CUDA(cudaSetDevice(h->device));
+    S_CUDA(cudaStreamSynchronize(h->stream));
+    S_CUDA(cudaMemcpy(status_bits, h->status, 4, cudaMemcpyDeviceToHost));
+    if (*status_bits) S_CUDA(cudaMemset(h->status, 0, 4));
+    return SAMPLER_OK;
+}
+
+int64_t sampler_b200_launch_count(const sampler_handle* h) { return h ? h->launches : -1; }
+
+}  // extern "C"
