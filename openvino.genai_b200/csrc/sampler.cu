@@ -6,11 +6,12 @@
 //   2. greedy rows: strict-> argmax with lowest-index ties over the row (one HBM pass);
 //   3. multinomial rows with an active top-k: the reference keeps a K-element min-heap whose final
 //      ARRAY ORDER feeds every later float sum and the draw itself, so the order is reproduced
-//      exactly: 31 producer warps stream the row, keep only elements above a (stale, hence
-//      conservative) copy of the heap minimum, and compact them in index order into a double
-//      buffer; one thread replays libstdc++'s pop_heap / push_heap on those few hundred survivors
-//      while the producers filter the next chunk.  Softmax, min-p, top-p and the draw then run
-//      over <= K elements in one thread, in the reference's order of operations;
+//      exactly: 15 producer warps stream the row with 16-byte loads, keep only elements above a
+//      (stale, hence conservative) copy of the heap minimum, and compact them in index order into
+//      a double buffer; warp 0 re-checks them 32 at a time and one lane replays libstdc++'s
+//      pop_heap / push_heap on the few hundred that really enter, while the producers filter the
+//      next chunk.  Softmax, min-p, top-p and the draw then run over <= K elements in one thread,
+//      in the reference's order of operations;
 //   4. multinomial rows over the full vocabulary: max, exp and sums are block reductions
 //      (deterministic, but not the reference's index-order float accumulation), top-p uses a
 //      three-level radix descent over the order-preserving bit pattern of the logits.
@@ -26,10 +27,11 @@ namespace sampler {
 
 namespace {
 
-constexpr int kThreads = 1024;
+constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kProducerThreads = kThreads - 32;       // warps 1..31 filter, warp 0 replays the heap
-constexpr int kChunk = kProducerThreads * 4;          // elements per filter round
+constexpr int kProducerThreads = kThreads - 32;       // warps 1..15 filter, warp 0 replays the heap
+constexpr int kPerThread = 8;                         // elements a producer thread filters per round
+constexpr int kChunk = kProducerThreads * kPerThread; // elements per filter round
 constexpr int kMaxTopK = 1024;                        // heap capacity in shared memory
 
 struct Cand {
@@ -236,7 +238,13 @@ __device__ __forceinline__ uint32_t float_key(float x) {
 
 struct Shared {
     Cand heap[kMaxTopK];
-    Cand cand[2][kChunk];
+    union {
+        Cand cand[2][kChunk];          // top-k path: survivors of two filter rounds
+        struct {                       // full-vocabulary path: radix histograms
+            unsigned int hist_cnt[2048];
+            unsigned long long hist_mass[2048];
+        };
+    };
     int cand_count[2];
     float tau;                 // producers' copy of the heap minimum (may lag, never leads)
     int warp_off[kWarps];
@@ -245,8 +253,6 @@ struct Shared {
     int red_i[kWarps];
     unsigned long long red_u[kWarps];
     ArgMax red_a[kWarps];
-    unsigned int hist_cnt[2048];
-    unsigned long long hist_mass[2048];
     int sel_bin;
     unsigned long long sel_mass_above;
     unsigned int sel_cnt_above;
@@ -380,7 +386,7 @@ __device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float*
     *out_idx = v[pick].idx;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) sampler_kernel(StepArgs a) {
+__global__ void __launch_bounds__(kThreads, 3) sampler_kernel(StepArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     Shared& sh = *reinterpret_cast<Shared*>(smem_raw);
     const int r = blockIdx.x;
@@ -403,9 +409,38 @@ __global__ void __launch_bounds__(kThreads, 1) sampler_kernel(StepArgs a) {
     // ---- 2. greedy ----------------------------------------------------------------------------------
     if (!p.do_sample) {
         ArgMax best{-CUDART_INF_F, 0x7fffffff};
-        for (long long i = tid; i < V; i += kThreads) {
+        long long done = 0;
+        if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+            // 16-byte loads, four in flight per thread; indices ascend per thread so the first maximum is kept
+            const float4* row4 = reinterpret_cast<const float4*>(row);
+            const long long n4 = V >> 2;
+            long long i = tid;
+            for (; i + 3 * kThreads < n4; i += 4 * kThreads) {
+                float4 q[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) q[u] = __ldcs(row4 + i + u * kThreads);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int b = (int)((i + u * kThreads) << 2);
+                    if (q[u].x > best.v) { best.v = q[u].x; best.i = b; }
+                    if (q[u].y > best.v) { best.v = q[u].y; best.i = b + 1; }
+                    if (q[u].z > best.v) { best.v = q[u].z; best.i = b + 2; }
+                    if (q[u].w > best.v) { best.v = q[u].w; best.i = b + 3; }
+                }
+            }
+            for (; i < n4; i += kThreads) {
+                const float4 q = __ldcs(row4 + i);
+                const int b = (int)(i << 2);
+                if (q.x > best.v) { best.v = q.x; best.i = b; }
+                if (q.y > best.v) { best.v = q.y; best.i = b + 1; }
+                if (q.z > best.v) { best.v = q.z; best.i = b + 2; }
+                if (q.w > best.v) { best.v = q.w; best.i = b + 3; }
+            }
+            done = V;
+        }
+        for (long long i = done + tid; i < V; i += kThreads) {
             const float x = row[i];
-            if (x > best.v) { best.v = x; best.i = (int)i; }  // i ascends per thread: first maximum kept
+            if (x > best.v) { best.v = x; best.i = (int)i; }
         }
         best = block_reduce(best, ArgMax{-CUDART_INF_F, 0x7fffffff}, better, sh.red_a);
         if (tid == 0) {
@@ -419,47 +454,79 @@ __global__ void __launch_bounds__(kThreads, 1) sampler_kernel(StepArgs a) {
     if (top_k_active && p.top_k < V && p.top_k <= kMaxTopK) {
         // ---- 3. exact top-k heap replay --------------------------------------------------------------
         const int K = (int)p.top_k;
+        // the producers start at the first 16-byte boundary at or after K; warp 0 feeds the (at
+        // most 3) elements in between to the heap itself
+        const bool vec_ok = (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+        const long long start = vec_ok ? min(V, ((long long)K + 3) & ~3LL) : K;
         if (warp == 0) {
             for (int i = lane; i < K; i += 32) sh.heap[i] = Cand{row[i], i};
             __syncwarp();
             if (lane == 0) {
                 make_heap(sh.heap, K);
+                for (long long i = K; i < start; ++i) {
+                    const float x = row[i];
+                    if (x > sh.heap[0].v) replace_min(sh.heap, K, Cand{x, (int)i});
+                }
                 sh.tau = sh.heap[0].v;
             }
         }
         __syncthreads();
-        const long long n_rest = V - K;
+        const long long n_rest = V - start;
         const int rounds = (int)((n_rest + kChunk - 1) / kChunk);
         if (warp == 0) {
-            // consumer: replays the survivors of round c while the producers filter round c + 1
+            // consumer: re-checks the survivors of round c, 32 at a time, while the producers filter
+            // round c + 1; lane 0 owns the heap
+            float heap_min = sh.heap[0].v;
             for (int c = 0; c < rounds; ++c) {
                 const int b = c & 1;
                 named_sync(1 + b, kThreads);           // full[b]
-                if (lane == 0) {
-                    const int n = sh.cand_count[b];
-                    for (int i = 0; i < n; ++i) {
-                        const Cand x = sh.cand[b][i];
-                        if (x.v > sh.heap[0].v) replace_min(sh.heap, K, x);
+                const int n = sh.cand_count[b];
+                for (int base = 0; base < n; base += 32) {
+                    const int i = base + lane;
+                    Cand x = i < n ? sh.cand[b][i] : Cand{-CUDART_INF_F, 0};
+                    unsigned mask = __ballot_sync(0xffffffffu, i < n && x.v > heap_min);
+                    while (mask) {
+                        const int src = __ffs(mask) - 1;
+                        mask &= mask - 1;
+                        const float xv = __shfl_sync(0xffffffffu, x.v, src);
+                        const int xi = __shfl_sync(0xffffffffu, x.idx, src);
+                        if (xv > heap_min) {           // the minimum may have risen since the ballot
+                            if (lane == 0) replace_min(sh.heap, K, Cand{xv, xi});
+                            __syncwarp();
+                            heap_min = sh.heap[0].v;
+                        }
                     }
-                    *reinterpret_cast<volatile float*>(&sh.tau) = sh.heap[0].v;
                 }
+                if (lane == 0) *reinterpret_cast<volatile float*>(&sh.tau) = heap_min;
                 __syncwarp();
                 named_arrive(3 + b, kThreads);         // empty[b]
             }
         } else {
             const int ptid = tid - 32, pwarp = warp - 1;
+            float x[kPerThread], xn[kPerThread];
+            auto load_round = [&](int c, float (&dst)[kPerThread]) {
+                const long long base = start + (long long)c * kChunk + (long long)ptid * kPerThread;
+                if (vec_ok && base + kPerThread <= V) {
+                    const float4 q0 = __ldcs(reinterpret_cast<const float4*>(row + base));
+                    const float4 q1 = __ldcs(reinterpret_cast<const float4*>(row + base + 4));
+                    dst[0] = q0.x; dst[1] = q0.y; dst[2] = q0.z; dst[3] = q0.w;
+                    dst[4] = q1.x; dst[5] = q1.y; dst[6] = q1.z; dst[7] = q1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < kPerThread; ++e) dst[e] = base + e < V ? row[base + e] : CUDART_NAN_F;  // NaN never passes '>'
+                }
+            };
+            load_round(0, x);
             for (int c = 0; c < rounds; ++c) {
                 const int b = c & 1;
-                if (c >= 2) named_sync(3 + b, kThreads);  // wait until the consumer drained buffer b
+                if (c + 1 < rounds) load_round(c + 1, xn);  // in flight while this round is compacted
+                if (c >= 2) named_sync(3 + b, kThreads);    // wait until the consumer drained buffer b
                 const float tau = *reinterpret_cast<volatile float*>(&sh.tau);
-                const long long base = K + (long long)c * kChunk + (long long)ptid * 4;
-                float x[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) x[e] = base + e < V ? row[base + e] : -CUDART_INF_F;
+                const long long base = start + (long long)c * kChunk + (long long)ptid * kPerThread;
                 int mine = 0;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) mine += (base + e < V && x[e] > tau) ? 1 : 0;
-                // ordered compaction: exclusive prefix of `mine` over the 992 producer threads
+                for (int e = 0; e < kPerThread; ++e) mine += x[e] > tau ? 1 : 0;
+                // ordered compaction: exclusive prefix of `mine` over the producer threads
                 int incl = mine;
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
@@ -473,11 +540,13 @@ __global__ void __launch_bounds__(kThreads, 1) sampler_kernel(StepArgs a) {
                 if (ptid == kProducerThreads - 1) sh.cand_count[b] = off + incl;
                 int pos = off + incl - mine;
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (base + e < V && x[e] > tau) sh.cand[b][pos++] = Cand{x[e], (int)(base + e)};
+                for (int e = 0; e < kPerThread; ++e)
+                    if (x[e] > tau) sh.cand[b][pos++] = Cand{x[e], (int)(base + e)};
                 named_sync(6, kProducerThreads);       // warp_off is reused next round
                 __threadfence_block();
                 named_arrive(1 + b, kThreads);         // full[b]
+#pragma unroll
+                for (int e = 0; e < kPerThread; ++e) x[e] = xn[e];
             }
         }
         __syncthreads();

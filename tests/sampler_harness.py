@@ -102,15 +102,20 @@ class GpuSampler:
         rc = self.lib.sampler_b200_step_host(self.h, C.byref(args), 1 if copy_back else 0)
         return rc, tok, lp, lg
 
-    def step_device(self, logits_t, rows, hist=None, stream=None):
+    def stage(self, rows, hist, dev):
+        """Copies the row parameters and the CSR history to the device once."""
+        import torch
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8) if a.dtype.fields else a).to(dev)
+        return {"rows": t(rows), "hist": tuple(t(x) for x in hist) if hist is not None else None,
+                "tok": torch.full((len(rows),), -7, dtype=torch.int64, device=dev),
+                "lp": torch.zeros(len(rows), dtype=torch.float32, device=dev)}
+
+    def step_device(self, logits_t, rows, hist=None, stream=None, staged=None):
         """logits_t: CUDA torch tensor [rows, vocab] f32 (mutated in place)."""
         import torch
         dev = logits_t.device
-        t = lambda a, dt=None: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8) if a.dtype.fields else a).to(dev)
-        rows_t = t(rows)
-        tok = torch.full((len(rows),), -7, dtype=torch.int64, device=dev)
-        lp = torch.zeros(len(rows), dtype=torch.float32, device=dev)
-        hist_t = tuple(t(x) for x in hist) if hist is not None else None
+        staged = staged or self.stage(rows, hist, dev)
+        rows_t, hist_t, tok, lp = staged["rows"], staged["hist"], staged["tok"], staged["lp"]
         a = step_args(logits_t, rows_t, hist_t, tok, lp, ptr=lambda x: x.data_ptr())
         a.num_rows = len(rows)
         a.num_logit_rows, a.vocab = logits_t.shape
