@@ -184,6 +184,30 @@ int pa_b200_rotate_blocks(pa_handle* h, const pa_forward_args* args);
 int pa_b200_copy_blocks(pa_handle* h, void* key_cache, void* value_cache, int32_t num_blocks,
                         const int32_t* src_dst_pairs, int32_t num_pairs, void* stream);
 
+/* Allocation-free decode step.  It has no counterpart in the reference.
+ *
+ * For callers that cannot allocate device memory where they run the operator - code inside an
+ * allocator or memory-pool callback, a server whose device memory is fully handed out at start-up,
+ * a latency-critical loop that must not take the allocator's lock - this entry point needs no
+ * handle and calls no cudaMalloc / cudaFree: its scratch is one file-scope device array of
+ * PA_B200_STATIC_SCRATCH_BYTES that every GPU loading the library holds until the process exits.
+ *
+ * Same results as pa_b200_forward for a step in which every sequence has exactly one new token,
+ * without score output and without rotation inputs (PA_ERR_UNSUPPORTED otherwise).  All pointers
+ * are device memory; the launches go to args->stream (NULL = the default stream).
+ *  - A step whose scratch need exceeds the fixed array is rejected with PA_ERR_TOO_LARGE (the
+ *    message gives both sizes).  With G = Hq / Hkv the need is a few KB of counters plus
+ *    (num_sequences * Hkv * ceil(G/16) + 16 * SM count) * min(G,16) * (head_size + 2) * 4 bytes:
+ *    about 6 MB for 64 sequences of the 32/8-head, 128-dim shape on a 148-SM GPU.
+ *  - The first call on a device looks up the array's device address; make that call before any
+ *    stream capture.
+ *  - All calls on a device share the array: two calls that overlap on the GPU (different streams)
+ *    race.  Every call rewrites the parts that must start from a known state.
+ *  - Block-index errors are still skipped on the device, but this entry point has no way to
+ *    report the device status word; use pa_b200_forward to diagnose inputs. */
+#define PA_B200_STATIC_SCRATCH_BYTES (16u << 20)
+int pa_b200_decode_step_static(const pa_model_desc* desc, const pa_forward_args* args, int device);
+
 #ifdef __cplusplus
 }
 #endif

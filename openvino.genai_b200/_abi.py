@@ -95,6 +95,7 @@ PA_SYMBOLS = {
     "pa_b200_get_kernel_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "pa_b200_write_kv": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
     "pa_b200_rotate_blocks": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
+    "pa_b200_decode_step_static": (C.c_int, [C.POINTER(pa_model_desc), C.POINTER(pa_forward_args), C.c_int]),
     "pa_b200_copy_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
 }
 

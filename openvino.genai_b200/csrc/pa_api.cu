@@ -34,6 +34,10 @@ size_t act_bytes(int dt) { return dt == PA_DTYPE_F32 ? 4 : 2; }
 
 }  // namespace
 
+namespace pa {
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+}  // namespace pa
+
 struct pa_handle {
     pa_model_desc desc;
     pa::CacheGeom g;
