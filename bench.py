@@ -261,9 +261,11 @@ def run_ours(args):
         e2e_value = total_bytes / (ms_e2e_total / args.steps * 1e-3) / 1e9
         achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
         traffic = None
-        tp = ROOT / "profiles" / "decode_u8_llama3_8b.traffic.json"
+        tp = ROOT / "profiles" / "decode_u8_llama3_8b.md"
         if tp.exists() and wl.name == "llama3_8b_u8_decode":
-            traffic = json.loads(tp.read_text()).get("dram_bytes_per_launch")
+            import re
+            m = re.search(r"dram_bytes_per_launch:\s*(\d+)", tp.read_text())   # from the committed ncu summary of this workload
+            traffic = int(m.group(1)) if m else None
         line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma / f32 accumulate",
                 "data": "synthetic", "config": config_of(wl, world),
