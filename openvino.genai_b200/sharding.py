@@ -1,0 +1,57 @@
+"""Request-level sharding across ranks: sequences (and their KV block pools) are partitioned by
+rank, so the attention step needs no collective; the only exchange of an engine step is the
+all-gather of the sampled token ids (and of a status word) so that every rank's scheduler sees
+all of them.  The reference is single-process (its only multi-device notion is "all execution
+devices are GPU", src/cpp/src/continuous_batching/pipeline_impl.cpp:183-190); this module is the
+host logic of the multi-GPU extension and runs equally on the gloo backend for CPU tests."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def shard_sequences(context_lens: Sequence[int], world_size: int) -> List[np.ndarray]:
+    """Assigns sequences to ranks so that the summed context length (the KV bytes a decode step
+    reads) is balanced: longest first, each to the currently lightest rank.  Returns, per rank,
+    the ascending indices of its sequences."""
+    lens = np.asarray(context_lens, np.int64)
+    order = np.argsort(-lens, kind="stable")
+    load = np.zeros(world_size, np.int64)
+    owner = np.empty(len(lens), np.int64)
+    for i in order:
+        r = int(np.argmin(load))
+        owner[i] = r
+        load[r] += lens[i]
+    return [np.sort(np.nonzero(owner == r)[0]) for r in range(world_size)]
+
+
+def all_gather_token_ids(local_ids: torch.Tensor, local_index: torch.Tensor, total: int,
+                         group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gathers this rank's sampled ids (int64 [n_local], for the global sequence indices
+    `local_index`) into an int64 [total] tensor in global sequence order on every rank.
+    Ranks may own different numbers of sequences: shares are padded to the largest one."""
+    world = dist.get_world_size(group)
+    n_local = torch.tensor([local_ids.numel()], dtype=torch.int64, device=local_ids.device)
+    counts = [torch.zeros_like(n_local) for _ in range(world)]
+    dist.all_gather(counts, n_local, group=group)
+    cap = int(max(int(c.item()) for c in counts))
+    packed = torch.full((2, cap), -1, dtype=torch.int64, device=local_ids.device)
+    packed[0, : local_ids.numel()] = local_ids
+    packed[1, : local_ids.numel()] = local_index
+    gathered = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(gathered, packed, group=group)   # list form: available on both nccl and gloo
+    out = torch.full((total,), -1, dtype=torch.int64, device=local_ids.device)
+    for r in range(world):
+        n = int(counts[r].item())
+        out[gathered[r][1, :n]] = gathered[r][0, :n]
+    return out
+
+
+def max_over_ranks(value: float, device, group: Optional[dist.ProcessGroup] = None) -> float:
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())
