@@ -52,6 +52,7 @@ struct pa_handle {
     uint8_t* stage_host = nullptr;  // pinned
     size_t stage_host_bytes = 0;
     int64_t launches = 0;
+    bool force_generic_prefill = false;        // env PA_B200_GENERIC_PREFILL=1: cross-check path
     bool timing = false;                       // record events around the split-K decode kernel
     std::vector<cudaEvent_t> ev;               // pairs, created on demand
     size_t ev_used = 0;
@@ -84,7 +85,7 @@ pa::CacheGeom make_geom(const pa_model_desc& d) {
 // Scratch layout of one forward call.
 struct Plan {
     long long max_tiles;
-    size_t off_hdr, off_prefix, off_done, off_part_o, off_part_ml, off_lse, off_score_off, total;
+    size_t off_hdr, off_prefix, off_pprefix, off_done, off_part_o, off_part_ml, off_lse, off_score_off, total;
 };
 
 Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_context_len, int64_t scores_len,
@@ -101,6 +102,7 @@ Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_co
     size_t off = 0;
     p.off_hdr = off;       off += 256;
     p.off_prefix = off;    off += align_up((size_t)(B + 1) * sizeof(int), 256);
+    p.off_pprefix = off;   off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_done = off;      off += align_up((size_t)std::max(B, 1LL) * HK * sizeof(int), 256);
     p.off_part_o = off;    off += align_up((size_t)slots * RT * g.D * sizeof(float), 256);
     p.off_part_ml = off;   off += align_up((size_t)slots * RT * 2 * sizeof(float), 256);
@@ -180,6 +182,7 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.plan = (pa::PlanHeader*)(h->ws + p.off_hdr);
     k.tile_prefix = (int*)(h->ws + p.off_prefix);
     k.stream_done = (int*)(h->ws + p.off_done);
+    k.ptile_prefix = (int*)(h->ws + p.off_pprefix);
     k.max_tiles = p.max_tiles;
     k.rows_per_tile = std::min(h->g.Hq / h->g.Hkv, 16);
     return k;
@@ -205,7 +208,15 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
         h->ev_used += 2;
     }
     PA_CUDA(pa::launch_decode(k, stream, h->sm_count, &launches, ev0, ev1));
-    if (a->num_tokens > a->num_sequences) PA_CUDA(pa::launch_prefill(k, stream, &launches));
+    if (a->num_tokens > a->num_sequences) {
+        if (pa::prefill_tc_supported(h->g) && !h->force_generic_prefill) {
+            const int G = h->g.Hq / h->g.Hkv;
+            const long long max_items = ((long long)a->num_tokens * G / 128 + a->num_sequences) * h->g.Hkv;
+            PA_CUDA(pa::launch_prefill_tc(k, stream, h->sm_count, max_items, &launches));
+        } else {
+            PA_CUDA(pa::launch_prefill(k, stream, &launches));
+        }
+    }
     if (a->scores) PA_CUDA(pa::launch_scores(k, stream, &launches));
     h->launches += launches;
     return PA_OK;
@@ -250,6 +261,7 @@ int pa_b200_create(const pa_model_desc* desc, int device, pa_handle** out) {
     h->g = make_geom(*desc);
     h->device = device;
     h->sm_count = prop.multiProcessorCount;
+    if (const char* e = std::getenv("PA_B200_GENERIC_PREFILL")) h->force_generic_prefill = std::atoi(e) != 0;
     cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc((void**)&h->status, 256);
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);

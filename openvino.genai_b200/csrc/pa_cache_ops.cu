@@ -37,33 +37,44 @@ __device__ __forceinline__ int seq_tiles(const KernelArgs& a, int s) {
 __device__ void build_decode_plan(const KernelArgs& a) {
     __shared__ int sh_warp[8];
     __shared__ int sh_run;
+    __shared__ int sh_warp_p[8];
+    __shared__ int sh_run_p;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int B = a.num_sequences;
     const int G = a.g.Hq / a.g.Hkv, HK = a.g.Hkv * ((G + 15) / 16);
-    if (tid == 0) sh_run = 0;
+    if (tid == 0) { sh_run = 0; sh_run_p = 0; }
     __syncthreads();
     for (int base = 0; base < B; base += 256) {
         const int s = base + tid;
         const int n = s < B ? seq_tiles(a, s) : 0;
-        int v = n;
+        // prefill chunks: 128-row q tiles of (new token, q head of one group) pairs
+        int np = 0;
+        if (s < B) {
+            const int n_new = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
+            const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
+            if (n_new > 1 && a.past_lens[s] >= 0 && (long long)nb * a.g.bs >= (long long)a.past_lens[s] + n_new) np = (n_new * G + 127) / 128;
+        }
+        int v = n, vp = np;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int u = __shfl_up_sync(0xffffffffu, v, o);
-            if (lane >= o) v += u;
+            const int u = __shfl_up_sync(0xffffffffu, v, o), up = __shfl_up_sync(0xffffffffu, vp, o);
+            if (lane >= o) { v += u; vp += up; }
         }
-        if (lane == 31) sh_warp[wid] = v;
+        if (lane == 31) { sh_warp[wid] = v; sh_warp_p[wid] = vp; }
         __syncthreads();
-        int off = sh_run;
-        for (int w = 0; w < wid; ++w) off += sh_warp[w];
-        if (s < B) a.tile_prefix[s] = off + v - n;
+        int off = sh_run, offp = sh_run_p;
+        for (int w = 0; w < wid; ++w) { off += sh_warp[w]; offp += sh_warp_p[w]; }
+        if (s < B) { a.tile_prefix[s] = off + v - n; a.ptile_prefix[s] = offp + vp - np; }
         __syncthreads();
-        if (tid == 255) sh_run = off + v;
+        if (tid == 255) { sh_run = off + v; sh_run_p = offp + vp; }
         __syncthreads();
     }
     for (int i = tid; i < B * HK; i += 256) a.stream_done[i] = 0;
     if (tid == 0) {
         a.tile_prefix[B] = sh_run;
         a.plan->total_tiles = sh_run * HK;
+        a.ptile_prefix[B] = sh_run_p;
+        a.plan->total_ptiles = sh_run_p;
     }
 }
 

@@ -11,7 +11,8 @@ namespace pa {
 // Header of the plan area in the handle's scratch.
 struct PlanHeader {
     int total_tiles;   // 32-token tiles of all decode streams (rows x head tiles)
-    int pad[3];
+    int total_ptiles;  // 128-row q tiles of all prefill chunks (per kv head)
+    int pad[2];
 };
 
 // Everything a kernel needs, passed by value.  All pointers are device memory.
@@ -47,6 +48,7 @@ struct KernelArgs {
     PlanHeader* plan;      // decode plan header
     int* tile_prefix;      // [num_sequences + 1] exclusive prefix sum of tiles per row (one head tile)
     int* stream_done;      // [num_sequences * HK] partials of the stream published so far
+    int* ptile_prefix;     // [num_sequences + 1] exclusive prefix sum of prefill q tiles per row (one kv head)
     long long max_tiles;   // upper bound of total_tiles known on the host
     int rows_per_tile;     // q heads per head tile: min(G, 16)
     float* part_o;         // partial outputs    [slot = stream + worker][rows_per_tile][D]
@@ -72,8 +74,13 @@ cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count
 // Upper bound of the decode kernel's worker (warp) count, for sizing the partial-result scratch.
 int decode_max_workers(int sm_count);
 
-// Attention over rows with more than one new token (prefill chunks).
+// Attention over rows with more than one new token (prefill chunks): generic CUDA-core kernel.
 cudaError_t launch_prefill(const KernelArgs& a, cudaStream_t stream, int* launches);
+
+// The same on tcgen05 / TMEM for the shapes it supports (u8 cache, head size 128); walks the
+// plan's q-tile list.  `max_items` is the host's upper bound of q tiles x kv heads.
+bool prefill_tc_supported(const CacheGeom& g);
+cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_count, long long max_items, int* launches);
 
 // SnapKV-style score output: scores[pos] = sum over q heads and the last W rows of each chunk of
 // the softmax probabilities, using the log-sum-exp the attention kernels exported.

@@ -107,6 +107,7 @@ extern "C" int pa_b200_decode_step_static(const pa_model_desc* desc, const pa_fo
     const size_t o_status = off; off += 256;
     const size_t o_hdr = off;    off += 256;
     const size_t o_prefix = off; off += up256((size_t)(B + 1) * sizeof(int));
+    const size_t o_pprefix = off; off += up256((size_t)(B + 1) * sizeof(int));
     const size_t o_done = off;   off += up256((size_t)B * HK * sizeof(int));
     const size_t o_part_o = off; off += up256((size_t)slots * RT * g.D * sizeof(float));
     const size_t o_part_ml = off; off += up256((size_t)slots * RT * 2 * sizeof(float));
@@ -129,6 +130,7 @@ extern "C" int pa_b200_decode_step_static(const pa_model_desc* desc, const pa_fo
     k.status = reinterpret_cast<uint32_t*>(base + o_status);
     k.plan = reinterpret_cast<pa::PlanHeader*>(base + o_hdr);
     k.tile_prefix = reinterpret_cast<int*>(base + o_prefix);
+    k.ptile_prefix = reinterpret_cast<int*>(base + o_pprefix);
     k.stream_done = reinterpret_cast<int*>(base + o_done);
     k.part_o = reinterpret_cast<float*>(base + o_part_o);
     k.part_ml = reinterpret_cast<float*>(base + o_part_ml);

@@ -64,6 +64,28 @@ def test_prefill_and_mixed_parity(cache):
     _check(H.run_both(wl), cache, act)
 
 
+@pytest.mark.parametrize("hq,hkv,bs,past,new", [
+    (28, 4, 32, [0, 700, 63, 4000], [256, 256, 130, 64]),     # Qwen2.5-7B group of 7: q tiles straddle tokens
+    (32, 8, 16, [1000, 5], [200, 33]),                        # block size 16
+    (8, 8, 32, [300], [129]),                                 # no grouping: one head per q-tile row
+    (64, 8, 32, [0, 90], [40, 17]),                           # group of 8
+])
+def test_prefill_tensor_core_shapes(hq, hkv, bs, past, new):
+    """u8 cache, head size 128: the tcgen05 / TMEM chunk kernel."""
+    wl = H.small_workload(hq=hq, hkv=hkv, d=128, bs=bs, act=torch.bfloat16, cache="u8", past=past, new=new, seed=hq + bs)
+    _check(H.run_both(wl), "u8", torch.bfloat16)
+
+
+def test_prefill_tensor_core_matches_generic_kernel(monkeypatch):
+    wl = H.small_workload(hq=28, hkv=4, d=128, bs=32, act=torch.float16, cache="u8", past=[500, 0], new=[256, 100], seed=71)
+    data = H.make_host_data(wl)
+    tc = H.run_gpu(wl, data)
+    monkeypatch.setenv("PA_B200_GENERIC_PREFILL", "1")
+    gen = H.run_gpu(wl, data)
+    assert tc["status"] == 0 and gen["status"] == 0
+    assert H.rel_err(tc["out_gpu"], gen["out_gpu"]) < 2e-3
+
+
 def test_host_entry_point_matches():
     wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[0, 40, 300], new=[20, 1, 1], seed=43)
     _check(H.run_both(wl, host_entry=True), "u8", torch.bfloat16)
