@@ -85,7 +85,7 @@ pa::CacheGeom make_geom(const pa_model_desc& d) {
 // Scratch layout of one forward call.
 struct Plan {
     long long max_tiles;
-    size_t off_hdr, off_prefix, off_pprefix, off_done, off_part_o, off_part_ml, off_lse, off_score_off, total;
+    size_t off_hdr, off_prefix, off_pprefix, off_done, off_part_o, off_part_ml, off_lse, off_score_off, off_stile, off_score_part, total;
 };
 
 Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_context_len, int64_t scores_len,
@@ -108,7 +108,8 @@ Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_co
     p.off_part_ml = off;   off += align_up((size_t)slots * RT * 2 * sizeof(float), 256);
     p.off_lse = off;       off += align_up((size_t)std::max(num_tokens, 1) * g.Hq * sizeof(float), 256);
     p.off_score_off = off; off += align_up((size_t)(B + 1) * sizeof(int64_t), 256);
-    (void)scores_len;
+    p.off_stile = off;     off += align_up((size_t)(B + 1) * sizeof(int), 256);
+    p.off_score_part = off; off += align_up((size_t)std::max<int64_t>(scores_len, 0) * g.Hkv * sizeof(float), 256);
     p.total = off;
     return p;
 }
@@ -179,6 +180,8 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.part_ml = (float*)(h->ws + p.off_part_ml);
     k.lse = (float*)(h->ws + p.off_lse);
     k.score_offsets = (int64_t*)(h->ws + p.off_score_off);
+    k.stile_prefix = (int*)(h->ws + p.off_stile);
+    k.score_part = (float*)(h->ws + p.off_score_part);
     k.plan = (pa::PlanHeader*)(h->ws + p.off_hdr);
     k.tile_prefix = (int*)(h->ws + p.off_prefix);
     k.stream_done = (int*)(h->ws + p.off_done);
@@ -217,7 +220,7 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
             PA_CUDA(pa::launch_prefill(k, stream, &launches));
         }
     }
-    if (a->scores) PA_CUDA(pa::launch_scores(k, stream, &launches));
+    if (a->scores) PA_CUDA(pa::launch_scores(k, stream, h->sm_count, &launches));
     h->launches += launches;
     return PA_OK;
 }

@@ -72,6 +72,7 @@ struct DecodeCfg {
     static constexpr int RING = NSTAGE * STAGE;                 // per warp
     static constexpr int WARP_SMEM = RING + NSTAGE * (int)sizeof(StageDesc) + kRunRing * (int)sizeof(RunRec) + NSTAGE * 8;
     static constexpr int SMEM = kDecodeWarps * WARP_SMEM;
+    static_assert(WARP_SMEM % 16 == 0 && STAGE % 16 == 0 && REC % 16 == 0, "bulk copies and 16-byte loads need 16-byte aligned stages");
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {

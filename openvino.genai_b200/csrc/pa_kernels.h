@@ -55,6 +55,8 @@ struct KernelArgs {
     float* part_ml;        // partial (max, sum) [slot][rows_per_tile][2]
     float* lse;            // log-sum-exp per (token, q head), natural log, of the scaled logits
     int64_t* score_offsets;// [num_sequences + 1] prefix sum of past_len + new tokens
+    int* stile_prefix;     // [num_sequences + 1] prefix sum of key tiles of the sequences that want scores
+    float* score_part;     // [Hkv][scores_len] per-kv-head column sums of the window probabilities
     long long scores_len;
 };
 
@@ -84,6 +86,6 @@ cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_c
 
 // SnapKV-style score output: scores[pos] = sum over q heads and the last W rows of each chunk of
 // the softmax probabilities, using the log-sum-exp the attention kernels exported.
-cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int* launches);
+cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches);
 
 }  // namespace pa

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
     using Smem = PrefillSmem<BS>;
     extern __shared__ uint8_t smem_raw_[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw_) + 1023) & ~uintptr_t(1023));
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, warp = tid >> 5;
     const int G = a.g.Hq / a.g.Hkv;
     const int Hkv = a.g.Hkv;
     const int total_items = a.plan->total_ptiles * Hkv;

@@ -105,6 +105,19 @@ def test_scores_parity(cache):
     assert np.all(got[off:off + 301] == 0), "window 0 must write zeros"
 
 
+def test_scores_qwen_shape_windows_and_block16():
+    """Group of 7 heads, window larger than 16 rows / G (several row tiles), block size 16."""
+    wl = H.small_workload(hq=28, hkv=4, d=128, bs=16, act=torch.bfloat16, cache="u8", past=[0, 700, 64, 2000, 31],
+                          new=[256, 1, 40, 1, 3], seed=91)
+    wl.score_aggregation_window = np.array([8, 1, 16, 1, 5], np.int32)
+    res = H.run_both(wl)
+    _check(res, "u8", torch.bfloat16)
+    ref, got = res["scores_ref"], res["scores_gpu"]
+    assert not np.isnan(got).any()
+    assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+    assert abs(got.sum() - ref.sum()) <= 1e-2 * ref.sum()
+
+
 @pytest.mark.parametrize("cache", ["f16", "bf16", "u8"])
 def test_rotation_is_bit_exact(cache):
     from openvino_genai_b200 import workloads
