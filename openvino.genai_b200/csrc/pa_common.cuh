@@ -45,6 +45,50 @@ __device__ __forceinline__ float load_act(const void* p, long long i, int act) {
     return __bfloat162float(((const __nv_bfloat16*)p)[i]);
 }
 
+// N consecutive activations starting at element i (i a multiple of N, N*2 bytes <= 32 and the
+// tensor's base 16-byte aligned) with 16-byte / 8-byte / 4-byte loads.
+template <int N>
+__device__ __forceinline__ void load_act_vec(const void* p, long long i, int act, float (&out)[N]) {
+    static_assert(N == 2 || N == 4 || N == 8 || N == 16, "vector widths");
+    if (act == PA_DTYPE_F32) {
+        if constexpr (N >= 4) {
+#pragma unroll
+            for (int k = 0; k < N / 4; ++k) {
+                const float4 v = *reinterpret_cast<const float4*>((const float*)p + i + 4 * k);
+                out[4 * k] = v.x; out[4 * k + 1] = v.y; out[4 * k + 2] = v.z; out[4 * k + 3] = v.w;
+            }
+        } else {
+            const float2 v = *reinterpret_cast<const float2*>((const float*)p + i);
+            out[0] = v.x; out[1] = v.y;
+        }
+        return;
+    }
+    uint32_t w[N / 2];
+    const uint16_t* src = (const uint16_t*)p + i;
+    if constexpr (N >= 8) {
+#pragma unroll
+        for (int k = 0; k < N / 8; ++k) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + 8 * k);
+            w[4 * k] = v.x; w[4 * k + 1] = v.y; w[4 * k + 2] = v.z; w[4 * k + 3] = v.w;
+        }
+    } else if constexpr (N == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(src);
+        w[0] = v.x; w[1] = v.y;
+    } else {
+        w[0] = *reinterpret_cast<const uint32_t*>(src);
+    }
+#pragma unroll
+    for (int k = 0; k < N / 2; ++k) {
+        if (act == PA_DTYPE_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            out[2 * k] = f.x; out[2 * k + 1] = f.y;
+        } else {
+            out[2 * k] = __uint_as_float(w[k] << 16);
+            out[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+    }
+}
+
 __device__ __forceinline__ void store_act(void* p, long long i, int act, float v) {
     if (act == PA_DTYPE_F32) ((float*)p)[i] = v;
     else if (act == PA_DTYPE_F16) ((__half*)p)[i] = __float2half_rn(v);

@@ -42,7 +42,10 @@ __global__ void score_plan_kernel(KernelArgs a) {
             const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
             len = (long long)max(past, 0) + max(n, 0);
             const bool ok = n > 0 && past >= 0 && (long long)nb * a.g.bs >= len;
-            if (ok && min(max(a.score_aggregation_window[s], 0), n) > 0) tiles = (int)((len + kTileS - 1) / kTileS);
+            // cost of a sequence: key tiles x 16-row tiles of (window row, q head of the group) pairs
+            const int W = ok ? min(max(a.score_aggregation_window[s], 0), n) : 0;
+            const int G = a.g.Hq / a.g.Hkv;
+            if (W > 0) tiles = (int)((len + kTileS - 1) / kTileS) * ((W * G + 15) / 16);
         }
         long long incl = len;
         int incl_t = tiles;
@@ -113,17 +116,20 @@ __global__ void __launch_bounds__(kScoreWarps * 32) score_kernel(KernelArgs a) {
     const int Hkv = a.g.Hkv, G = a.g.Hq / a.g.Hkv;
     const float sm_scale = a.scale != 0.f ? a.scale : rsqrtf((float)D);
 
-    // ---- this worker's slice of the global (sequence, kv head, tile) sequence ------------------------
-    const int total_tiles = a.stile_prefix[a.num_sequences] * Hkv;
-    const int all_workers = gridDim.x * kScoreWarps;
-    const int workers = max(1, min(all_workers, (total_tiles + 3) / 4));
-    const int per_worker = (total_tiles + workers - 1) / workers;
-    const int wid = blockIdx.x * kScoreWarps + warp;
-    int g_tile = min(total_tiles, wid * per_worker);
-    const int g_end = min(total_tiles, g_tile + per_worker);
+    // ---- this worker's slice --------------------------------------------------------------------------
+    // Cost space: sequence s occupies [P[s]*Hkv, P[s+1]*Hkv) with P = stile_prefix, kv head hk the
+    // hk-th equal part of it, and tile t of that part starts at t * weight(s).  A worker owns the
+    // tiles whose start lies in its equal slice [c_pos, c_end) of the cost range.
+    const long long total_cost = (long long)a.stile_prefix[a.num_sequences] * Hkv;
+    const long long all_workers = (long long)gridDim.x * kScoreWarps;
+    const long long workers = max(1LL, min(all_workers, (total_cost + 3) / 4));
+    const long long per_worker = (total_cost + workers - 1) / workers;
+    const long long wid = (long long)blockIdx.x * kScoreWarps + warp;
+    long long c_pos = min(total_cost, wid * per_worker);
+    const long long c_end = min(total_cost, c_pos + per_worker);
 
     // ---- loader state (warp-uniform) ------------------------------------------------------------------
-    int r_s = -1, r_hk = 0, r_tiles = 0, r_tile = 0, r_tile_end = 0, r_ctx = 0, r_tb = 0, r_nb = 0;
+    int r_s = -1, r_hk = 0, r_tile = 0, r_tile_end = 0, r_ctx = 0, r_tb = 0, r_nb = 0;
     int w_blk0 = 0, tbl = 0;
     bool r_first = false;
 
@@ -137,44 +143,43 @@ __global__ void __launch_bounds__(kScoreWarps * 32) score_kernel(KernelArgs a) {
         }
         tbl = blk;
     };
-    auto next_run = [&]() {
-        int tile0;
-        if (r_s < 0) {
-            const int key = g_tile / Hkv;
+    // Finds the next run of tiles of one (sequence, kv head) inside the slice; false when the slice is done.
+    auto next_run = [&]() -> bool {
+        while (c_pos < c_end) {
+            const int key = (int)(c_pos / Hkv);
             int lo = 0, hi = a.num_sequences;
             while (hi - lo > 1) {
                 const int mid = (lo + hi) >> 1;
                 if (a.stile_prefix[mid] <= key) lo = mid; else hi = mid;
             }
+            const int p0 = a.stile_prefix[lo];
+            const long long seq_cost = a.stile_prefix[lo + 1] - p0;
+            const int n = a.subsequence_begins[lo + 1] - a.subsequence_begins[lo];
+            const int ctx = a.past_lens[lo] + n;
+            const int tiles = (ctx + kTileS - 1) / kTileS;
+            const long long weight = seq_cost / tiles;
+            const long long off = c_pos - (long long)p0 * Hkv;
+            const int hk = (int)(off / seq_cost);
+            const long long head_base = (long long)p0 * Hkv + hk * seq_cost;
+            const int tile0 = (int)((c_pos - head_base + weight - 1) / weight);
+            const int tile1 = (int)((min(c_end, head_base + seq_cost) - head_base + weight - 1) / weight);
+            c_pos = min(c_end, head_base + seq_cost);
+            if (tile0 >= tile1) continue;
             r_s = lo;
-            const int p0 = a.stile_prefix[r_s];
-            r_tiles = a.stile_prefix[r_s + 1] - p0;
-            const int off = g_tile - p0 * Hkv;
-            r_hk = off / r_tiles;
-            tile0 = off % r_tiles;
-        } else {
-            tile0 = 0;
-            if (++r_hk == Hkv) {
-                r_hk = 0;
-                do {
-                    ++r_s;
-                    r_tiles = a.stile_prefix[r_s + 1] - a.stile_prefix[r_s];
-                } while (r_tiles == 0);
-            }
+            r_hk = hk;
+            r_tile = tile0;
+            r_tile_end = tile1;
+            r_ctx = ctx;
+            r_tb = a.block_indices_begins[lo];
+            r_nb = a.block_indices_begins[lo + 1] - r_tb;
+            r_first = true;
+            load_window(tile0 * kTileS / BS);
+            return true;
         }
-        const int ntile = min(r_tiles - tile0, g_end - g_tile);
-        r_tile = tile0;
-        r_tile_end = tile0 + ntile;
-        r_ctx = a.past_lens[r_s] + (a.subsequence_begins[r_s + 1] - a.subsequence_begins[r_s]);
-        r_tb = a.block_indices_begins[r_s];
-        r_nb = a.block_indices_begins[r_s + 1] - r_tb;
-        g_tile += ntile;
-        r_first = true;
-        load_window(tile0 * kTileS / BS);
+        return false;
     };
     auto produce = [&](int slot) {
-        if (r_tile >= r_tile_end && g_tile < g_end) next_run();
-        if (r_tile >= r_tile_end) {
+        if (r_tile >= r_tile_end && !next_run()) {
             if (lane == 0) descs[slot] = ScoreDesc{-1, 0, 0, 0};
             if constexpr (!U8) cp_async_commit();
             return;
@@ -238,14 +243,27 @@ __global__ void __launch_bounds__(kScoreWarps * 32) score_kernel(KernelArgs a) {
             const long long grow = (long long)(t0 + j) * a.g.Hq + h;
             float q[D / 4];
             float amax = 0.f;
+            if constexpr (U8) {
+                // element e is dimension 64*(e/16) + 16*c + e%16: runs of 16
 #pragma unroll
-            for (int e = 0; e < D / 4; ++e) {
-                int dd;
-                if constexpr (U8) dd = 64 * (e / 16) + 16 * c + (e % 16);
-                else dd = 16 * (e / 4) + 2 * c + (e & 1) + 8 * ((e >> 1) & 1);
-                q[e] = live ? load_act(a.query, grow * D + dd, a.g.act) : 0.f;
-                amax = fmaxf(amax, fabsf(q[e]));
+                for (int h = 0; h < D / 64; ++h) {
+                    float v[16];
+                    if (live) load_act_vec<16>(a.query, grow * D + 64 * h + 16 * c, a.g.act, v);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) q[16 * h + e] = live ? v[e] : 0.f;
+                }
+            } else {
+                // element e is dimension 16*(e/4) + 8*((e>>1)&1) + 2*c + (e&1): pairs
+#pragma unroll
+                for (int e = 0; e < D / 4; e += 2) {
+                    float v[2];
+                    if (live) load_act_vec<2>(a.query, grow * D + 16 * (e / 4) + 8 * ((e >> 1) & 1) + 2 * c, a.g.act, v);
+                    q[e] = live ? v[0] : 0.f;
+                    q[e + 1] = live ? v[1] : 0.f;
+                }
             }
+#pragma unroll
+            for (int e = 0; e < D / 4; ++e) amax = fmaxf(amax, fabsf(q[e]));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             float qmul = 1.f;
