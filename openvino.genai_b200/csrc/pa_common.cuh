@@ -95,6 +95,29 @@ __device__ __forceinline__ void store_act(void* p, long long i, int act, float v
     else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
 }
 
+// 8 consecutive activations starting at element i (i a multiple of 8, base 16-byte aligned).
+__device__ __forceinline__ void store_act_vec8(void* p, long long i, int act, const float (&v)[8]) {
+    if (act == PA_DTYPE_F32) {
+        float4* dst = reinterpret_cast<float4*>((float*)p + i);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+        return;
+    }
+    uint4 w;
+    if (act == PA_DTYPE_F16) {
+        __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+        __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+        w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
+        w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
+    } else {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+        w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
+        w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
+    }
+    *reinterpret_cast<uint4*>((uint16_t*)p + i) = w;
+}
+
 // ---- by-token asymmetric u8 quantiser --------------------------------------------------------
 // scale = (max - min) / 255 (1 for a constant row), zp = -min / scale,
 // q = clamp(rint(fma(x, 1/scale, zp)), 0, 255).  Every step is individually rounded so that the

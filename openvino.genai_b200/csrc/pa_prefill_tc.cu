@@ -3,18 +3,22 @@
 //
 // One CTA (128 threads) owns a q tile of 128 rows = (new token, q head of one GQA group) pairs of
 // one (sequence, kv head), so a K/V byte is read once for the whole group.  Per 64-token KV tile:
-//   1. lane 0 of the CTA has the TMA engine copy the tile's (block, head) records (u8 data +
-//      per-token scale / zero-point) into a raw staging buffer (bulk copy, mbarrier completion);
-//   2. all threads turn the bytes into f16 (byte | 0x6400 = 1024 + byte, the offset is removed
-//      algebraically with the zero-point) and write them into 128-byte-swizzled operand tiles:
-//      K as [64 tokens][128 dims] (K-major B operand), V^T as [128 dims][64 tokens] (the cache keeps
-//      value bytes token-minor, so V^T is K-major for P.V as well);
+//   1. one thread has the TMA engine copy the tile's (block, head) records (u8 data + per-token
+//      scale / zero-point) into a raw staging buffer (bulk copy, mbarrier completion);
+//   2. all threads turn the bytes into f16 (byte | 0x6400 = 1024 + byte) and write them into
+//      128-byte-swizzled operand tiles: K as [64 tokens][128 dims] (K-major B operand), V^T as
+//      [128 dims][64 tokens] (the cache keeps value bytes token-minor, so V^T is K-major for P.V too);
 //   3. one thread issues tcgen05.mma: S[128 x 64] = Q.K^T into TMEM, commit -> mbarrier;
-//   4. thread r reads row r of S from TMEM (tcgen05.ld 32x32b), applies per-token scale,
-//      zero-point, causal mask and the online softmax, and stores P' = P * v_scale as f16 into a
-//      swizzled A-operand tile;
-//   5. one thread issues tcgen05.mma: PV[128 x 128] = P'.V into TMEM; every thread folds its row of
-//      PV into register accumulators (O = O * alpha + PV), so TMEM is never read-modify-written.
+//   4. thread r reads row r of S from TMEM (tcgen05.ld 32x32b), applies the per-token scale, the
+//      causal mask (diagonal tiles only) and the online softmax, and stores P' = P * v_scale as f16
+//      into a swizzled A-operand tile;
+//   5. one thread issues tcgen05.mma: O[128 x 144] += P'.V in TMEM; it runs while the CTA converts
+//      the next tile's keys.
+// The zero-points ride on the tensor core: Q and K carry 16 extra dims holding the row's sum of q
+// and minus (1024 + k zero-point), split into f16 pieces, so S comes out with the offset term
+// already subtracted; V^T carries 16 extra rows holding 1024 + v zero-point, whose P'.V columns
+// are subtracted from O in the epilogue.  The running maximum is lazy: O in TMEM is rescaled only
+// when a row's maximum grows by more than 2^4, so most tiles never touch the accumulator.
 // Tensor-bound for long contexts: 4 * Hq * D flops per (new token, context token) pair.
 #include <algorithm>
 
@@ -28,8 +32,11 @@ namespace {
 
 constexpr int kRows = 128;     // q-tile rows = UMMA M
 constexpr int kD = 128;        // head size
+constexpr int kDx = 16;        // extra dims / extra V^T rows that carry the zero-point terms
 constexpr int kKv = 64;        // context tokens per KV tile = UMMA N of Q.K^T
-constexpr int kTmemCols = 256; // S: columns [0, 64), PV: columns [64, 192)
+constexpr int kNo = kD + kDx;  // UMMA N of P.V
+constexpr int kTmemCols = 256; // S: columns [0, 64), O: columns [64, 208)
+constexpr float kLazy = 4.f;   // log2 of the growth of a row maximum that forces a rescale of O
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLn2P = 0.6931471805599453f;
 
@@ -39,27 +46,50 @@ struct PrefillSmem {
     static constexpr int NREC = kKv / BS;
     alignas(1024) uint8_t q[kRows * kD * 2];       // 2 swizzle atoms of [128 rows][64 dims]
     alignas(1024) uint8_t k[kKv * kD * 2];         // 2 atoms of [64 tokens][64 dims]
-    alignas(1024) uint8_t vt[kD * kKv * 2];        // 1 atom of [128 dims][64 tokens]
+    alignas(1024) uint8_t vt[kNo * kKv * 2];       // [144 dims][64 tokens], 18 groups of 8 rows
     alignas(1024) uint8_t p[kRows * kKv * 2];      // 1 atom of [128 rows][64 tokens]
+    alignas(128) uint8_t qx[kRows * kDx * 2];      // unswizzled [128 rows][16 dims]
+    alignas(128) uint8_t kx[kKv * kDx * 2];        // unswizzled [64 tokens][16 dims]
     alignas(128) uint8_t raw_k[NREC * REC];        // staged key records
     alignas(128) uint8_t raw_v[NREC * REC];        // staged value records
-    alignas(16) float k_scale[kKv];
-    alignas(16) float k_zp[kKv];
+    alignas(16) float col_a[kKv];                  // k scale * softmax scale * log2(e)
     alignas(16) float v_scale[kKv];
-    alignas(16) float v_zp[kKv];
     alignas(8) uint64_t bar_raw;
     alignas(8) uint64_t bar_s;
     alignas(8) uint64_t bar_o;
     uint32_t tmem_base;
-    int failed;
 };
 
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
+// unswizzled K-major tile of 16 dims: 8-row groups 256 bytes apart, the two 8-dim halves 128 apart
+__device__ __forceinline__ uint32_t plain16(uint32_t row, uint32_t half) { return (row >> 3) * 256u + half * 128u + (row & 7u) * 16u; }
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
+// z = h + m + l up to 2^-33 |z|, every piece an f16
+__device__ __forceinline__ void split3(float z, __half& h, __half& m, __half& l) {
+    h = __float2half_rn(z);
+    const float r = z - __half2float(h);
+    m = __float2half_rn(r);
+    l = __float2half_rn(r - __half2float(m));
+}
+__device__ __forceinline__ uint32_t h2_bits(__half a, __half b) {
+    return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
+}
+// 16 cache bytes -> 16 f16 values 1024 + byte
+__device__ __forceinline__ void bytes16_to_h(const uint4 w, uint4& lo4, uint4& hi4) {
+    lo4.x = __byte_perm(w.x, 0x64646464u, 0x4140); lo4.y = __byte_perm(w.x, 0x64646464u, 0x4342);
+    lo4.z = __byte_perm(w.y, 0x64646464u, 0x4140); lo4.w = __byte_perm(w.y, 0x64646464u, 0x4342);
+    hi4.x = __byte_perm(w.z, 0x64646464u, 0x4140); hi4.y = __byte_perm(w.z, 0x64646464u, 0x4342);
+    hi4.z = __byte_perm(w.w, 0x64646464u, 0x4140); hi4.w = __byte_perm(w.w, 0x64646464u, 0x4342);
 }
 
 template <int BS>
@@ -71,15 +101,16 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
     const int G = a.g.Hq / a.g.Hkv;
     const int Hkv = a.g.Hkv;
     const int total_items = a.plan->total_ptiles * Hkv;
-    const float sm_scale = a.scale != 0.f ? a.scale : rsqrtf((float)kD);
+    const float qscale = (a.scale != 0.f ? a.scale : rsqrtf((float)kD)) * kLog2eP;
 
     if (tid == 0) {
         mbar_init(&sm.bar_raw, 1);
         mbar_init(&sm.bar_s, 1);
         mbar_init(&sm.bar_o, 1);
         mbar_fence_init();
-        sm.failed = 0;
     }
+    // rows 131..143 of V^T stay zero for the whole kernel
+    if (tid < (kNo - kD - 3) * 8) *reinterpret_cast<uint4*>(sm.vt + (kD + 3) * 128 + tid * 16) = make_uint4(0, 0, 0, 0);
     if (warp == 0) tc05::tmem_alloc(&sm.tmem_base, kTmemCols);
     tc05::fence_before_thread_sync();
     __syncthreads();
@@ -89,11 +120,13 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;   // this warp's TMEM lanes
 
     constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
-    constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kD, 0, 0, 0);
+    constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kNo, 0, 0, 0);
     const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), vt_addr = smem_u32(sm.vt), p_addr = smem_u32(sm.p);
+    const uint32_t qx_addr = smem_u32(sm.qx), kx_addr = smem_u32(sm.kx);
 
     uint32_t phase_raw = 0, phase_s = 0, phase_o = 0;
     bool bad_index = false;
+    bool failed = false;
 
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
         // ---- which q tile -------------------------------------------------------------------------
@@ -109,43 +142,16 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
         const int t0 = a.subsequence_begins[s];
         const int n_new = a.subsequence_begins[s + 1] - t0;
         const int past = a.past_lens[s];
-        const int tb = a.block_indices_begins[s];
-        const int32_t* table = a.block_indices + tb;
+        const int32_t* table = a.block_indices + a.block_indices_begins[s];
 
         // ---- this thread's row ---------------------------------------------------------------------
         const int flat = qt * kRows + tid;
         const int tok = flat / G, hq = hk * G + flat % G;
         const bool row_live = tok < n_new;
-        const int tok_lo = (qt * kRows) / G;
         const int tok_hi = min(n_new - 1, (qt * kRows + kRows - 1) / G);
         const int ctx_hi = past + tok_hi + 1;             // context the last row of the tile sees
         const int ntiles = (ctx_hi + kKv - 1) / kKv;
         const int my_ctx = row_live ? past + tok + 1 : ctx_hi;
-
-        // ---- Q -> f16 swizzled A operand; sum of the row for the zero-point term ------------------
-        float qsum = 0.f, qscale;
-        {
-            const long long qoff = ((long long)(t0 + (row_live ? tok : 0)) * a.g.Hq + hq) * kD;
-            float amax = 0.f;
-            for (int c = 0; c < kD / 8; ++c) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) { v[e] = row_live ? load_act(a.query, qoff + 8 * c + e, a.g.act) : 0.f; amax = fmaxf(amax, fabsf(v[e])); }
-                uint4 w;
-                w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
-                const __half2* h = reinterpret_cast<const __half2*>(&w);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
-                *reinterpret_cast<uint4*>(sm.q + (c / 8) * (kRows * 128) + sw128(tid, c % 8)) = w;
-            }
-            (void)amax;  // no power-of-two prescale here: |q| is assumed to stay inside the f16 range
-            qscale = sm_scale * kLog2eP;
-        }
-
-        float o[kD];
-#pragma unroll
-        for (int d = 0; d < kD; ++d) o[d] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, z_run = 0.f;
 
         auto issue_raw = [&](int j) {   // thread 0: TMA-engine copies of tile j's records
             uint32_t bytes = 0;
@@ -171,67 +177,98 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
                     bulk_g2s(sm.raw_v + r * Smem::REC, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
                 }
         };
-
-        __syncthreads();                 // Q tile written; previous item's operand buffers are free
+        // every tensor-core read of the previous item has completed (its waits sit in program order
+        // before this point) and every thread has finished reading the raw buffers
         if (tid == 0) issue_raw(0);
+
+        // ---- Q -> f16 swizzled A operand; the row's sum goes into the extra dims ------------------
+        {
+            const long long qoff = ((long long)(t0 + (row_live ? tok : 0)) * a.g.Hq + hq) * kD;
+            float qsum = 0.f;
+#pragma unroll 4
+            for (int c = 0; c < kD / 8; ++c) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = 0.f;
+                if (row_live) load_act_vec<8>(a.query, qoff + 8 * c, a.g.act, v);
+                uint4 w;
+                w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
+                const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
+                *reinterpret_cast<uint4*>(sm.q + (c / 8) * (kRows * 128) + sw128(tid, c % 8)) = w;
+            }
+            // |q| is assumed to stay inside the f16 range (no power-of-two prescale here)
+            const __half qh = __float2half_rn(qsum), ql = __float2half_rn(qsum - __half2float(qh));
+            const __half zero = __ushort_as_half(0);
+            *reinterpret_cast<uint4*>(sm.qx + plain16(tid, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
+            *reinterpret_cast<uint4*>(sm.qx + plain16(tid, 1)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+
+        float m_run = -INFINITY, l_run = 0.f;
 
         // A wait that runs out sets `failed`; the flag is made uniform at the next block barrier so
         // that every thread leaves the loop at the same place.
-        bool failed = false;
         for (int j = 0; j < ntiles; ++j) {
+            const int col0 = j * kKv;
+            const int live_tokens = min(kKv, ctx_hi - col0);
             // ---- 1-2. raw records -> f16 operand tiles -------------------------------------------
-            if (!failed && !mbar_wait_bounded(&sm.bar_raw, phase_raw)) { failed = true; }
+            if (!mbar_wait_bounded(&sm.bar_raw, phase_raw)) failed = true;
             phase_raw ^= 1;
-            const int live_tokens = min(kKv, ctx_hi - j * kKv);
             if (!failed) {
-                // K: unit u = 16 dims of one token
+                // K: unit u = 16 dims of one token.  S of the previous tile has completed.
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int u = tid + kRows * i;
                     const int token = u >> 3, seg = u & 7;
-                    uint4 lo4 = make_uint4(0x64006400u, 0x64006400u, 0x64006400u, 0x64006400u), hi4 = lo4;  // 1024.0: cancels with the offset term
-                    if (token < live_tokens) {
-                        const uint4 w = *reinterpret_cast<const uint4*>(sm.raw_k + (token / BS) * Smem::REC + (token % BS) * kD + 16 * seg);
-                        lo4.x = __byte_perm(w.x, 0x64646464u, 0x4140); lo4.y = __byte_perm(w.x, 0x64646464u, 0x4342);
-                        lo4.z = __byte_perm(w.y, 0x64646464u, 0x4140); lo4.w = __byte_perm(w.y, 0x64646464u, 0x4342);
-                        hi4.x = __byte_perm(w.z, 0x64646464u, 0x4140); hi4.y = __byte_perm(w.z, 0x64646464u, 0x4342);
-                        hi4.z = __byte_perm(w.w, 0x64646464u, 0x4140); hi4.w = __byte_perm(w.w, 0x64646464u, 0x4342);
-                    }
+                    uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
+                    if (token < live_tokens)
+                        bytes16_to_h(*reinterpret_cast<const uint4*>(sm.raw_k + (token / BS) * Smem::REC + (token % BS) * kD + 16 * seg), lo4, hi4);
                     uint8_t* atom = sm.k + (seg >> 2) * (kKv * 128);
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg) & 7)) = lo4;
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg + 1) & 7)) = hi4;
                 }
-                // V^T: thread = dim row, 64 token bytes from the tile's records
-                {
-                    const int d = tid;
-#pragma unroll
-                    for (int r = 0; r < Smem::NREC; ++r) {
-#pragma unroll
-                        for (int q16 = 0; q16 < BS / 16; ++q16) {
-                            const int tbase = r * BS + 16 * q16;   // first of 16 tokens
-                            uint4 lo4 = make_uint4(0x64006400u, 0x64006400u, 0x64006400u, 0x64006400u), hi4 = lo4;
-                            if (tbase < live_tokens) {
-                                const uint4 w = *reinterpret_cast<const uint4*>(sm.raw_v + r * Smem::REC + d * BS + 16 * q16);
-                                lo4.x = __byte_perm(w.x, 0x64646464u, 0x4140); lo4.y = __byte_perm(w.x, 0x64646464u, 0x4342);
-                                lo4.z = __byte_perm(w.y, 0x64646464u, 0x4140); lo4.w = __byte_perm(w.y, 0x64646464u, 0x4342);
-                                hi4.x = __byte_perm(w.z, 0x64646464u, 0x4140); hi4.y = __byte_perm(w.z, 0x64646464u, 0x4342);
-                                hi4.z = __byte_perm(w.w, 0x64646464u, 0x4140); hi4.w = __byte_perm(w.w, 0x64646464u, 0x4342);
-                            }
-                            *reinterpret_cast<uint4*>(sm.vt + sw128(d, (tbase >> 3))) = lo4;
-                            *reinterpret_cast<uint4*>(sm.vt + sw128(d, (tbase >> 3) + 1)) = hi4;
-                        }
-                    }
-                }
-                // per-token parameters outlive the raw buffer
                 if (tid < kKv) {
                     const int token = tid;
                     const bool ok = token < live_tokens;
                     const float* kp = reinterpret_cast<const float*>(sm.raw_k + (token / BS) * Smem::REC + BS * kD);
+                    sm.col_a[token] = ok ? kp[token % BS] * qscale : 0.f;
+                    __half zh, zm, zl;
+                    split3(ok ? -(kp[BS + token % BS] + 1024.f) : 0.f, zh, zm, zl);
+                    const __half zero = __ushort_as_half(0);
+                    *reinterpret_cast<uint4*>(sm.kx + plain16(token, 0)) = make_uint4(h2_bits(zh, zm), h2_bits(zl, zh), h2_bits(zm, zero), 0u);
+                    *reinterpret_cast<uint4*>(sm.kx + plain16(token, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            if (j > 0) {   // P.V of the previous tile still reads V^T and P
+                if (!failed && !mbar_wait_bounded(&sm.bar_o, phase_o)) failed = true;
+                phase_o ^= 1;
+                tc05::fence_after_thread_sync();
+            }
+            if (!failed) {
+                // V^T: thread = dim row, 64 token bytes from the tile's records
+                const int d = tid;
+#pragma unroll
+                for (int r = 0; r < Smem::NREC; ++r) {
+#pragma unroll
+                    for (int q16 = 0; q16 < BS / 16; ++q16) {
+                        const int tbase = r * BS + 16 * q16;   // first of 16 tokens
+                        uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
+                        if (tbase < live_tokens) bytes16_to_h(*reinterpret_cast<const uint4*>(sm.raw_v + r * Smem::REC + d * BS + 16 * q16), lo4, hi4);
+                        *reinterpret_cast<uint4*>(sm.vt + sw128(d, (tbase >> 3))) = lo4;
+                        *reinterpret_cast<uint4*>(sm.vt + sw128(d, (tbase >> 3) + 1)) = hi4;
+                    }
+                }
+                if (tid < kKv) {
+                    const int token = tid;
+                    const bool ok = token < live_tokens;
                     const float* vp = reinterpret_cast<const float*>(sm.raw_v + (token / BS) * Smem::REC + BS * kD);
-                    sm.k_scale[token] = ok ? kp[token % BS] : 0.f;
-                    sm.k_zp[token] = ok ? kp[BS + token % BS] + 1024.f : 0.f;
                     sm.v_scale[token] = ok ? vp[token % BS] : 0.f;
-                    sm.v_zp[token] = ok ? vp[BS + token % BS] + 1024.f : 0.f;
+                    __half zh, zm, zl;
+                    split3(ok ? vp[BS + token % BS] + 1024.f : 0.f, zh, zm, zl);
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 0, token >> 3) + (token & 7) * 2) = zh;
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 1, token >> 3) + (token & 7) * 2) = zm;
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 2, token >> 3) + (token & 7) * 2) = zl;
                 }
             }
             tc05::fence_proxy_async_smem();
@@ -248,94 +285,142 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
                     const uint64_t db = tc05::smem_desc_sw128(k_addr + (kk >> 2) * (kKv * 128) + (kk & 3) * 32, 1024);
                     tc05::mma_ss(tmem_s, da, db, idesc_s, kk > 0 ? 1u : 0u);
                 }
+                tc05::mma_ss(tmem_s, tc05::smem_desc_plain(qx_addr, 128, 256), tc05::smem_desc_plain(kx_addr, 128, 256), idesc_s, 1u);
                 tc05::commit(&sm.bar_s);
             }
             if (!mbar_wait_bounded(&sm.bar_s, phase_s)) failed = true;
             phase_s ^= 1;
+            failed = __any_sync(0xffffffffu, failed);   // the TMEM accesses below are warp-collective
             tc05::fence_after_thread_sync();
 
             // ---- 4. softmax of this thread's row ------------------------------------------------------
-            float alpha = 1.f;
             if (!failed) {
-                uint32_t sreg[2][32];
-                tc05::ld_32x32b_x32(tmem_s + lane_base, sreg[0]);
-                tc05::ld_32x32b_x32(tmem_s + lane_base + 32, sreg[1]);
-                tc05::wait_ld();
                 float sv[kKv];
-                float mx = -INFINITY;
-                const int col0 = j * kKv;
+                {
+                    uint32_t s0[32], s1[32];
+                    tc05::ld_32x32b_x32(tmem_s + lane_base, s0);
+                    tc05::ld_32x32b_x32(tmem_s + lane_base + 32, s1);
+                    tc05::wait_ld();
 #pragma unroll
-                for (int c = 0; c < kKv; ++c) {
-                    const float raw = __uint_as_float(sreg[c >> 5][c & 31]);
-                    float v = (raw - sm.k_zp[c] * qsum) * (sm.k_scale[c] * qscale);
-                    v = (col0 + c < my_ctx) ? v : -INFINITY;
-                    sv[c] = v;
-                    mx = fmaxf(mx, v);
+                    for (int c = 0; c < 32; ++c) { sv[c] = __uint_as_float(s0[c]); sv[32 + c] = __uint_as_float(s1[c]); }
                 }
-                const float m_new = fmaxf(m_run, mx);      // finite: column 0 of every tile is visible to every row
-                alpha = ex2(m_run - m_new);
-                m_run = m_new;
-                float lsum = 0.f, zsum = 0.f;
+                const float4* ca4 = reinterpret_cast<const float4*>(sm.col_a);
+                float mx = -INFINITY;
+                if (col0 + kKv <= my_ctx) {   // the whole tile is visible to this row
+#pragma unroll
+                    for (int c = 0; c < kKv; c += 4) {
+                        const float4 A = ca4[c >> 2];
+                        sv[c] *= A.x; sv[c + 1] *= A.y; sv[c + 2] *= A.z; sv[c + 3] *= A.w;
+                        mx = max3(mx, sv[c], sv[c + 1]);
+                        mx = max3(mx, sv[c + 2], sv[c + 3]);
+                    }
+                } else {
+                    const int nvis = my_ctx - col0;   // columns this row sees; may be <= 0
+#pragma unroll
+                    for (int c = 0; c < kKv; c += 4) {
+                        const float4 A = ca4[c >> 2];
+                        sv[c] = c < nvis ? sv[c] * A.x : -INFINITY;
+                        sv[c + 1] = c + 1 < nvis ? sv[c + 1] * A.y : -INFINITY;
+                        sv[c + 2] = c + 2 < nvis ? sv[c + 2] * A.z : -INFINITY;
+                        sv[c + 3] = c + 3 < nvis ? sv[c + 3] * A.w : -INFINITY;
+                        mx = max3(mx, sv[c], sv[c + 1]);
+                        mx = max3(mx, sv[c + 2], sv[c + 3]);
+                    }
+                }
+                if (j == 0) {
+                    m_run = mx;      // finite: column 0 of tile 0 is visible to every row
+                } else {
+                    const bool grow = mx > m_run + kLazy;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        // rescale this warp's rows of O in TMEM; P.V of the previous tile has completed
+                        const float alpha = grow ? ex2(m_run - mx) : 1.f;
+                        if (grow) m_run = mx;
+                        l_run *= alpha;
+#pragma unroll
+                        for (int q4 = 0; q4 < kD / 32; ++q4) {
+                            uint32_t r[32];
+                            tc05::ld_32x32b_x32(tmem_o + lane_base + 32 * q4, r);
+                            tc05::wait_ld();
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                            tc05::st_32x32b_x32(tmem_o + lane_base + 32 * q4, r);
+                        }
+                        uint32_t r[16];
+                        tc05::ld_32x32b_x16(tmem_o + lane_base + kD, r);
+                        tc05::wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                        tc05::st_32x32b_x16(tmem_o + lane_base + kD, r);
+                        tc05::wait_st();
+                    }
+                }
+                const float4* vs4 = reinterpret_cast<const float4*>(sm.v_scale);
+                float lsum = 0.f;
 #pragma unroll
                 for (int c = 0; c < kKv; c += 8) {
-                    uint32_t packed[4];
+                    const float4 V0 = vs4[c >> 2], V1 = vs4[(c >> 2) + 1];
+                    float p[8];
 #pragma unroll
-                    for (int e = 0; e < 8; e += 2) {
-                        const float p0 = ex2(sv[c + e] - m_new), p1 = ex2(sv[c + e + 1] - m_new);
-                        lsum += p0 + p1;
-                        const uint32_t pk = pack_h2(p0 * sm.v_scale[c + e], p1 * sm.v_scale[c + e + 1]);
-                        const __half2 h = *reinterpret_cast<const __half2*>(&pk);
-                        zsum += __low2float(h) * sm.v_zp[c + e] + __high2float(h) * sm.v_zp[c + e + 1];
-                        packed[e >> 1] = pk;
-                    }
-                    *reinterpret_cast<uint4*>(sm.p + sw128(tid, c >> 3)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    for (int e = 0; e < 8; ++e) { p[e] = ex2(sv[c + e] - m_run); lsum += p[e]; }
+                    uint4 w;
+                    w.x = pack_h2(p[0] * V0.x, p[1] * V0.y);
+                    w.y = pack_h2(p[2] * V0.z, p[3] * V0.w);
+                    w.z = pack_h2(p[4] * V1.x, p[5] * V1.y);
+                    w.w = pack_h2(p[6] * V1.z, p[7] * V1.w);
+                    *reinterpret_cast<uint4*>(sm.p + sw128(tid, c >> 3)) = w;
                 }
-                l_run = l_run * alpha + lsum;
-                z_run = z_run * alpha + zsum;
+                l_run += lsum;
             }
             tc05::fence_proxy_async_smem();
             tc05::fence_before_thread_sync();
             failed = __syncthreads_or(failed ? 1 : 0) != 0;
             if (failed) break;
-            // ---- 5. PV = P'.V, folded into the register accumulators ------------------------------------
+            // ---- 5. O += P'.V; overlaps the next tile's key conversion -----------------------------------
             if (tid == 0) {
                 tc05::fence_after_thread_sync();
 #pragma unroll
                 for (int kk = 0; kk < kKv / 16; ++kk) {
                     const uint64_t da = tc05::smem_desc_sw128(p_addr + kk * 32, 1024);
                     const uint64_t db = tc05::smem_desc_sw128(vt_addr + kk * 32, 1024);
-                    tc05::mma_ss(tmem_o, da, db, idesc_o, kk > 0 ? 1u : 0u);
+                    tc05::mma_ss(tmem_o, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc05::commit(&sm.bar_o);
             }
-            if (!mbar_wait_bounded(&sm.bar_o, phase_o)) failed = true;
-            phase_o ^= 1;
-            tc05::fence_after_thread_sync();
-            if (!failed) {
-#pragma unroll
-                for (int q4 = 0; q4 < kD / 32; ++q4) {
-                    uint32_t oreg[32];
-                    tc05::ld_32x32b_x32(tmem_o + lane_base + 32 * q4, oreg);
-                    tc05::wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[32 * q4 + c] = o[32 * q4 + c] * alpha + __uint_as_float(oreg[c]);
-                }
-            }
-            tc05::fence_before_thread_sync();
         }
+        if (!failed && !mbar_wait_bounded(&sm.bar_o, phase_o)) failed = true;
+        phase_o ^= 1;
+        tc05::fence_after_thread_sync();
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
         if (failed) {
-            if (tid == 0) { atomicOr(a.status, 0x40000000u); sm.failed = 1; }
+            if (tid == 0) atomicOr(a.status, 0x40000000u);
             break;
         }
-        // ---- epilogue: out = (O - z) / l -----------------------------------------------------------
-        if (row_live) {
+        // ---- epilogue: out = (O - z) / l, z = the three zero-point columns ---------------------------
+        {
+            uint32_t zr[16];
+            tc05::ld_32x32b_x16(tmem_o + lane_base + kD, zr);
+            tc05::wait_ld();
+            const float z = __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]);
             const float inv = 1.f / l_run;
-            const long long ooff = ((long long)(t0 + tok) * a.g.Hq + hq) * kD;
-            for (int d = 0; d < kD; ++d) store_act(a.output, ooff + d, a.g.act, (o[d] - z_run) * inv);
-            if (a.lse) a.lse[(long long)(t0 + tok) * a.g.Hq + hq] = (m_run + log2f(l_run)) * kLn2P;
+            const long long ooff = ((long long)(t0 + (row_live ? tok : 0)) * a.g.Hq + hq) * kD;
+#pragma unroll
+            for (int q4 = 0; q4 < kD / 32; ++q4) {
+                uint32_t r[32];
+                tc05::ld_32x32b_x32(tmem_o + lane_base + 32 * q4, r);
+                tc05::wait_ld();
+                if (row_live) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = (__uint_as_float(r[c + e]) - z) * inv;
+                        store_act_vec8(a.output, ooff + 32 * q4 + c, a.g.act, v);
+                    }
+                }
+            }
+            if (row_live && a.lse) a.lse[(long long)(t0 + tok) * a.g.Hq + hq] = (m_run + log2f(l_run)) * kLn2P;
         }
-        (void)tok_lo;
+        tc05::fence_before_thread_sync();
     }
     if (__syncthreads_or(bad_index ? 1 : 0) && tid == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
     tc05::fence_before_thread_sync();
