@@ -44,16 +44,16 @@ template <int BS>
 struct PrefillSmem {
     static constexpr int REC = BS * (kD + 8);
     static constexpr int NREC = kKv / BS;
+    static constexpr int RSTRIDE = REC + 64;       // records 64 bytes out of phase: conflict-free 16-byte reads across records
     alignas(1024) uint8_t q[kRows * kD * 2];       // 2 swizzle atoms of [128 rows][64 dims]
     alignas(1024) uint8_t k[kKv * kD * 2];         // 2 atoms of [64 tokens][64 dims]
     alignas(1024) uint8_t vt[kNo * kKv * 2];       // [144 dims][64 tokens], 18 groups of 8 rows
     alignas(1024) uint8_t p[kRows * kKv * 2];      // 1 atom of [128 rows][64 tokens]
     alignas(128) uint8_t qx[kRows * kDx * 2];      // unswizzled [128 rows][16 dims]
     alignas(128) uint8_t kx[kKv * kDx * 2];        // unswizzled [64 tokens][16 dims]
-    alignas(128) uint8_t raw_k[NREC * REC];        // staged key records
-    alignas(128) uint8_t raw_v[NREC * REC];        // staged value records
-    alignas(16) float col_a[kKv];                  // k scale * softmax scale * log2(e)
-    alignas(16) float v_scale[kKv];
+    alignas(128) uint8_t raw_k[NREC * RSTRIDE];    // staged key records
+    alignas(128) uint8_t raw_v[NREC * RSTRIDE];    // staged value records
+    alignas(16) uint2 v_tab[kRows / 32][kKv / 2];  // per warp: (scale, -1024 * scale) as f16 pairs of two tokens
     alignas(8) uint64_t bar_raw;
     alignas(8) uint64_t bar_s;
     alignas(8) uint64_t bar_o;
@@ -84,12 +84,47 @@ __device__ __forceinline__ void split3(float z, __half& h, __half& m, __half& l)
 __device__ __forceinline__ uint32_t h2_bits(__half a, __half b) {
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
 }
+__device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t y;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(y) : "r"(a), "r"(b), "r"(c));
+    return y;
+}
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+    uint32_t y;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+    return y;
+}
+__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
+    uint32_t y;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+    return y;
+}
 // 16 cache bytes -> 16 f16 values 1024 + byte
 __device__ __forceinline__ void bytes16_to_h(const uint4 w, uint4& lo4, uint4& hi4) {
     lo4.x = __byte_perm(w.x, 0x64646464u, 0x4140); lo4.y = __byte_perm(w.x, 0x64646464u, 0x4342);
     lo4.z = __byte_perm(w.y, 0x64646464u, 0x4140); lo4.w = __byte_perm(w.y, 0x64646464u, 0x4342);
     hi4.x = __byte_perm(w.z, 0x64646464u, 0x4140); hi4.y = __byte_perm(w.z, 0x64646464u, 0x4342);
     hi4.z = __byte_perm(w.w, 0x64646464u, 0x4140); hi4.w = __byte_perm(w.w, 0x64646464u, 0x4342);
+}
+// (1024 + byte) -> byte * scale, rounded once.  The fused form needs -1024 * scale inside the f16
+// range; scales of 32 and more take the two-step form.
+__device__ __forceinline__ void scale16(uint4& lo4, uint4& hi4, __half sc) {
+    const uint32_t s2 = h2_bits(sc, sc);
+    uint32_t* w0 = reinterpret_cast<uint32_t*>(&lo4);
+    uint32_t* w1 = reinterpret_cast<uint32_t*>(&hi4);
+    if (fabsf(__half2float(sc)) < 32.f) {
+        const uint32_t c2 = hmul2_bits(s2, 0xE400E400u);   // -1024 * scale, exact
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { w0[k] = hfma2_bits(w0[k], s2, c2); w1[k] = hfma2_bits(w1[k], s2, c2); }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { w0[k] = hmul2_bits(hadd2_bits(w0[k], 0xE400E400u), s2); w1[k] = hmul2_bits(hadd2_bits(w1[k], 0xE400E400u), s2); }
+    }
 }
 
 template <int BS>
@@ -109,8 +144,8 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
         mbar_init(&sm.bar_o, 1);
         mbar_fence_init();
     }
-    // rows 131..143 of V^T stay zero for the whole kernel
-    if (tid < (kNo - kD - 3) * 8) *reinterpret_cast<uint4*>(sm.vt + (kD + 3) * 128 + tid * 16) = make_uint4(0, 0, 0, 0);
+    // rows 132..143 of V^T stay zero for the whole kernel
+    if (tid < (kNo - kD - 4) * 8) *reinterpret_cast<uint4*>(sm.vt + (kD + 4) * 128 + tid * 16) = make_uint4(0, 0, 0, 0);
     if (warp == 0) tc05::tmem_alloc(&sm.tmem_base, kTmemCols);
     tc05::fence_before_thread_sync();
     __syncthreads();
@@ -173,8 +208,8 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
             for (int r = 0; r < Smem::NREC; ++r)
                 if (blocks[r] >= 0) {
-                    bulk_g2s(sm.raw_k + r * Smem::REC, kc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
-                    bulk_g2s(sm.raw_v + r * Smem::REC, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
+                    bulk_g2s(sm.raw_k + r * Smem::RSTRIDE, kc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
+                    bulk_g2s(sm.raw_v + r * Smem::RSTRIDE, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
                 }
         };
         // every tensor-core read of the previous item has completed (its waits sit in program order
@@ -205,7 +240,7 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
             *reinterpret_cast<uint4*>(sm.qx + plain16(tid, 1)) = make_uint4(0u, 0u, 0u, 0u);
         }
 
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY;   // running maximum of q.k' (before the softmax scale)
 
         // A wait that runs out sets `failed`; the flag is made uniform at the next block barrier so
         // that every thread leaves the loop at the same place.
@@ -216,14 +251,18 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
             if (!mbar_wait_bounded(&sm.bar_raw, phase_raw)) failed = true;
             phase_raw ^= 1;
             if (!failed) {
-                // K: unit u = 16 dims of one token.  S of the previous tile has completed.
+                // K' = byte * f16(k scale): unit u = 16 dims of one token.  S of the previous tile has completed.
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int u = tid + kRows * i;
                     const int token = u >> 3, seg = u & 7;
                     uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
-                    if (token < live_tokens)
-                        bytes16_to_h(*reinterpret_cast<const uint4*>(sm.raw_k + (token / BS) * Smem::REC + (token % BS) * kD + 16 * seg), lo4, hi4);
+                    if (token < live_tokens) {
+                        const uint8_t* rec = sm.raw_k + (token / BS) * Smem::RSTRIDE;
+                        const __half ksh = __float2half_rn(*reinterpret_cast<const float*>(rec + BS * kD + 4 * (token % BS)));
+                        bytes16_to_h(*reinterpret_cast<const uint4*>(rec + (token % BS) * kD + 16 * seg), lo4, hi4);
+                        scale16(lo4, hi4, ksh);
+                    }
                     uint8_t* atom = sm.k + (seg >> 2) * (kKv * 128);
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg) & 7)) = lo4;
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg + 1) & 7)) = hi4;
@@ -231,10 +270,10 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
                 if (tid < kKv) {
                     const int token = tid;
                     const bool ok = token < live_tokens;
-                    const float* kp = reinterpret_cast<const float*>(sm.raw_k + (token / BS) * Smem::REC + BS * kD);
-                    sm.col_a[token] = ok ? kp[token % BS] * qscale : 0.f;
+                    const float* kp = reinterpret_cast<const float*>(sm.raw_k + (token / BS) * Smem::RSTRIDE + BS * kD);
+                    const float ksf = __half2float(__float2half_rn(kp[token % BS]));
                     __half zh, zm, zl;
-                    split3(ok ? -(kp[BS + token % BS] + 1024.f) : 0.f, zh, zm, zl);
+                    split3(ok ? -(ksf * kp[BS + token % BS]) : 0.f, zh, zm, zl);
                     const __half zero = __ushort_as_half(0);
                     *reinterpret_cast<uint4*>(sm.kx + plain16(token, 0)) = make_uint4(h2_bits(zh, zm), h2_bits(zl, zh), h2_bits(zm, zero), 0u);
                     *reinterpret_cast<uint4*>(sm.kx + plain16(token, 1)) = make_uint4(0u, 0u, 0u, 0u);
@@ -245,30 +284,59 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
                 phase_o ^= 1;
                 tc05::fence_after_thread_sync();
             }
+            failed = __any_sync(0xffffffffu, failed);
             if (!failed) {
-                // V^T: thread = dim row, 64 token bytes from the tile's records
-                const int d = tid;
+                // this warp's table of (scale, -1024 * scale) for the tile's token pairs
+                const int lane = tid & 31;
+                __syncwarp();
+                float vs0 = 0.f, vs1 = 0.f;
+                {
+                    const int t0k = 2 * lane, t1k = 2 * lane + 1;
+                    if (t0k < live_tokens) vs0 = *reinterpret_cast<const float*>(sm.raw_v + (t0k / BS) * Smem::RSTRIDE + BS * kD + 4 * (t0k % BS));
+                    if (t1k < live_tokens) vs1 = *reinterpret_cast<const float*>(sm.raw_v + (t1k / BS) * Smem::RSTRIDE + BS * kD + 4 * (t1k % BS));
+                }
+                const uint32_t s2 = pack_h2(vs0, vs1);
+                sm.v_tab[warp][lane] = make_uint2(s2, hmul2_bits(s2, 0xE400E400u));
+                const bool big = __any_sync(0xffffffffu, !(fabsf(vs0) < 32.f) || !(fabsf(vs1) < 32.f));
+                __syncwarp();
+                // V'^T = byte * f16(v scale): unit = 16 tokens of one dim
+                const int tg = tid & 3;
+                uint2 tab[8];
 #pragma unroll
-                for (int r = 0; r < Smem::NREC; ++r) {
+                for (int k = 0; k < 8; k += 2) {
+                    const uint4 t4 = *reinterpret_cast<const uint4*>(&sm.v_tab[warp][8 * tg + k]);
+                    tab[k] = make_uint2(t4.x, t4.y);
+                    tab[k + 1] = make_uint2(t4.z, t4.w);
+                }
+                constexpr int UPR = BS / 16;   // 16-token units per record
 #pragma unroll
-                    for (int q16 = 0; q16 < BS / 16; ++q16) {
-                        const int tbase = r * BS + 16 * q16;   // first of 16 tokens
-                        uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
-                        if (tbase < live_tokens) bytes16_to_h(*reinterpret_cast<const uint4*>(sm.raw_v + r * Smem::REC + d * BS + 16 * q16), lo4, hi4);
-                        *reinterpret_cast<uint4*>(sm.vt + sw128(d, (tbase >> 3))) = lo4;
-                        *reinterpret_cast<uint4*>(sm.vt + sw128(d, (tbase >> 3) + 1)) = hi4;
+                for (int i = 0; i < 4; ++i) {
+                    const int d = (tid >> 2) + 32 * i;
+                    uint4 lo4, hi4;
+                    bytes16_to_h(*reinterpret_cast<const uint4*>(sm.raw_v + (tg / UPR) * Smem::RSTRIDE + d * BS + 16 * (tg % UPR)), lo4, hi4);
+                    uint32_t w[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+                    if (!big) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) w[k] = hfma2_bits(w[k], tab[k].x, tab[k].y);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) w[k] = hmul2_bits(hadd2_bits(w[k], 0xE400E400u), tab[k].x);
                     }
+                    *reinterpret_cast<uint4*>(sm.vt + sw128(d, 2 * tg)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(sm.vt + sw128(d, 2 * tg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
                 if (tid < kKv) {
                     const int token = tid;
                     const bool ok = token < live_tokens;
-                    const float* vp = reinterpret_cast<const float*>(sm.raw_v + (token / BS) * Smem::REC + BS * kD);
-                    sm.v_scale[token] = ok ? vp[token % BS] : 0.f;
+                    const float* vp = reinterpret_cast<const float*>(sm.raw_v + (token / BS) * Smem::RSTRIDE + BS * kD);
+                    const float vsf = __half2float(__float2half_rn(vp[token % BS]));
                     __half zh, zm, zl;
-                    split3(ok ? vp[BS + token % BS] + 1024.f : 0.f, zh, zm, zl);
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 0, token >> 3) + (token & 7) * 2) = zh;
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 1, token >> 3) + (token & 7) * 2) = zm;
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 2, token >> 3) + (token & 7) * 2) = zl;
+                    split3(ok ? vsf * vp[BS + token % BS] : 0.f, zh, zm, zl);
+                    const uint32_t off = (token & 7) * 2;
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 0, token >> 3) + off) = zh;
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 1, token >> 3) + off) = zm;
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 2, token >> 3) + off) = zl;
+                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 3, token >> 3) + off) = __float2half_rn(ok ? 1.f : 0.f);
                 }
             }
             tc05::fence_proxy_async_smem();
@@ -295,7 +363,7 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
 
             // ---- 4. softmax of this thread's row ------------------------------------------------------
             if (!failed) {
-                float sv[kKv];
+                float sv[kKv];   // q.k' in units of 1 / qscale
                 {
                     uint32_t s0[32], s1[32];
                     tc05::ld_32x32b_x32(tmem_s + lane_base, s0);
@@ -304,38 +372,22 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) { sv[c] = __uint_as_float(s0[c]); sv[32 + c] = __uint_as_float(s1[c]); }
                 }
-                const float4* ca4 = reinterpret_cast<const float4*>(sm.col_a);
-                float mx = -INFINITY;
-                if (col0 + kKv <= my_ctx) {   // the whole tile is visible to this row
+                if (col0 + kKv > my_ctx) {   // diagonal tile: hide what this row cannot see
+                    const int nvis = my_ctx - col0;   // may be <= 0
 #pragma unroll
-                    for (int c = 0; c < kKv; c += 4) {
-                        const float4 A = ca4[c >> 2];
-                        sv[c] *= A.x; sv[c + 1] *= A.y; sv[c + 2] *= A.z; sv[c + 3] *= A.w;
-                        mx = max3(mx, sv[c], sv[c + 1]);
-                        mx = max3(mx, sv[c + 2], sv[c + 3]);
-                    }
-                } else {
-                    const int nvis = my_ctx - col0;   // columns this row sees; may be <= 0
-#pragma unroll
-                    for (int c = 0; c < kKv; c += 4) {
-                        const float4 A = ca4[c >> 2];
-                        sv[c] = c < nvis ? sv[c] * A.x : -INFINITY;
-                        sv[c + 1] = c + 1 < nvis ? sv[c + 1] * A.y : -INFINITY;
-                        sv[c + 2] = c + 2 < nvis ? sv[c + 2] * A.z : -INFINITY;
-                        sv[c + 3] = c + 3 < nvis ? sv[c + 3] * A.w : -INFINITY;
-                        mx = max3(mx, sv[c], sv[c + 1]);
-                        mx = max3(mx, sv[c + 2], sv[c + 3]);
-                    }
+                    for (int c = 0; c < kKv; ++c) sv[c] = c < nvis ? sv[c] : -INFINITY;
                 }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < kKv; c += 2) mx = max3(mx, sv[c], sv[c + 1]);
                 if (j == 0) {
                     m_run = mx;      // finite: column 0 of tile 0 is visible to every row
                 } else {
-                    const bool grow = mx > m_run + kLazy;
+                    const bool grow = (mx - m_run) * qscale > kLazy;
                     if (__any_sync(0xffffffffu, grow)) {
                         // rescale this warp's rows of O in TMEM; P.V of the previous tile has completed
-                        const float alpha = grow ? ex2(m_run - mx) : 1.f;
+                        const float alpha = grow ? ex2((m_run - mx) * qscale) : 1.f;
                         if (grow) m_run = mx;
-                        l_run *= alpha;
 #pragma unroll
                         for (int q4 = 0; q4 < kD / 32; ++q4) {
                             uint32_t r[32];
@@ -354,22 +406,18 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
                         tc05::wait_st();
                     }
                 }
-                const float4* vs4 = reinterpret_cast<const float4*>(sm.v_scale);
-                float lsum = 0.f;
+                // P = 2^(qscale * (s - m)) in f16 pairs: the exponent is rounded to f16 first, which costs
+                // at most 2^-12 of the exponent's magnitude in relative error of p
+                const float mq = m_run * qscale;
 #pragma unroll
                 for (int c = 0; c < kKv; c += 8) {
-                    const float4 V0 = vs4[c >> 2], V1 = vs4[(c >> 2) + 1];
-                    float p[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) { p[e] = ex2(sv[c + e] - m_run); lsum += p[e]; }
                     uint4 w;
-                    w.x = pack_h2(p[0] * V0.x, p[1] * V0.y);
-                    w.y = pack_h2(p[2] * V0.z, p[3] * V0.w);
-                    w.z = pack_h2(p[4] * V1.x, p[5] * V1.y);
-                    w.w = pack_h2(p[6] * V1.z, p[7] * V1.w);
+                    w.x = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
+                    w.y = ex2_h2(pack_h2(fmaf(sv[c + 2], qscale, -mq), fmaf(sv[c + 3], qscale, -mq)));
+                    w.z = ex2_h2(pack_h2(fmaf(sv[c + 4], qscale, -mq), fmaf(sv[c + 5], qscale, -mq)));
+                    w.w = ex2_h2(pack_h2(fmaf(sv[c + 6], qscale, -mq), fmaf(sv[c + 7], qscale, -mq)));
                     *reinterpret_cast<uint4*>(sm.p + sw128(tid, c >> 3)) = w;
                 }
-                l_run += lsum;
             }
             tc05::fence_proxy_async_smem();
             tc05::fence_before_thread_sync();
@@ -401,6 +449,7 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
             tc05::ld_32x32b_x16(tmem_o + lane_base + kD, zr);
             tc05::wait_ld();
             const float z = __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]);
+            const float l_run = __uint_as_float(zr[3]);   // the all-ones row of V^T sums the probabilities
             const float inv = 1.f / l_run;
             const long long ooff = ((long long)(t0 + (row_live ? tok : 0)) * a.g.Hq + hq) * kD;
 #pragma unroll
@@ -418,7 +467,7 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
                     }
                 }
             }
-            if (row_live && a.lse) a.lse[(long long)(t0 + tok) * a.g.Hq + hq] = (m_run + log2f(l_run)) * kLn2P;
+            if (row_live && a.lse) a.lse[(long long)(t0 + tok) * a.g.Hq + hq] = (m_run * qscale + log2f(l_run)) * kLn2P;
         }
         tc05::fence_before_thread_sync();
     }
