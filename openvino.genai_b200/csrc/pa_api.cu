@@ -214,7 +214,7 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     if (a->num_tokens > a->num_sequences) {
         if (pa::prefill_tc_supported(h->g) && !h->force_generic_prefill) {
             const int G = h->g.Hq / h->g.Hkv;
-            const long long max_items = ((long long)a->num_tokens * G / 128 + a->num_sequences) * h->g.Hkv;
+            const long long max_items = ((long long)a->num_tokens * G / pa::kPrefillItemRows + a->num_sequences) * h->g.Hkv;
             PA_CUDA(pa::launch_prefill_tc(k, stream, h->sm_count, max_items, &launches));
         } else {
             PA_CUDA(pa::launch_prefill(k, stream, &launches));

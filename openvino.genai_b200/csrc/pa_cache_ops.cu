@@ -47,12 +47,12 @@ __device__ void build_decode_plan(const KernelArgs& a) {
     for (int base = 0; base < B; base += 256) {
         const int s = base + tid;
         const int n = s < B ? seq_tiles(a, s) : 0;
-        // prefill chunks: 128-row q tiles of (new token, q head of one group) pairs
+        // prefill chunks: q tiles of kPrefillItemRows (new token, q head of one group) pairs
         int np = 0;
         if (s < B) {
             const int n_new = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
             const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
-            if (n_new > 1 && a.past_lens[s] >= 0 && (long long)nb * a.g.bs >= (long long)a.past_lens[s] + n_new) np = (n_new * G + 127) / 128;
+            if (n_new > 1 && a.past_lens[s] >= 0 && (long long)nb * a.g.bs >= (long long)a.past_lens[s] + n_new) np = (n_new * G + kPrefillItemRows - 1) / kPrefillItemRows;
         }
         int v = n, vp = np;
 #pragma unroll

@@ -8,10 +8,13 @@
 
 namespace pa {
 
+// Rows of one prefill work item: (new token, q head of one GQA group) pairs of one kv head.
+constexpr int kPrefillItemRows = 256;
+
 // Header of the plan area in the handle's scratch.
 struct PlanHeader {
     int total_tiles;   // 32-token tiles of all decode streams (rows x head tiles)
-    int total_ptiles;  // 128-row q tiles of all prefill chunks (per kv head)
+    int total_ptiles;  // kPrefillItemRows-row q tiles of all prefill chunks (per kv head)
     int pad[2];
 };
 

@@ -1,24 +1,27 @@
 // Prefill-chunk attention on the 5th-generation tensor cores (tcgen05 + TMEM) for the u8 cache,
 // head size 128.
 //
-// One CTA (128 threads) owns a q tile of 128 rows = (new token, q head of one GQA group) pairs of
-// one (sequence, kv head), so a K/V byte is read once for the whole group.  Per 64-token KV tile:
-//   1. one thread has the TMA engine copy the tile's (block, head) records (u8 data + per-token
-//      scale / zero-point) into a raw staging buffer (bulk copy, mbarrier completion);
-//   2. all threads turn the bytes into f16 (byte | 0x6400 = 1024 + byte) and write them into
-//      128-byte-swizzled operand tiles: K as [64 tokens][128 dims] (K-major B operand), V^T as
-//      [128 dims][64 tokens] (the cache keeps value bytes token-minor, so V^T is K-major for P.V too);
-//   3. one thread issues tcgen05.mma: S[128 x 64] = Q.K^T into TMEM, commit -> mbarrier;
-//   4. thread r reads row r of S from TMEM (tcgen05.ld 32x32b), applies the per-token scale, the
-//      causal mask (diagonal tiles only) and the online softmax, and stores P' = P * v_scale as f16
-//      into a swizzled A-operand tile;
-//   5. one thread issues tcgen05.mma: O[128 x 144] += P'.V in TMEM; it runs while the CTA converts
-//      the next tile's keys.
-// The zero-points ride on the tensor core: Q and K carry 16 extra dims holding the row's sum of q
-// and minus (1024 + k zero-point), split into f16 pieces, so S comes out with the offset term
-// already subtracted; V^T carries 16 extra rows holding 1024 + v zero-point, whose P'.V columns
-// are subtracted from O in the epilogue.  The running maximum is lazy: O in TMEM is rescaled only
-// when a row's maximum grows by more than 2^4, so most tiles never touch the accumulator.
+// A work item is a q tile of 256 rows = (new token, q head of one GQA group) pairs of one
+// (sequence, kv head), so a K/V byte is read once for the whole group.  The item is split into two
+// halves A and B of 128 rows (UMMA M) that share the key / value operand tiles.  One persistent
+// CTA per SM runs four roles that meet only through mbarriers:
+//   loader    (1 thread)   TMA-engine bulk copies of the (block, head) records of 64-token tiles
+//                          into a two-stage raw ring;
+//   converter (4 warps)    raw bytes -> f16 operand tiles in 128-byte-swizzled layout:
+//                          K' = byte * f16(k scale) as [64 tokens][128 dims], V'^T = byte *
+//                          f16(v scale) as [128 dims][64 tokens] (the cache keeps value bytes
+//                          token-minor, so both are K-major operands), two stages each;
+//   mma       (1 thread)   tcgen05.mma: S_X = Q_X.K'^T into TMEM, O_X += P_X.V' in TMEM, for X = A, B;
+//                          the S of the next tile is queued before the P.V of the current one;
+//   softmax   (2 x 4 warps) thread r owns row r of its half: reads S from TMEM, masks (diagonal
+//                          tiles only), keeps a lazy running maximum, writes P = 2^(scale*(s-m)) as
+//                          f16 into the A-operand tile; rescales O in TMEM only when a row maximum
+//                          grew by more than 2^4; normalises and stores the output at the end.
+// The zero-points ride on the tensor core: Q and K' carry 16 extra dims holding the row's sum of q
+// and minus scale * zero-point split into f16 pieces, so S comes out with the offset term already
+// subtracted; V'^T carries extra rows holding scale * zero-point (subtracted from O in the
+// epilogue) and an all-ones row whose P.V column is the softmax denominator.
+// Every wait is bounded; a wait that runs out raises a flag that all roles poll.
 // Tensor-bound for long contexts: 4 * Hq * D flops per (new token, context token) pair.
 #include <algorithm>
 
@@ -30,34 +33,49 @@ namespace pa {
 
 namespace {
 
-constexpr int kRows = 128;     // q-tile rows = UMMA M
+constexpr int kRows = 128;     // rows of one half = UMMA M
 constexpr int kD = 128;        // head size
 constexpr int kDx = 16;        // extra dims / extra V^T rows that carry the zero-point terms
 constexpr int kKv = 64;        // context tokens per KV tile = UMMA N of Q.K^T
 constexpr int kNo = kD + kDx;  // UMMA N of P.V
-constexpr int kTmemCols = 256; // S: columns [0, 64), O: columns [64, 208)
+constexpr int kTmemCols = 512; // S_A [0,64) S_B [64,128) O_A [128,272) O_B [272,416)
+constexpr int kStages = 2;
 constexpr float kLazy = 4.f;   // log2 of the growth of a row maximum that forces a rescale of O
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLn2P = 0.6931471805599453f;
+
+constexpr int kSoftmaxWarps = 8, kConvWarps = 4;
+constexpr int kWarpMma = kSoftmaxWarps + kConvWarps, kWarpLoad = kWarpMma + 1;
+constexpr int kThreads = (kWarpLoad + 1) * 32;
+static_assert(kPrefillItemRows == 2 * kRows, "an item is two UMMA row tiles");
 
 template <int BS>
 struct PrefillSmem {
     static constexpr int REC = BS * (kD + 8);
     static constexpr int NREC = kKv / BS;
     static constexpr int RSTRIDE = REC + 64;       // records 64 bytes out of phase: conflict-free 16-byte reads across records
-    alignas(1024) uint8_t q[kRows * kD * 2];       // 2 swizzle atoms of [128 rows][64 dims]
-    alignas(1024) uint8_t k[kKv * kD * 2];         // 2 atoms of [64 tokens][64 dims]
-    alignas(1024) uint8_t vt[kNo * kKv * 2];       // [144 dims][64 tokens], 18 groups of 8 rows
-    alignas(1024) uint8_t p[kRows * kKv * 2];      // 1 atom of [128 rows][64 tokens]
-    alignas(128) uint8_t qx[kRows * kDx * 2];      // unswizzled [128 rows][16 dims]
-    alignas(128) uint8_t kx[kKv * kDx * 2];        // unswizzled [64 tokens][16 dims]
-    alignas(128) uint8_t raw_k[NREC * RSTRIDE];    // staged key records
-    alignas(128) uint8_t raw_v[NREC * RSTRIDE];    // staged value records
-    alignas(16) uint2 v_tab[kRows / 32][kKv / 2];  // per warp: (scale, -1024 * scale) as f16 pairs of two tokens
-    alignas(8) uint64_t bar_raw;
-    alignas(8) uint64_t bar_s;
-    alignas(8) uint64_t bar_o;
+    alignas(1024) uint8_t q[2][kRows * kD * 2];    // per half: 2 swizzle atoms of [128 rows][64 dims]
+    alignas(1024) uint8_t k[kStages][kKv * kD * 2];   // 2 atoms of [64 tokens][64 dims]
+    alignas(1024) uint8_t vt[kStages][kNo * kKv * 2]; // [144 dims][64 tokens], 18 groups of 8 rows
+    alignas(1024) uint8_t p[2][kRows * kKv * 2];   // per half: 1 atom of [128 rows][64 tokens]
+    alignas(128) uint8_t qx[2][kRows * kDx * 2];   // unswizzled [128 rows][16 dims]
+    alignas(128) uint8_t kx[kStages][kKv * kDx * 2];  // unswizzled [64 tokens][16 dims]
+    alignas(128) uint8_t raw_k[kStages][NREC * RSTRIDE];
+    alignas(128) uint8_t raw_v[kStages][NREC * RSTRIDE];
+    alignas(16) uint2 v_tab[kConvWarps][kKv / 2];  // per converter warp: (scale, -1024 * scale) f16 pairs of two tokens
+    alignas(8) uint64_t raw_full[kStages];   // loader -> converter (transaction bytes)
+    alignas(8) uint64_t raw_free[kStages];   // converter -> loader
+    alignas(8) uint64_t k_full[kStages];     // converter -> mma
+    alignas(8) uint64_t v_full[kStages];
+    alignas(8) uint64_t k_free[kStages];     // mma (commit) -> converter
+    alignas(8) uint64_t v_free[kStages];
+    alignas(8) uint64_t q_full[2];           // softmax -> mma, per item
+    alignas(8) uint64_t s_full[2];           // mma (commit) -> softmax
+    alignas(8) uint64_t s_free[2];           // softmax -> mma: S is in registers
+    alignas(8) uint64_t p_full[2];           // softmax -> mma: P written, O rescaled
+    alignas(8) uint64_t o_done[2];           // mma (commit) -> softmax: P.V complete
     uint32_t tmem_base;
+    volatile int abort;
 };
 
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
@@ -69,24 +87,14 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float y;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
-    return y;
-}
-// z = h + m + l up to 2^-33 |z|, every piece an f16
-__device__ __forceinline__ void split3(float z, __half& h, __half& m, __half& l) {
-    h = __float2half_rn(z);
-    const float r = z - __half2float(h);
-    m = __float2half_rn(r);
-    l = __float2half_rn(r - __half2float(m));
-}
-__device__ __forceinline__ uint32_t h2_bits(__half a, __half b) {
-    return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
-}
 __device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
     uint32_t y;
     asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
     return y;
 }
 __device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, uint32_t b, uint32_t c) {
@@ -103,6 +111,16 @@ __device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
     uint32_t y;
     asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
     return y;
+}
+// z = h + m + l up to 2^-33 |z|, every piece an f16
+__device__ __forceinline__ void split3(float z, __half& h, __half& m, __half& l) {
+    h = __float2half_rn(z);
+    const float r = z - __half2float(h);
+    m = __float2half_rn(r);
+    l = __float2half_rn(r - __half2float(m));
+}
+__device__ __forceinline__ uint32_t h2_bits(__half a, __half b) {
+    return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
 }
 // 16 cache bytes -> 16 f16 values 1024 + byte
 __device__ __forceinline__ void bytes16_to_h(const uint4 w, uint4& lo4, uint4& hi4) {
@@ -127,193 +145,324 @@ __device__ __forceinline__ void scale16(uint4& lo4, uint4& hi4, __half sc) {
     }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One work item as every role sees it.
+struct Item {
+    int s, hk, t0, n_new, past;
+    int row0;            // first (token, head) pair of half A
+    int ctx_hi[2];       // context the last row of each half sees (0: the half has no rows)
+    int nt[2];           // 64-token tiles of each half
+    int ntiles;          // max of the two
+    const int32_t* table;
+};
+
+__device__ __forceinline__ Item locate_item(const KernelArgs& a, int item, int G, int Hkv) {
+    Item it;
+    const int gq = item / Hkv;
+    it.hk = item % Hkv;
+    int lo = 0, hi = a.num_sequences;  // ptile_prefix[lo] <= gq < ptile_prefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldcg(a.ptile_prefix + mid) <= gq) lo = mid; else hi = mid;
+    }
+    it.s = lo;
+    const int p0 = __ldcg(a.ptile_prefix + lo), np = __ldcg(a.ptile_prefix + lo + 1) - p0;
+    const int qt = np - 1 - (gq - p0);           // heavy (late) tiles first
+    it.t0 = a.subsequence_begins[lo];
+    it.n_new = a.subsequence_begins[lo + 1] - it.t0;
+    it.past = a.past_lens[lo];
+    it.table = a.block_indices + a.block_indices_begins[lo];
+    it.row0 = qt * kPrefillItemRows;
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int r0 = it.row0 + x * kRows;
+        if (r0 < it.n_new * G) {
+            const int tok_hi = min(it.n_new - 1, (r0 + kRows - 1) / G);
+            it.ctx_hi[x] = it.past + tok_hi + 1;
+            it.nt[x] = (it.ctx_hi[x] + kKv - 1) / kKv;
+        } else {
+            it.ctx_hi[x] = 0;
+            it.nt[x] = 0;
+        }
+    }
+    it.ntiles = max(it.nt[0], it.nt[1]);
+    return it;
+}
+
 template <int BS>
-__global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     using Smem = PrefillSmem<BS>;
     extern __shared__ uint8_t smem_raw_[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw_) + 1023) & ~uintptr_t(1023));
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.g.Hq / a.g.Hkv;
     const int Hkv = a.g.Hkv;
     const int total_items = a.plan->total_ptiles * Hkv;
     const float qscale = (a.scale != 0.f ? a.scale : rsqrtf((float)kD)) * kLog2eP;
 
     if (tid == 0) {
-        mbar_init(&sm.bar_raw, 1);
-        mbar_init(&sm.bar_s, 1);
-        mbar_init(&sm.bar_o, 1);
+#pragma unroll
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&sm.raw_full[i], 1);
+            mbar_init(&sm.raw_free[i], kConvWarps * 32);
+            mbar_init(&sm.k_full[i], kConvWarps * 32);
+            mbar_init(&sm.v_full[i], kConvWarps * 32);
+            mbar_init(&sm.k_free[i], 1);
+            mbar_init(&sm.v_free[i], 1);
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(&sm.q_full[x], kRows);
+            mbar_init(&sm.s_full[x], 1);
+            mbar_init(&sm.s_free[x], kRows);
+            mbar_init(&sm.p_full[x], kRows);
+            mbar_init(&sm.o_done[x], 1);
+        }
         mbar_fence_init();
+        sm.abort = 0;
     }
-    // rows 132..143 of V^T stay zero for the whole kernel
-    if (tid < (kNo - kD - 4) * 8) *reinterpret_cast<uint4*>(sm.vt + (kD + 4) * 128 + tid * 16) = make_uint4(0, 0, 0, 0);
+    // rows 132..143 of V'^T stay zero for the whole kernel
+    if (tid < kStages * (kNo - kD - 4) * 8) {
+        const int st = tid / ((kNo - kD - 4) * 8), i = tid % ((kNo - kD - 4) * 8);
+        *reinterpret_cast<uint4*>(sm.vt[st] + (kD + 4) * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+    }
     if (warp == 0) tc05::tmem_alloc(&sm.tmem_base, kTmemCols);
+    tc05::fence_proxy_async_smem();
     tc05::fence_before_thread_sync();
     __syncthreads();
     tc05::fence_after_thread_sync();
     const uint32_t tmem = sm.tmem_base;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + kKv;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;   // this warp's TMEM lanes
 
-    constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
-    constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kNo, 0, 0, 0);
-    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), vt_addr = smem_u32(sm.vt), p_addr = smem_u32(sm.p);
-    const uint32_t qx_addr = smem_u32(sm.qx), kx_addr = smem_u32(sm.kx);
-
-    uint32_t phase_raw = 0, phase_s = 0, phase_o = 0;
-    bool bad_index = false;
-    bool failed = false;
-
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-        // ---- which q tile -------------------------------------------------------------------------
-        const int gq = item / Hkv, hk = item % Hkv;
-        int lo = 0, hi = a.num_sequences;  // ptile_prefix[lo] <= gq < ptile_prefix[hi]
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (__ldcg(a.ptile_prefix + mid) <= gq) lo = mid; else hi = mid;
+    // A wait that runs out raises sm.abort; every waiter polls the flag, so all roles unwind.
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+            if ((i & 255u) == 255u && sm.abort) return false;
         }
-        const int s = lo;
-        const int p0 = __ldcg(a.ptile_prefix + s), ntile_s = __ldcg(a.ptile_prefix + s + 1) - p0;
-        const int qt = ntile_s - 1 - (gq - p0);           // heavy (late) tiles first
-        const int t0 = a.subsequence_begins[s];
-        const int n_new = a.subsequence_begins[s + 1] - t0;
-        const int past = a.past_lens[s];
-        const int32_t* table = a.block_indices + a.block_indices_begins[s];
+        sm.abort = 1;
+        atomicOr(a.status, 0x40000000u);
+        return false;
+    };
 
-        // ---- this thread's row ---------------------------------------------------------------------
-        const int flat = qt * kRows + tid;
-        const int tok = flat / G, hq = hk * G + flat % G;
-        const bool row_live = tok < n_new;
-        const int tok_hi = min(n_new - 1, (qt * kRows + kRows - 1) / G);
-        const int ctx_hi = past + tok_hi + 1;             // context the last row of the tile sees
-        const int ntiles = (ctx_hi + kKv - 1) / kKv;
-        const int my_ctx = row_live ? past + tok + 1 : ctx_hi;
+    auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)) != 0; };
 
-        auto issue_raw = [&](int j) {   // thread 0: TMA-engine copies of tile j's records
-            uint32_t bytes = 0;
-            int blocks[Smem::NREC];
-#pragma unroll
-            for (int r = 0; r < Smem::NREC; ++r) {
-                const int bi = j * Smem::NREC + r;
-                int blk = -1;
-                if (bi * BS < ctx_hi) {
-                    blk = table[bi];
-                    if (blk < 0 || blk >= a.num_blocks) { blk = 0; bad_index = true; }
-                    bytes += 2 * Smem::REC;
-                }
-                blocks[r] = blk;
-            }
-            mbar_expect_tx(&sm.bar_raw, bytes);
-            const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)hk * a.g.head_bytes;
-            const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)hk * a.g.head_bytes;
-#pragma unroll
-            for (int r = 0; r < Smem::NREC; ++r)
-                if (blocks[r] >= 0) {
-                    bulk_g2s(sm.raw_k + r * Smem::RSTRIDE, kc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
-                    bulk_g2s(sm.raw_v + r * Smem::RSTRIDE, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.bar_raw);
-                }
-        };
-        // every tensor-core read of the previous item has completed (its waits sit in program order
-        // before this point) and every thread has finished reading the raw buffers
-        if (tid == 0) issue_raw(0);
+    if (warp < kSoftmaxWarps) {
+        // ======================= softmax + epilogue of half X ==========================================
+        const int X = warp >> 2, r = tid & (kRows - 1);
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // this warp's TMEM lanes
+        const uint32_t tmem_s = tmem + kKv * X + lane_base, tmem_o = tmem + 2 * kKv + kNo * X + lane_base;
+        uint8_t* const sq = sm.q[X];
+        uint8_t* const sp = sm.p[X];
+        uint32_t n = 0;   // tiles of this half so far, over all items
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            const Item it = locate_item(a, item, G, Hkv);
+            if (it.nt[X] == 0) continue;
+            const int flat = it.row0 + X * kRows + r;
+            const int tok = flat / G, hq = it.hk * G + flat % G;
+            const bool row_live = tok < it.n_new;
+            const int my_ctx = row_live ? it.past + tok + 1 : it.ctx_hi[X];
+            const long long grow_off = ((long long)(it.t0 + (row_live ? tok : 0)) * a.g.Hq + hq);
 
-        // ---- Q -> f16 swizzled A operand; the row's sum goes into the extra dims ------------------
-        {
-            const long long qoff = ((long long)(t0 + (row_live ? tok : 0)) * a.g.Hq + hq) * kD;
-            float qsum = 0.f;
+            // ---- Q -> f16 swizzled A operand; the row's sum goes into the extra dims.  Every S of this
+            // half's previous item has completed, so the tile is free. ------------------------------
+            {
+                float qsum = 0.f;
 #pragma unroll 4
-            for (int c = 0; c < kD / 8; ++c) {
-                float v[8];
+                for (int c = 0; c < kD / 8; ++c) {
+                    float v[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = 0.f;
-                if (row_live) load_act_vec<8>(a.query, qoff + 8 * c, a.g.act, v);
-                uint4 w;
-                w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
-                const __half2* h = reinterpret_cast<const __half2*>(&w);
+                    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+                    if (row_live) load_act_vec<8>(a.query, grow_off * kD + 8 * c, a.g.act, v);
+                    uint4 w;
+                    w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
+                    const __half2* h = reinterpret_cast<const __half2*>(&w);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
-                *reinterpret_cast<uint4*>(sm.q + (c / 8) * (kRows * 128) + sw128(tid, c % 8)) = w;
+                    for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
+                    *reinterpret_cast<uint4*>(sq + (c / 8) * (kRows * 128) + sw128(r, c % 8)) = w;
+                }
+                // |q| is assumed to stay inside the f16 range (no power-of-two prescale here)
+                const __half qh = __float2half_rn(qsum), ql = __float2half_rn(qsum - __half2float(qh));
+                const __half zero = __ushort_as_half(0);
+                *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
+                *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                tc05::fence_proxy_async_smem();
+                mbar_arrive(&sm.q_full[X]);
             }
-            // |q| is assumed to stay inside the f16 range (no power-of-two prescale here)
-            const __half qh = __float2half_rn(qsum), ql = __float2half_rn(qsum - __half2float(qh));
-            const __half zero = __ushort_as_half(0);
-            *reinterpret_cast<uint4*>(sm.qx + plain16(tid, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
-            *reinterpret_cast<uint4*>(sm.qx + plain16(tid, 1)) = make_uint4(0u, 0u, 0u, 0u);
+
+            float m_run = -INFINITY;   // running maximum of q.k' (before the softmax scale)
+            for (int j = 0; j < it.nt[X]; ++j, ++n) {
+                const int col0 = j * kKv;
+                if (!wait_warp(&sm.s_full[X], n & 1)) goto done;
+                tc05::fence_after_thread_sync();
+                float sv[kKv];   // q.k' in units of 1 / qscale
+                {
+                    uint32_t s0[32], s1[32];
+                    tc05::ld_32x32b_x32(tmem_s, s0);
+                    tc05::ld_32x32b_x32(tmem_s + 32, s1);
+                    tc05::wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) { sv[c] = __uint_as_float(s0[c]); sv[32 + c] = __uint_as_float(s1[c]); }
+                }
+                tc05::fence_before_thread_sync();
+                mbar_arrive(&sm.s_free[X]);    // the next S of this half may overwrite TMEM
+                if (col0 + kKv > my_ctx) {     // diagonal tile: hide what this row cannot see
+                    const int nvis = my_ctx - col0;   // may be <= 0
+#pragma unroll
+                    for (int c = 0; c < kKv; ++c) sv[c] = c < nvis ? sv[c] : -INFINITY;
+                }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < kKv; c += 2) mx = max3(mx, sv[c], sv[c + 1]);
+                float alpha = 1.f;
+                bool rescale = false;
+                if (j == 0) {
+                    m_run = mx;      // finite: column 0 of tile 0 is visible to every row
+                } else {
+                    const bool grow = (mx - m_run) * qscale > kLazy;
+                    rescale = __any_sync(0xffffffffu, grow);
+                    if (grow) { alpha = ex2((m_run - mx) * qscale); m_run = mx; }
+                }
+                // P = 2^(qscale * (s - m)) in f16 pairs: the exponent is rounded to f16 first, which costs
+                // at most 2^-12 of the exponent's magnitude in relative error of p
+                const float mq = m_run * qscale;
+                uint32_t pw[kKv / 2];
+#pragma unroll
+                for (int c = 0; c < kKv; c += 2) pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
+                // P.V of the previous tile of this half still reads the P tile and writes O
+                if (n > 0) {
+                    if (!wait_warp(&sm.o_done[X], (n - 1) & 1)) goto done;
+                    tc05::fence_after_thread_sync();
+                }
+                if (rescale) {
+#pragma unroll
+                    for (int q4 = 0; q4 < kD / 32; ++q4) {
+                        uint32_t t[32];
+                        tc05::ld_32x32b_x32(tmem_o + 32 * q4, t);
+                        tc05::wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) t[c] = __float_as_uint(__uint_as_float(t[c]) * alpha);
+                        tc05::st_32x32b_x32(tmem_o + 32 * q4, t);
+                    }
+                    uint32_t t[16];
+                    tc05::ld_32x32b_x16(tmem_o + kD, t);
+                    tc05::wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) t[c] = __float_as_uint(__uint_as_float(t[c]) * alpha);
+                    tc05::st_32x32b_x16(tmem_o + kD, t);
+                    tc05::wait_st();
+                }
+#pragma unroll
+                for (int c = 0; c < kKv / 8; ++c)
+                    *reinterpret_cast<uint4*>(sp + sw128(r, c)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
+                tc05::fence_proxy_async_smem();
+                tc05::fence_before_thread_sync();
+                mbar_arrive(&sm.p_full[X]);
+            }
+            // ---- epilogue: out = (O - z) / l; z = the three zero-point columns, l = the all-ones column
+            if (!wait_warp(&sm.o_done[X], (n - 1) & 1)) goto done;
+            tc05::fence_after_thread_sync();
+            {
+                uint32_t zr[16];
+                tc05::ld_32x32b_x16(tmem_o + kD, zr);
+                tc05::wait_ld();
+                const float z = __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]);
+                const float l_run = __uint_as_float(zr[3]);
+                const float inv = 1.f / l_run;
+#pragma unroll
+                for (int q4 = 0; q4 < kD / 32; ++q4) {
+                    uint32_t t[32];
+                    tc05::ld_32x32b_x32(tmem_o + 32 * q4, t);
+                    tc05::wait_ld();
+                    if (row_live) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = (__uint_as_float(t[c + e]) - z) * inv;
+                            store_act_vec8(a.output, grow_off * kD + 32 * q4 + c, a.g.act, v);
+                        }
+                    }
+                }
+                if (row_live && a.lse) a.lse[grow_off] = (m_run * qscale + log2f(l_run)) * kLn2P;
+            }
+            tc05::fence_before_thread_sync();
         }
-
-        float m_run = -INFINITY;   // running maximum of q.k' (before the softmax scale)
-
-        // A wait that runs out sets `failed`; the flag is made uniform at the next block barrier so
-        // that every thread leaves the loop at the same place.
-        for (int j = 0; j < ntiles; ++j) {
-            const int col0 = j * kKv;
-            const int live_tokens = min(kKv, ctx_hi - col0);
-            // ---- 1-2. raw records -> f16 operand tiles -------------------------------------------
-            if (!mbar_wait_bounded(&sm.bar_raw, phase_raw)) failed = true;
-            phase_raw ^= 1;
-            if (!failed) {
-                // K' = byte * f16(k scale): unit u = 16 dims of one token.  S of the previous tile has completed.
+    } else if (warp < kWarpMma) {
+        // ======================= converter: raw records -> f16 operand tiles =============================
+        const int ctid = tid - kSoftmaxWarps * 32, cwarp = warp - kSoftmaxWarps;
+        uint32_t t = 0;   // tiles so far, over all items
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            const Item it = locate_item(a, item, G, Hkv);
+            const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
+            for (int j = 0; j < it.ntiles; ++j, ++t) {
+                const int st = t & 1;
+                const uint32_t use = t >> 1;
+                const int live_tokens = min(kKv, ctx_hi - j * kKv);
+                const uint8_t* raw_k = sm.raw_k[st];
+                const uint8_t* raw_v = sm.raw_v[st];
+                if (!wait_warp(&sm.raw_full[st], use & 1)) goto done;
+                if (use > 0 && !wait_warp(&sm.k_free[st], (use - 1) & 1)) goto done;
+                // K' = byte * f16(k scale): unit u = 16 dims of one token
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int u = tid + kRows * i;
+                    const int u = ctid + 128 * i;
                     const int token = u >> 3, seg = u & 7;
                     uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
                     if (token < live_tokens) {
-                        const uint8_t* rec = sm.raw_k + (token / BS) * Smem::RSTRIDE;
+                        const uint8_t* rec = raw_k + (token / BS) * Smem::RSTRIDE;
                         const __half ksh = __float2half_rn(*reinterpret_cast<const float*>(rec + BS * kD + 4 * (token % BS)));
                         bytes16_to_h(*reinterpret_cast<const uint4*>(rec + (token % BS) * kD + 16 * seg), lo4, hi4);
                         scale16(lo4, hi4, ksh);
                     }
-                    uint8_t* atom = sm.k + (seg >> 2) * (kKv * 128);
+                    uint8_t* atom = sm.k[st] + (seg >> 2) * (kKv * 128);
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg) & 7)) = lo4;
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg + 1) & 7)) = hi4;
                 }
-                if (tid < kKv) {
-                    const int token = tid;
+                if (ctid < kKv) {
+                    const int token = ctid;
                     const bool ok = token < live_tokens;
-                    const float* kp = reinterpret_cast<const float*>(sm.raw_k + (token / BS) * Smem::RSTRIDE + BS * kD);
+                    const float* kp = reinterpret_cast<const float*>(raw_k + (token / BS) * Smem::RSTRIDE + BS * kD);
                     const float ksf = __half2float(__float2half_rn(kp[token % BS]));
                     __half zh, zm, zl;
                     split3(ok ? -(ksf * kp[BS + token % BS]) : 0.f, zh, zm, zl);
                     const __half zero = __ushort_as_half(0);
-                    *reinterpret_cast<uint4*>(sm.kx + plain16(token, 0)) = make_uint4(h2_bits(zh, zm), h2_bits(zl, zh), h2_bits(zm, zero), 0u);
-                    *reinterpret_cast<uint4*>(sm.kx + plain16(token, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(sm.kx[st] + plain16(token, 0)) = make_uint4(h2_bits(zh, zm), h2_bits(zl, zh), h2_bits(zm, zero), 0u);
+                    *reinterpret_cast<uint4*>(sm.kx[st] + plain16(token, 1)) = make_uint4(0u, 0u, 0u, 0u);
                 }
-            }
-            if (j > 0) {   // P.V of the previous tile still reads V^T and P
-                if (!failed && !mbar_wait_bounded(&sm.bar_o, phase_o)) failed = true;
-                phase_o ^= 1;
-                tc05::fence_after_thread_sync();
-            }
-            failed = __any_sync(0xffffffffu, failed);
-            if (!failed) {
+                tc05::fence_proxy_async_smem();
+                mbar_arrive(&sm.k_full[st]);
+
+                if (use > 0 && !wait_warp(&sm.v_free[st], (use - 1) & 1)) goto done;
                 // this warp's table of (scale, -1024 * scale) for the tile's token pairs
-                const int lane = tid & 31;
                 __syncwarp();
                 float vs0 = 0.f, vs1 = 0.f;
                 {
                     const int t0k = 2 * lane, t1k = 2 * lane + 1;
-                    if (t0k < live_tokens) vs0 = *reinterpret_cast<const float*>(sm.raw_v + (t0k / BS) * Smem::RSTRIDE + BS * kD + 4 * (t0k % BS));
-                    if (t1k < live_tokens) vs1 = *reinterpret_cast<const float*>(sm.raw_v + (t1k / BS) * Smem::RSTRIDE + BS * kD + 4 * (t1k % BS));
+                    if (t0k < live_tokens) vs0 = *reinterpret_cast<const float*>(raw_v + (t0k / BS) * Smem::RSTRIDE + BS * kD + 4 * (t0k % BS));
+                    if (t1k < live_tokens) vs1 = *reinterpret_cast<const float*>(raw_v + (t1k / BS) * Smem::RSTRIDE + BS * kD + 4 * (t1k % BS));
                 }
                 const uint32_t s2 = pack_h2(vs0, vs1);
-                sm.v_tab[warp][lane] = make_uint2(s2, hmul2_bits(s2, 0xE400E400u));
+                sm.v_tab[cwarp][lane] = make_uint2(s2, hmul2_bits(s2, 0xE400E400u));
                 const bool big = __any_sync(0xffffffffu, !(fabsf(vs0) < 32.f) || !(fabsf(vs1) < 32.f));
                 __syncwarp();
                 // V'^T = byte * f16(v scale): unit = 16 tokens of one dim
-                const int tg = tid & 3;
+                const int tg = ctid & 3;
                 uint2 tab[8];
 #pragma unroll
                 for (int k = 0; k < 8; k += 2) {
-                    const uint4 t4 = *reinterpret_cast<const uint4*>(&sm.v_tab[warp][8 * tg + k]);
+                    const uint4 t4 = *reinterpret_cast<const uint4*>(&sm.v_tab[cwarp][8 * tg + k]);
                     tab[k] = make_uint2(t4.x, t4.y);
                     tab[k + 1] = make_uint2(t4.z, t4.w);
                 }
                 constexpr int UPR = BS / 16;   // 16-token units per record
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int d = (tid >> 2) + 32 * i;
+                    const int d = (ctid >> 2) + 32 * i;
                     uint4 lo4, hi4;
-                    bytes16_to_h(*reinterpret_cast<const uint4*>(sm.raw_v + (tg / UPR) * Smem::RSTRIDE + d * BS + 16 * (tg % UPR)), lo4, hi4);
+                    bytes16_to_h(*reinterpret_cast<const uint4*>(raw_v + (tg / UPR) * Smem::RSTRIDE + d * BS + 16 * (tg % UPR)), lo4, hi4);
                     uint32_t w[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
                     if (!big) {
 #pragma unroll
@@ -322,156 +471,145 @@ __global__ void __launch_bounds__(kRows, 2) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
                         for (int k = 0; k < 8; ++k) w[k] = hmul2_bits(hadd2_bits(w[k], 0xE400E400u), tab[k].x);
                     }
-                    *reinterpret_cast<uint4*>(sm.vt + sw128(d, 2 * tg)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(sm.vt + sw128(d, 2 * tg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
+                    *reinterpret_cast<uint4*>(sm.vt[st] + sw128(d, 2 * tg)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(sm.vt[st] + sw128(d, 2 * tg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
-                if (tid < kKv) {
-                    const int token = tid;
+                if (ctid < kKv) {
+                    const int token = ctid;
                     const bool ok = token < live_tokens;
-                    const float* vp = reinterpret_cast<const float*>(sm.raw_v + (token / BS) * Smem::RSTRIDE + BS * kD);
+                    const float* vp = reinterpret_cast<const float*>(raw_v + (token / BS) * Smem::RSTRIDE + BS * kD);
                     const float vsf = __half2float(__float2half_rn(vp[token % BS]));
                     __half zh, zm, zl;
                     split3(ok ? vsf * vp[BS + token % BS] : 0.f, zh, zm, zl);
                     const uint32_t off = (token & 7) * 2;
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 0, token >> 3) + off) = zh;
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 1, token >> 3) + off) = zm;
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 2, token >> 3) + off) = zl;
-                    *reinterpret_cast<__half*>(sm.vt + sw128(kD + 3, token >> 3) + off) = __float2half_rn(ok ? 1.f : 0.f);
+                    uint8_t* vt = sm.vt[st];
+                    *reinterpret_cast<__half*>(vt + sw128(kD + 0, token >> 3) + off) = zh;
+                    *reinterpret_cast<__half*>(vt + sw128(kD + 1, token >> 3) + off) = zm;
+                    *reinterpret_cast<__half*>(vt + sw128(kD + 2, token >> 3) + off) = zl;
+                    *reinterpret_cast<__half*>(vt + sw128(kD + 3, token >> 3) + off) = __float2half_rn(ok ? 1.f : 0.f);
                 }
+                tc05::fence_proxy_async_smem();
+                mbar_arrive(&sm.v_full[st]);
+                mbar_arrive(&sm.raw_free[st]);
             }
-            tc05::fence_proxy_async_smem();
-            tc05::fence_before_thread_sync();
-            failed = __syncthreads_or(failed ? 1 : 0) != 0;
-            if (failed) break;
-            // ---- 3. S = Q.K^T ------------------------------------------------------------------------
-            if (tid == 0) {
-                tc05::fence_after_thread_sync();
-                if (j + 1 < ntiles) issue_raw(j + 1);   // the raw buffers are free again
+        }
+    } else if (warp == kWarpMma) {
+        // ======================= mma issue ================================================================
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
+            constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kNo, 0, 0, 0);
+            auto issue_s = [&](int X, int st) {
+                const uint32_t q_addr = smem_u32(sm.q[X]), k_addr = smem_u32(sm.k[st]);
+                const uint32_t d = tmem + kKv * X;
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint64_t da = tc05::smem_desc_sw128(q_addr + (kk >> 2) * (kRows * 128) + (kk & 3) * 32, 1024);
                     const uint64_t db = tc05::smem_desc_sw128(k_addr + (kk >> 2) * (kKv * 128) + (kk & 3) * 32, 1024);
-                    tc05::mma_ss(tmem_s, da, db, idesc_s, kk > 0 ? 1u : 0u);
+                    tc05::mma_ss(d, da, db, idesc_s, kk > 0 ? 1u : 0u);
                 }
-                tc05::mma_ss(tmem_s, tc05::smem_desc_plain(qx_addr, 128, 256), tc05::smem_desc_plain(kx_addr, 128, 256), idesc_s, 1u);
-                tc05::commit(&sm.bar_s);
-            }
-            if (!mbar_wait_bounded(&sm.bar_s, phase_s)) failed = true;
-            phase_s ^= 1;
-            failed = __any_sync(0xffffffffu, failed);   // the TMEM accesses below are warp-collective
-            tc05::fence_after_thread_sync();
-
-            // ---- 4. softmax of this thread's row ------------------------------------------------------
-            if (!failed) {
-                float sv[kKv];   // q.k' in units of 1 / qscale
-                {
-                    uint32_t s0[32], s1[32];
-                    tc05::ld_32x32b_x32(tmem_s + lane_base, s0);
-                    tc05::ld_32x32b_x32(tmem_s + lane_base + 32, s1);
-                    tc05::wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) { sv[c] = __uint_as_float(s0[c]); sv[32 + c] = __uint_as_float(s1[c]); }
-                }
-                if (col0 + kKv > my_ctx) {   // diagonal tile: hide what this row cannot see
-                    const int nvis = my_ctx - col0;   // may be <= 0
-#pragma unroll
-                    for (int c = 0; c < kKv; ++c) sv[c] = c < nvis ? sv[c] : -INFINITY;
-                }
-                float mx = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < kKv; c += 2) mx = max3(mx, sv[c], sv[c + 1]);
-                if (j == 0) {
-                    m_run = mx;      // finite: column 0 of tile 0 is visible to every row
-                } else {
-                    const bool grow = (mx - m_run) * qscale > kLazy;
-                    if (__any_sync(0xffffffffu, grow)) {
-                        // rescale this warp's rows of O in TMEM; P.V of the previous tile has completed
-                        const float alpha = grow ? ex2((m_run - mx) * qscale) : 1.f;
-                        if (grow) m_run = mx;
-#pragma unroll
-                        for (int q4 = 0; q4 < kD / 32; ++q4) {
-                            uint32_t r[32];
-                            tc05::ld_32x32b_x32(tmem_o + lane_base + 32 * q4, r);
-                            tc05::wait_ld();
-#pragma unroll
-                            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                            tc05::st_32x32b_x32(tmem_o + lane_base + 32 * q4, r);
-                        }
-                        uint32_t r[16];
-                        tc05::ld_32x32b_x16(tmem_o + lane_base + kD, r);
-                        tc05::wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                        tc05::st_32x32b_x16(tmem_o + lane_base + kD, r);
-                        tc05::wait_st();
-                    }
-                }
-                // P = 2^(qscale * (s - m)) in f16 pairs: the exponent is rounded to f16 first, which costs
-                // at most 2^-12 of the exponent's magnitude in relative error of p
-                const float mq = m_run * qscale;
-#pragma unroll
-                for (int c = 0; c < kKv; c += 8) {
-                    uint4 w;
-                    w.x = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
-                    w.y = ex2_h2(pack_h2(fmaf(sv[c + 2], qscale, -mq), fmaf(sv[c + 3], qscale, -mq)));
-                    w.z = ex2_h2(pack_h2(fmaf(sv[c + 4], qscale, -mq), fmaf(sv[c + 5], qscale, -mq)));
-                    w.w = ex2_h2(pack_h2(fmaf(sv[c + 6], qscale, -mq), fmaf(sv[c + 7], qscale, -mq)));
-                    *reinterpret_cast<uint4*>(sm.p + sw128(tid, c >> 3)) = w;
-                }
-            }
-            tc05::fence_proxy_async_smem();
-            tc05::fence_before_thread_sync();
-            failed = __syncthreads_or(failed ? 1 : 0) != 0;
-            if (failed) break;
-            // ---- 5. O += P'.V; overlaps the next tile's key conversion -----------------------------------
-            if (tid == 0) {
-                tc05::fence_after_thread_sync();
+                tc05::mma_ss(d, tc05::smem_desc_plain(smem_u32(sm.qx[X]), 128, 256), tc05::smem_desc_plain(smem_u32(sm.kx[st]), 128, 256), idesc_s, 1u);
+                tc05::commit(&sm.s_full[X]);
+            };
+            auto issue_pv = [&](int X, int st, bool acc) {
+                const uint32_t p_addr = smem_u32(sm.p[X]), vt_addr = smem_u32(sm.vt[st]);
+                const uint32_t d = tmem + 2 * kKv + kNo * X;
 #pragma unroll
                 for (int kk = 0; kk < kKv / 16; ++kk) {
                     const uint64_t da = tc05::smem_desc_sw128(p_addr + kk * 32, 1024);
                     const uint64_t db = tc05::smem_desc_sw128(vt_addr + kk * 32, 1024);
-                    tc05::mma_ss(tmem_o, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                    tc05::mma_ss(d, da, db, idesc_o, (acc || kk > 0) ? 1u : 0u);
                 }
-                tc05::commit(&sm.bar_o);
-            }
-        }
-        if (!failed && !mbar_wait_bounded(&sm.bar_o, phase_o)) failed = true;
-        phase_o ^= 1;
-        tc05::fence_after_thread_sync();
-        failed = __syncthreads_or(failed ? 1 : 0) != 0;
-        if (failed) {
-            if (tid == 0) atomicOr(a.status, 0x40000000u);
-            break;
-        }
-        // ---- epilogue: out = (O - z) / l, z = the three zero-point columns ---------------------------
-        {
-            uint32_t zr[16];
-            tc05::ld_32x32b_x16(tmem_o + lane_base + kD, zr);
-            tc05::wait_ld();
-            const float z = __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]);
-            const float l_run = __uint_as_float(zr[3]);   // the all-ones row of V^T sums the probabilities
-            const float inv = 1.f / l_run;
-            const long long ooff = ((long long)(t0 + (row_live ? tok : 0)) * a.g.Hq + hq) * kD;
+                tc05::commit(&sm.o_done[X]);
+            };
+            uint32_t t = 0, n[2] = {0, 0}, iq[2] = {0, 0};
+            for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+                const Item it = locate_item(a, item, G, Hkv);
+                // first S of the item
 #pragma unroll
-            for (int q4 = 0; q4 < kD / 32; ++q4) {
-                uint32_t r[32];
-                tc05::ld_32x32b_x32(tmem_o + lane_base + 32 * q4, r);
-                tc05::wait_ld();
-                if (row_live) {
-#pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        float v[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] = (__uint_as_float(r[c + e]) - z) * inv;
-                        store_act_vec8(a.output, ooff + 32 * q4 + c, a.g.act, v);
+                for (int X = 0; X < 2; ++X)
+                    if (it.nt[X] > 0) {
+                        if (!wait(&sm.q_full[X], iq[X] & 1)) goto done;
+                        ++iq[X];
                     }
+                if (!wait(&sm.k_full[t & 1], (t >> 1) & 1)) goto done;
+#pragma unroll
+                for (int X = 0; X < 2; ++X)
+                    if (it.nt[X] > 0) {
+                        if (n[X] > 0 && !wait(&sm.s_free[X], (n[X] - 1) & 1)) goto done;
+                        tc05::fence_after_thread_sync();
+                        issue_s(X, t & 1);
+                    }
+                tc05::commit(&sm.k_free[t & 1]);
+                for (int j = 0; j < it.ntiles; ++j, ++t) {
+                    const int st = t & 1;
+                    if (j + 1 < it.ntiles) {
+                        const int st1 = (t + 1) & 1;
+                        if (!wait(&sm.k_full[st1], ((t + 1) >> 1) & 1)) goto done;
+#pragma unroll
+                        for (int X = 0; X < 2; ++X)
+                            if (j + 1 < it.nt[X]) {
+                                if (!wait(&sm.s_free[X], (n[X] + j) & 1)) goto done;
+                                tc05::fence_after_thread_sync();
+                                issue_s(X, st1);
+                            }
+                        tc05::commit(&sm.k_free[st1]);
+                    }
+                    if (!wait(&sm.v_full[st], (t >> 1) & 1)) goto done;
+#pragma unroll
+                    for (int X = 0; X < 2; ++X)
+                        if (j < it.nt[X]) {
+                            if (!wait(&sm.p_full[X], (n[X] + j) & 1)) goto done;
+                            tc05::fence_after_thread_sync();
+                            issue_pv(X, st, j > 0);
+                        }
+                    tc05::commit(&sm.v_free[st]);
+                }
+                n[0] += it.nt[0];
+                n[1] += it.nt[1];
+            }
+            // every commit has landed before the CTA's shared memory is given up
+            if (t > 0) wait(&sm.v_free[(t - 1) & 1], ((t - 1) >> 1) & 1);
+        }
+    } else {
+        // ======================= loader: TMA-engine copies of the tiles' records =========================
+        if (lane == 0) {
+            uint32_t t = 0;
+            bool bad_index = false;
+            for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+                const Item it = locate_item(a, item, G, Hkv);
+                const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
+                const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes;
+                const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)it.hk * a.g.head_bytes;
+                for (int j = 0; j < it.ntiles; ++j, ++t) {
+                    const int st = t & 1;
+                    const uint32_t use = t >> 1;
+                    if (use > 0 && !wait(&sm.raw_free[st], (use - 1) & 1)) goto done;
+                    uint32_t bytes = 0;
+                    int blocks[Smem::NREC];
+#pragma unroll
+                    for (int r = 0; r < Smem::NREC; ++r) {
+                        const int bi = j * Smem::NREC + r;
+                        int blk = -1;
+                        if (bi * BS < ctx_hi) {
+                            blk = it.table[bi];
+                            if (blk < 0 || blk >= a.num_blocks) { blk = 0; bad_index = true; }
+                            bytes += 2 * Smem::REC;
+                        }
+                        blocks[r] = blk;
+                    }
+                    mbar_expect_tx(&sm.raw_full[st], bytes);
+#pragma unroll
+                    for (int r = 0; r < Smem::NREC; ++r)
+                        if (blocks[r] >= 0) {
+                            bulk_g2s(sm.raw_k[st] + r * Smem::RSTRIDE, kc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.raw_full[st]);
+                            bulk_g2s(sm.raw_v[st] + r * Smem::RSTRIDE, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.raw_full[st]);
+                        }
                 }
             }
-            if (row_live && a.lse) a.lse[(long long)(t0 + tok) * a.g.Hq + hq] = (m_run * qscale + log2f(l_run)) * kLn2P;
+            if (bad_index) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
         }
-        tc05::fence_before_thread_sync();
     }
-    if (__syncthreads_or(bad_index ? 1 : 0) && tid == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
+done:
     tc05::fence_before_thread_sync();
     __syncthreads();
     if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
@@ -485,18 +623,18 @@ bool prefill_tc_supported(const CacheGeom& g) {
 
 cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_count, long long max_items, int* launches) {
     if (max_items <= 0) return cudaSuccess;
-    const int grid = (int)std::min<long long>(max_items, 2LL * sm_count);
+    const int grid = (int)std::min<long long>(max_items, sm_count);
     cudaError_t e;
     if (a.g.bs == 32) {
         const int bytes = (int)sizeof(PrefillSmem<32>) + 1024;
         e = cudaFuncSetAttribute(prefill_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e != cudaSuccess) return e;
-        prefill_tc_kernel<32><<<grid, kRows, bytes, stream>>>(a);
+        prefill_tc_kernel<32><<<grid, kThreads, bytes, stream>>>(a);
     } else {
         const int bytes = (int)sizeof(PrefillSmem<16>) + 1024;
         e = cudaFuncSetAttribute(prefill_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e != cudaSuccess) return e;
-        prefill_tc_kernel<16><<<grid, kRows, bytes, stream>>>(a);
+        prefill_tc_kernel<16><<<grid, kThreads, bytes, stream>>>(a);
     }
     ++*launches;
     return cudaGetLastError();
