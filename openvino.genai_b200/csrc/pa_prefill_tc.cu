@@ -15,7 +15,7 @@
 //                          the S of the next tile is queued before the P.V of the current one;
 //   softmax   (2 x 4 warps) thread r owns row r of its half: reads S from TMEM, masks (diagonal
 //                          tiles only), keeps a lazy running maximum, writes P = 2^(scale*(s-m)) as
-//                          f16 into the A-operand tile; rescales O in TMEM only when a row maximum
+//                          f16 into TMEM (the A operand of P.V); rescales O in TMEM only when a row maximum
 //                          grew by more than 2^4; normalises and stores the output at the end.
 // The zero-points ride on the tensor core: Q and K' carry 16 extra dims holding the row's sum of q
 // and minus scale * zero-point split into f16 pieces, so S comes out with the offset term already
@@ -24,6 +24,7 @@
 // Every wait is bounded; a wait that runs out raises a flag that all roles poll.
 // Tensor-bound for long contexts: 4 * Hq * D flops per (new token, context token) pair.
 #include <algorithm>
+#include <cstdio>
 
 #include "pa_common.cuh"
 #include "pa_kernels.h"
@@ -38,7 +39,8 @@ constexpr int kD = 128;        // head size
 constexpr int kDx = 16;        // extra dims / extra V^T rows that carry the zero-point terms
 constexpr int kKv = 64;        // context tokens per KV tile = UMMA N of Q.K^T
 constexpr int kNo = kD + kDx;  // UMMA N of P.V
-constexpr int kTmemCols = 512; // S_A [0,64) S_B [64,128) O_A [128,272) O_B [272,416)
+constexpr int kTmemCols = 512; // S_A [0,64) S_B [64,128) O_A [128,272) O_B [272,416) P_A [416,448) P_B [448,480)
+constexpr int kTmemP = 2 * kKv + 2 * kNo;
 constexpr int kStages = 2;
 constexpr float kLazy = 4.f;   // log2 of the growth of a row maximum that forces a rescale of O
 constexpr float kLog2eP = 1.4426950408889634f;
@@ -57,7 +59,6 @@ struct PrefillSmem {
     alignas(1024) uint8_t q[2][kRows * kD * 2];    // per half: 2 swizzle atoms of [128 rows][64 dims]
     alignas(1024) uint8_t k[kStages][kKv * kD * 2];   // 2 atoms of [64 tokens][64 dims]
     alignas(1024) uint8_t vt[kStages][kNo * kKv * 2]; // [144 dims][64 tokens], 18 groups of 8 rows
-    alignas(1024) uint8_t p[2][kRows * kKv * 2];   // per half: 1 atom of [128 rows][64 tokens]
     alignas(128) uint8_t qx[2][kRows * kDx * 2];   // unswizzled [128 rows][16 dims]
     alignas(128) uint8_t kx[kStages][kKv * kDx * 2];  // unswizzled [64 tokens][16 dims]
     alignas(128) uint8_t raw_k[kStages][NREC * RSTRIDE];
@@ -148,6 +149,11 @@ __device__ __forceinline__ void scale16(uint4& lo4, uint4& hi4, __half sc) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for the whole warp, after every lane's preceding writes.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 
 // One work item as every role sees it.
 struct Item {
@@ -207,18 +213,18 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.raw_full[i], 1);
-            mbar_init(&sm.raw_free[i], kConvWarps * 32);
-            mbar_init(&sm.k_full[i], kConvWarps * 32);
-            mbar_init(&sm.v_full[i], kConvWarps * 32);
+            mbar_init(&sm.raw_free[i], kConvWarps);
+            mbar_init(&sm.k_full[i], kConvWarps);
+            mbar_init(&sm.v_full[i], kConvWarps);
             mbar_init(&sm.k_free[i], 1);
             mbar_init(&sm.v_free[i], 1);
         }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-            mbar_init(&sm.q_full[x], kRows);
+            mbar_init(&sm.q_full[x], kRows / 32);
             mbar_init(&sm.s_full[x], 1);
-            mbar_init(&sm.s_free[x], kRows);
-            mbar_init(&sm.p_full[x], kRows);
+            mbar_init(&sm.s_free[x], kRows / 32);
+            mbar_init(&sm.p_full[x], kRows / 32);
             mbar_init(&sm.o_done[x], 1);
         }
         mbar_fence_init();
@@ -237,17 +243,30 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     const uint32_t tmem = sm.tmem_base;
 
     // A wait that runs out raises sm.abort; every waiter polls the flag, so all roles unwind.
-    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    // `cat` names the wait for the optional cycle accounting (-DPA_PREFILL_PROF).
+#ifdef PA_PREFILL_PROF
+    long long prof[5] = {0, 0, 0, 0, 0};
+    const long long prof_begin = clock64();
+#endif
+    auto wait = [&](uint64_t* bar, uint32_t parity, int cat) -> bool {
+#ifdef PA_PREFILL_PROF
+        const long long w0 = clock64();
+#endif
+        bool ok = false;
         for (uint32_t i = 0; i < (1u << 22); ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait(bar, parity)) { ok = true; break; }
             if ((i & 255u) == 255u && sm.abort) return false;
         }
+#ifdef PA_PREFILL_PROF
+        prof[cat] += clock64() - w0;
+#endif
+        (void)cat;
+        if (ok) return true;
         sm.abort = 1;
         atomicOr(a.status, 0x40000000u);
         return false;
     };
-
-    auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)) != 0; };
+    auto wait_warp = [&](uint64_t* bar, uint32_t parity, int cat) -> bool { return __all_sync(0xffffffffu, wait(bar, parity, cat)) != 0; };
 
     if (warp < kSoftmaxWarps) {
         // ======================= softmax + epilogue of half X ==========================================
@@ -255,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // this warp's TMEM lanes
         const uint32_t tmem_s = tmem + kKv * X + lane_base, tmem_o = tmem + 2 * kKv + kNo * X + lane_base;
         uint8_t* const sq = sm.q[X];
-        uint8_t* const sp = sm.p[X];
+        const uint32_t tmem_p = tmem + kTmemP + (kKv / 2) * X + lane_base;
         uint32_t n = 0;   // tiles of this half so far, over all items
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
             const Item it = locate_item(a, item, G, Hkv);
@@ -289,13 +308,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
                 *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
                 tc05::fence_proxy_async_smem();
-                mbar_arrive(&sm.q_full[X]);
+                warp_arrive(&sm.q_full[X]);
             }
 
             float m_run = -INFINITY;   // running maximum of q.k' (before the softmax scale)
             for (int j = 0; j < it.nt[X]; ++j, ++n) {
                 const int col0 = j * kKv;
-                if (!wait_warp(&sm.s_full[X], n & 1)) goto done;
+                if (!wait_warp(&sm.s_full[X], n & 1, 0)) goto done;
                 tc05::fence_after_thread_sync();
                 float sv[kKv];   // q.k' in units of 1 / qscale
                 {
@@ -307,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     for (int c = 0; c < 32; ++c) { sv[c] = __uint_as_float(s0[c]); sv[32 + c] = __uint_as_float(s1[c]); }
                 }
                 tc05::fence_before_thread_sync();
-                mbar_arrive(&sm.s_free[X]);    // the next S of this half may overwrite TMEM
+                warp_arrive(&sm.s_free[X]);    // the next S of this half may overwrite TMEM
                 if (col0 + kKv > my_ctx) {     // diagonal tile: hide what this row cannot see
                     const int nvis = my_ctx - col0;   // may be <= 0
 #pragma unroll
@@ -333,7 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 for (int c = 0; c < kKv; c += 2) pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
                 // P.V of the previous tile of this half still reads the P tile and writes O
                 if (n > 0) {
-                    if (!wait_warp(&sm.o_done[X], (n - 1) & 1)) goto done;
+                    if (!wait_warp(&sm.o_done[X], (n - 1) & 1, 1)) goto done;
                     tc05::fence_after_thread_sync();
                 }
                 if (rescale) {
@@ -354,15 +373,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     tc05::st_32x32b_x16(tmem_o + kD, t);
                     tc05::wait_st();
                 }
-#pragma unroll
-                for (int c = 0; c < kKv / 8; ++c)
-                    *reinterpret_cast<uint4*>(sp + sw128(r, c)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
-                tc05::fence_proxy_async_smem();
+                tc05::st_32x32b_x32(tmem_p, pw);   // row r of the A operand: lane r, two tokens per column
+                tc05::wait_st();
                 tc05::fence_before_thread_sync();
-                mbar_arrive(&sm.p_full[X]);
+                warp_arrive(&sm.p_full[X]);
             }
             // ---- epilogue: out = (O - z) / l; z = the three zero-point columns, l = the all-ones column
-            if (!wait_warp(&sm.o_done[X], (n - 1) & 1)) goto done;
+            if (!wait_warp(&sm.o_done[X], (n - 1) & 1, 2)) goto done;
             tc05::fence_after_thread_sync();
             {
                 uint32_t zr[16];
@@ -403,8 +420,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 const int live_tokens = min(kKv, ctx_hi - j * kKv);
                 const uint8_t* raw_k = sm.raw_k[st];
                 const uint8_t* raw_v = sm.raw_v[st];
-                if (!wait_warp(&sm.raw_full[st], use & 1)) goto done;
-                if (use > 0 && !wait_warp(&sm.k_free[st], (use - 1) & 1)) goto done;
+                if (!wait_warp(&sm.raw_full[st], use & 1, 0)) goto done;
+                if (use > 0 && !wait_warp(&sm.k_free[st], (use - 1) & 1, 1)) goto done;
                 // K' = byte * f16(k scale): unit u = 16 dims of one token
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -433,9 +450,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     *reinterpret_cast<uint4*>(sm.kx[st] + plain16(token, 1)) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 tc05::fence_proxy_async_smem();
-                mbar_arrive(&sm.k_full[st]);
+                warp_arrive(&sm.k_full[st]);
 
-                if (use > 0 && !wait_warp(&sm.v_free[st], (use - 1) & 1)) goto done;
+                if (use > 0 && !wait_warp(&sm.v_free[st], (use - 1) & 1, 2)) goto done;
                 // this warp's table of (scale, -1024 * scale) for the tile's token pairs
                 __syncwarp();
                 float vs0 = 0.f, vs1 = 0.f;
@@ -489,8 +506,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     *reinterpret_cast<__half*>(vt + sw128(kD + 3, token >> 3) + off) = __float2half_rn(ok ? 1.f : 0.f);
                 }
                 tc05::fence_proxy_async_smem();
-                mbar_arrive(&sm.v_full[st]);
-                mbar_arrive(&sm.raw_free[st]);
+                warp_arrive(&sm.v_full[st]);
+                warp_arrive(&sm.raw_free[st]);
             }
         }
     } else if (warp == kWarpMma) {
@@ -498,27 +515,33 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
             constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kNo, 0, 0, 0);
+            // operand descriptors are built once; a step along K or to another buffer only moves the
+            // start-address field (bits [0,14) of the low word, in 16-byte units, no carry out of it)
+            const uint64_t dq = tc05::smem_desc_sw128(smem_u32(sm.q[0]), 1024), dk = tc05::smem_desc_sw128(smem_u32(sm.k[0]), 1024);
+            const uint64_t dv = tc05::smem_desc_sw128(smem_u32(sm.vt[0]), 1024);
+            const uint64_t dqx = tc05::smem_desc_plain(smem_u32(sm.qx[0]), 128, 256), dkx = tc05::smem_desc_plain(smem_u32(sm.kx[0]), 128, 256);
+            constexpr uint32_t q_step = sizeof(sm.q[0]) >> 4, k_step = sizeof(sm.k[0]) >> 4, v_step = sizeof(sm.vt[0]) >> 4;
+            constexpr uint32_t qx_step = sizeof(sm.qx[0]) >> 4, kx_step = sizeof(sm.kx[0]) >> 4;
             auto issue_s = [&](int X, int st) {
-                const uint32_t q_addr = smem_u32(sm.q[X]), k_addr = smem_u32(sm.k[st]);
+                const uint64_t da0 = dq + X * q_step, db0 = dk + st * k_step;
                 const uint32_t d = tmem + kKv * X;
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint64_t da = tc05::smem_desc_sw128(q_addr + (kk >> 2) * (kRows * 128) + (kk & 3) * 32, 1024);
-                    const uint64_t db = tc05::smem_desc_sw128(k_addr + (kk >> 2) * (kKv * 128) + (kk & 3) * 32, 1024);
-                    tc05::mma_ss(d, da, db, idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t a_off = ((kk >> 2) * (kRows * 128) + (kk & 3) * 32) >> 4, b_off = ((kk >> 2) * (kKv * 128) + (kk & 3) * 32) >> 4;
+                    if (kk == 0) tc05::mma_ss<0>(d, da0 + a_off, db0 + b_off, idesc_s);
+                    else tc05::mma_ss<1>(d, da0 + a_off, db0 + b_off, idesc_s);
                 }
-                tc05::mma_ss(d, tc05::smem_desc_plain(smem_u32(sm.qx[X]), 128, 256), tc05::smem_desc_plain(smem_u32(sm.kx[st]), 128, 256), idesc_s, 1u);
+                tc05::mma_ss<1>(d, dqx + X * qx_step, dkx + st * kx_step, idesc_s);
                 tc05::commit(&sm.s_full[X]);
             };
             auto issue_pv = [&](int X, int st, bool acc) {
-                const uint32_t p_addr = smem_u32(sm.p[X]), vt_addr = smem_u32(sm.vt[st]);
+                const uint32_t pa = tmem + kTmemP + (kKv / 2) * X;   // 16 tokens of P = 8 columns
+                const uint64_t db0 = dv + st * v_step;
                 const uint32_t d = tmem + 2 * kKv + kNo * X;
+                if (acc) tc05::mma_ts<1>(d, pa, db0, idesc_o);
+                else tc05::mma_ts<0>(d, pa, db0, idesc_o);
 #pragma unroll
-                for (int kk = 0; kk < kKv / 16; ++kk) {
-                    const uint64_t da = tc05::smem_desc_sw128(p_addr + kk * 32, 1024);
-                    const uint64_t db = tc05::smem_desc_sw128(vt_addr + kk * 32, 1024);
-                    tc05::mma_ss(d, da, db, idesc_o, (acc || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 2 * kk, idesc_o);
                 tc05::commit(&sm.o_done[X]);
             };
             uint32_t t = 0, n[2] = {0, 0}, iq[2] = {0, 0};
@@ -528,14 +551,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
                 for (int X = 0; X < 2; ++X)
                     if (it.nt[X] > 0) {
-                        if (!wait(&sm.q_full[X], iq[X] & 1)) goto done;
+                        if (!wait(&sm.q_full[X], iq[X] & 1, 0)) goto done;
                         ++iq[X];
                     }
-                if (!wait(&sm.k_full[t & 1], (t >> 1) & 1)) goto done;
+                if (!wait(&sm.k_full[t & 1], (t >> 1) & 1, 1)) goto done;
 #pragma unroll
                 for (int X = 0; X < 2; ++X)
                     if (it.nt[X] > 0) {
-                        if (n[X] > 0 && !wait(&sm.s_free[X], (n[X] - 1) & 1)) goto done;
+                        if (n[X] > 0 && !wait(&sm.s_free[X], (n[X] - 1) & 1, 2)) goto done;
                         tc05::fence_after_thread_sync();
                         issue_s(X, t & 1);
                     }
@@ -544,21 +567,21 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     const int st = t & 1;
                     if (j + 1 < it.ntiles) {
                         const int st1 = (t + 1) & 1;
-                        if (!wait(&sm.k_full[st1], ((t + 1) >> 1) & 1)) goto done;
+                        if (!wait(&sm.k_full[st1], ((t + 1) >> 1) & 1, 1)) goto done;
 #pragma unroll
                         for (int X = 0; X < 2; ++X)
                             if (j + 1 < it.nt[X]) {
-                                if (!wait(&sm.s_free[X], (n[X] + j) & 1)) goto done;
+                                if (!wait(&sm.s_free[X], (n[X] + j) & 1, 2)) goto done;
                                 tc05::fence_after_thread_sync();
                                 issue_s(X, st1);
                             }
                         tc05::commit(&sm.k_free[st1]);
                     }
-                    if (!wait(&sm.v_full[st], (t >> 1) & 1)) goto done;
+                    if (!wait(&sm.v_full[st], (t >> 1) & 1, 3)) goto done;
 #pragma unroll
                     for (int X = 0; X < 2; ++X)
                         if (j < it.nt[X]) {
-                            if (!wait(&sm.p_full[X], (n[X] + j) & 1)) goto done;
+                            if (!wait(&sm.p_full[X], (n[X] + j) & 1, 4)) goto done;
                             tc05::fence_after_thread_sync();
                             issue_pv(X, st, j > 0);
                         }
@@ -568,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 n[1] += it.nt[1];
             }
             // every commit has landed before the CTA's shared memory is given up
-            if (t > 0) wait(&sm.v_free[(t - 1) & 1], ((t - 1) >> 1) & 1);
+            if (t > 0) wait(&sm.v_free[(t - 1) & 1], ((t - 1) >> 1) & 1, 0);
         }
     } else {
         // ======================= loader: TMA-engine copies of the tiles' records =========================
@@ -583,7 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 for (int j = 0; j < it.ntiles; ++j, ++t) {
                     const int st = t & 1;
                     const uint32_t use = t >> 1;
-                    if (use > 0 && !wait(&sm.raw_free[st], (use - 1) & 1)) goto done;
+                    if (use > 0 && !wait(&sm.raw_free[st], (use - 1) & 1, 0)) goto done;
                     uint32_t bytes = 0;
                     int blocks[Smem::NREC];
 #pragma unroll
@@ -610,6 +633,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         }
     }
 done:
+#ifdef PA_PREFILL_PROF
+    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == kSoftmaxWarps || warp >= kWarpMma))
+        printf("prefill prof warp %d total %lld waits %lld %lld %lld %lld %lld\n", warp, clock64() - prof_begin, prof[0], prof[1], prof[2], prof[3], prof[4]);
+#endif
     tc05::fence_before_thread_sync();
     __syncthreads();
     if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
