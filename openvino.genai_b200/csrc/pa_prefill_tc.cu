@@ -11,8 +11,10 @@
 //                          K' = byte * f16(k scale) as [64 tokens][128 dims], V'^T = byte *
 //                          f16(v scale) as [128 dims][64 tokens] (the cache keeps value bytes
 //                          token-minor, so both are K-major operands), two stages each;
-//   mma       (1 thread)   tcgen05.mma: S_X = Q_X.K'^T into TMEM, O_X += P_X.V' in TMEM, for X = A, B;
-//                          the S of the next tile is queued before the P.V of the current one;
+//   mma       (1 warp, one elected lane issues) tcgen05.mma: S_X = Q_X.K'^T into TMEM, O_X += P_X.V' in
+//                          TMEM, for X = A, B; as soon as half X has published P of tile j its P.V and
+//                          the S of tile j + 1 are queued, so the tensor core works on one half while the
+//                          other half's softmax runs;
 //   softmax   (2 x 4 warps) thread r owns row r of its half: reads S from TMEM, masks (diagonal
 //                          tiles only), keeps a lazy running maximum, writes P = 2^(scale*(s-m)) as
 //                          f16 into TMEM (the A operand of P.V); rescales O in TMEM only when a row maximum
@@ -72,7 +74,6 @@ struct PrefillSmem {
     alignas(8) uint64_t v_free[kStages];
     alignas(8) uint64_t q_full[2];           // softmax -> mma, per item
     alignas(8) uint64_t s_full[2];           // mma (commit) -> softmax
-    alignas(8) uint64_t s_free[2];           // softmax -> mma: S is in registers
     alignas(8) uint64_t p_full[2];           // softmax -> mma: P written, O rescaled
     alignas(8) uint64_t o_done[2];           // mma (commit) -> softmax: P.V complete
     uint32_t tmem_base;
@@ -223,7 +224,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         for (int x = 0; x < 2; ++x) {
             mbar_init(&sm.q_full[x], kRows / 32);
             mbar_init(&sm.s_full[x], 1);
-            mbar_init(&sm.s_free[x], kRows / 32);
             mbar_init(&sm.p_full[x], kRows / 32);
             mbar_init(&sm.o_done[x], 1);
         }
@@ -247,6 +247,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #ifdef PA_PREFILL_PROF
     long long prof[5] = {0, 0, 0, 0, 0};
     const long long prof_begin = clock64();
+    __shared__ long long trace[5][8][4];   // role, event, tile 64..67 of this CTA
+#define PA_TRACE(role, ev, tile) do { if (lane == 0 && (tile) >= 64 && (tile) < 68) trace[role][ev][(tile) - 64] = clock64(); } while (0)
+#else
+#define PA_TRACE(role, ev, tile) do { } while (0)
 #endif
     auto wait = [&](uint64_t* bar, uint32_t parity, int cat) -> bool {
 #ifdef PA_PREFILL_PROF
@@ -315,6 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             for (int j = 0; j < it.nt[X]; ++j, ++n) {
                 const int col0 = j * kKv;
                 if (!wait_warp(&sm.s_full[X], n & 1, 0)) goto done;
+                if ((warp & 3) == 0) PA_TRACE(X, 0, n);
                 tc05::fence_after_thread_sync();
                 float sv[kKv];   // q.k' in units of 1 / qscale
                 {
@@ -325,8 +330,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) { sv[c] = __uint_as_float(s0[c]); sv[32 + c] = __uint_as_float(s1[c]); }
                 }
-                tc05::fence_before_thread_sync();
-                warp_arrive(&sm.s_free[X]);    // the next S of this half may overwrite TMEM
+                if ((warp & 3) == 0) PA_TRACE(X, 1, n);
+#ifdef PA_EXP_NOSOFTMAX
+                float alpha = 1.f;
+                bool rescale = false;
+                uint32_t pw[kKv / 2];
+#pragma unroll
+                for (int c = 0; c < kKv; c += 2) pw[c >> 1] = __float_as_uint(sv[c]) ^ __float_as_uint(sv[c + 1]);
+                m_run = 0.f;
+#else
                 if (col0 + kKv > my_ctx) {     // diagonal tile: hide what this row cannot see
                     const int nvis = my_ctx - col0;   // may be <= 0
 #pragma unroll
@@ -349,12 +361,23 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 const float mq = m_run * qscale;
                 uint32_t pw[kKv / 2];
 #pragma unroll
-                for (int c = 0; c < kKv; c += 2) pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
+                for (int c = 0; c < kKv; c += 2) {
+#if defined(PA_EXP_NOEXP)
+                    pw[c >> 1] = __byte_perm(__float_as_uint(fmaf(sv[c], qscale, -mq)), __float_as_uint(fmaf(sv[c + 1], qscale, -mq)), 0x7632);
+#elif defined(PA_EXP_NOCVT)
+                    pw[c >> 1] = ex2_h2(__byte_perm(__float_as_uint(fmaf(sv[c], qscale, -mq)), __float_as_uint(fmaf(sv[c + 1], qscale, -mq)), 0x7632));
+#else
+                    pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
+#endif
+                }
+#endif
                 // P.V of the previous tile of this half still reads the P tile and writes O
+                if ((warp & 3) == 0) PA_TRACE(X, 2, n);
                 if (n > 0) {
                     if (!wait_warp(&sm.o_done[X], (n - 1) & 1, 1)) goto done;
                     tc05::fence_after_thread_sync();
                 }
+                if ((warp & 3) == 0) PA_TRACE(X, 3, n);
                 if (rescale) {
 #pragma unroll
                     for (int q4 = 0; q4 < kD / 32; ++q4) {
@@ -377,6 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 tc05::wait_st();
                 tc05::fence_before_thread_sync();
                 warp_arrive(&sm.p_full[X]);
+                if ((warp & 3) == 0) PA_TRACE(X, 4, n);
             }
             // ---- epilogue: out = (O - z) / l; z = the three zero-point columns, l = the all-ones column
             if (!wait_warp(&sm.o_done[X], (n - 1) & 1, 2)) goto done;
@@ -421,8 +445,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 const uint8_t* raw_k = sm.raw_k[st];
                 const uint8_t* raw_v = sm.raw_v[st];
                 if (!wait_warp(&sm.raw_full[st], use & 1, 0)) goto done;
+                if (cwarp == 0) PA_TRACE(2, 0, t);
                 if (use > 0 && !wait_warp(&sm.k_free[st], (use - 1) & 1, 1)) goto done;
+                if (cwarp == 0) PA_TRACE(2, 1, t);
                 // K' = byte * f16(k scale): unit u = 16 dims of one token
+#ifndef PA_EXP_NOCONV
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int u = ctid + 128 * i;
@@ -438,6 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg) & 7)) = lo4;
                     *reinterpret_cast<uint4*>(atom + sw128(token, (2 * seg + 1) & 7)) = hi4;
                 }
+#endif
                 if (ctid < kKv) {
                     const int token = ctid;
                     const bool ok = token < live_tokens;
@@ -451,8 +479,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 }
                 tc05::fence_proxy_async_smem();
                 warp_arrive(&sm.k_full[st]);
+                if (cwarp == 0) PA_TRACE(2, 2, t);
 
                 if (use > 0 && !wait_warp(&sm.v_free[st], (use - 1) & 1, 2)) goto done;
+                if (cwarp == 0) PA_TRACE(2, 3, t);
                 // this warp's table of (scale, -1024 * scale) for the tile's token pairs
                 __syncwarp();
                 float vs0 = 0.f, vs1 = 0.f;
@@ -475,6 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     tab[k + 1] = make_uint2(t4.z, t4.w);
                 }
                 constexpr int UPR = BS / 16;   // 16-token units per record
+#ifndef PA_EXP_NOCONV
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int d = (ctid >> 2) + 32 * i;
@@ -491,6 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     *reinterpret_cast<uint4*>(sm.vt[st] + sw128(d, 2 * tg)) = make_uint4(w[0], w[1], w[2], w[3]);
                     *reinterpret_cast<uint4*>(sm.vt[st] + sw128(d, 2 * tg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
+#endif
                 if (ctid < kKv) {
                     const int token = ctid;
                     const bool ok = token < live_tokens;
@@ -508,11 +540,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 tc05::fence_proxy_async_smem();
                 warp_arrive(&sm.v_full[st]);
                 warp_arrive(&sm.raw_free[st]);
+                if (cwarp == 0) PA_TRACE(2, 4, t);
             }
         }
     } else if (warp == kWarpMma) {
         // ======================= mma issue ================================================================
-        if (lane == 0) {
+        // The whole warp runs the loop (uniform control flow keeps the descriptors in uniform registers);
+        // one elected lane issues the tensor-core instructions.
+        {
             constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
             constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kNo, 0, 0, 0);
             // operand descriptors are built once; a step along K or to another buffer only moves the
@@ -525,6 +560,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             auto issue_s = [&](int X, int st) {
                 const uint64_t da0 = dq + X * q_step, db0 = dk + st * k_step;
                 const uint32_t d = tmem + kKv * X;
+                if (tc05::elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t a_off = ((kk >> 2) * (kRows * 128) + (kk & 3) * 32) >> 4, b_off = ((kk >> 2) * (kKv * 128) + (kk & 3) * 32) >> 4;
@@ -533,65 +569,72 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 }
                 tc05::mma_ss<1>(d, dqx + X * qx_step, dkx + st * kx_step, idesc_s);
                 tc05::commit(&sm.s_full[X]);
+                }
+                __syncwarp();
             };
             auto issue_pv = [&](int X, int st, bool acc) {
                 const uint32_t pa = tmem + kTmemP + (kKv / 2) * X;   // 16 tokens of P = 8 columns
                 const uint64_t db0 = dv + st * v_step;
                 const uint32_t d = tmem + 2 * kKv + kNo * X;
+                if (tc05::elect_one()) {
                 if (acc) tc05::mma_ts<1>(d, pa, db0, idesc_o);
                 else tc05::mma_ts<0>(d, pa, db0, idesc_o);
 #pragma unroll
                 for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 2 * kk, idesc_o);
                 tc05::commit(&sm.o_done[X]);
+                }
+                __syncwarp();
             };
             uint32_t t = 0, n[2] = {0, 0}, iq[2] = {0, 0};
             for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
                 const Item it = locate_item(a, item, G, Hkv);
-                // first S of the item
+                // first S of the item.  The S region of a half is free: its softmax published the last P of
+                // the previous item (waited below) after reading that tile's S.
 #pragma unroll
                 for (int X = 0; X < 2; ++X)
                     if (it.nt[X] > 0) {
-                        if (!wait(&sm.q_full[X], iq[X] & 1, 0)) goto done;
+                        if (!wait_warp(&sm.q_full[X], iq[X] & 1, 0)) goto done;
                         ++iq[X];
                     }
-                if (!wait(&sm.k_full[t & 1], (t >> 1) & 1, 1)) goto done;
+                if (!wait_warp(&sm.k_full[t & 1], (t >> 1) & 1, 1)) goto done;
+                tc05::fence_after_thread_sync();
 #pragma unroll
                 for (int X = 0; X < 2; ++X)
-                    if (it.nt[X] > 0) {
-                        if (n[X] > 0 && !wait(&sm.s_free[X], (n[X] - 1) & 1, 2)) goto done;
-                        tc05::fence_after_thread_sync();
-                        issue_s(X, t & 1);
-                    }
-                tc05::commit(&sm.k_free[t & 1]);
+                    if (it.nt[X] > 0) issue_s(X, t & 1);
+                if (tc05::elect_one()) tc05::commit(&sm.k_free[t & 1]);
                 for (int j = 0; j < it.ntiles; ++j, ++t) {
-                    const int st = t & 1;
-                    if (j + 1 < it.ntiles) {
-                        const int st1 = (t + 1) & 1;
-                        if (!wait(&sm.k_full[st1], ((t + 1) >> 1) & 1, 1)) goto done;
-#pragma unroll
-                        for (int X = 0; X < 2; ++X)
-                            if (j + 1 < it.nt[X]) {
-                                if (!wait(&sm.s_free[X], (n[X] + j) & 1, 2)) goto done;
-                                tc05::fence_after_thread_sync();
-                                issue_s(X, st1);
-                            }
-                        tc05::commit(&sm.k_free[st1]);
+                    const int st = t & 1, st1 = (t + 1) & 1;
+                    const bool more = j + 1 < it.ntiles;
+                    PA_TRACE(3, 0, t);
+                    // The converter finishes V' of tile j before K' of tile j + 1, so the latter's barrier
+                    // covers both; only the item's last tile waits for its V' directly.
+                    if (more) {
+                        if (!wait_warp(&sm.k_full[st1], ((t + 1) >> 1) & 1, 1)) goto done;
+                    } else {
+                        if (!wait_warp(&sm.v_full[st], (t >> 1) & 1, 3)) goto done;
                     }
-                    if (!wait(&sm.v_full[st], (t >> 1) & 1, 3)) goto done;
+                    PA_TRACE(3, 3, t);
 #pragma unroll
                     for (int X = 0; X < 2; ++X)
                         if (j < it.nt[X]) {
-                            if (!wait(&sm.p_full[X], (n[X] + j) & 1, 4)) goto done;
+                            // P of tile j is in TMEM, so S of tile j has been read: both MMAs may go
+                            if (!wait_warp(&sm.p_full[X], (n[X] + j) & 1, 4)) goto done;
+                            PA_TRACE(3, 4 + 2 * X, t);
                             tc05::fence_after_thread_sync();
                             issue_pv(X, st, j > 0);
+                            if (j + 1 < it.nt[X]) issue_s(X, st1);
+                            PA_TRACE(3, 5 + 2 * X, t);
                         }
-                    tc05::commit(&sm.v_free[st]);
+                    if (tc05::elect_one()) {
+                        if (more) tc05::commit(&sm.k_free[st1]);
+                        tc05::commit(&sm.v_free[st]);
+                    }
                 }
                 n[0] += it.nt[0];
                 n[1] += it.nt[1];
             }
             // every commit has landed before the CTA's shared memory is given up
-            if (t > 0) wait(&sm.v_free[(t - 1) & 1], ((t - 1) >> 1) & 1, 0);
+            if (t > 0) wait_warp(&sm.v_free[(t - 1) & 1], ((t - 1) >> 1) & 1, 0);
         }
     } else {
         // ======================= loader: TMA-engine copies of the tiles' records =========================
@@ -607,6 +650,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     const int st = t & 1;
                     const uint32_t use = t >> 1;
                     if (use > 0 && !wait(&sm.raw_free[st], (use - 1) & 1, 0)) goto done;
+                    PA_TRACE(4, 0, t);
                     uint32_t bytes = 0;
                     int blocks[Smem::NREC];
 #pragma unroll
@@ -620,10 +664,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                         }
                         blocks[r] = blk;
                     }
+#ifdef PA_EXP_NOLOAD
+                    bytes = 0;
+#endif
                     mbar_expect_tx(&sm.raw_full[st], bytes);
 #pragma unroll
                     for (int r = 0; r < Smem::NREC; ++r)
-                        if (blocks[r] >= 0) {
+                        if (blocks[r] >= 0 && bytes) {
                             bulk_g2s(sm.raw_k[st] + r * Smem::RSTRIDE, kc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.raw_full[st]);
                             bulk_g2s(sm.raw_v[st] + r * Smem::RSTRIDE, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.raw_full[st]);
                         }
@@ -634,6 +681,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     }
 done:
 #ifdef PA_PREFILL_PROF
+    __syncthreads();
+    if (blockIdx.x == 0 && tid == 0) {
+        const long long base = trace[3][0][0];
+        for (int role = 0; role < 5; ++role)
+            for (int tl = 0; tl < 4; ++tl)
+                printf("trace role %d tile %d: %lld %lld %lld %lld %lld %lld %lld %lld\n", role, 64 + tl, trace[role][0][tl] - base, trace[role][1][tl] - base,
+                       trace[role][2][tl] - base, trace[role][3][tl] - base, trace[role][4][tl] - base, trace[role][5][tl] - base, trace[role][6][tl] - base,
+                       trace[role][7][tl] - base);
+    }
     if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == kSoftmaxWarps || warp >= kWarpMma))
         printf("prefill prof warp %d total %lld waits %lld %lld %lld %lld %lld\n", warp, clock64() - prof_begin, prof[0], prof[1], prof[2], prof[3], prof[4]);
 #endif

@@ -26,6 +26,13 @@ __device__ __forceinline__ void fence_after_thread_sync() { asm volatile("tcgen0
 // Makes generic-proxy writes to shared memory visible to the async proxy (tensor core, TMA).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- descriptors ------------------------------------------------------------------------------------
 // Shared-memory operand descriptor for a 128-byte-swizzled tile whose rows are 128 bytes
 // (64 16-bit elements) and whose 8-row groups are `sbo_bytes` apart.  Bits: [0,14) start >> 4,
