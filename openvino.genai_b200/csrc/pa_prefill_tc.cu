@@ -114,12 +114,15 @@ __device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
     asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
     return y;
 }
+// f32 -> f16 through the packed conversion: the scalar form runs on the quarter-rate special
+// function unit, which the softmax warps keep busy with exponentials
+__device__ __forceinline__ __half f2h(float x) { return __ushort_as_half((unsigned short)(pack_h2(x, 0.f) & 0xffffu)); }
 // z = h + m + l up to 2^-33 |z|, every piece an f16
 __device__ __forceinline__ void split3(float z, __half& h, __half& m, __half& l) {
-    h = __float2half_rn(z);
+    h = f2h(z);
     const float r = z - __half2float(h);
-    m = __float2half_rn(r);
-    l = __float2half_rn(r - __half2float(m));
+    m = f2h(r);
+    l = f2h(r - __half2float(m));
 }
 __device__ __forceinline__ uint32_t h2_bits(__half a, __half b) {
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
@@ -307,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     *reinterpret_cast<uint4*>(sq + (c / 8) * (kRows * 128) + sw128(r, c % 8)) = w;
                 }
                 // |q| is assumed to stay inside the f16 range (no power-of-two prescale here)
-                const __half qh = __float2half_rn(qsum), ql = __float2half_rn(qsum - __half2float(qh));
+                const __half qh = f2h(qsum), ql = f2h(qsum - __half2float(qh));
                 const __half zero = __ushort_as_half(0);
                 *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
                 *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
@@ -457,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
                     if (token < live_tokens) {
                         const uint8_t* rec = raw_k + (token / BS) * Smem::RSTRIDE;
-                        const __half ksh = __float2half_rn(*reinterpret_cast<const float*>(rec + BS * kD + 4 * (token % BS)));
+                        const __half ksh = f2h(*reinterpret_cast<const float*>(rec + BS * kD + 4 * (token % BS)));
                         bytes16_to_h(*reinterpret_cast<const uint4*>(rec + (token % BS) * kD + 16 * seg), lo4, hi4);
                         scale16(lo4, hi4, ksh);
                     }
@@ -470,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     const int token = ctid;
                     const bool ok = token < live_tokens;
                     const float* kp = reinterpret_cast<const float*>(raw_k + (token / BS) * Smem::RSTRIDE + BS * kD);
-                    const float ksf = __half2float(__float2half_rn(kp[token % BS]));
+                    const float ksf = __half2float(f2h(kp[token % BS]));
                     __half zh, zm, zl;
                     split3(ok ? -(ksf * kp[BS + token % BS]) : 0.f, zh, zm, zl);
                     const __half zero = __ushort_as_half(0);
@@ -527,7 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     const int token = ctid;
                     const bool ok = token < live_tokens;
                     const float* vp = reinterpret_cast<const float*>(raw_v + (token / BS) * Smem::RSTRIDE + BS * kD);
-                    const float vsf = __half2float(__float2half_rn(vp[token % BS]));
+                    const float vsf = __half2float(f2h(vp[token % BS]));
                     __half zh, zm, zl;
                     split3(ok ? vsf * vp[BS + token % BS] : 0.f, zh, zm, zl);
                     const uint32_t off = (token & 7) * 2;
@@ -535,7 +538,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     *reinterpret_cast<__half*>(vt + sw128(kD + 0, token >> 3) + off) = zh;
                     *reinterpret_cast<__half*>(vt + sw128(kD + 1, token >> 3) + off) = zm;
                     *reinterpret_cast<__half*>(vt + sw128(kD + 2, token >> 3) + off) = zl;
-                    *reinterpret_cast<__half*>(vt + sw128(kD + 3, token >> 3) + off) = __float2half_rn(ok ? 1.f : 0.f);
+                    *reinterpret_cast<__half*>(vt + sw128(kD + 3, token >> 3) + off) = __ushort_as_half(ok ? (unsigned short)0x3C00u : (unsigned short)0u);
                 }
                 tc05::fence_proxy_async_smem();
                 warp_arrive(&sm.v_full[st]);
