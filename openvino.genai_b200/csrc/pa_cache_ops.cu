@@ -75,6 +75,7 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         a.plan->total_tiles = sh_run * HK;
         a.ptile_prefix[B] = sh_run_p;
         a.plan->total_ptiles = sh_run_p;
+        a.plan->next_pitem = 0;
     }
 }
 

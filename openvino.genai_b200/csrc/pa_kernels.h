@@ -15,7 +15,8 @@ constexpr int kPrefillItemRows = 256;
 struct PlanHeader {
     int total_tiles;   // 32-token tiles of all decode streams (rows x head tiles)
     int total_ptiles;  // kPrefillItemRows-row q tiles of all prefill chunks (per kv head)
-    int pad[2];
+    int next_pitem;    // work counter of the prefill kernel: next (q tile, kv head) item to hand out
+    int pad;
 };
 
 // Everything a kernel needs, passed by value.  All pointers are device memory.

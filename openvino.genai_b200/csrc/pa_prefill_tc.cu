@@ -44,6 +44,7 @@ constexpr int kNo = kD + kDx;  // UMMA N of P.V
 constexpr int kTmemCols = 512; // S_A [0,64) S_B [64,128) O_A [128,272) O_B [272,416) P_A [416,448) P_B [448,480)
 constexpr int kTmemP = 2 * kKv + 2 * kNo;
 constexpr int kStages = 2;
+constexpr int kItemSlots = 4;   // depth of the queue that hands work items from the loader to the other roles
 constexpr float kLazy = 4.f;   // log2 of the growth of a row maximum that forces a rescale of O
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLn2P = 0.6931471805599453f;
@@ -76,6 +77,9 @@ struct PrefillSmem {
     alignas(8) uint64_t s_full[2];           // mma (commit) -> softmax
     alignas(8) uint64_t p_full[2];           // softmax -> mma: P written, O rescaled
     alignas(8) uint64_t o_done[2];           // mma (commit) -> softmax: P.V complete
+    alignas(8) uint64_t item_full[kItemSlots];   // loader -> every other warp
+    alignas(8) uint64_t item_free[kItemSlots];   // every other warp -> loader: the slot has been read
+    int item_ring[kItemSlots];
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -230,6 +234,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             mbar_init(&sm.p_full[x], kRows / 32);
             mbar_init(&sm.o_done[x], 1);
         }
+#pragma unroll
+        for (int i = 0; i < kItemSlots; ++i) {
+            mbar_init(&sm.item_full[i], 1);
+            mbar_init(&sm.item_free[i], kWarpMma + 1);
+        }
         mbar_fence_init();
         sm.abort = 0;
     }
@@ -274,6 +283,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         return false;
     };
     auto wait_warp = [&](uint64_t* bar, uint32_t parity, int cat) -> bool { return __all_sync(0xffffffffu, wait(bar, parity, cat)) != 0; };
+    // Work items come from a global counter: the loader draws them and publishes each through a
+    // small ring, so that all roles of the CTA walk the same sequence.  -1 ends the sequence, -2
+    // reports a wait that ran out.
+    auto fetch_item = [&](uint32_t k) -> int {
+        const int slot = k & (kItemSlots - 1);
+        if (!wait_warp(&sm.item_full[slot], (k / kItemSlots) & 1, 0)) return -2;
+        const int item = sm.item_ring[slot];
+        warp_arrive(&sm.item_free[slot]);
+        return item;
+    };
 
     if (warp < kSoftmaxWarps) {
         // ======================= softmax + epilogue of half X ==========================================
@@ -283,7 +302,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         uint8_t* const sq = sm.q[X];
         const uint32_t tmem_p = tmem + kTmemP + (kKv / 2) * X + lane_base;
         uint32_t n = 0;   // tiles of this half so far, over all items
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        for (uint32_t ik = 0;; ++ik) {
+            const int item = fetch_item(ik);
+            if (item == -2) goto done;
+            if (item < 0) break;
             const Item it = locate_item(a, item, G, Hkv);
             if (it.nt[X] == 0) continue;
             const int flat = it.row0 + X * kRows + r;
@@ -438,7 +460,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         // ======================= converter: raw records -> f16 operand tiles =============================
         const int ctid = tid - kSoftmaxWarps * 32, cwarp = warp - kSoftmaxWarps;
         uint32_t t = 0;   // tiles so far, over all items
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        for (uint32_t ik = 0;; ++ik) {
+            const int item = fetch_item(ik);
+            if (item == -2) goto done;
+            if (item < 0) break;
             const Item it = locate_item(a, item, G, Hkv);
             const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
             for (int j = 0; j < it.ntiles; ++j, ++t) {
@@ -589,7 +614,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 __syncwarp();
             };
             uint32_t t = 0, n[2] = {0, 0}, iq[2] = {0, 0};
-            for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            for (uint32_t ik = 0;; ++ik) {
+                const int item = fetch_item(ik);
+                if (item == -2) goto done;
+                if (item < 0) break;
                 const Item it = locate_item(a, item, G, Hkv);
                 // first S of the item.  The S region of a half is free: its softmax published the last P of
                 // the previous item (waited below) after reading that tile's S.
@@ -644,7 +672,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         if (lane == 0) {
             uint32_t t = 0;
             bool bad_index = false;
-            for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            for (uint32_t ik = 0;; ++ik) {
+                const int slot = ik & (kItemSlots - 1);
+                if (ik >= kItemSlots && !wait(&sm.item_free[slot], ((ik / kItemSlots) - 1) & 1, 1)) goto done;
+                int item = atomicAdd(&a.plan->next_pitem, 1);
+                if (item >= total_items) item = -1;
+                sm.item_ring[slot] = item;
+                mbar_arrive(&sm.item_full[slot]);
+                if (item < 0) break;
                 const Item it = locate_item(a, item, G, Hkv);
                 const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
                 const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes;
