@@ -162,91 +162,114 @@ __global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
     }
 }
 
-// One warp per (rotated block, kv head, token).  Lane l owns the pairs (j, j + D/2) for
-// j in {l + 32*i}.  k'[j] = fma(-k[j+D/2], s, k[j]*c);  k'[j+D/2] = fma(k[j], s, k[j+D/2]*c)
+// D/8 lanes per (rotated block, kv head, token).  Lane l owns the pairs (j, j + D/2) for
+// j in 4*l .. 4*l+3.  k'[j] = fma(-k[j+D/2], s, k[j]*c);  k'[j+D/2] = fma(k[j], s, k[j+D/2]*c)
 // with c = lut[row][j], s = lut[row][D/2 + j].
 template <int D>
 __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
+    // HALF / 4 lanes per token: a lane owns dims 4*l .. 4*l+3 of the first half and their partners
+    // in the second half, so every access is a 4-byte (u8) or 8-byte (f16 / bf16) vector.
     constexpr int HALF = D / 2;
-    constexpr int PER = HALF / 32;
+    constexpr int LPT = HALF / 4;          // lanes per token: 16 (D = 128) or 8 (D = 64)
+    constexpr int TPW = 32 / LPT;          // tokens per warp
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, sub = lane / LPT, l = lane % LPT;
     const long long total = (long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs;
-    if (warp >= total) return;
-    const int tok = (int)(warp % a.g.bs);
-    const int h = (int)((warp / a.g.bs) % a.g.Hkv);
-    const int r = (int)(warp / ((long long)a.g.bs * a.g.Hkv));
+    const long long unit = warp * TPW + sub;   // (rotated block, kv head, token)
+    if (warp * TPW >= total) return;
+    const bool live = unit < total;
+    const long long u = live ? unit : total - 1;
+    const int tok = (int)(u % a.g.bs);
+    const int h = (int)((u / a.g.bs) % a.g.Hkv);
+    const int r = (int)(u / ((long long)a.g.bs * a.g.Hkv));
     const int block = a.rotated_block_indices[r];
     const int row = a.rotation_deltas[r];
-    if (block < 0 || block >= a.num_blocks || row < 0 || row >= a.rotation_lut_rows) {
-        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_ROTATION);
-        return;
-    }
-    const float* lut = a.rotation_trig_lut + (long long)row * D;
-    uint8_t* rec = (uint8_t*)a.key_cache + (long long)block * a.g.block_bytes + (long long)h * a.g.head_bytes;
-    float lo[PER], hi[PER];
+    const bool bad = block < 0 || block >= a.num_blocks || row < 0 || row >= a.rotation_lut_rows;
+    if (bad && l == 0) atomicOr(a.status, PA_DEV_BAD_ROTATION);
+    const bool work = live && !bad;
+    const float* lut = a.rotation_trig_lut + (long long)(bad ? 0 : row) * D;
+    uint8_t* rec = (uint8_t*)a.key_cache + (long long)(bad ? 0 : block) * a.g.block_bytes + (long long)h * a.g.head_bytes;
     float* params = (float*)(rec + (long long)a.g.bs * D);
-    if (a.g.cache == PA_DTYPE_U8) {
-        const float sc = params[tok], zp = params[a.g.bs + tok];
+    float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+    if (work) {
+        if (a.g.cache == PA_DTYPE_U8) {
+            const float sc = params[tok], zp = params[a.g.bs + tok];
+            const uint32_t wl = *reinterpret_cast<const uint32_t*>(rec + (long long)tok * D + 4 * l);
+            const uint32_t wh = *reinterpret_cast<const uint32_t*>(rec + (long long)tok * D + HALF + 4 * l);
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int j = lane + 32 * i;
-            lo[i] = dequant_one(rec[(long long)tok * D + j], sc, zp);
-            hi[i] = dequant_one(rec[(long long)tok * D + HALF + j], sc, zp);
-        }
-    } else {
-        const uint16_t* p = (const uint16_t*)rec + (long long)tok * D;
+            for (int i = 0; i < 4; ++i) {
+                lo[i] = dequant_one((wl >> (8 * i)) & 0xffu, sc, zp);
+                hi[i] = dequant_one((wh >> (8 * i)) & 0xffu, sc, zp);
+            }
+        } else {
+            const uint16_t* p = (const uint16_t*)rec + (long long)tok * D;
+            const uint2 wl = *reinterpret_cast<const uint2*>(p + 4 * l), wh = *reinterpret_cast<const uint2*>(p + HALF + 4 * l);
+            const uint32_t wlv[2] = {wl.x, wl.y}, whv[2] = {wh.x, wh.y};
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int j = lane + 32 * i;
-            if (a.g.cache == PA_DTYPE_F16) {
-                lo[i] = __half2float(__ushort_as_half(p[j]));
-                hi[i] = __half2float(__ushort_as_half(p[HALF + j]));
-            } else {
-                lo[i] = __bfloat162float(__ushort_as_bfloat16(p[j]));
-                hi[i] = __bfloat162float(__ushort_as_bfloat16(p[HALF + j]));
+            for (int i = 0; i < 4; ++i) {
+                const unsigned short el = (unsigned short)(wlv[i >> 1] >> (16 * (i & 1))), eh = (unsigned short)(whv[i >> 1] >> (16 * (i & 1)));
+                if (a.g.cache == PA_DTYPE_F16) {
+                    lo[i] = __half2float(__ushort_as_half(el));
+                    hi[i] = __half2float(__ushort_as_half(eh));
+                } else {
+                    lo[i] = __bfloat162float(__ushort_as_bfloat16(el));
+                    hi[i] = __bfloat162float(__ushort_as_bfloat16(eh));
+                }
             }
         }
     }
-    float nlo[PER], nhi[PER];
+    const float4 c4 = *reinterpret_cast<const float4*>(lut + 4 * l), s4 = *reinterpret_cast<const float4*>(lut + HALF + 4 * l);
+    const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+    float nlo[4], nhi[4];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int j = lane + 32 * i;
-        const float c = lut[j], s = lut[HALF + j];
-        nlo[i] = __fmaf_rn(-hi[i], s, __fmul_rn(lo[i], c));
-        nhi[i] = __fmaf_rn(lo[i], s, __fmul_rn(hi[i], c));
+    for (int i = 0; i < 4; ++i) {
+        nlo[i] = __fmaf_rn(-hi[i], sv[i], __fmul_rn(lo[i], cv[i]));
+        nhi[i] = __fmaf_rn(lo[i], sv[i], __fmul_rn(hi[i], cv[i]));
     }
     if (a.g.cache == PA_DTYPE_U8) {
         float mn = fminf(nlo[0], nhi[0]), mx = fmaxf(nlo[0], nhi[0]);
 #pragma unroll
-        for (int i = 1; i < PER; ++i) {
+        for (int i = 1; i < 4; ++i) {
             mn = fminf(mn, fminf(nlo[i], nhi[i]));
             mx = fmaxf(mx, fmaxf(nlo[i], nhi[i]));
         }
-        mn = warp_min(mn); mx = warp_max(mx);
+#pragma unroll
+        for (int o = LPT / 2; o > 0; o >>= 1) {   // over the token's lanes (every lane of the warp takes part)
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
         float sc, zp, inv;
         quant_params(mn, mx, sc, zp, inv);
-        __syncwarp();
-        if (lane == 0) { params[tok] = sc; params[a.g.bs + tok] = zp; }
+        __syncwarp();   // every lane has read the old parameters
+        if (work) {
+            if (l == 0) { params[tok] = sc; params[a.g.bs + tok] = zp; }
+            uint32_t wl = 0, wh = 0;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int j = lane + 32 * i;
-            rec[(long long)tok * D + j] = (uint8_t)quant_one(nlo[i], inv, zp);
-            rec[(long long)tok * D + HALF + j] = (uint8_t)quant_one(nhi[i], inv, zp);
-        }
-    } else {
-        uint16_t* p = (uint16_t*)rec + (long long)tok * D;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int j = lane + 32 * i;
-            if (a.g.cache == PA_DTYPE_F16) {
-                p[j] = __half_as_ushort(__float2half_rn(nlo[i]));
-                p[HALF + j] = __half_as_ushort(__float2half_rn(nhi[i]));
-            } else {
-                p[j] = __bfloat16_as_ushort(__float2bfloat16_rn(nlo[i]));
-                p[HALF + j] = __bfloat16_as_ushort(__float2bfloat16_rn(nhi[i]));
+            for (int i = 0; i < 4; ++i) {
+                wl |= quant_one(nlo[i], inv, zp) << (8 * i);
+                wh |= quant_one(nhi[i], inv, zp) << (8 * i);
             }
+            *reinterpret_cast<uint32_t*>(rec + (long long)tok * D + 4 * l) = wl;
+            *reinterpret_cast<uint32_t*>(rec + (long long)tok * D + HALF + 4 * l) = wh;
         }
+    } else if (work) {
+        uint16_t* p = (uint16_t*)rec + (long long)tok * D;
+        uint32_t wlv[2] = {0, 0}, whv[2] = {0, 0};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            unsigned short el, eh;
+            if (a.g.cache == PA_DTYPE_F16) {
+                el = __half_as_ushort(__float2half_rn(nlo[i]));
+                eh = __half_as_ushort(__float2half_rn(nhi[i]));
+            } else {
+                el = __bfloat16_as_ushort(__float2bfloat16_rn(nlo[i]));
+                eh = __bfloat16_as_ushort(__float2bfloat16_rn(nhi[i]));
+            }
+            wlv[i >> 1] |= (uint32_t)el << (16 * (i & 1));
+            whv[i >> 1] |= (uint32_t)eh << (16 * (i & 1));
+        }
+        *reinterpret_cast<uint2*>(p + 4 * l) = make_uint2(wlv[0], wlv[1]);
+        *reinterpret_cast<uint2*>(p + HALF + 4 * l) = make_uint2(whv[0], whv[1]);
     }
 }
 
@@ -288,7 +311,8 @@ cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream, bool with_
 
 cudaError_t launch_rotate(const KernelArgs& a, cudaStream_t stream) {
     if (a.num_rotated_blocks <= 0) return cudaSuccess;
-    const long long warps = (long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs;
+    const int tokens_per_warp = 32 / (a.g.D / 8);
+    const long long warps = ((long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs + tokens_per_warp - 1) / tokens_per_warp;
     const int grid = (int)((warps * 32 + 255) / 256);
     if (a.g.D == 128) rotate_kernel<128><<<grid, 256, 0, stream>>>(a);
     else rotate_kernel<64><<<grid, 256, 0, stream>>>(a);

@@ -368,6 +368,7 @@ __global__ void __launch_bounds__(kScoreWarps * 32) score_kernel(KernelArgs a) {
                 }
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
+                    if (r == 1 && rows - 16 * rt <= 8) break;   // rows 8..15 of the tile are padding (warp-uniform)
                     float s0 = acc4[2 * r], s1 = acc4[2 * r + 1];
                     if constexpr (U8) {
                         s0 = (s0 - kz0 * qsum[r]) * (ks0 * qsc[r]);
