@@ -171,21 +171,19 @@ __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
     // in the second half, so every access is a 4-byte (u8) or 8-byte (f16 / bf16) vector.
     constexpr int HALF = D / 2;
     constexpr int LPT = HALF / 4;          // lanes per token: 16 (D = 128) or 8 (D = 64)
-    constexpr int TPW = 32 / LPT;          // tokens per warp
-    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31, sub = lane / LPT, l = lane % LPT;
-    const long long total = (long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs;
-    const long long unit = warp * TPW + sub;   // (rotated block, kv head, token)
-    if (warp * TPW >= total) return;
-    const bool live = unit < total;
-    const long long u = live ? unit : total - 1;
-    const int tok = (int)(u % a.g.bs);
-    const int h = (int)((u / a.g.bs) % a.g.Hkv);
-    const int r = (int)(u / ((long long)a.g.bs * a.g.Hkv));
+    // One CTA per rotated block; its sub-warps walk the block's (kv head, token) units.
+    const int l = threadIdx.x % LPT;
+    const int r = blockIdx.x;
+    const int units = a.g.Hkv * a.g.bs;
     const int block = a.rotated_block_indices[r];
     const int row = a.rotation_deltas[r];
     const bool bad = block < 0 || block >= a.num_blocks || row < 0 || row >= a.rotation_lut_rows;
-    if (bad && l == 0) atomicOr(a.status, PA_DEV_BAD_ROTATION);
+    if (bad && threadIdx.x == 0) atomicOr(a.status, PA_DEV_BAD_ROTATION);
+    for (int base = 0; base < units; base += blockDim.x / LPT) {   // warp-uniform trip count
+    const int unit = base + threadIdx.x / LPT;
+    const bool live = unit < units;
+    const int uu = live ? unit : units - 1;
+    const int tok = uu % a.g.bs, h = uu / a.g.bs;
     const bool work = live && !bad;
     const float* lut = a.rotation_trig_lut + (long long)(bad ? 0 : row) * D;
     uint8_t* rec = (uint8_t*)a.key_cache + (long long)(bad ? 0 : block) * a.g.block_bytes + (long long)h * a.g.head_bytes;
@@ -271,6 +269,7 @@ __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
         *reinterpret_cast<uint2*>(p + 4 * l) = make_uint2(wlv[0], wlv[1]);
         *reinterpret_cast<uint2*>(p + HALF + 4 * l) = make_uint2(whv[0], whv[1]);
     }
+    }
 }
 
 // Block copies: grid.x = pair, grid.y = slice of the block.  16-byte vectors.
@@ -311,9 +310,7 @@ cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream, bool with_
 
 cudaError_t launch_rotate(const KernelArgs& a, cudaStream_t stream) {
     if (a.num_rotated_blocks <= 0) return cudaSuccess;
-    const int tokens_per_warp = 32 / (a.g.D / 8);
-    const long long warps = ((long long)a.num_rotated_blocks * a.g.Hkv * a.g.bs + tokens_per_warp - 1) / tokens_per_warp;
-    const int grid = (int)((warps * 32 + 255) / 256);
+    const int grid = a.num_rotated_blocks;
     if (a.g.D == 128) rotate_kernel<128><<<grid, 256, 0, stream>>>(a);
     else rotate_kernel<64><<<grid, 256, 0, stream>>>(a);
     return cudaGetLastError();
