@@ -285,6 +285,79 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+SECONDARY = {
+    # name: (constructor keyword arguments of workloads.config_qwen_mixed, keep scores, what it is)
+    "qwen25_7b_mixed": (dict(), True, "16 prefill chunks of 256 + 240 decode rows, score output, 10 % of the blocks re-rotated"),
+    "qwen25_7b_prefill": (dict(num_decode=0, rotated_fraction=0.0), False, "16 prefill chunks of 256 tokens, past U[0,4096]"),
+    "qwen25_7b_prefill_large": (dict(num_prefill=64, chunk=512, prefill_hi=8192, num_decode=0, rotated_fraction=0.0), False,
+                                "64 prefill chunks of 512 tokens, past U[0,8192]"),
+}
+
+
+def run_secondary(args):
+    """Secondary workloads (not the headline line): the mixed step of BASELINE.json configs[2] and
+    prefill-only steps that exercise the tcgen05 kernel.  One JSON line: step time, and for the
+    prefill-only workloads the tensor-core rate of the whole step against the measured bf16 peaks."""
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    pkg.load_library()
+    from openvino_genai_b200 import workloads
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    kw, keep_scores, what = SECONDARY[args.workload]
+    dev = torch.device("cuda", 0)
+    wl = workloads.config_qwen_mixed(**kw)
+    if not keep_scores:
+        wl.score_aggregation_window = None
+    op = pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, 0)
+    kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
+    workloads.fill_cache_on_device(op, wl, kc, vc)
+    q, k, v = workloads.random_activations(wl, dev)
+    out = torch.empty_like(q)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev) if a is not None else None
+    scores = torch.zeros(wl.scores_len, dtype=torch.float32, device=dev) if wl.score_aggregation_window is not None else None
+    stream = torch.cuda.Stream(dev)
+    torch.cuda.synchronize(dev)
+    dargs = op.make_args(q, k, v, out, kc, vc, t(wl.past_lens), t(wl.subsequence_begins), t(wl.block_indices), t(wl.block_indices_begins),
+                         wl.scale, wl.max_context_len, t(wl.score_aggregation_window), scores, t(wl.rotated_block_indices),
+                         t(wl.rotation_deltas), t(wl.rotation_trig_lut), stream=stream.cuda_stream)
+    for _ in range(max(args.warmup, 3)):
+        op.forward_args(dargs)
+    torch.cuda.synchronize(dev)
+    launches0 = op.launch_count()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        op.forward_args(dargs)
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    status = op.device_status()
+    if status:
+        raise SystemExit(f"device status word {status:#x} after the timed region")
+    flops = wl.prefill_flops()
+    line = {"metric": "pa_step_ms", "value": round(ms, 4), "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 tcgen05 / f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "what": what, "tokens": int(wl.num_tokens), "sequences": int(wl.num_sequences),
+                       "kv_cache": "u8 by-token asymmetric", "prefill_gflop": round(flops / 1e9, 1),
+                       "decode_kv_mb": round(wl.decode_kv_bytes() / 1e6, 1), "l2_policy": "KV bytes per step exceed L2"},
+            "gpu_launches": int(op.launch_count() - launches0), "clocks": clocks}
+    if wl.decode_kv_bytes() == 0 and flops:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        achieved = flops / (ms * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
+                            "traffic": None, "kernel": "prefill_tc_kernel (whole step: cache write + attention)",
+                            "algorithmic_flops_per_launch": int(flops),
+                            "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained" if peaks else "fallback"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -297,6 +370,10 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in SECONDARY:
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            raise SystemExit("the secondary workloads run on one GPU")
+        run_secondary(args)
     else:
         run_ours(args)
 
