@@ -39,6 +39,8 @@ __device__ void build_decode_plan(const KernelArgs& a) {
     __shared__ int sh_run;
     __shared__ int sh_warp_p[8];
     __shared__ int sh_run_p;
+    constexpr int kPrefixCap = 2048;           // rows whose prefix sums are also kept in shared memory
+    __shared__ int sh_prefix[kPrefixCap + 1];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int B = a.num_sequences;
     const int G = a.g.Hq / a.g.Hkv, HK = a.g.Hkv * ((G + 15) / 16);
@@ -64,12 +66,46 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         __syncthreads();
         int off = sh_run, offp = sh_run_p;
         for (int w = 0; w < wid; ++w) { off += sh_warp[w]; offp += sh_warp_p[w]; }
-        if (s < B) { a.tile_prefix[s] = off + v - n; a.ptile_prefix[s] = offp + vp - np; }
+        if (s < B) {
+            a.tile_prefix[s] = off + v - n;
+            a.ptile_prefix[s] = offp + vp - np;
+            if (s <= kPrefixCap) sh_prefix[s] = off + v - n;
+        }
         __syncthreads();
         if (tid == 255) { sh_run = off + v; sh_run_p = offp + vp; }
         __syncthreads();
     }
     for (int i = tid; i < B * HK; i += 256) a.stream_done[i] = 0;
+    // start records of the decode workers: the row that holds each slice's first tile
+    if (a.worker_start && a.decode_all_workers > 0) {
+        const int total_tiles = sh_run * HK;
+        if (B <= kPrefixCap) {
+            if (tid == 0) sh_prefix[B] = sh_run;
+            __syncthreads();
+            int workers, per_worker;
+            decode_slices(total_tiles, a.decode_all_workers, workers, per_worker);
+            for (int w = tid; w < a.decode_all_workers; w += 256) {
+                WorkerStart ws{-1, 0, 0, total_tiles, 0, 0, 0, 0};
+                const long long g_tile = (long long)w * per_worker;
+                if (w < workers && g_tile < total_tiles) {
+                    const int key = (int)(g_tile / HK);
+                    int lo = 0, hi = B;   // sh_prefix[lo] <= key < sh_prefix[hi]
+                    while (hi - lo > 1) {
+                        const int mid = (lo + hi) >> 1;
+                        if (sh_prefix[mid] <= key) lo = mid; else hi = mid;
+                    }
+                    const int tb = a.block_indices_begins[lo];
+                    ws = WorkerStart{lo, sh_prefix[lo], sh_prefix[lo + 1] - sh_prefix[lo], total_tiles, a.past_lens[lo] + 1, tb,
+                                     a.block_indices_begins[lo + 1] - tb, a.subsequence_begins[lo]};
+                } else {
+                    ws.s = -2;   // no tiles for this worker
+                }
+                a.worker_start[w] = ws;
+            }
+        } else {
+            for (int w = tid; w < a.decode_all_workers; w += 256) a.worker_start[w] = WorkerStart{-1, 0, 0, total_tiles, 0, 0, 0, 0};
+        }
+    }
     if (tid == 0) {
         a.tile_prefix[B] = sh_run;
         a.plan->total_tiles = sh_run * HK;

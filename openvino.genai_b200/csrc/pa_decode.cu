@@ -21,6 +21,7 @@
 // completes it (one atomic counter per stream, no waiting).
 // HBM-bound: 2*Hkv*(D+8) bytes per context token for the u8 cache.
 #include <algorithm>
+#include <cstdio>
 
 #include "pa_common.cuh"
 #include "pa_kernels.h"
@@ -32,7 +33,12 @@ namespace {
 constexpr int kTile = 32;  // context tokens per pipeline stage
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeMaxCtasPerSm = 4;
-constexpr int kMinSlice = 4;     // a worker is given at least this many tiles
+#ifndef PA_DECODE_WAVES
+#define PA_DECODE_WAVES 1
+#endif
+// CTAs launched per resident CTA slot: more than one lets the hardware block scheduler hand the
+// later slices to whichever SM finishes first
+constexpr int kDecodeWaves = PA_DECODE_WAVES;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLazyMax = 8.f;  // the running reference may lag the true row maximum by 2^8
@@ -68,9 +74,13 @@ struct DecodeCfg {
     static constexpr int NREC = kTile / BS;                     // records per tile
     static constexpr int HALF_STAGE = NREC * REC;               // K part (V part has the same size)
     static constexpr int STAGE = 2 * HALF_STAGE;
-    static constexpr int NSTAGE = 2;
+#ifndef PA_DECODE_STAGES
+#define PA_DECODE_STAGES 2
+#endif
+    static constexpr int NSTAGE = PA_DECODE_STAGES;
     static constexpr int RING = NSTAGE * STAGE;                 // per warp
-    static constexpr int WARP_SMEM = RING + NSTAGE * (int)sizeof(StageDesc) + kRunRing * (int)sizeof(RunRec) + NSTAGE * 8;
+    // rounded to 128 bytes: every warp's ring must start 16-byte aligned for bulk copies and 16-byte loads
+    static constexpr int WARP_SMEM = (RING + NSTAGE * (int)sizeof(StageDesc) + kRunRing * (int)sizeof(RunRec) + NSTAGE * 8 + 127) / 128 * 128;
     static constexpr int SMEM = kDecodeWarps * WARP_SMEM;
     static_assert(WARP_SMEM % 16 == 0 && STAGE % 16 == 0 && REC % 16 == 0, "bulk copies and 16-byte loads need 16-byte aligned stages");
 };
@@ -88,7 +98,7 @@ __device__ __forceinline__ void store_pair(void* out, long long idx, int act, fl
 }
 
 template <int D, int BS, int CACHE, bool HI>
-__global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(KernelArgs a) {
+__global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2) ? 2 : 3) decode_kernel(KernelArgs a) {
     using Cfg = DecodeCfg<D, BS, CACHE>;
     constexpr bool U8 = Cfg::U8;
     constexpr bool BF16 = Cfg::BF16;
@@ -121,11 +131,18 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
     bool bad_index = false;
 
     // ---- this worker's slice of the global tile sequence -----------------------------------------
-    const int total_tiles = a.plan->total_tiles;                  // all streams
     const int all_workers = gridDim.x * kDecodeWarps;
-    const int workers = max(1, min(all_workers, (total_tiles + kMinSlice - 1) / kMinSlice));
-    const int per_worker = (total_tiles + workers - 1) / workers;
     const int wid = blockIdx.x * kDecodeWarps + warp;
+    WorkerStart ws;
+    ws.s = -1;
+    if (a.worker_start && a.decode_all_workers == all_workers) {
+        const int4 lo4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + wid));
+        const int4 hi4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + wid) + 1);
+        ws = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+    }
+    const int total_tiles = ws.s != -1 ? ws.total_tiles : a.plan->total_tiles;   // all streams
+    int workers, per_worker;
+    decode_slices(total_tiles, all_workers, workers, per_worker);
     int g_tile = min(total_tiles, wid * per_worker);               // next global tile to load
     const int g_end = min(total_tiles, g_tile + per_worker);
 
@@ -147,10 +164,43 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
         tbl = blk;
     };
 
-    // Starts the run that contains global tile g_tile (g_tile < g_end).
+    // Common part of starting a run at tile `tile0` of stream (r_s, r_hkp).
+    auto start_run = [&](int tile0, int p0, int ctx, int t0row) {
+        const int ntile = min(r_tiles - tile0, g_end - g_tile);
+        r_tok = tile0 * kTile;
+        r_end = min(ctx, (tile0 + ntile) * kTile);
+        const int s_begin = p0 * HK + r_hkp * r_tiles;             // global tile range of the stream
+        const int first_w = s_begin / per_worker, last_w = (s_begin + r_tiles - 1) / per_worker;
+        const int stream = r_s * HK + r_hkp;
+        ++r_seq;
+        if (lane == 0)
+            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, {0, 0}};
+        g_tile += ntile;
+        r_first = true;
+        load_window(r_tok / BS);
+    };
+    // Later runs start at the first tile of the next stream.
     auto next_run = [&]() {
-        int tile0;
-        if (r_s < 0) {  // first run: locate the row by binary search in the prefix sums
+        if (++r_hkp == HK) {
+            r_hkp = 0;
+            do {
+                ++r_s;
+                r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
+            } while (r_tiles == 0);
+        }
+        r_tb = a.block_indices_begins[r_s];
+        r_nb = a.block_indices_begins[r_s + 1] - r_tb;
+        start_run(0, __ldcg(a.tile_prefix + r_s), a.past_lens[r_s] + 1, a.subsequence_begins[r_s]);
+    };
+    // The first run: from the record the plan step prepared, else by binary search in the prefix sums.
+    if (g_tile < g_end) {
+        int p0, ctx, t0row;
+        if (ws.s >= 0) {
+            r_s = ws.s;
+            p0 = ws.p0;
+            r_tiles = ws.r_tiles;
+            ctx = ws.ctx; r_tb = ws.tb; r_nb = ws.nb; t0row = ws.t0;
+        } else {
             const int key = g_tile / HK;
             int lo = 0, hi = a.num_sequences;  // tile_prefix[lo] <= key < tile_prefix[hi]
             while (hi - lo > 1) {
@@ -158,38 +208,17 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
                 if (__ldcg(a.tile_prefix + mid) <= key) lo = mid; else hi = mid;
             }
             r_s = lo;
-            const int p0 = __ldcg(a.tile_prefix + r_s);
+            p0 = __ldcg(a.tile_prefix + r_s);
             r_tiles = __ldcg(a.tile_prefix + r_s + 1) - p0;
-            const int off = g_tile - p0 * HK;
-            r_hkp = off / r_tiles;
-            tile0 = off % r_tiles;
-        } else {        // later runs start at the first tile of the next stream
-            tile0 = 0;
-            if (++r_hkp == HK) {
-                r_hkp = 0;
-                do {
-                    ++r_s;
-                    r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
-                } while (r_tiles == 0);
-            }
+            ctx = a.past_lens[r_s] + 1;
+            r_tb = a.block_indices_begins[r_s];
+            r_nb = a.block_indices_begins[r_s + 1] - r_tb;
+            t0row = a.subsequence_begins[r_s];
         }
-        const int p0 = __ldcg(a.tile_prefix + r_s);
-        const int ntile = min(r_tiles - tile0, g_end - g_tile);
-        const int ctx = a.past_lens[r_s] + 1;
-        r_tok = tile0 * kTile;
-        r_end = min(ctx, (tile0 + ntile) * kTile);
-        r_tb = a.block_indices_begins[r_s];
-        r_nb = a.block_indices_begins[r_s + 1] - r_tb;
-        const int s_begin = p0 * HK + r_hkp * r_tiles;             // global tile range of the stream
-        const int first_w = s_begin / per_worker, last_w = (s_begin + r_tiles - 1) / per_worker;
-        const int stream = r_s * HK + r_hkp;
-        ++r_seq;
-        if (lane == 0)
-            runs[r_seq % kRunRing] = RunRec{a.subsequence_begins[r_s], r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, {0, 0}};
-        g_tile += ntile;
-        r_first = true;
-        load_window(r_tok / BS);
-    };
+        const int off = g_tile - p0 * HK;
+        r_hkp = off / r_tiles;
+        start_run(off % r_tiles, p0, ctx, t0row);
+    }
 
     // Issues the next tile of the load stream into ring stage `slot` and records its descriptor.
     auto produce = [&](int slot) {
@@ -257,6 +286,10 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
     float m_run[ROWS], l_run[ROWS], z_run[ROWS];
     int hbase = 0, hcount = 0, t0 = 0;
 
+#ifdef PA_DECODE_PROF
+    unsigned long long prof_t[4] = {0, 0, 0, 0};
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[0]));
+#endif
 #pragma unroll
     for (int p = 0; p < NS - 1; ++p) produce(p);
 
@@ -276,6 +309,10 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
             cp_async_wait<NS - 1>();
             __syncwarp();
         }
+#ifdef PA_DECODE_PROF
+        if (it == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[1]));
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[2]));
+#endif
         const uint8_t* st = ring + slot * Cfg::STAGE;
         const int valid = d.valid;
 
@@ -550,20 +587,36 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
             const int hrow = g + 8 * r;
             if (hrow >= hcount) continue;
             float m = -INFINITY;
-            for (int j = 0; j < nparts; ++j) m = fmaxf(m, __ldcg(a.part_ml + ((long long)(fin.first_slot + j) * RT + hrow) * 2));
             float l = 0.f;
             float o[NDT][2];
 #pragma unroll
             for (int i = 0; i < NDT; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; }
-            for (int j = 0; j < nparts; ++j) {
-                const long long prow = (long long)(fin.first_slot + j) * RT + hrow;
-                const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + prow * 2));
-                const float f = fast_exp2(ml.x - m);
-                l += f * ml.y;
+            // the partials are read in groups of four with all loads of a group in flight together
+            for (int j0 = 0; j0 < nparts; j0 += 4) m = fmaxf(m, [&] {
+                float mm = -INFINITY;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (j0 + u < nparts) mm = fmaxf(mm, __ldcg(a.part_ml + ((long long)(fin.first_slot + j0 + u) * RT + hrow) * 2));
+                return mm;
+            }());
+            for (int j0 = 0; j0 < nparts; j0 += 4) {
+                float f[4];
+                long long prow[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const bool on = j0 + u < nparts;
+                    prow[u] = (long long)(fin.first_slot + (on ? j0 + u : 0)) * RT + hrow;
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + prow[u] * 2));
+                    f[u] = on ? fast_exp2(ml.x - m) : 0.f;
+                    l += f[u] * ml.y;
+                }
 #pragma unroll
                 for (int i = 0; i < NDT; ++i) {
-                    const float2 v = __ldcg(reinterpret_cast<const float2*>(a.part_o + prow * D + 8 * i + 2 * c));
-                    o[i][0] += f * v.x; o[i][1] += f * v.y;
+                    float2 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(a.part_o + prow[u] * D + 8 * i + 2 * c));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { o[i][0] += f[u] * v[u].x; o[i][1] += f[u] * v[u].y; }
                 }
             }
             const long long row = (long long)t0 * a.g.Hq + hbase + hrow;
@@ -575,6 +628,30 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, HI ? 2 : 3) decode_kernel(K
     }
     if constexpr (!U8) cp_async_wait<0>();
     if (__any_sync(0xffffffffu, bad_index) && lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
+#ifdef PA_DECODE_PROF
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[3]));
+    if (lane == 0 && wid % 61 == 0)
+        printf("decode prof wid %d sm-start %llu first-tile +%llu last-tile-ready +%llu end +%llu tiles %d\n", wid, prof_t[0] % 100000000ull,
+               prof_t[1] - prof_t[0], prof_t[2] - prof_t[0], prof_t[3] - prof_t[0], g_end - min(total_tiles, wid * per_worker));
+#endif
+}
+
+// no more workers than slices could ever exist (upper bound known on the host)
+long long decode_ctas(const KernelArgs& a, int per_sm, int sm_count) {
+    const long long max_slices = (a.max_tiles + kDecodeMinSlice - 1) / kDecodeMinSlice;
+    long long ctas = (long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count * kDecodeWaves;
+    return std::max(1LL, std::min(ctas, (max_slices + kDecodeWarps - 1) / kDecodeWarps));
+}
+
+template <int D, int BS, int CACHE>
+int occupancy_t(const KernelArgs& a) {
+    using Cfg = DecodeCfg<D, BS, CACHE>;
+    const bool hi = a.g.Hq / a.g.Hkv > 8;
+    auto kern = hi ? decode_kernel<D, BS, CACHE, true> : decode_kernel<D, BS, CACHE, false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return 0;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeWarps * 32, Cfg::SMEM) != cudaSuccess) return 0;
+    return per_sm;
 }
 
 template <int D, int BS, int CACHE>
@@ -589,12 +666,9 @@ cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeWarps * 32, Cfg::SMEM);
     if (e != cudaSuccess) return e;
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
-    // no more workers than slices could ever exist (upper bound known on the host)
-    const long long max_slices = (a.max_tiles + kMinSlice - 1) / kMinSlice;
-    long long ctas = (long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count;
-    ctas = std::min(ctas, (max_slices + kDecodeWarps - 1) / kDecodeWarps);
+    const long long ctas = decode_ctas(a, per_sm, sm_count);
     if (ev0) cudaEventRecord(ev0, stream);
-    kern<<<(unsigned)std::max(1LL, ctas), kDecodeWarps * 32, Cfg::SMEM, stream>>>(a);
+    kern<<<(unsigned)ctas, kDecodeWarps * 32, Cfg::SMEM, stream>>>(a);
     if (ev1) cudaEventRecord(ev1, stream);
     ++*launches;
     return cudaGetLastError();
@@ -612,7 +686,25 @@ cudaError_t launch_decode_c(const KernelArgs& a, cudaStream_t stream, int sm_cou
 
 }  // namespace
 
-int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps; }
+int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps * kDecodeWaves; }
+
+int decode_launch_workers(const KernelArgs& a, int sm_count) {
+    if (a.num_sequences <= 0) return 0;
+    int per_sm = 0;
+#define PA_OCC(D_, BS_)                                                                           \
+    switch (a.g.cache) {                                                                          \
+        case PA_DTYPE_U8: per_sm = occupancy_t<D_, BS_, PA_DTYPE_U8>(a); break;                   \
+        case PA_DTYPE_F16: per_sm = occupancy_t<D_, BS_, PA_DTYPE_F16>(a); break;                 \
+        case PA_DTYPE_BF16: per_sm = occupancy_t<D_, BS_, PA_DTYPE_BF16>(a); break;               \
+    }
+    if (a.g.D == 128 && a.g.bs == 32) { PA_OCC(128, 32) }
+    else if (a.g.D == 128 && a.g.bs == 16) { PA_OCC(128, 16) }
+    else if (a.g.D == 64 && a.g.bs == 32) { PA_OCC(64, 32) }
+    else if (a.g.D == 64 && a.g.bs == 16) { PA_OCC(64, 16) }
+#undef PA_OCC
+    if (per_sm < 1) return 0;
+    return (int)decode_ctas(a, per_sm, sm_count) * kDecodeWarps;
+}
 
 cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {
     if (a.num_sequences <= 0) return cudaSuccess;

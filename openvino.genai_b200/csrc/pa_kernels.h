@@ -19,6 +19,28 @@ struct PlanHeader {
     int pad;
 };
 
+// Where a decode worker's slice of the global tile sequence starts, prepared by the plan step so
+// that the worker's first load is one 32-byte record instead of a binary search.
+struct __align__(16) WorkerStart {
+    int s;            // decode row that holds the slice's first tile; -1: not prepared, search
+    int p0;           // tile_prefix[s]
+    int r_tiles;      // tiles of row s (per head tile)
+    int total_tiles;  // of the step, all streams
+    int ctx;          // past_lens[s] + 1
+    int tb, nb;       // block table of the row: begin and length
+    int t0;           // row of the token in query / output
+};
+
+constexpr int kDecodeMinSlice = 4;   // a worker is given at least this many tiles
+
+// The slice every worker takes: `workers` of the launched `all_workers` get `per_worker` tiles each.
+__host__ __device__ inline void decode_slices(int total_tiles, int all_workers, int& workers, int& per_worker) {
+    const int want = (total_tiles + kDecodeMinSlice - 1) / kDecodeMinSlice;
+    workers = all_workers < want ? all_workers : want;
+    if (workers < 1) workers = 1;
+    per_worker = (total_tiles + workers - 1) / workers;
+}
+
 // Everything a kernel needs, passed by value.  All pointers are device memory.
 struct KernelArgs {
     CacheGeom g;
@@ -53,6 +75,8 @@ struct KernelArgs {
     int* tile_prefix;      // [num_sequences + 1] exclusive prefix sum of tiles per row (one head tile)
     int* stream_done;      // [num_sequences * HK] partials of the stream published so far
     int* ptile_prefix;     // [num_sequences + 1] exclusive prefix sum of prefill q tiles per row (one kv head)
+    int decode_all_workers;      // warps the decode launch will have (0: the plan prepares no start records)
+    WorkerStart* worker_start;   // [decode_all_workers], may be null
     long long max_tiles;   // upper bound of total_tiles known on the host
     int rows_per_tile;     // q heads per head tile: min(G, 16)
     float* part_o;         // partial outputs    [slot = stream + worker][rows_per_tile][D]
@@ -79,6 +103,8 @@ cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count
 
 // Upper bound of the decode kernel's worker (warp) count, for sizing the partial-result scratch.
 int decode_max_workers(int sm_count);
+// Warps the decode launch of this step will have (the plan step prepares one start record each).
+int decode_launch_workers(const KernelArgs& a, int sm_count);
 
 // Attention over rows with more than one new token (prefill chunks): generic CUDA-core kernel.
 cudaError_t launch_prefill(const KernelArgs& a, cudaStream_t stream, int* launches);

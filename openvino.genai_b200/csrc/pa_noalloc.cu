@@ -129,6 +129,8 @@ extern "C" int pa_b200_decode_step_static(const pa_model_desc* desc, const pa_fo
     unsigned char* base = st.scratch;  // device address from cudaGetSymbolAddress, never the symbol's name
     k.status = reinterpret_cast<uint32_t*>(base + o_status);
     k.plan = reinterpret_cast<pa::PlanHeader*>(base + o_hdr);
+    k.worker_start = nullptr;      // the workers locate their slices themselves on this path
+    k.decode_all_workers = 0;
     k.tile_prefix = reinterpret_cast<int*>(base + o_prefix);
     k.ptile_prefix = reinterpret_cast<int*>(base + o_pprefix);
     k.stream_done = reinterpret_cast<int*>(base + o_done);
