@@ -34,7 +34,7 @@ constexpr int kPerThread = 8;                         // elements a producer thr
 constexpr int kChunk = kProducerThreads * kPerThread; // elements per filter round
 constexpr int kMaxTopK = 1024;                        // heap capacity in shared memory
 
-struct Cand {
+struct __align__(8) Cand {
     float v;
     int idx;
 };
@@ -62,8 +62,10 @@ __device__ void adjust_heap(Cand* h, int hole, int len, Cand value) {
     int child = hole;
     while (child < (len - 1) / 2) {
         child = 2 * (child + 1);
-        if (h[child].v > h[child - 1].v) --child;
-        h[hole] = h[child];
+        const Cand right = h[child], left = h[child - 1];   // both children in flight together
+        const bool take_left = right.v > left.v;
+        if (take_left) --child;
+        h[hole] = take_left ? left : right;
         hole = child;
     }
     if ((len & 1) == 0 && child == (len - 2) / 2) {
@@ -92,6 +94,70 @@ __device__ __forceinline__ void replace_min(Cand* h, int k, Cand x) {
     }
     h[k - 1] = x;
     push_heap_from(h, k - 1, 0, x);
+}
+
+// replace_min for the replay lane of the top-k path: the same comparisons and moves, written with
+// 32-bit shared-memory addresses and paired 8-byte accesses so that one level of the heap costs
+// one shared-memory round trip.  The writes of the popped minimum and of x into slot k - 1 that
+// libstdc++ performs in between are dead (the slot is not read before it is overwritten).
+__device__ __forceinline__ void lds_cand(uint32_t addr, float& v, int& i) {
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=f"(v), "=r"(i) : "r"(addr));
+}
+__device__ __forceinline__ void sts_cand(uint32_t addr, float v, int i) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "f"(v), "r"(i) : "memory");
+}
+__device__ __forceinline__ void replace_min_shared(uint32_t base, int k, float xv, int xi) {
+    if (k > 1) {
+        const int len = k - 1;
+        float lastv;
+        int lasti;
+        lds_cand(base + 8u * len, lastv, lasti);
+        // __adjust_heap(first, 0, len, last)
+        int hole = 0, child = 0;
+        const int half = (len - 1) / 2;
+        while (child < half) {
+            child = 2 * (child + 1);
+            float rv, lv;
+            int ri, li;
+            lds_cand(base + 8u * child, rv, ri);
+            lds_cand(base + 8u * (child - 1), lv, li);
+            const bool take_left = rv > lv;
+            if (take_left) --child;
+            sts_cand(base + 8u * hole, take_left ? lv : rv, take_left ? li : ri);
+            hole = child;
+        }
+        if ((len & 1) == 0 && child == (len - 2) / 2) {
+            child = 2 * (child + 1);
+            float v;
+            int i;
+            lds_cand(base + 8u * (child - 1), v, i);
+            sts_cand(base + 8u * hole, v, i);
+            hole = child - 1;
+        }
+        // __push_heap(first, hole, 0, last)
+        while (hole > 0) {
+            const int parent = (hole - 1) / 2;
+            float pv;
+            int pi;
+            lds_cand(base + 8u * parent, pv, pi);
+            if (!(pv > lastv)) break;
+            sts_cand(base + 8u * hole, pv, pi);
+            hole = parent;
+        }
+        sts_cand(base + 8u * hole, lastv, lasti);
+    }
+    // push_heap(first, first + k) with x in the last slot
+    int hole = k - 1;
+    while (hole > 0) {
+        const int parent = (hole - 1) / 2;
+        float pv;
+        int pi;
+        lds_cand(base + 8u * parent, pv, pi);
+        if (!(pv > xv)) break;
+        sts_cand(base + 8u * hole, pv, pi);
+        hole = parent;
+    }
+    sts_cand(base + 8u * hole, xv, xi);
 }
 
 // ---- libstdc++ partial_sort / sort on (value, index) pairs with comp(a, b) = a.v > b.v --------------
@@ -386,7 +452,7 @@ __device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float*
     *out_idx = v[pick].idx;
 }
 
-__global__ void __launch_bounds__(kThreads, 3) sampler_kernel(StepArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     Shared& sh = *reinterpret_cast<Shared*>(smem_raw);
     const int r = blockIdx.x;
@@ -477,6 +543,7 @@ __global__ void __launch_bounds__(kThreads, 3) sampler_kernel(StepArgs a) {
             // consumer: re-checks the survivors of round c, 32 at a time, while the producers filter
             // round c + 1; lane 0 owns the heap
             float heap_min = sh.heap[0].v;
+            const uint32_t heap_addr = (uint32_t)__cvta_generic_to_shared(sh.heap);
             for (int c = 0; c < rounds; ++c) {
                 const int b = c & 1;
                 named_sync(1 + b, kThreads);           // full[b]
@@ -491,14 +558,18 @@ __global__ void __launch_bounds__(kThreads, 3) sampler_kernel(StepArgs a) {
                         const float xv = __shfl_sync(0xffffffffu, x.v, src);
                         const int xi = __shfl_sync(0xffffffffu, x.idx, src);
                         if (xv > heap_min) {           // the minimum may have risen since the ballot
-                            if (lane == 0) replace_min(sh.heap, K, Cand{xv, xi});
+                            if (lane == 0) replace_min_shared(heap_addr, K, xv, xi);
                             __syncwarp();
                             heap_min = sh.heap[0].v;
+                            // the minimum rose: drop the survivors it has overtaken in one vote
+                            mask &= __ballot_sync(0xffffffffu, i < n && x.v > heap_min);
                         }
                     }
                 }
                 if (lane == 0) *reinterpret_cast<volatile float*>(&sh.tau) = heap_min;
                 __syncwarp();
+                __threadfence_block();
+                if (c == 0 && rounds > 1) named_arrive(7, kThreads);   // round 1 is filtered with the minimum reached after round 0
                 named_arrive(3 + b, kThreads);         // empty[b]
             }
         } else {
@@ -521,6 +592,9 @@ __global__ void __launch_bounds__(kThreads, 3) sampler_kernel(StepArgs a) {
                 const int b = c & 1;
                 if (c + 1 < rounds) load_round(c + 1, xn);  // in flight while this round is compacted
                 if (c >= 2) named_sync(3 + b, kThreads);    // wait until the consumer drained buffer b
+                // The first elements raise the heap minimum quickly; filtering round 1 with the stale
+                // minimum of the first K elements would let nearly all of it through.
+                if (c == 1) named_sync(7, kThreads);
                 const float tau = *reinterpret_cast<volatile float*>(&sh.tau);
                 const long long base = start + (long long)c * kChunk + (long long)ptid * kPerThread;
                 int mine = 0;
