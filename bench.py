@@ -358,6 +358,112 @@ def run_secondary(args):
     print(json.dumps(line), flush=True)
 
 
+def run_engine_step(args):
+    """BASELINE.json configs[4]: one engine step of a sharded batch - Llama-3-70B attention shape,
+    1024 sequences with log-uniform contexts over all ranks (balanced by context length), u8 cache
+    with block size 16; paged decode, then the Sampler over [rows, 128256] f32 logits (T = 1,
+    top_p 0.95: the full-vocabulary path), then the all-gather of the sampled ids.  Reports whole-job
+    tokens per second; weak in sequences per rank is not assumed: the 1024 sequences are split."""
+    import math
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    pkg.load_library()
+    from openvino_genai_b200 import workloads, sharding, sampler as sampler_mod, _sampler_abi as SA
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    total_seqs, vocab = 1024, 128256
+    rng = np.random.default_rng(1005)
+    past_all = np.exp(rng.uniform(math.log(1024), math.log(32768), size=total_seqs)).astype(np.int64)
+    mine = sharding.shard_sequences(past_all + 1, world)[rank]
+    past = past_all[mine]
+    need = int(((past + 1 + 15) // 16).sum())
+    wl = workloads.make_workload("llama3_70b_u8_step", hq=64, hkv=8, d=128, bs=16, act=torch.bfloat16, cache="u8", past=past,
+                                 new=np.ones(len(past), np.int64), num_blocks=need + 16, seed=1005 + 97 * rank)
+    op = pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, local)
+    kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
+    workloads.fill_cache_on_device(op, wl, kc, vc)
+    q, k, v = workloads.random_activations(wl, dev)
+    out = torch.empty_like(q)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    stream = torch.cuda.Stream(dev)
+    dargs = op.make_args(q, k, v, out, kc, vc, t(wl.past_lens), t(wl.subsequence_begins), t(wl.block_indices), t(wl.block_indices_begins),
+                         wl.scale, wl.max_context_len, stream=stream.cuda_stream)
+    n = len(past)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4242 + rank)
+    logits = torch.randn((n, vocab), generator=gen, device=dev, dtype=torch.float32) * 2.0
+    rows = np.zeros(n, dtype=np.dtype(SA.ROW_DTYPE))
+    rows["logits_row"] = np.arange(n)
+    rows["top_k"] = SA.TOP_K_OFF
+    rows["do_sample"] = 1
+    rows["temperature"] = 1.0
+    rows["top_p"] = 0.95
+    rows["repetition_penalty"] = 1.0
+    rows["rand_u"] = np.random.default_rng(77 + rank).random(n, dtype=np.float32)
+    smp = sampler_mod.SamplerStep(local)
+    staged = smp.stage(rows)
+    index = torch.from_numpy(mine).to(dev)
+    torch.cuda.synchronize(dev)
+
+    def step():
+        op.forward_args(dargs)
+        tok, _ = smp.step(logits, staged, stream=stream.cuda_stream)
+        if world > 1:
+            with torch.cuda.stream(stream):
+                return sharding.all_gather_token_ids(tok, index, total_seqs)
+        return tok
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        ids = step()
+    barrier()
+    assert int((ids < 0).sum().item()) == 0, "a sampled id is missing after the all-gather"
+    launches0 = op.launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    stats = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    sums = torch.tensor([float(wl.decode_kv_bytes()), float(op.launch_count() - launches0 + args.steps)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        ms = float(stats[0]) / args.steps
+        line = {"metric": "engine_step_tokens_per_s", "value": round(total_seqs / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16 mma / f32 accumulate; f32 sampler", "data": "synthetic",
+                "config": {"workload": "llama3_70b_u8_step", "sequences_total": total_seqs, "contexts": "log-uniform [1024, 32768]",
+                           "kv_cache": "u8 by-token asymmetric, block 16", "vocab": vocab, "sampler": "T 1, top_p 0.95 (full vocabulary)",
+                           "exchange": "all-gather of sampled ids" if world > 1 else "none (one rank)",
+                           "parallelism": f"sequences balanced by context length over {world} rank(s)", "l2_policy": "KV bytes per step exceed L2"},
+                "kv_gbps": round(float(sums[0]) / (ms * 1e-3) / 1e9, 1), "gpu_launches": int(sums[1]), "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -370,6 +476,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "llama3_70b_u8_step":
+        run_engine_step(args)
     elif args.workload in SECONDARY:
         if int(os.environ.get("WORLD_SIZE", "1")) > 1:
             raise SystemExit("the secondary workloads run on one GPU")
