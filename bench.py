@@ -384,7 +384,9 @@ def run_engine_step(args):
     total_seqs, vocab = 1024, 128256
     rng = np.random.default_rng(1005)
     past_all = np.exp(rng.uniform(math.log(1024), math.log(32768), size=total_seqs)).astype(np.int64)
-    mine = sharding.shard_sequences(past_all + 1, world)[rank]
+    shards = sharding.shard_sequences(past_all + 1, world)
+    mine = shards[rank]
+    shard_sizes = [len(x) for x in shards]
     past = past_all[mine]
     need = int(((past + 1 + 15) // 16).sum())
     wl = workloads.make_workload("llama3_70b_u8_step", hq=64, hkv=8, d=128, bs=16, act=torch.bfloat16, cache="u8", past=past,
@@ -420,7 +422,7 @@ def run_engine_step(args):
         tok, _ = smp.step(logits, staged, stream=stream.cuda_stream)
         if world > 1:
             with torch.cuda.stream(stream):
-                return sharding.all_gather_token_ids(tok, index, total_seqs)
+                return sharding.all_gather_token_ids(tok, index, total_seqs, counts=shard_sizes)
         return tok
 
     def barrier():

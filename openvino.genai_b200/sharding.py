@@ -29,14 +29,19 @@ def shard_sequences(context_lens: Sequence[int], world_size: int) -> List[np.nda
 
 
 def all_gather_token_ids(local_ids: torch.Tensor, local_index: torch.Tensor, total: int,
-                         group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+                         group: Optional[dist.ProcessGroup] = None, counts: Optional[Sequence[int]] = None) -> torch.Tensor:
     """All-gathers this rank's sampled ids (int64 [n_local], for the global sequence indices
     `local_index`) into an int64 [total] tensor in global sequence order on every rank.
-    Ranks may own different numbers of sequences: shares are padded to the largest one."""
+    Ranks may own different numbers of sequences: shares are padded to the largest one.
+    `counts` (sequences per rank) saves the size exchange and its host synchronisation when the
+    partition is known on every rank, as it is after shard_sequences()."""
     world = dist.get_world_size(group)
-    n_local = torch.tensor([local_ids.numel()], dtype=torch.int64, device=local_ids.device)
-    counts = [torch.zeros_like(n_local) for _ in range(world)]
-    dist.all_gather(counts, n_local, group=group)
+    if counts is not None:
+        counts = [torch.tensor([int(c)], dtype=torch.int64) for c in counts]
+    else:
+        n_local = torch.tensor([local_ids.numel()], dtype=torch.int64, device=local_ids.device)
+        counts = [torch.zeros_like(n_local) for _ in range(world)]
+        dist.all_gather(counts, n_local, group=group)
     cap = int(max(int(c.item()) for c in counts))
     packed = torch.full((2, cap), -1, dtype=torch.int64, device=local_ids.device)
     packed[0, : local_ids.numel()] = local_ids

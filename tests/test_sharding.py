@@ -25,6 +25,8 @@ def _worker(rank, world, port, lens, result_dir):
         mine = torch.from_numpy(shards[rank])
         ids = mine * 10 + rank                                   # a recognisable "sampled id" per sequence
         out = sharding.all_gather_token_ids(ids, mine, len(lens))
+        same = sharding.all_gather_token_ids(ids, mine, len(lens), counts=[len(p) for p in shards])
+        assert torch.equal(out, same), "known partition sizes must give the same result as the size exchange"
         mx = sharding.max_over_ranks(float(rank + 1), "cpu")
         np.save(os.path.join(result_dir, f"out{rank}.npy"), out.numpy())
         np.save(os.path.join(result_dir, f"mx{rank}.npy"), np.array([mx]))
