@@ -358,6 +358,55 @@ def run_secondary(args):
     print(json.dumps(line), flush=True)
 
 
+def run_sampler(args):
+    """BASELINE.json configs[3]: one Sampler step over 256 x 151936 f32 logits (top-k path or greedy),
+    logits resident on the device and restored from a pristine copy before every step (the step
+    applies the penalties in place).  Reports microseconds per step and the HBM roofline of one
+    mandatory read of the logits."""
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    pkg.load_library()
+    from openvino_genai_b200 import workloads, sampler as sampler_mod
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    greedy = args.workload == "qwen25_sampler_greedy"
+    logits_h, par, hist = workloads.config_qwen_sampler(greedy=greedy)
+    pristine = torch.from_numpy(logits_h).to(dev)
+    work = pristine.clone()
+    smp = sampler_mod.SamplerStep(0)
+    staged = smp.stage(par, hist)
+    stream = torch.cuda.Stream(dev)
+    times = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    with torch.cuda.stream(stream):
+        for it in range(max(args.warmup, 3) + args.steps):
+            work.copy_(pristine)      # also evicts the previous step's logits from L2 (311 MB moved)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            smp.step(work, staged, stream=stream.cuda_stream)
+            e1.record(stream)
+            stream.synchronize()
+            if it >= max(args.warmup, 3):
+                times.append(e0.elapsed_time(e1) * 1e3)
+    clocks = sampler.stop()
+    us = statistics.median(times)
+    peak, peak_kind = load_peaks()
+    achieved = logits_h.nbytes / (us * 1e-6) / 1e9
+    line = {"metric": "sampler_step_us", "value": round(us, 1), "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(us / 1e3, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "rows": int(logits_h.shape[0]), "vocab": int(logits_h.shape[1]),
+                       "sampling": "greedy + penalties" if greedy else "top_k 50, T 0.7, top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1",
+                       "history": "1024 generated ids per row", "l2_policy": "logits rewritten from a pristine copy before every step"},
+            "min_us": round(min(times), 1),
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                         "kernel": "sampler_kernel", "algorithmic_bytes_per_launch": int(logits_h.nbytes), "peak_source": peak_kind},
+            "gpu_launches": args.steps, "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
 def run_engine_step(args):
     """BASELINE.json configs[4]: one engine step of a sharded batch - Llama-3-70B attention shape,
     1024 sequences with log-uniform contexts over all ranks (balanced by context length), u8 cache
@@ -478,6 +527,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in ("qwen25_sampler_topk", "qwen25_sampler_greedy"):
+        run_sampler(args)
     elif args.workload == "llama3_70b_u8_step":
         run_engine_step(args)
     elif args.workload in SECONDARY:

@@ -206,3 +206,47 @@ def fill_cache_on_device(op, wl: AttnWorkload, key_cache: torch.Tensor, value_ca
             op._check(op.lib.pa_b200_write_kv(op._h, __import__("ctypes").byref(args)))
             torch.cuda.synchronize(dev)
         s = e
+
+
+# ---- Sampler workloads ---------------------------------------------------------------------------
+def sampler_history(rng: np.random.Generator, rows: int, vocab: int, generated_len: int, prompt_len: int = 0):
+    """CSR history of distinct ids per row for the Sampler step: prompt ids (flag 1), generated ids
+    with their counts (flag 2), as `(offsets int64, ids int32, meta uint32)`."""
+    offs, ids, meta = [0], [], []
+    for _ in range(rows):
+        gen = rng.integers(0, vocab, size=generated_len)
+        prompt = rng.integers(0, vocab, size=prompt_len)
+        uniq = {}
+        for t in prompt:
+            uniq.setdefault(int(t), [0, 0])[0] = 1
+        for t in gen:
+            uniq.setdefault(int(t), [0, 0])[1] += 1
+        for t in sorted(uniq):
+            flag = (1 if uniq[t][0] else 0) | (2 if uniq[t][1] else 0)
+            ids.append(t)
+            meta.append((uniq[t][1] << 3) | flag)
+        offs.append(len(ids))
+    return np.array(offs, np.int64), np.array(ids, np.int32), np.array(meta, np.uint32)
+
+
+def config_qwen_sampler(rows: int = 256, vocab: int = 151936, greedy: bool = False, history: int = 1024, seed: int = 1004):
+    """Qwen2.5 vocabulary, 256 rows: logits N(0, 4) with 8 spikes of +15 per row, T 0.7, top_k 50,
+    top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1 over a 1024-token generated history.
+    Returns (logits f32 [rows, vocab], packed row parameters, history)."""
+    from . import _sampler_abi as SA
+    rng = np.random.default_rng(seed)
+    logits = (rng.standard_normal((rows, vocab)) * 2.0).astype(np.float32)
+    for r in range(rows):
+        logits[r, rng.choice(vocab, size=8, replace=False)] += np.float32(15.0)
+    hist = sampler_history(rng, rows, vocab, history)
+    par = np.zeros(rows, dtype=np.dtype(SA.ROW_DTYPE))
+    par["logits_row"] = np.arange(rows)
+    par["top_k"] = SA.TOP_K_OFF if greedy else 50
+    par["do_sample"] = 0 if greedy else 1
+    par["temperature"] = 1.0 if greedy else 0.7
+    par["top_p"] = 1.0 if greedy else 0.9
+    par["repetition_penalty"] = 1.1
+    par["presence_penalty"] = 0.2
+    par["frequency_penalty"] = 0.1
+    par["rand_u"] = np.random.default_rng(seed + 1).random(rows, dtype=np.float32)
+    return logits, par, hist
