@@ -177,3 +177,40 @@ def test_copy_blocks():
     k = kc.cpu().numpy()
     for f in free:
         assert np.array_equal(k[f * bb:(f + 1) * bb], k[src * bb:(src + 1) * bb])
+
+
+@pytest.mark.parametrize("cache,bs", [("u8", 32), ("u8", 16), ("f16", 32)])
+def test_contexts_on_block_and_tile_boundaries(cache, bs):
+    """Decode rows whose context ends exactly on, one before and one after a block / tile boundary
+    (the first token of a sequence included), and chunks that start or end on one."""
+    act = torch.float16 if cache == "f16" else torch.bfloat16
+    past = [0, 15, 16, 31, 32, 63, 64, 127, 128, 255, 0, 0, 63, 64, 33]
+    new = [1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 2, 128, 65, 64, 31]
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=bs, act=act, cache=cache, past=past, new=new, seed=97)
+    _check(H.run_both(wl), cache, act)
+
+
+def test_score_window_longer_than_the_chunk_is_clamped():
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[100, 0, 40], new=[1, 5, 3], seed=101)
+    wl.score_aggregation_window = np.array([7, 64, 3], np.int32)   # 7 > 1 and 64 > 5: clamped to the chunk
+    res = H.run_both(wl)
+    _check(res, "u8", torch.bfloat16)
+    ref, got = res["scores_ref"], res["scores_gpu"]
+    assert np.abs(got - ref).max() <= 1e-2 * max(1.0, np.abs(ref).max())
+    # one decode row with 8 q heads: its scores are one probability distribution per head
+    assert abs(got[:101].sum() - 8.0) < 1e-2
+
+
+def test_empty_step_is_a_no_op():
+    import ctypes as C
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[10], new=[1], seed=3)
+    op = H.make_op(wl)
+    kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
+    dev = kc.device
+    z = torch.zeros((0, 8 * 128), dtype=torch.bfloat16, device=dev)
+    zk = torch.zeros((0, 2 * 128), dtype=torch.bfloat16, device=dev)
+    zi = torch.zeros(1, dtype=torch.int32, device=dev)
+    before = op.launch_count()
+    args = op.make_args(z, zk, zk, z, kc, vc, zi[:0], zi, zi[:0], zi, wl.scale, 0)
+    assert op.lib.pa_b200_forward(op._h, C.byref(args)) == 0
+    assert op.launch_count() == before and op.device_status() == 0
