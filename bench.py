@@ -466,8 +466,10 @@ def run_engine_step(args):
     index = torch.from_numpy(mine).to(dev)
     torch.cuda.synchronize(dev)
 
-    def step():
+    def step(mid=None):
         op.forward_args(dargs)
+        if mid is not None:
+            mid.record(stream)
         tok, _ = smp.step(logits, staged, stream=stream.cuda_stream)
         if world > 1:
             with torch.cuda.stream(stream):
@@ -495,6 +497,13 @@ def run_engine_step(args):
     e1.record(stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    # where the step's time goes: one more step with an event between the operator and the sampler
+    p0, p1, p2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    p0.record(stream)
+    step(p1)
+    p2.record(stream)
+    barrier()
+    parts = {"attention_ms": round(p0.elapsed_time(p1), 4), "sampler_and_exchange_ms": round(p1.elapsed_time(p2), 4)}
     stats = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     sums = torch.tensor([float(wl.decode_kv_bytes()), float(op.launch_count() - launches0 + args.steps)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -509,7 +518,7 @@ def run_engine_step(args):
                            "kv_cache": "u8 by-token asymmetric, block 16", "vocab": vocab, "sampler": "T 1, top_p 0.95 (full vocabulary)",
                            "exchange": "all-gather of sampled ids" if world > 1 else "none (one rank)",
                            "parallelism": f"sequences balanced by context length over {world} rank(s)", "l2_policy": "KV bytes per step exceed L2"},
-                "kv_gbps": round(float(sums[0]) / (ms * 1e-3) / 1e9, 1), "gpu_launches": int(sums[1]), "clocks": clocks}
+                "kv_gbps": round(float(sums[0]) / (ms * 1e-3) / 1e9, 1), "parts_rank0": parts, "gpu_launches": int(sums[1]), "clocks": clocks}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

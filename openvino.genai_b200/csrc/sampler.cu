@@ -302,13 +302,43 @@ __device__ __forceinline__ uint32_t float_key(float x) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// Calls fn(value, index) once for every element of a row, in no particular order. 16-byte loads,
+// four of them in flight per thread: with one 4-byte load per iteration a pass over the row is bound
+// by the latency of that load, not by bandwidth.
+template <class F>
+__device__ __forceinline__ void for_row(const float* row, long long V, int tid, F&& fn) {
+    if ((reinterpret_cast<uintptr_t>(row) & 15) != 0) {
+        for (long long i = tid; i < V; i += kThreads) fn(row[i], i);
+        return;
+    }
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    const long long n4 = V >> 2;
+    long long i = tid;
+    for (; i + 3 * kThreads < n4; i += 4 * kThreads) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = r4[i + u * kThreads];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long e = 4 * (i + u * kThreads);
+            fn(v[u].x, e); fn(v[u].y, e + 1); fn(v[u].z, e + 2); fn(v[u].w, e + 3);
+        }
+    }
+    for (; i < n4; i += kThreads) {
+        const float4 v = r4[i];
+        fn(v.x, 4 * i); fn(v.y, 4 * i + 1); fn(v.z, 4 * i + 2); fn(v.w, 4 * i + 3);
+    }
+    for (long long j = 4 * n4 + tid; j < V; j += kThreads) fn(row[j], j);
+}
+
 struct Shared {
     Cand heap[kMaxTopK];
     union {
         Cand cand[2][kChunk];          // top-k path: survivors of two filter rounds
         struct {                       // full-vocabulary path: radix histograms
-            unsigned int hist_cnt[2048];
             unsigned long long hist_mass[2048];
+            unsigned int hist_piece[3][2048];      // the same masses while they are being added, in pieces
+            unsigned long long first_mass[2048];   // first level of the top-p descent, kept for the draw
         };
     };
     int cand_count[2];
@@ -638,11 +668,13 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     const float T = p.temperature;
     const float f = 1.0f / T;
     float mx = -CUDART_INF_F;
-    for (long long i = tid; i < V; i += kThreads) mx = fmaxf(mx, row[i]);
+    for_row(row, V, tid, [&](float x, long long) { mx = fmaxf(mx, x); });
     mx = block_reduce(mx, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
-    auto weight = [&](float x) { return T == 1.0f ? exp_as_float(x - mx) : exp_as_float((x - mx) * f); };
+    // single-precision expf here: this path does not reproduce the reference's order of summation
+    // anyway, and the double-precision form costs an order of magnitude more over a whole vocabulary
+    auto weight = [&](float x) { return T == 1.0f ? expf(x - mx) : expf((x - mx) * f); };
     double dsum = 0.0;
-    for (long long i = tid; i < V; i += kThreads) dsum += (double)weight(row[i]);
+    for_row(row, V, tid, [&](float x, long long) { dsum += (double)weight(x); });
     dsum = block_reduce(dsum, 0.0, [](double x, double y) { return x + y; }, sh.red_d);
     const float norm = (float)dsum;
     auto prob = [&](float x) { return __fdiv_rn(weight(x), norm); };
@@ -650,11 +682,89 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     const bool min_p_active = p.min_p > 0.0f;
     const bool top_p_active = p.top_p != 1.0f;
     // probabilities as 2^-40 fixed point so that sums do not depend on the order of addition
-    auto fixed = [](float pr) { return (unsigned long long)((double)pr * 1099511627776.0); };
+    // (the product with 2^40 is exact in single precision, so this equals the double-precision form)
+    auto fixed = [](float pr) { return __float2ull_rz(pr * 1099511627776.0f); };
     const float pmax = prob(mx);
     const float min_thr = min_p_active ? (float)(double)p.min_p * pmax : -1.0f;
 
+    // One histogram level over the elements whose key matches `prefix` above `shift + bits`.
+    // Most of a row falls into a handful of first-level bins, so lanes of a warp collide all the time:
+    // the masses are therefore added as three pieces (14 + 14 + 13 bits) with native 32-bit shared
+    // atomics, which resolve collisions in hardware, instead of 64-bit ones (a compare-and-swap loop).
+    // A piece's sum stays below 2^32 for rows of fewer than 2^18 elements; longer rows add 64-bit.
+    const bool pieces = V < (1ll << 18);
+    auto build_level = [&](uint32_t prefix, int shift, int bits, bool first, uint32_t lo_key) {
+        const int nb = 1 << bits;
+        for (int i = tid; i < nb; i += kThreads) {
+            sh.hist_mass[i] = 0;
+            sh.hist_piece[0][i] = 0; sh.hist_piece[1][i] = 0; sh.hist_piece[2][i] = 0;
+        }
+        __syncthreads();
+        const uint32_t hi_mask = first ? 0u : (0xffffffffu << (shift + bits));
+        for_row(row, V, tid, [&](float x, long long) {
+            const uint32_t k = float_key(x);
+            if (k < lo_key || (k & hi_mask) != prefix) return;
+            const float pr = prob(x);
+            if (pr < min_thr) return;
+            const int bin = (k >> shift) & (nb - 1);
+            const unsigned long long m = fixed(pr);
+            if (pieces) {
+                atomicAdd(&sh.hist_piece[0][bin], (unsigned int)(m & 0x3fffu));
+                atomicAdd(&sh.hist_piece[1][bin], (unsigned int)((m >> 14) & 0x3fffu));
+                atomicAdd(&sh.hist_piece[2][bin], (unsigned int)(m >> 28));
+            } else {
+                atomicAdd(&sh.hist_mass[bin], m);
+            }
+        });
+        __syncthreads();
+        if (pieces) {
+            for (int i = tid; i < nb; i += kThreads)
+                sh.hist_mass[i] = (unsigned long long)sh.hist_piece[0][i] + ((unsigned long long)sh.hist_piece[1][i] << 14) +
+                                  ((unsigned long long)sh.hist_piece[2][i] << 28);
+            __syncthreads();
+        }
+    };
+    // Walk the bins from the highest down, starting at mass `start`: sel_bin = the first bin at which the
+    // running mass exceeds `thr`, sel_mass_above = the mass before it. When no bin does, sel_bin = -1
+    // and sel_mass_above = the whole mass.
+    auto select_bin = [&](int nb, unsigned long long start, unsigned long long thr) {
+        if (warp == 0) {
+            const int per = nb >> 5;
+            const int top = nb - 1 - lane * per;    // lane 0 owns the highest bins
+            unsigned long long mine = 0;
+            for (int j = 0; j < per; ++j) mine += sh.hist_mass[top - j];
+            unsigned long long incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += u;
+            }
+            const unsigned long long before = start + incl - mine;
+            const uint32_t hit = __ballot_sync(0xffffffffu, before + mine > thr);
+            if (hit) {
+                if (lane == __ffs(hit) - 1) {
+                    unsigned long long acc = before;
+                    int sel = top - per + 1;
+                    for (int j = 0; j < per; ++j) {
+                        const unsigned long long mj = sh.hist_mass[top - j];
+                        if (acc + mj > thr) { sel = top - j; break; }
+                        acc += mj;
+                    }
+                    sh.sel_bin = sel;
+                    sh.sel_mass_above = acc;
+                }
+            } else {
+                const unsigned long long total_mass = __shfl_sync(0xffffffffu, start + incl, 31);
+                if (lane == 0) { sh.sel_bin = -1; sh.sel_mass_above = total_mass; }
+            }
+        }
+        __syncthreads();
+    };
+
     uint32_t key_lo = 0;  // candidates are the elements with key >= key_lo that pass min-p
+    unsigned long long kept = 0;
+    int first_bin = -1;                      // bin of key_lo in the first-level histogram (-1: whole row kept)
+    unsigned long long first_above = 0;      // mass of the first-level bins above it
     if (top_p_active) {
         // radix descent (11 + 11 + 10 bits) for the smallest key whose descending cumulative mass
         // first exceeds top_p: elements above it are in the nucleus, the boundary key itself too.
@@ -663,54 +773,34 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         uint32_t prefix = 0;
         int shift = 32;
         bool found_all = false;
-        for (int level = 0; level < 3 && !found_all; ++level) {
+        for (int level = 0; level < 3; ++level) {
             const int bits = level == 2 ? 10 : 11;
             shift -= bits;
-            const int nb = 1 << bits;
-            for (int i = tid; i < nb; i += kThreads) { sh.hist_cnt[i] = 0; sh.hist_mass[i] = 0; }
-            __syncthreads();
-            const uint32_t hi_mask = level == 0 ? 0u : (0xffffffffu << (shift + bits));
-            for (long long i = tid; i < V; i += kThreads) {
-                const float x = row[i];
-                const uint32_t k = float_key(x);
-                if ((k & hi_mask) != prefix) continue;
-                const float pr = prob(x);
-                if (pr < min_thr) continue;
-                const int bin = (k >> shift) & (nb - 1);
-                atomicAdd(&sh.hist_cnt[bin], 1u);
-                atomicAdd(&sh.hist_mass[bin], fixed(pr));
-            }
-            __syncthreads();
-            if (tid == 0) {
-                unsigned long long acc = mass_above;
-                int sel = -1;
-                for (int bin = nb - 1; bin >= 0; --bin) {
-                    if (sh.hist_cnt[bin] == 0) continue;
-                    if (acc + sh.hist_mass[bin] > target) { sel = bin; break; }
-                    acc += sh.hist_mass[bin];
-                }
-                sh.sel_bin = sel;
-                sh.sel_mass_above = acc;
-            }
-            __syncthreads();
-            if (sh.sel_bin < 0) { found_all = true; prefix = 0; shift = 0; break; }  // the whole row stays
+            build_level(prefix, shift, bits, level == 0, 0u);
+            if (level == 0)   // the second descent starts from this histogram
+                for (int i = tid; i < 2048; i += kThreads) sh.first_mass[i] = sh.hist_mass[i];
+            select_bin(1 << bits, mass_above, target);
             mass_above = sh.sel_mass_above;
+            // no bin reaches top_p (only possible on the first level, where the bins hold the whole row)
+            if (sh.sel_bin < 0) { found_all = true; break; }
+            if (level == 0) { first_bin = sh.sel_bin; first_above = mass_above; }
             prefix |= (uint32_t)sh.sel_bin << shift;
         }
         key_lo = found_all ? 0u : prefix;
+        // kept mass = everything above the boundary key plus the boundary key's own bin of the last level
+        kept = found_all ? mass_above : mass_above + sh.hist_mass[sh.sel_bin];
+        if (found_all) first_bin = -1;
+        __syncthreads();
+    } else {
+        for_row(row, V, tid, [&](float x, long long) {
+            const float pr = prob(x);
+            if (!(pr < min_thr)) kept += fixed(pr);
+        });
+        kept = block_reduce(kept, 0ull, [](unsigned long long x, unsigned long long y) { return x + y; }, sh.red_u);
     }
 
-    // total kept mass, then the draw: r = total * u, first element (descending by key when top-p
-    // sorted the candidates, ascending by index otherwise) whose running sum exceeds r.
-    unsigned long long kept = 0;
-    for (long long i = tid; i < V; i += kThreads) {
-        const float x = row[i];
-        if (float_key(x) < key_lo) continue;
-        const float pr = prob(x);
-        if (pr < min_thr) continue;
-        kept += fixed(pr);
-    }
-    kept = block_reduce(kept, 0ull, [](unsigned long long x, unsigned long long y) { return x + y; }, sh.red_u);
+    // the draw: r = total * u, first element (descending by key when top-p sorted the candidates,
+    // ascending by index otherwise) whose running sum exceeds r.
     const float total = (float)((double)kept / 1099511627776.0);
     const unsigned long long rfix = fixed(total * p.rand_u);
 
@@ -724,41 +814,38 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
             const int bits = level == 2 ? 10 : 11;
             shift -= bits;
             const int nb = 1 << bits;
-            for (int i = tid; i < nb; i += kThreads) { sh.hist_cnt[i] = 0; sh.hist_mass[i] = 0; }
-            __syncthreads();
-            const uint32_t hi_mask = level == 0 ? 0u : (0xffffffffu << (shift + bits));
-            for (long long i = tid; i < V; i += kThreads) {
-                const float x = row[i];
-                const uint32_t k = float_key(x);
-                if (k < key_lo || (k & hi_mask) != prefix) continue;
-                const float pr = prob(x);
-                if (pr < min_thr) continue;
-                const int bin = (k >> shift) & (nb - 1);
-                atomicAdd(&sh.hist_cnt[bin], 1u);
-                atomicAdd(&sh.hist_mass[bin], fixed(pr));
+            if (level == 0) {
+                // the kept elements' first level: the saved bins above the boundary key's bin, and of
+                // that bin the part at or above the boundary key
+                for (int i = tid; i < nb; i += kThreads)
+                    sh.hist_mass[i] = i > first_bin ? sh.first_mass[i] : (i == first_bin ? kept - first_above : 0ull);
+                __syncthreads();
+            } else {
+                build_level(prefix, shift, bits, false, key_lo);
             }
-            __syncthreads();
-            if (tid == 0) {
-                unsigned long long acc = mass_above;
-                int sel = -1, last_nonempty = -1;
-                for (int bin = nb - 1; bin >= 0; --bin) {
-                    if (sh.hist_cnt[bin] == 0) continue;
-                    last_nonempty = bin;
-                    if (acc + sh.hist_mass[bin] > rfix) { sel = bin; break; }
-                    acc += sh.hist_mass[bin];
-                }
-                if (sel < 0) { sel = last_nonempty; acc -= last_nonempty >= 0 ? sh.hist_mass[last_nonempty] : 0; }  // fallback: last element
-                sh.sel_bin = sel;
-                sh.sel_mass_above = acc;
-            }
-            __syncthreads();
+            select_bin(nb, mass_above, rfix);
+            const int sel = sh.sel_bin;
             mass_above = sh.sel_mass_above;
-            prefix |= (uint32_t)max(sh.sel_bin, 0) << shift;
+            __syncthreads();
+            if (sel < 0) {
+                // rounding left r at or beyond the kept mass (only seen on the first level, whose bins
+                // hold all of it): the last element in descending order, the smallest kept key
+                unsigned long long lowest = ~0ull;
+                for_row(row, V, tid, [&](float x, long long) {
+                    const uint32_t k = float_key(x);
+                    if (k >= key_lo && !(prob(x) < min_thr)) lowest = min(lowest, (unsigned long long)k);
+                });
+                lowest = block_reduce(lowest, ~0ull, [](unsigned long long x, unsigned long long y) { return min(x, y); }, sh.red_u);
+                prefix = (uint32_t)lowest;
+                break;
+            }
+            prefix |= (uint32_t)sel << shift;
         }
         // all elements with this exact key have the same probability: the lowest index is taken
         int pick = 0x7fffffff;
-        for (long long i = tid; i < V; i += kThreads)
-            if (float_key(row[i]) == prefix) pick = min(pick, (int)i);
+        for_row(row, V, tid, [&](float x, long long i) {
+            if (float_key(x) == prefix) pick = min(pick, (int)i);
+        });
         pick = block_reduce(pick, 0x7fffffff, [](int x, int y) { return min(x, y); }, sh.red_i);
         if (tid == 0) {
             const float pr = prob(row[pick]);

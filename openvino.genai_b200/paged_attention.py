@@ -104,6 +104,10 @@ class PagedAttentionExtension:
         if stream == 0:
             stream = 1  # cudaStreamLegacy: NULL would select the handle's own stream instead of the default stream
         a.stream = stream
+        # the struct holds raw addresses: keep every buffer alive for as long as the struct is
+        a._buffers = (query, key, value, output, key_cache, value_cache, past_lens, subsequence_begins, block_indices,
+                      block_indices_begins, alibi_slopes, score_aggregation_window, scores, rotated_block_indices,
+                      rotation_deltas, rotation_trig_lut)
         return a
 
     def forward_args(self, args: _abi.pa_forward_args, host: bool = False) -> None:
