@@ -42,6 +42,7 @@ constexpr int kDecodeWaves = PA_DECODE_WAVES;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLazyMax = 8.f;  // the running reference may lag the true row maximum by 2^8
+constexpr int kFoldEvery = 4;     // u8: tiles between two removals of the zero-point term from the accumulators
 
 enum : int { kFirst = 1, kLast = 2, kEnd = 4 };
 
@@ -536,7 +537,26 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
                 }
         }
 
-        if (!(d.flags & kLast)) continue;
+        if (!(d.flags & kLast)) {
+            if constexpr (U8) {
+                // The value bytes enter the MMA as 1024 + byte, so the accumulators carry about a
+                // thousand times the magnitude of the result until the zero-point term is taken out,
+                // and the tensor core truncates every accumulation at that magnitude: over thousands
+                // of tiles the lost bits add up to a visible bias. Taking the term out every few
+                // tiles keeps the accumulators near the size of the result.
+                if ((it & (kFoldEvery - 1)) == kFoldEvery - 1) {
+#pragma unroll
+                    for (int r = 0; r < ROWS; ++r) {
+                        float z = z_run[r];
+                        z += __shfl_xor_sync(0xffffffffu, z, 1); z += __shfl_xor_sync(0xffffffffu, z, 2);
+                        z_run[r] = 0.f;
+#pragma unroll
+                        for (int i = 0; i < NDT; ++i) { oacc[i][2 * r] -= z; oacc[i][2 * r + 1] -= z; }
+                    }
+                }
+            }
+            continue;
+        }
 
         // ---- end of the run: fold the zero-point term, publish ---------------------------------------
         float lrow[ROWS];

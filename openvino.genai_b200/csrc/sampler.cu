@@ -763,6 +763,9 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
 
     uint32_t key_lo = 0;  // candidates are the elements with key >= key_lo that pass min-p
     unsigned long long kept = 0;
+    // without top-p: rows that can be read in 16-byte pieces and have at most 2048 groups of 128 elements
+    const int groups = (int)((V + 127) >> 7);
+    const bool grouped = !top_p_active && (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0 && groups <= 2048;
     int first_bin = -1;                      // bin of key_lo in the first-level histogram (-1: whole row kept)
     unsigned long long first_above = 0;      // mass of the first-level bins above it
     if (top_p_active) {
@@ -791,6 +794,119 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         kept = found_all ? mass_above : mass_above + sh.hist_mass[sh.sel_bin];
         if (found_all) first_bin = -1;
         __syncthreads();
+    } else if (grouped) {
+        // index-order draw, one pass: the mass of every group of 128 consecutive elements (one 16-byte
+        // load per lane, summed over the warp as three 14-bit pieces); the running sums over the groups
+        // then give both the kept mass and, below, the group in which the draw falls
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const long long n4 = V >> 2;
+        auto lane_mass = [&](long long i4) {
+            unsigned long long m = 0;
+            if (i4 < n4) {
+                const float4 q = r4[i4];
+                const float pr0 = prob(q.x), pr1 = prob(q.y), pr2 = prob(q.z), pr3 = prob(q.w);
+                if (!(pr0 < min_thr)) m += fixed(pr0);
+                if (!(pr1 < min_thr)) m += fixed(pr1);
+                if (!(pr2 < min_thr)) m += fixed(pr2);
+                if (!(pr3 < min_thr)) m += fixed(pr3);
+            }
+            return m;
+        };
+        for (int g0 = warp; g0 < groups; g0 += 4 * kWarps) {
+            float4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long i4 = (long long)(g0 + u * kWarps) * 32 + lane;
+                q[u] = i4 < n4 ? r4[i4] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int g = g0 + u * kWarps;
+                if (g >= groups) break;
+                const long long i4 = (long long)g * 32 + lane;
+                unsigned long long m = 0;
+                if (i4 < n4) {
+                    const float pr0 = prob(q[u].x), pr1 = prob(q[u].y), pr2 = prob(q[u].z), pr3 = prob(q[u].w);
+                    if (!(pr0 < min_thr)) m += fixed(pr0);
+                    if (!(pr1 < min_thr)) m += fixed(pr1);
+                    if (!(pr2 < min_thr)) m += fixed(pr2);
+                    if (!(pr3 < min_thr)) m += fixed(pr3);
+                }
+                const uint32_t lo = __reduce_add_sync(0xffffffffu, (uint32_t)(m & 0x3fffu));
+                const uint32_t mid = __reduce_add_sync(0xffffffffu, (uint32_t)((m >> 14) & 0x3fffu));
+                const uint32_t hi = __reduce_add_sync(0xffffffffu, (uint32_t)(m >> 28));
+                if (lane == 0) sh.hist_mass[g] = (unsigned long long)lo + ((unsigned long long)mid << 14) + ((unsigned long long)hi << 28);
+            }
+        }
+        __syncthreads();
+        // warp 0: lane l owns `per` consecutive groups; kept mass, r, the group where the running sum
+        // first exceeds r, then the lane and the element inside that group
+        if (warp == 0) {
+            const int per = (groups + 31) >> 5;
+            const int g_lo = lane * per, g_hi = min(groups, g_lo + per);
+            unsigned long long mine = 0;
+            for (int g = g_lo; g < g_hi; ++g) mine += sh.hist_mass[g];
+            unsigned long long incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += u;
+            }
+            const unsigned long long kept_all = __shfl_sync(0xffffffffu, incl, 31);
+            const float total_f = (float)((double)kept_all / 1099511627776.0);
+            const unsigned long long rf = fixed(total_f * p.rand_u);
+            const uint32_t hit = __ballot_sync(0xffffffffu, incl > rf);
+            int sel_g = -1;
+            unsigned long long sel_before = 0;
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                if (lane == src) {
+                    unsigned long long acc = incl - mine;
+                    sel_g = g_lo;
+                    for (int g = g_lo; g < g_hi; ++g) {
+                        const unsigned long long mg = sh.hist_mass[g];
+                        if (acc + mg > rf) { sel_g = g; break; }
+                        acc += mg;
+                    }
+                    sel_before = acc;
+                }
+                sel_g = __shfl_sync(0xffffffffu, sel_g, src);
+                sel_before = __shfl_sync(0xffffffffu, sel_before, src);
+            }
+            int chosen = -1;
+            if (sel_g >= 0) {
+                const long long i4 = (long long)sel_g * 32 + lane;
+                const unsigned long long m = lane_mass(i4);
+                unsigned long long inc2 = m;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned long long u = __shfl_up_sync(0xffffffffu, inc2, o);
+                    if (lane >= o) inc2 += u;
+                }
+                const uint32_t hit2 = __ballot_sync(0xffffffffu, sel_before + inc2 > rf);
+                if (hit2 && lane == __ffs(hit2) - 1) {
+                    unsigned long long run = sel_before + inc2 - m;
+                    const float4 q = r4[i4];
+                    const float xs[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pr = prob(xs[e]);
+                        if (pr < min_thr) continue;
+                        run += fixed(pr);
+                        if (run > rf && chosen < 0) chosen = (int)(4 * i4 + e);
+                    }
+                }
+                chosen = __reduce_max_sync(0xffffffffu, chosen);
+            }
+            if (lane == 0) {
+                // rounding left r at or beyond the total: the reference falls back to the last element
+                if (chosen < 0) chosen = (int)V - 1;
+                const float pr = prob(row[chosen]);
+                a.out_token[r] = chosen;
+                a.out_log_prob[r] = logf(pr) - logf(total_f);
+            }
+        }
+        return;
     } else {
         for_row(row, V, tid, [&](float x, long long) {
             const float pr = prob(x);
@@ -855,7 +971,8 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         return;
     }
 
-    // index-order draw (no top-p): running sums over chunks of the row
+    // index-order draw (no top-p) for rows the grouped form above does not take: running sums over
+    // one contiguous chunk of the row per thread
     {
         unsigned long long before = 0;
         int pick = -1;
