@@ -12,7 +12,14 @@
  *
  * What stays on the host (and is mirrored by the C++ class in csrc/host/sampler_host.hpp): the
  * per-request RNG engine, the token-count maps, stop conditions.  Structured-output masks,
- * beam search, tree search and logprobs > 0 are outside this entry point (SAMPLER_ERR_UNSUPPORTED).
+ * beam search and tree search are outside this entry point (SAMPLER_ERR_UNSUPPORTED).
+ *
+ * logprobs > 0 (logit_processor.hpp:36-47): the reference first takes log(sum(exp(raw logits)))
+ * over the whole vocabulary (FullVocabLogSumExpTransform, logit_transformers.hpp:264-277), lets the
+ * penalties and filters work on a copy, and reports raw_logit[token] - that log-partition as the
+ * token's log-probability (sampler.cpp:967-974, 1022-1029, 1076-1081).  A row asks for this with
+ * SAMPLER_ROW_RAW_LOG_PROB; the selected token is the same as without it.  Unlike the reference
+ * the logits row is still left with the penalties applied.
  */
 #ifndef SAMPLER_B200_H
 #define SAMPLER_B200_H
@@ -38,13 +45,17 @@ typedef enum sampler_status {
 #define SAMPLER_HIST_GENERATED 0x2u    /* id has an entry in the generated-token map (all three penalties) */
 #define SAMPLER_HIST_STOP_MASK 0x4u    /* id is a stop token and generated_len < min_new_tokens: -inf      */
 
+/* Bits of sampler_row_params.do_sample. */
+#define SAMPLER_ROW_MULTINOMIAL 0x1   /* multinomial sampling (GenerationConfig::is_multinomial); clear = greedy */
+#define SAMPLER_ROW_RAW_LOG_PROB 0x2  /* logprobs > 0: report raw_logit[token] - log-partition of the raw row   */
+
 /* Per-row parameters: the GenerationConfig fields LogitProcessor reads
  * (src/cpp/include/openvino/genai/generation_config.hpp:649-709), same defaults and same
  * activation rules (logit_processor.hpp:59-104). */
 typedef struct sampler_row_params {
     int64_t logits_row;        /* row of `logits` to sample from (rows are not assumed to be in request order) */
     int64_t top_k;             /* active iff 0 < top_k < INT64_MAX; >= vocab leaves the full vocabulary   */
-    int32_t do_sample;         /* 0 = greedy, 1 = multinomial                                           */
+    int32_t do_sample;         /* 0 = greedy, 1 = multinomial; SAMPLER_ROW_* bits                       */
     float temperature;         /* 1.0 = off                                                            */
     float top_p;               /* 1.0 = off                                                            */
     float min_p;               /* 0.0 = off                                                            */
@@ -68,6 +79,10 @@ typedef struct sampler_step_args {
     int64_t* out_token;           /* [num_rows] */
     float* out_log_prob;          /* [num_rows] */
     void* stream;                 /* cudaStream_t, NULL => the handle's stream */
+    float* hist_raw;              /* scratch, one float per history entry (same length as hist_ids): the raw logits the
+                                     penalties overwrite.  Needed by sampler_b200_step when a row that has history sets
+                                     SAMPLER_ROW_RAW_LOG_PROB (else status bit 2 and a NaN log-probability); may be NULL
+                                     otherwise; ignored by sampler_b200_step_host, which stages its own. */
 } sampler_step_args;
 
 typedef struct sampler_handle sampler_handle;
@@ -86,7 +101,8 @@ int sampler_b200_step(sampler_handle* h, const sampler_step_args* args);
  * synchronises.  Returns SAMPLER_ERR_BAD_TOKEN_ID if the kernel met an out-of-range history id. */
 int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* args, int copy_logits_back);
 
-/* Reads (and clears) the device status word: bit 0 = out-of-range history id. */
+/* Reads (and clears) the device status word: bit 0 = out-of-range history id, bit 1 = logits_row out of
+ * range, bit 2 = SAMPLER_ROW_RAW_LOG_PROB on a row with history but no hist_raw scratch. */
 int sampler_b200_last_device_status(sampler_handle* h, uint32_t* status_bits);
 
 int64_t sampler_b200_launch_count(const sampler_handle* h);

@@ -16,6 +16,9 @@ HIST_STOP_MASK = 0x4
 
 TOP_K_OFF = 2 ** 63 - 1
 
+ROW_MULTINOMIAL = 0x1
+ROW_RAW_LOG_PROB = 0x2
+
 
 class sampler_row_params(C.Structure):
     _fields_ = [
@@ -46,6 +49,7 @@ class sampler_step_args(C.Structure):
         ("out_token", C.c_void_p),
         ("out_log_prob", C.c_void_p),
         ("stream", C.c_void_p),
+        ("hist_raw", C.c_void_p),
     ]
 
 

@@ -71,7 +71,6 @@ struct GenerationConfig {
             if (!(min_p >= 0.0f && min_p < 1.0f)) fail("When 'do_sample' is true, min_p must be in [0.0, 1.0)");
         }
         if (is_beam_search() || is_tree_search()) fail("beam search and tree search are outside the accelerated Sampler step");
-        if (logprobs > 0) fail("logprobs > 0 is outside the accelerated Sampler step");
         if (num_return_sequences != 1) fail("num_return_sequences > 1 is outside the accelerated Sampler step");
     }
 };

@@ -65,7 +65,8 @@ Sampler::PackedStep Sampler::pack(const std::vector<SequenceGroup*>& sequence_gr
         const GenerationConfig& cfg = g->sampling_params;
         sampler_row_params row{};
         row.logits_row = g->logits_row;
-        row.do_sample = cfg.is_multinomial() ? 1 : 0;
+        row.do_sample = cfg.is_multinomial() ? SAMPLER_ROW_MULTINOMIAL : 0;
+        if (cfg.logprobs > 0) row.do_sample |= SAMPLER_ROW_RAW_LOG_PROB;   // logit_processor.hpp:36-47
         // top_k: SIZE_MAX (and anything that does not fit) means "off" on both sides of the boundary
         row.top_k = cfg.top_k >= (size_t)std::numeric_limits<int64_t>::max() ? std::numeric_limits<int64_t>::max() : (int64_t)cfg.top_k;
         row.temperature = cfg.temperature;
@@ -77,7 +78,7 @@ Sampler::PackedStep Sampler::pack(const std::vector<SequenceGroup*>& sequence_gr
         // one draw per sampled token from the request's own engine (sampler.cpp:979-1095); greedy
         // rows leave the engine untouched
         row.rand_u = 0.f;
-        if (row.do_sample) {
+        if (row.do_sample & SAMPLER_ROW_MULTINOMIAL) {
             std::uniform_real_distribution<float> dist(0.0f, 1.0f);
             row.rand_u = dist(ctx.rng_engine);
         }
@@ -179,7 +180,8 @@ SamplerOutput Sampler::sample_device(const std::vector<SequenceGroup*>& sequence
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     const size_t o_rows = 0, o_off = o_rows + up(n * sizeof(sampler_row_params)), o_ids = o_off + up((n + 1) * 8);
     const size_t o_meta = o_ids + up(st.hist_ids.size() * 4), o_tok = o_meta + up(st.hist_meta.size() * 4), o_lp = o_tok + up(n * 8);
-    const size_t total = o_lp + up(n * 4);
+    const size_t o_raw = o_lp + up(n * 4);   // device only: raw logits of the history entries
+    const size_t total = o_raw + up(st.hist_ids.size() * 4);
     if (total > m_dev_bytes) {   // grow-only staging
         if (m_dev_buf) check_cuda(cudaFree(m_dev_buf), "cudaFree");
         if (m_pinned) check_cuda(cudaFreeHost(m_pinned), "cudaFreeHost");
@@ -208,9 +210,10 @@ SamplerOutput Sampler::sample_device(const std::vector<SequenceGroup*>& sequence
     a.hist_meta = (const uint32_t*)(dp + o_meta);
     a.out_token = (int64_t*)(dp + o_tok);
     a.out_log_prob = (float*)(dp + o_lp);
+    a.hist_raw = (float*)(dp + o_raw);
     a.stream = (void*)s;
     check(sampler_b200_step(m_handle, &a), "sampler_b200_step");
-    check_cuda(cudaMemcpyAsync(hp + o_tok, dp + o_tok, total - o_tok, cudaMemcpyDeviceToHost, s), "copy of the sampled ids");
+    check_cuda(cudaMemcpyAsync(hp + o_tok, dp + o_tok, o_raw - o_tok, cudaMemcpyDeviceToHost, s), "copy of the sampled ids");
     check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
     uint32_t bits = 0;
     check(sampler_b200_last_device_status(m_handle, &bits), "sampler_b200_last_device_status");

@@ -358,7 +358,7 @@ struct Shared {
 
 // ---- phase 1: penalties ---------------------------------------------------------------------------------
 __device__ void apply_history(float* row, long long V, const sampler_row_params& p, const int32_t* ids, const uint32_t* meta,
-                              long long n, uint32_t* status) {
+                              long long n, uint32_t* status, float* raw_out) {
     const double rep = (double)p.repetition_penalty, pres = (double)p.presence_penalty, freq = (double)p.frequency_penalty;
     for (long long i = threadIdx.x; i < n; i += blockDim.x) {
         const int id = ids[i];
@@ -368,6 +368,7 @@ __device__ void apply_history(float* row, long long V, const sampler_row_params&
             continue;
         }
         float v = row[id];
+        if (raw_out) raw_out[i] = v;   // the raw logit, for rows that report raw log-probabilities
         if (m & SAMPLER_HIST_STOP_MASK) v = -CUDART_INF_F;
         if (p.repetition_penalty != 1.0f && (m & (SAMPLER_HIST_IN_PROMPT | SAMPLER_HIST_GENERATED)))
             v = v >= 0 ? (float)__ddiv_rn((double)v, rep) : (float)__dmul_rn((double)v, rep);
@@ -385,7 +386,8 @@ __device__ void apply_history(float* row, long long V, const sampler_row_params&
 // ---- phase 3 tail: softmax / min-p / top-p / draw over the K heap entries, one thread ---------------
 // Mirrors TemperatureLogitTransform, MinPFilter, TopPFilter (logit_transformers.hpp:90-362) and
 // Sampler::_multinomial_sample (sampler.cpp:979-1095) statement by statement.
-__device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float* out_p, long long* out_idx) {
+__device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float* out_p, long long* out_idx, bool* uniform_fallback) {
+    *uniform_fallback = false;
     const bool min_p_active = p.min_p > 0.0f;
     const bool defer = p.top_p == 1.0f && !min_p_active;
     const float T = p.temperature;
@@ -411,6 +413,7 @@ __device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float*
         }
         *out_p = uniform ? logf(1.0f / (float)n) : v[pick].v - log_sum;
         *out_idx = v[pick].idx;
+        *uniform_fallback = uniform;
         return;
     }
     {   // softmax(logits / T) over the heap array, in array order
@@ -468,6 +471,7 @@ __device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float*
         if (pick > n - 1) pick = n - 1;
         *out_p = logf(1.0f / (float)n);
         *out_idx = v[pick].idx;
+        *uniform_fallback = true;
         return;
     }
     const float log_total = logf(total);
@@ -495,15 +499,43 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     }
     float* row = a.logits + p.logits_row * V;
 
-    // ---- 1. penalties ------------------------------------------------------------------------------
-    if (a.hist_offsets) {
-        const long long h0 = a.hist_offsets[r], h1 = a.hist_offsets[r + 1];
-        if (h1 > h0) apply_history(row, V, p, a.hist_ids + h0, a.hist_meta + h0, h1 - h0, a.status);
+    const bool multinomial = (p.do_sample & SAMPLER_ROW_MULTINOMIAL) != 0;
+    const bool raw_lp = (p.do_sample & SAMPLER_ROW_RAW_LOG_PROB) != 0;
+    const long long h0 = a.hist_offsets ? a.hist_offsets[r] : 0, h1 = a.hist_offsets ? a.hist_offsets[r + 1] : 0;
+
+    // ---- 0. log-partition of the raw row (FullVocabLogSumExpTransform, logit_transformers.hpp:264-277) ----
+    // The reference adds the exponentials in single precision in index order; here they are added in
+    // double precision in parallel and rounded once, which is within an ulp or two of any float order.
+    float raw_lse = 0.f;
+    bool raw_ok = true;
+    if (raw_lp) {
+        float mx0 = -CUDART_INF_F;
+        for_row(row, V, tid, [&](float x, long long) { mx0 = fmaxf(mx0, x); });
+        mx0 = block_reduce(mx0, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
+        double s0 = 0.0;
+        for_row(row, V, tid, [&](float x, long long) { s0 += (double)expf(x - mx0); });
+        s0 = block_reduce(s0, 0.0, [](double x, double y) { return x + y; }, sh.red_d);
+        raw_lse = logf((float)s0) + mx0;
+        if (h1 > h0 && !a.hist_raw) {
+            raw_ok = false;
+            if (tid == 0) atomicOr(a.status, 4u);
+        }
     }
+    // the raw log-probability of the selected token: its logit before the penalties minus the log-partition
+    auto raw_log_prob = [&](long long idx) {
+        if (!raw_ok) return CUDART_NAN_F;
+        float raw = row[idx];
+        for (long long i = h0; i < h1; ++i)
+            if (a.hist_ids[i] == idx) { raw = a.hist_raw[i]; break; }
+        return raw - raw_lse;
+    };
+
+    // ---- 1. penalties ------------------------------------------------------------------------------
+    if (h1 > h0) apply_history(row, V, p, a.hist_ids + h0, a.hist_meta + h0, h1 - h0, a.status, raw_lp && raw_ok ? a.hist_raw + h0 : nullptr);
     __syncthreads();
 
     // ---- 2. greedy ----------------------------------------------------------------------------------
-    if (!p.do_sample) {
+    if (!multinomial) {
         ArgMax best{-CUDART_INF_F, 0x7fffffff};
         long long done = 0;
         if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
@@ -540,8 +572,9 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         }
         best = block_reduce(best, ArgMax{-CUDART_INF_F, 0x7fffffff}, better, sh.red_a);
         if (tid == 0) {
-            a.out_token[r] = best.i == 0x7fffffff ? 0 : best.i;  // all -inf / NaN: the reference returns index 0
-            a.out_log_prob[r] = 0.f;
+            const int chosen = best.i == 0x7fffffff ? 0 : best.i;  // all -inf / NaN: the reference returns index 0
+            a.out_token[r] = chosen;
+            a.out_log_prob[r] = raw_lp ? raw_log_prob(chosen) : 0.f;   // sampler.cpp:965-974
         }
         return;
     }
@@ -657,9 +690,10 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         if (tid == 0) {
             float lp;
             long long idx;
-            finish_top_k(sh.heap, K, p, &lp, &idx);
+            bool uniform_fallback;
+            finish_top_k(sh.heap, K, p, &lp, &idx, &uniform_fallback);
             a.out_token[r] = idx;
-            a.out_log_prob[r] = lp;
+            a.out_log_prob[r] = raw_lp && !uniform_fallback ? raw_log_prob(idx) : lp;   // sampler.cpp:1022-1029, 1076-1081
         }
         return;
     }
@@ -903,7 +937,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
                 if (chosen < 0) chosen = (int)V - 1;
                 const float pr = prob(row[chosen]);
                 a.out_token[r] = chosen;
-                a.out_log_prob[r] = logf(pr) - logf(total_f);
+                a.out_log_prob[r] = raw_lp ? raw_log_prob(chosen) : logf(pr) - logf(total_f);
             }
         }
         return;
@@ -966,7 +1000,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         if (tid == 0) {
             const float pr = prob(row[pick]);
             a.out_token[r] = pick;
-            a.out_log_prob[r] = logf(pr) - logf(total);
+            a.out_log_prob[r] = raw_lp ? raw_log_prob(pick) : logf(pr) - logf(total);
         }
         return;
     }
@@ -1016,7 +1050,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
             }
             const float pr = prob(row[chosen]);
             a.out_token[r] = chosen;
-            a.out_log_prob[r] = logf(pr) - logf(total);
+            a.out_log_prob[r] = raw_lp ? raw_log_prob(chosen) : logf(pr) - logf(total);
         }
     }
 }

@@ -67,7 +67,7 @@ sampler::StepArgs kernel_args(sampler_handle* h, const sampler_step_args* a) {
     sampler::StepArgs k;
     k.logits = a->logits; k.num_logit_rows = a->num_logit_rows; k.vocab = a->vocab; k.num_rows = a->num_rows;
     k.rows = a->rows; k.hist_offsets = a->hist_offsets; k.hist_ids = a->hist_ids; k.hist_meta = a->hist_meta;
-    k.out_token = a->out_token; k.out_log_prob = a->out_log_prob; k.status = h->status;
+    k.out_token = a->out_token; k.out_log_prob = a->out_log_prob; k.status = h->status; k.hist_raw = a->hist_raw;
     return k;
 }
 
@@ -139,6 +139,7 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
     const size_t small_in = off;
     const size_t o_tok = off;   off += up(n * sizeof(int64_t));
     const size_t o_lp = off;    off += up(n * sizeof(float));
+    const size_t o_hraw = off;  off += up(hist_n * sizeof(float));
     const size_t o_logits = off; off += up(logits_bytes);
     rc = ensure_stage(h, off);
     if (rc != SAMPLER_OK) return rc;
@@ -158,6 +159,7 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
     d.hist_meta = (const uint32_t*)(h->stage_dev + o_hmeta);
     d.out_token = (int64_t*)(h->stage_dev + o_tok);
     d.out_log_prob = (float*)(h->stage_dev + o_lp);
+    d.hist_raw = (float*)(h->stage_dev + o_hraw);
     S_CUDA(sampler::launch_sampler(kernel_args(h, &d), stream));
     h->launches += 1;
     S_CUDA(cudaMemcpyAsync(a->out_token, d.out_token, n * sizeof(int64_t), cudaMemcpyDeviceToHost, stream));

@@ -20,7 +20,8 @@ struct StepArgs {
     const uint32_t* hist_meta;
     int64_t* out_token;
     float* out_log_prob;
-    uint32_t* status;  // bit 0: history id out of range, bit 1: logits_row out of range
+    uint32_t* status;  // bit 0: history id out of range, bit 1: logits_row out of range, bit 2: raw log-prob without scratch
+    float* hist_raw;   // raw logits of the history entries (rows that report raw log-probabilities), may be null
 };
 
 cudaError_t launch_sampler(const StepArgs& a, cudaStream_t stream);

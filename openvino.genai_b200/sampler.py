@@ -35,7 +35,8 @@ class SamplerStep:
         dev = torch.device("cuda", self.device)
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8) if a.dtype.fields else np.ascontiguousarray(a)).to(dev)
         n = len(rows)
-        return {"n": n, "rows": t(rows), "hist": tuple(t(x) for x in hist) if hist is not None else None,
+        raw = torch.empty(len(hist[1]), dtype=torch.float32, device=dev) if hist is not None else None
+        return {"n": n, "rows": t(rows), "hist": tuple(t(x) for x in hist) if hist is not None else None, "hist_raw": raw,
                 "tokens": torch.full((n,), -1, dtype=torch.int64, device=dev), "log_probs": torch.zeros(n, dtype=torch.float32, device=dev)}
 
     def step(self, logits: torch.Tensor, staged: dict, stream: int = 0):
@@ -49,6 +50,7 @@ class SamplerStep:
         a.rows = staged["rows"].data_ptr()
         if staged["hist"] is not None:
             a.hist_offsets, a.hist_ids, a.hist_meta = (x.data_ptr() for x in staged["hist"])
+            a.hist_raw = staged["hist_raw"].data_ptr()   # scratch for rows that report raw log-probabilities
         a.out_token = staged["tokens"].data_ptr()
         a.out_log_prob = staged["log_probs"].data_ptr()
         a.stream = stream if stream else 1   # 1 = cudaStreamLegacy: a null handle would select the handle's own stream

@@ -151,7 +151,8 @@ Tok greedy(const RowState& st) {
 }
 
 // sampler.cpp:979-1095 for one draw with the uniform number already drawn
-Tok multinomial(const RowState& st, float u) {
+Tok multinomial(const RowState& st, float u, bool* uniform_fallback) {
+    *uniform_fallback = false;
     if (st.defer_expf) {
         float mx = st.vec[0].p;
         for (size_t i = 1; i < st.size; ++i) if (st.vec[i].p > mx) mx = st.vec[i].p;
@@ -166,6 +167,7 @@ Tok multinomial(const RowState& st, float u) {
         size_t pick = st.size - 1;
         for (size_t i = 0; i < st.size; ++i) { run += w[i]; if (run > r) { pick = i; break; } }
         const float lp = uniform ? std::log(1.0f / static_cast<float>(st.size)) : st.vec[pick].p - log_sum;
+        *uniform_fallback = uniform;
         return Tok{lp, st.vec[pick].idx};
     }
     float total = 0.0f;
@@ -175,6 +177,7 @@ Tok multinomial(const RowState& st, float u) {
         // the reference draws an index with uniform_int_distribution here; with a pre-drawn u the
         // restatement maps u to an index the same way the kernel does
         const size_t pick = std::min(st.size - 1, (size_t)(u * (float)st.size));
+        *uniform_fallback = true;
         return Tok{std::log(1.0f / st.size), st.has_vec() ? st.vec[pick].idx : (int64_t)pick};
     }
     const float log_total = std::log(total);
@@ -197,6 +200,21 @@ int process_row(const sampler_step_args* a, int r, std::vector<float>& scratch) 
     const int64_t h0 = a->hist_offsets ? a->hist_offsets[r] : 0, h1 = a->hist_offsets ? a->hist_offsets[r + 1] : 0;
     for (int64_t i = h0; i < h1; ++i)
         if (a->hist_ids[i] < 0 || (size_t)a->hist_ids[i] >= V) return SAMPLER_ERR_BAD_TOKEN_ID;
+
+    // logprobs > 0: log-partition of the raw row first (logit_transformers.hpp:264-277), and the raw
+    // logits kept aside: the reference's penalties then work on a copy and the reported
+    // log-probability is raw_logit[token] - log-partition (sampler.cpp:967-974, 1022-1029, 1076-1081).
+    // This restatement keeps the penalties in place, as the entry point it checks does.
+    const bool raw_lp = (p.do_sample & SAMPLER_ROW_RAW_LOG_PROB) != 0;
+    float raw_lse = 0.0f;
+    std::vector<float> raw;
+    if (raw_lp) {
+        const float max_logit = *std::max_element(row, row + V);
+        float sum = 0.0f;
+        for (size_t i = 0; i < V; ++i) sum += expf(row[i] - max_logit);
+        raw_lse = logf(sum) + max_logit;
+        raw.assign(row, row + V);
+    }
 
     // stop-token mask while generated_len < min_new_tokens (logit_transformers.hpp:452-463)
     for (int64_t i = h0; i < h1; ++i)
@@ -234,7 +252,8 @@ int process_row(const sampler_step_args* a, int r, std::vector<float>& scratch) 
     st.data = row;
     st.size = V;
     Tok out;
-    if (!p.do_sample) {
+    bool uniform_fallback = false;
+    if (!(p.do_sample & SAMPLER_ROW_MULTINOMIAL)) {
         out = greedy(st);
     } else {
         const bool top_k_active = p.top_k > 0 && p.top_k < std::numeric_limits<int64_t>::max();
@@ -248,8 +267,9 @@ int process_row(const sampler_step_args* a, int r, std::vector<float>& scratch) 
         temperature(st, p.temperature, defer);
         if (min_p_active) min_p_filter(st, p.min_p);
         if (p.top_p != 1.0f) top_p_filter(st, p.top_p);
-        out = multinomial(st, p.rand_u);
+        out = multinomial(st, p.rand_u, &uniform_fallback);
     }
+    if (raw_lp && !uniform_fallback) out.p = raw[(size_t)out.idx] - raw_lse;
     a->out_token[r] = out.idx;
     a->out_log_prob[r] = out.p;
     return SAMPLER_OK;

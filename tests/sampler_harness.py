@@ -107,6 +107,7 @@ class GpuSampler:
         import torch
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8) if a.dtype.fields else a).to(dev)
         return {"rows": t(rows), "hist": tuple(t(x) for x in hist) if hist is not None else None,
+                "hist_raw": torch.empty(len(hist[1]), dtype=torch.float32, device=dev) if hist is not None else None,
                 "tok": torch.full((len(rows),), -7, dtype=torch.int64, device=dev),
                 "lp": torch.zeros(len(rows), dtype=torch.float32, device=dev)}
 
@@ -121,8 +122,10 @@ class GpuSampler:
         a.num_logit_rows, a.vocab = logits_t.shape
         s = torch.cuda.current_stream(dev).cuda_stream if stream is None else stream
         a.stream = s if s else 1
+        if staged.get("hist_raw") is not None:
+            a.hist_raw = staged["hist_raw"].data_ptr()
         rc = self.lib.sampler_b200_step(self.h, C.byref(a))
-        self._keep = (rows_t, hist_t)
+        self._keep = (rows_t, hist_t, staged.get("hist_raw"))
         return rc, tok, lp
 
 

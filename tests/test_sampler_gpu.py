@@ -133,6 +133,68 @@ def test_full_vocab_plain_sampling_agreement_rate(gpu):
     assert rate >= 0.9
 
 
+@pytest.mark.parametrize("mode", ["greedy", "top_k", "top_k_deferred", "plain"])
+def test_raw_log_probabilities_for_logprobs_rows(gpu, mode):
+    """logprobs > 0: the same token as without the flag, and its log-probability is the raw logit
+    minus the log-partition of the raw row, also for a token the penalties rewrote."""
+    rng = np.random.default_rng(41)
+    n, vocab = 12, 32000
+    x = H.synthetic_logits(rng, n, vocab)
+    hist = H.make_history(rng, n, vocab, generated_len=300, prompt_len=50)
+    # make the strongest logit of every row a penalised one, so that greedy rows pick a rewritten token
+    for r in range(n):
+        x[r, hist[1][hist[0][r]]] = 40.0
+    kw = dict(repetition_penalty=1.3, presence_penalty=0.3, frequency_penalty=0.2)
+    if mode == "greedy":
+        kw.update(do_sample=0)
+    elif mode == "top_k":
+        kw.update(top_k=40, temperature=0.8, top_p=0.9)
+    elif mode == "top_k_deferred":
+        kw.update(top_k=40, temperature=0.8)
+    else:
+        kw.update(temperature=1.3)
+    rows = H.make_rows(n, **kw)
+    rows["rand_u"] = rng.random(n, dtype=np.float32)
+    flagged = rows.copy()
+    flagged["do_sample"] |= A.ROW_RAW_LOG_PROB
+    tok_plain = _both(gpu, x, rows, hist)[3]
+    tok_o, lp_o, _, tok_g, lp_g, _ = _both(gpu, x, flagged, hist)
+    assert np.array_equal(tok_g, tok_plain)
+    if mode != "plain":   # the full-vocabulary path is compared by agreement rate elsewhere
+        assert np.array_equal(tok_g, tok_o)
+    x64 = x.astype(np.float64)
+    lse = np.log(np.exp(x64 - x64.max(axis=1, keepdims=True)).sum(axis=1)) + x64.max(axis=1)
+    want = x64[np.arange(n), tok_g] - lse
+    np.testing.assert_allclose(lp_g, want, rtol=0, atol=2e-5)
+    same = tok_g == tok_o
+    np.testing.assert_allclose(lp_g[same], lp_o[same], rtol=0, atol=2e-5)
+    # the device entry point with its scratch gives the same answer
+    xt = torch.from_numpy(x).cuda()
+    rc, tok_d, lp_d = gpu.step_device(xt, flagged, hist)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(tok_d.cpu().numpy(), tok_g)
+    np.testing.assert_array_equal(lp_d.cpu().numpy(), lp_g)
+
+
+def test_raw_log_probabilities_need_the_scratch_on_the_device_entry(gpu):
+    rng = np.random.default_rng(42)
+    x = H.synthetic_logits(rng, 2, 4096)
+    hist = H.make_history(rng, 2, 4096, generated_len=10)
+    rows = H.make_rows(2, do_sample=0, repetition_penalty=1.2)
+    rows["do_sample"] |= A.ROW_RAW_LOG_PROB
+    xt = torch.from_numpy(x).cuda()
+    staged = gpu.stage(rows, hist, xt.device)
+    staged["hist_raw"] = None
+    rc, tok, lp = gpu.step_device(xt, rows, hist, staged=staged)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.isnan(lp.cpu().numpy()).all()
+    bits = __import__("ctypes").c_uint32(0)
+    assert gpu.lib.sampler_b200_last_device_status(gpu.h, __import__("ctypes").byref(bits)) == 0
+    assert bits.value & 4
+
+
 def test_out_of_range_history_id_is_reported(gpu):
     x = np.zeros((1, 100), np.float32)
     hist = (np.array([0, 1], np.int64), np.array([1337], np.int32), np.array([(1 << 3) | A.HIST_GENERATED], np.uint32))

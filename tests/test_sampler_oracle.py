@@ -104,6 +104,25 @@ def test_golden_eos_mask(case):
     assert rc == 0 and np.array_equal(lg[0], exp)
 
 
+def test_raw_log_probability_rows_report_the_unpenalised_logit():
+    """logprobs > 0 (logit_processor.hpp:36-47, sampler.cpp:967-974): same token, log-probability =
+    raw logit - log-partition of the raw row."""
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((3, 500)) * 3).astype(np.float32)
+    hist = H.make_history(rng, 3, 500, generated_len=40)
+    for do_sample, kw in ((0, {}), (1, dict(top_k=10, temperature=0.7)), (1, dict(top_k=10, top_p=0.8))):
+        rows = H.make_rows(3, do_sample=do_sample, repetition_penalty=1.5, presence_penalty=0.5, **kw)
+        rows["rand_u"] = rng.random(3, dtype=np.float32)
+        rc, tok0, _, _ = H.run_oracle(x, rows, hist)
+        assert rc == 0
+        rows["do_sample"] |= A.ROW_RAW_LOG_PROB
+        rc, tok1, lp1, _ = H.run_oracle(x, rows, hist)
+        assert rc == 0 and np.array_equal(tok0, tok1)
+        x64 = x.astype(np.float64)
+        lse = np.log(np.exp(x64 - x64.max(axis=1, keepdims=True)).sum(axis=1)) + x64.max(axis=1)
+        np.testing.assert_allclose(lp1, x64[np.arange(3), tok1] - lse, atol=1e-5, rtol=0)
+
+
 def test_uniform_stream_is_the_mt19937_stream():
     u = SO.uniform_stream(0, 2)
     assert abs(float(u[0]) - 0.548813522) < 1e-7 and abs(float(u[1]) - 0.592844605) < 1e-7
