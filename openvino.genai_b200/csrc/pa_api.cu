@@ -85,7 +85,8 @@ pa::CacheGeom make_geom(const pa_model_desc& d) {
 // Scratch layout of one forward call.
 struct Plan {
     long long max_tiles;
-    size_t off_hdr, off_prefix, off_pprefix, off_wstart, off_done, off_part_o, off_part_ml, off_lse, off_score_off, off_stile, off_score_part, total;
+    size_t off_hdr, off_prefix, off_pprefix, off_wstart, off_done, off_part_o, off_part_ml, off_lse, off_score_off, off_stile, off_score_part, off_score_raw, total;
+    bool has_score_raw;
 };
 
 Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_context_len, int64_t scores_len,
@@ -111,6 +112,11 @@ Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_co
     p.off_score_off = off; off += align_up((size_t)(B + 1) * sizeof(int64_t), 256);
     p.off_stile = off;     off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_score_part = off; off += align_up((size_t)std::max<int64_t>(scores_len, 0) * g.Hkv * sizeof(float), 256);
+    // scaled logits of the decode rows, [head tiles][scores_len][8 or 16]: kept only while they stay below 1 GiB; beyond
+    // that every sequence goes through the score kernel, which reads the keys again instead
+    const size_t raw_bytes = (size_t)std::max<int64_t>(scores_len, 0) * HK * (RT <= 8 ? 8 : 16) * sizeof(float);
+    p.has_score_raw = raw_bytes > 0 && raw_bytes <= ((size_t)1 << 30);
+    p.off_score_raw = off; off += p.has_score_raw ? align_up(raw_bytes, 256) : 0;
     p.total = off;
     return p;
 }
@@ -183,6 +189,7 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.score_offsets = (int64_t*)(h->ws + p.off_score_off);
     k.stile_prefix = (int*)(h->ws + p.off_stile);
     k.score_part = (float*)(h->ws + p.off_score_part);
+    k.score_raw = a->scores && a->score_aggregation_window && p.has_score_raw ? (float*)(h->ws + p.off_score_raw) : nullptr;
     k.plan = (pa::PlanHeader*)(h->ws + p.off_hdr);
     k.tile_prefix = (int*)(h->ws + p.off_prefix);
     k.stream_done = (int*)(h->ws + p.off_done);
@@ -203,6 +210,7 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count);   // the plan step prepares one start record per worker
     int launches = 0;
     if (a->num_rotated_blocks > 0) { PA_CUDA(pa::launch_rotate(k, stream)); ++launches; }
+    if (a->scores) PA_CUDA(pa::launch_score_plan(k, stream, &launches));   // the decode kernel needs the offsets
     PA_CUDA(pa::launch_write_kv(k, stream, /*with_plan=*/true)); ++launches;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (h->timing && h->ev_used + 2 <= 8192) {

@@ -21,6 +21,7 @@
 // completes it (one atomic counter per stream, no waiting).
 // HBM-bound: 2*Hkv*(D+8) bytes per context token for the u8 cache.
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 
 #include "pa_common.cuh"
@@ -51,7 +52,7 @@ struct __align__(16) StageDesc {
     int flags;  // kFirst (run starts: load Q, clear state) | kLast (run ends: publish) | kEnd
     int valid;  // live tokens in the tile (1..32)
     int run;    // index of the run's record in the warp's run ring
-    int pad;
+    int tok0;   // context position of the tile's first token
 };
 
 // One run (consecutive tiles of one stream inside a worker's slice), kept in shared memory so that
@@ -63,7 +64,7 @@ struct __align__(16) RunRec {
     int nparts;      // workers whose slices touch the stream (1 => write the output directly)
     int first_slot;  // partial slot of the stream's first worker (slots are consecutive)
     int slot;        // this worker's partial slot
-    int pad[2];
+    long long score_off;  // index into score_raw of position 0 of the stream, -1: the row's logits are not kept
 };
 constexpr int kRunRing = 4;
 
@@ -130,6 +131,8 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     const int RT = a.rows_per_tile;
     const float sm_scale = a.scale != 0.f ? a.scale : rsqrtf((float)D);
     bool bad_index = false;
+    // everything below reads what the launch before this one wrote (plan, start records, cache)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- this worker's slice of the global tile sequence -----------------------------------------
     const int all_workers = gridDim.x * kDecodeWarps;
@@ -174,8 +177,13 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         const int first_w = s_begin / per_worker, last_w = (s_begin + r_tiles - 1) / per_worker;
         const int stream = r_s * HK + r_hkp;
         ++r_seq;
-        if (lane == 0)
-            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, {0, 0}};
+        if (lane == 0) {
+            // rows whose attention scores are wanted (window > 0) leave their scaled logits behind
+            long long score_off = -1;
+            if (a.score_raw && a.score_aggregation_window[r_s] > 0)
+                score_off = ((long long)r_hkp * a.scores_len + a.score_offsets[r_s]) * (RT <= 8 ? 8 : 16);
+            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, score_off};
+        }
         g_tile += ntile;
         r_first = true;
         load_window(r_tok / BS);
@@ -275,7 +283,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         const int valid = min(kTile, r_end - r_tok);
         const bool last = r_tok + kTile >= r_end;
         if (lane == 0)
-            descs[slot] = StageDesc{(r_first ? kFirst : 0) | (last ? kLast : 0), valid, r_seq % kRunRing, 0};
+            descs[slot] = StageDesc{(r_first ? kFirst : 0) | (last ? kLast : 0), valid, r_seq % kRunRing, r_tok};
         r_first = false;
         r_tok += kTile;
     };
@@ -421,6 +429,16 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         float tmax[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) tmax[r] = -INFINITY;
+        // Score output of decode rows: the scaled logits (base 2) of every (position, q head) are left in
+        // score_raw[head tile][position][8 or 16 head rows]; the score step turns them into probabilities
+        // once the row's log-sum-exp is known, instead of reading the keys and multiplying a second time.
+        // All 8 lanes of a token write, dead head rows too, so that every store fills whole 32-byte sectors.
+        constexpr int SL = 8 * ROWS;
+        float* score_dst = nullptr;
+        if (a.score_raw) {
+            const long long so = runs[d.run].score_off;
+            if (so >= 0) score_dst = a.score_raw + so + (long long)d.tok0 * SL + g;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int tk = U8 ? 8 * c + 2 * j : 8 * j + 2 * c;  // tile token of accumulator column 0
@@ -447,6 +465,10 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
                 }
                 s0 = ok0 ? s0 : -INFINITY;
                 s1 = ok1 ? s1 : -INFINITY;
+                if (score_dst) {
+                    if (ok0) __stcs(score_dst + tk * SL + 8 * r, s0);
+                    if (ok1) __stcs(score_dst + (tk + 1) * SL + 8 * r, s1);
+                }
                 sacc[j][2 * r] = s0; sacc[j][2 * r + 1] = s1;
                 tmax[r] = fmaxf(tmax[r], fmaxf(s0, s1));
             }
@@ -663,14 +685,26 @@ long long decode_ctas(const KernelArgs& a, int per_sm, int sm_count) {
     return std::max(1LL, std::min(ctas, (max_slices + kDecodeWarps - 1) / kDecodeWarps));
 }
 
+// Resident CTAs per SM of one instantiation on the current device; the shared-memory opt-in and the
+// occupancy query are made once per (instantiation, device), not on every step.
 template <int D, int BS, int CACHE>
 int occupancy_t(const KernelArgs& a) {
     using Cfg = DecodeCfg<D, BS, CACHE>;
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> cache[2][kMaxDevices];   // 0 = unknown, else per_sm + 1
     const bool hi = a.g.Hq / a.g.Hkv > 8;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    const bool cached = dev >= 0 && dev < kMaxDevices;
+    if (cached) {
+        const int v = cache[hi][dev].load(std::memory_order_acquire);
+        if (v > 0) return v - 1;
+    }
     auto kern = hi ? decode_kernel<D, BS, CACHE, true> : decode_kernel<D, BS, CACHE, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return 0;
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeWarps * 32, Cfg::SMEM) != cudaSuccess) return 0;
+    if (cached) cache[hi][dev].store(per_sm + 1, std::memory_order_release);
     return per_sm;
 }
 
@@ -680,15 +714,25 @@ cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
     const int G = a.g.Hq / a.g.Hkv;
     const bool hi = G > 8;
     auto kern = hi ? decode_kernel<D, BS, CACHE, true> : decode_kernel<D, BS, CACHE, false>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-    if (e != cudaSuccess) return e;
-    int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeWarps * 32, Cfg::SMEM);
-    if (e != cudaSuccess) return e;
+    const int per_sm = occupancy_t<D, BS, CACHE>(a);
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
     const long long ctas = decode_ctas(a, per_sm, sm_count);
     if (ev0) cudaEventRecord(ev0, stream);
-    kern<<<(unsigned)ctas, kDecodeWarps * 32, Cfg::SMEM, stream>>>(a);
+    // Programmatic dependent launch: the kernel's CTAs may be placed and run their set-up while the
+    // cache-write launch before it drains; they wait (griddepcontrol.wait) before the first read of
+    // anything that launch writes.  An event record in between (kernel timing) serialises as usual.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kDecodeWarps * 32);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    if (e != cudaSuccess) return e;
     if (ev1) cudaEventRecord(ev1, stream);
     ++*launches;
     return cudaGetLastError();

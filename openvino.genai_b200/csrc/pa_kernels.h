@@ -85,6 +85,9 @@ struct KernelArgs {
     int64_t* score_offsets;// [num_sequences + 1] prefix sum of past_len + new tokens
     int* stile_prefix;     // [num_sequences + 1] prefix sum of key tiles of the sequences that want scores
     float* score_part;     // [Hkv][scores_len] per-kv-head column sums of the window probabilities
+    float* score_raw;      // [head tiles][scores_len][8 or 16] scaled logits (base 2) the decode kernel leaves for rows
+                           // with one new token and a non-zero window (8 slots per head tile when the GQA group has at
+                           // most 8 heads); null: every sequence goes through the score kernel
     long long scores_len;
 };
 
@@ -117,5 +120,8 @@ cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_c
 // SnapKV-style score output: scores[pos] = sum over q heads and the last W rows of each chunk of
 // the softmax probabilities, using the log-sum-exp the attention kernels exported.
 cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches);
+// Offsets of the sequences inside `scores` and the score kernel's work list; launched before the decode
+// kernel, which needs the offsets to leave its logits behind.
+cudaError_t launch_score_plan(const KernelArgs& a, cudaStream_t stream, int* launches);
 
 }  // namespace pa

@@ -45,7 +45,9 @@ __global__ void score_plan_kernel(KernelArgs a) {
             // cost of a sequence: key tiles x 16-row tiles of (window row, q head of the group) pairs
             const int W = ok ? min(max(a.score_aggregation_window[s], 0), n) : 0;
             const int G = a.g.Hq / a.g.Hkv;
-            if (W > 0) tiles = (int)((len + kTileS - 1) / kTileS) * ((W * G + 15) / 16);
+            // rows with one new token are served from the logits the decode kernel left in score_raw
+            const bool from_decode = a.score_raw != nullptr && n == 1;
+            if (W > 0 && !from_decode) tiles = (int)((len + kTileS - 1) / kTileS) * ((W * G + 15) / 16);
         }
         long long incl = len;
         int incl_t = tiles;
@@ -413,7 +415,37 @@ __global__ void __launch_bounds__(256) score_reduce_kernel(KernelArgs a) {
     const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
     const long long off = a.score_offsets[s], len = a.score_offsets[s + 1] - off;
     const bool live = a.stile_prefix[s + 1] > a.stile_prefix[s];
-    (void)n;
+    const int past = a.past_lens[s];
+    const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
+    const bool from_decode = a.score_raw != nullptr && n == 1 && past >= 0 && (long long)nb * a.g.bs >= len &&
+                             a.score_aggregation_window[s] > 0;
+    if (from_decode) {
+        // probabilities from the decode kernel's scaled logits (base 2) and the row's log-sum-exp, added
+        // over the q heads in head order
+        const int G = a.g.Hq / a.g.Hkv, gtiles = (G + 15) / 16, HK = a.g.Hkv * gtiles;
+        const int SL = a.rows_per_tile <= 8 ? 8 : 16;
+        const float* lse = a.lse + (long long)a.subsequence_begins[s] * a.g.Hq;
+        constexpr float kLog2e = 1.4426950408889634f;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (long long)gridDim.x * blockDim.x) {
+            if (off + i >= a.scores_len) break;
+            float v = 0.f;
+            for (int hkp = 0; hkp < HK; ++hkp) {
+                const int hk = hkp / gtiles;
+                const int hbase = hk * G + (hkp % gtiles) * 16;
+                const int hcount = min(16, hk * G + G - hbase);
+                const float4* raw = reinterpret_cast<const float4*>(a.score_raw + ((long long)hkp * a.scores_len + off + i) * SL);
+                for (int q = 0; q < SL / 4; ++q) {
+                    const float4 x = __ldcs(raw + q);
+                    const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (4 * q + e < hcount) v += exp2_fast(xs[e] - __ldg(lse + hbase + 4 * q + e) * kLog2e);
+                }
+            }
+            a.scores[off + i] = v;
+        }
+        return;
+    }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (long long)gridDim.x * blockDim.x) {
         float v = 0.f;
         if (live)
@@ -451,10 +483,15 @@ cudaError_t launch_score_c(const KernelArgs& a, cudaStream_t stream, int sm_coun
 
 }  // namespace
 
-cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches) {
+cudaError_t launch_score_plan(const KernelArgs& a, cudaStream_t stream, int* launches) {
     if (!a.scores || !a.score_aggregation_window || a.num_sequences <= 0) return cudaSuccess;
     score_plan_kernel<<<1, 32, 0, stream>>>(a);
     ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches) {
+    if (!a.scores || !a.score_aggregation_window || a.num_sequences <= 0) return cudaSuccess;
     cudaError_t e = cudaErrorInvalidValue;
     if (a.g.D == 128 && a.g.bs == 32) e = launch_score_c<128, 32>(a, stream, sm_count);
     else if (a.g.D == 128 && a.g.bs == 16) e = launch_score_c<128, 16>(a, stream, sm_count);

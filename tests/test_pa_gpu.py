@@ -130,6 +130,25 @@ def test_scores_qwen_shape_windows_and_block16():
     assert abs(got.sum() - ref.sum()) <= 1e-2 * ref.sum()
 
 
+@pytest.mark.parametrize("hq,hkv,cache", [(32, 2, "u8"), (40, 2, "u8"), (24, 2, "f16"), (8, 8, "u8")])
+def test_scores_of_decode_rows_come_from_the_decode_kernel(hq, hkv, cache):
+    """Rows with one new token take their scores from the logits the decode kernel leaves behind:
+    GQA groups above 8 and above 16 heads (two head tiles), a group of one, a context long enough
+    to be split over many workers, a window of 0 among them."""
+    wl = H.small_workload(hq=hq, hkv=hkv, d=128, bs=32, act=torch.float16, cache=cache, past=[6000, 33, 0, 250, 1023],
+                          new=[1, 1, 1, 1, 1], seed=hq + hkv)
+    wl.score_aggregation_window = np.array([1, 1, 1, 0, 1], np.int32)
+    res = H.run_both(wl)
+    _check(res, cache, torch.float16)
+    ref, got = res["scores_ref"], res["scores_gpu"]
+    assert not np.isnan(got).any()
+    assert np.abs(got - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+    off = 6001 + 34 + 1
+    assert np.all(got[off:off + 251] == 0), "window 0 must write zeros"
+    # every sequence's scores add up to the number of q heads (one softmax row per head)
+    assert abs(got[:6001].sum() - hq) < 1e-2 * hq
+
+
 @pytest.mark.parametrize("cache", ["f16", "bf16", "u8"])
 def test_rotation_is_bit_exact(cache):
     from openvino_genai_b200 import workloads
