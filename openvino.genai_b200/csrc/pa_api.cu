@@ -85,7 +85,7 @@ pa::CacheGeom make_geom(const pa_model_desc& d) {
 // Scratch layout of one forward call.
 struct Plan {
     long long max_tiles;
-    size_t off_hdr, off_prefix, off_pprefix, off_wstart, off_done, off_part_o, off_part_ml, off_lse, off_score_off, off_stile, off_score_part, off_score_raw, total;
+    size_t off_hdr, off_prefix, off_pprefix, off_porder, off_wstart, off_done, off_part_o, off_part_ml, off_lse, off_score_off, off_stile, off_score_part, off_score_raw, total;
     bool has_score_raw;
 };
 
@@ -104,6 +104,7 @@ Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_co
     p.off_hdr = off;       off += 256;
     p.off_prefix = off;    off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_pprefix = off;   off += align_up((size_t)(B + 1) * sizeof(int), 256);
+    p.off_porder = off;    off += align_up((size_t)pa::kPrefillSortCap * sizeof(int), 256);
     p.off_wstart = off;    off += align_up((size_t)pa::decode_max_workers(h->sm_count) * sizeof(pa::WorkerStart), 256);
     p.off_done = off;      off += align_up((size_t)std::max(B, 1LL) * HK * sizeof(int), 256);
     p.off_part_o = off;    off += align_up((size_t)slots * RT * g.D * sizeof(float), 256);
@@ -194,6 +195,7 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.tile_prefix = (int*)(h->ws + p.off_prefix);
     k.stream_done = (int*)(h->ws + p.off_done);
     k.ptile_prefix = (int*)(h->ws + p.off_pprefix);
+    k.pitem_order = (int*)(h->ws + p.off_porder);
     k.worker_start = (pa::WorkerStart*)(h->ws + p.off_wstart);
     k.decode_all_workers = 0;
     k.max_tiles = p.max_tiles;
@@ -210,7 +212,6 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count);   // the plan step prepares one start record per worker
     int launches = 0;
     if (a->num_rotated_blocks > 0) { PA_CUDA(pa::launch_rotate(k, stream)); ++launches; }
-    if (a->scores) PA_CUDA(pa::launch_score_plan(k, stream, &launches));   // the decode kernel needs the offsets
     PA_CUDA(pa::launch_write_kv(k, stream, /*with_plan=*/true)); ++launches;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (h->timing && h->ev_used + 2 <= 8192) {

@@ -106,12 +106,44 @@ __device__ void build_decode_plan(const KernelArgs& a) {
             for (int w = tid; w < a.decode_all_workers; w += 256) a.worker_start[w] = WorkerStart{-1, 0, 0, total_tiles, 0, 0, 0, 0};
         }
     }
+    // The prefill kernel hands out (q tile, kv head) items from a counter.  Longest context first keeps
+    // the last items short, so the CTAs finish together; sequence order leaves a long item for the end.
+    const int total_p = sh_run_p;
+    const bool sort_items = a.pitem_order != nullptr && total_p > 1 && total_p <= kPrefillSortCap;
+    if (sort_items) {
+        __shared__ int sh_cost[kPrefillSortCap];
+        if (tid == 0) a.ptile_prefix[B] = total_p;
+        __syncthreads();   // the prefix sums written above are visible to the whole block
+        for (int t = tid; t < total_p; t += 256) {
+            int lo = 0, hi = B;   // ptile_prefix[lo] <= t < ptile_prefix[hi]
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (a.ptile_prefix[mid] <= t) lo = mid; else hi = mid;
+            }
+            const int p0 = a.ptile_prefix[lo], np = a.ptile_prefix[lo + 1] - p0;
+            const int qt = np - 1 - (t - p0);   // the kernel's mapping: late (heavy) q tiles first
+            const int n_new = a.subsequence_begins[lo + 1] - a.subsequence_begins[lo];
+            const int r_hi = min(n_new * G, (qt + 1) * kPrefillItemRows) - 1;
+            sh_cost[t] = a.past_lens[lo] + r_hi / G + 1;   // context of the q tile's last row
+        }
+        __syncthreads();
+        for (int t = tid; t < total_p; t += 256) {
+            const int c = sh_cost[t];
+            int rank = 0;
+            for (int u = 0; u < total_p; ++u) {
+                const int cu = sh_cost[u];
+                rank += (cu > c || (cu == c && u < t)) ? 1 : 0;
+            }
+            a.pitem_order[rank] = t;
+        }
+    }
     if (tid == 0) {
         a.tile_prefix[B] = sh_run;
         a.plan->total_tiles = sh_run * HK;
         a.ptile_prefix[B] = sh_run_p;
         a.plan->total_ptiles = sh_run_p;
         a.plan->next_pitem = 0;
+        a.plan->pitems_sorted = sort_items ? 1 : 0;
     }
 }
 
@@ -126,6 +158,11 @@ __global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
     if constexpr (PLAN) {
         if (blockIdx.x == gridDim.x - 1) {
             build_decode_plan(a);
+            return;
+        }
+        // with a score output the block before the last prepares the score offsets and work list
+        if (a.scores && a.score_aggregation_window && blockIdx.x == gridDim.x - 2) {
+            if (threadIdx.x < 32) build_score_plan(a);
             return;
         }
     }
@@ -336,7 +373,7 @@ __global__ void __launch_bounds__(256) copy_blocks_kernel(uint8_t* key_cache, ui
 cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream, bool with_plan) {
     if (a.num_tokens <= 0 && !with_plan) return cudaSuccess;
     const long long warps = (long long)a.num_tokens * a.g.Hkv;
-    const int grid = (int)((warps * 32 + 255) / 256) + (with_plan ? 1 : 0);
+    const int grid = (int)((warps * 32 + 255) / 256) + (with_plan ? 1 : 0) + (with_plan && a.scores && a.score_aggregation_window ? 1 : 0);
     if (a.g.D == 128) {
         if (with_plan) write_kv_kernel<128, true><<<grid, 256, 0, stream>>>(a);
         else write_kv_kernel<128, false><<<grid, 256, 0, stream>>>(a);

@@ -16,8 +16,10 @@ struct PlanHeader {
     int total_tiles;   // 32-token tiles of all decode streams (rows x head tiles)
     int total_ptiles;  // kPrefillItemRows-row q tiles of all prefill chunks (per kv head)
     int next_pitem;    // work counter of the prefill kernel: next (q tile, kv head) item to hand out
-    int pad;
+    int pitems_sorted; // 1: pitem_order lists the q tiles by decreasing context length
 };
+
+constexpr int kPrefillSortCap = 512;   // q tiles (per kv head) up to which the plan step orders them
 
 // Where a decode worker's slice of the global tile sequence starts, prepared by the plan step so
 // that the worker's first load is one 32-byte record instead of a binary search.
@@ -75,6 +77,7 @@ struct KernelArgs {
     int* tile_prefix;      // [num_sequences + 1] exclusive prefix sum of tiles per row (one head tile)
     int* stream_done;      // [num_sequences * HK] partials of the stream published so far
     int* ptile_prefix;     // [num_sequences + 1] exclusive prefix sum of prefill q tiles per row (one kv head)
+    int* pitem_order;      // [kPrefillSortCap] q tiles, longest context first (valid when plan->pitems_sorted); may be null
     int decode_all_workers;      // warps the decode launch will have (0: the plan prepares no start records)
     WorkerStart* worker_start;   // [decode_all_workers], may be null
     long long max_tiles;   // upper bound of total_tiles known on the host
@@ -120,8 +123,48 @@ cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_c
 // SnapKV-style score output: scores[pos] = sum over q heads and the last W rows of each chunk of
 // the softmax probabilities, using the log-sum-exp the attention kernels exported.
 cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches);
-// Offsets of the sequences inside `scores` and the score kernel's work list; launched before the decode
-// kernel, which needs the offsets to leave its logits behind.
-cudaError_t launch_score_plan(const KernelArgs& a, cudaStream_t stream, int* launches);
+
+constexpr int kScoreTile = 32;   // keys per tile of the score kernel
+
+#ifdef __CUDACC__
+// Per-sequence offsets into `scores` (prefix sum of past_len + new tokens) and the prefix sum of the
+// score kernel's work (key tiles x row tiles) over the sequences it serves.  Run by one warp of the
+// cache-write launch, because the decode kernel needs the offsets to leave its logits behind.
+__device__ inline void build_score_plan(const KernelArgs& a) {
+    long long run = 0;
+    int run_t = 0;
+    const int lane = threadIdx.x & 31;
+    for (int base = 0; base < a.num_sequences; base += 32) {
+        const int s = base + lane;
+        long long len = 0;
+        int tiles = 0;
+        if (s < a.num_sequences) {
+            const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
+            const int past = a.past_lens[s];
+            const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
+            len = (long long)max(past, 0) + max(n, 0);
+            const bool ok = n > 0 && past >= 0 && (long long)nb * a.g.bs >= len;
+            // cost of a sequence: key tiles x 16-row tiles of (window row, q head of the group) pairs
+            const int W = ok ? min(max(a.score_aggregation_window[s], 0), n) : 0;
+            const int G = a.g.Hq / a.g.Hkv;
+            // rows with one new token are served from the logits the decode kernel left in score_raw
+            const bool from_decode = a.score_raw != nullptr && n == 1;
+            if (W > 0 && !from_decode) tiles = (int)((len + kScoreTile - 1) / kScoreTile) * ((W * G + 15) / 16);
+        }
+        long long incl = len;
+        int incl_t = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long v = __shfl_up_sync(0xffffffffu, incl, o);
+            const int vt = __shfl_up_sync(0xffffffffu, incl_t, o);
+            if (lane >= o) { incl += v; incl_t += vt; }
+        }
+        if (s < a.num_sequences) { a.score_offsets[s] = run + incl - len; a.stile_prefix[s] = run_t + incl_t - tiles; }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+        run_t += __shfl_sync(0xffffffffu, incl_t, 31);
+    }
+    if (lane == 0) { a.score_offsets[a.num_sequences] = run; a.stile_prefix[a.num_sequences] = run_t; }
+}
+#endif
 
 }  // namespace pa

@@ -175,7 +175,8 @@ struct Item {
 
 __device__ __forceinline__ Item locate_item(const KernelArgs& a, int item, int G, int Hkv) {
     Item it;
-    const int gq = item / Hkv;
+    // q tiles in the plan's order (longest context first) when it made one, else in sequence order
+    const int gq = a.plan->pitems_sorted ? __ldcg(a.pitem_order + item / Hkv) : item / Hkv;
     it.hk = item % Hkv;
     int lo = 0, hi = a.num_sequences;  // ptile_prefix[lo] <= gq < ptile_prefix[hi]
     while (hi - lo > 1) {

@@ -22,47 +22,9 @@ namespace pa {
 
 namespace {
 
-constexpr int kTileS = 32;
+constexpr int kTileS = kScoreTile;
 constexpr int kScoreWarps = 4;
 constexpr float kLog2eS = 1.4426950408889634f;
-
-// Per-sequence offsets into `scores` (prefix sum of past_len + new tokens) and the prefix sum of key
-// tiles of the sequences whose window is non-zero.  One warp.
-__global__ void score_plan_kernel(KernelArgs a) {
-    long long run = 0;
-    int run_t = 0;
-    const int lane = threadIdx.x;
-    for (int base = 0; base < a.num_sequences; base += 32) {
-        const int s = base + lane;
-        long long len = 0;
-        int tiles = 0;
-        if (s < a.num_sequences) {
-            const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
-            const int past = a.past_lens[s];
-            const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
-            len = (long long)max(past, 0) + max(n, 0);
-            const bool ok = n > 0 && past >= 0 && (long long)nb * a.g.bs >= len;
-            // cost of a sequence: key tiles x 16-row tiles of (window row, q head of the group) pairs
-            const int W = ok ? min(max(a.score_aggregation_window[s], 0), n) : 0;
-            const int G = a.g.Hq / a.g.Hkv;
-            // rows with one new token are served from the logits the decode kernel left in score_raw
-            const bool from_decode = a.score_raw != nullptr && n == 1;
-            if (W > 0 && !from_decode) tiles = (int)((len + kTileS - 1) / kTileS) * ((W * G + 15) / 16);
-        }
-        long long incl = len;
-        int incl_t = tiles;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const long long v = __shfl_up_sync(0xffffffffu, incl, o);
-            const int vt = __shfl_up_sync(0xffffffffu, incl_t, o);
-            if (lane >= o) { incl += v; incl_t += vt; }
-        }
-        if (s < a.num_sequences) { a.score_offsets[s] = run + incl - len; a.stile_prefix[s] = run_t + incl_t - tiles; }
-        run += __shfl_sync(0xffffffffu, incl, 31);
-        run_t += __shfl_sync(0xffffffffu, incl_t, 31);
-    }
-    if (lane == 0) { a.score_offsets[a.num_sequences] = run; a.stile_prefix[a.num_sequences] = run_t; }
-}
 
 template <int D, int BS, int CACHE>
 struct ScoreCfg {
@@ -482,13 +444,6 @@ cudaError_t launch_score_c(const KernelArgs& a, cudaStream_t stream, int sm_coun
 }
 
 }  // namespace
-
-cudaError_t launch_score_plan(const KernelArgs& a, cudaStream_t stream, int* launches) {
-    if (!a.scores || !a.score_aggregation_window || a.num_sequences <= 0) return cudaSuccess;
-    score_plan_kernel<<<1, 32, 0, stream>>>(a);
-    ++*launches;
-    return cudaGetLastError();
-}
 
 cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches) {
     if (!a.scores || !a.score_aggregation_window || a.num_sequences <= 0) return cudaSuccess;
