@@ -99,7 +99,9 @@ __device__ __forceinline__ void store_pair(void* out, long long idx, int act, fl
     else *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)out + idx) = __floats2bfloat162_rn(v0, v1);
 }
 
-template <int D, int BS, int CACHE, bool HI>
+// SC: the launch keeps the scaled logits of rows whose scores are wanted (a.score_raw is set); a
+// separate instantiation so that steps without a score output run the same code as before.
+template <int D, int BS, int CACHE, bool HI, bool SC>
 __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2) ? 2 : 3) decode_kernel(KernelArgs a) {
     using Cfg = DecodeCfg<D, BS, CACHE>;
     constexpr bool U8 = Cfg::U8;
@@ -180,8 +182,10 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         if (lane == 0) {
             // rows whose attention scores are wanted (window > 0) leave their scaled logits behind
             long long score_off = -1;
-            if (a.score_raw && a.score_aggregation_window[r_s] > 0)
-                score_off = ((long long)r_hkp * a.scores_len + a.score_offsets[r_s]) * (RT <= 8 ? 8 : 16);
+            if constexpr (SC) {
+                if (a.score_aggregation_window[r_s] > 0)
+                    score_off = ((long long)r_hkp * a.scores_len + a.score_offsets[r_s]) * (RT <= 8 ? 8 : 16);
+            }
             runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, score_off};
         }
         g_tile += ntile;
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         // All 8 lanes of a token write, dead head rows too, so that every store fills whole 32-byte sectors.
         constexpr int SL = 8 * ROWS;
         float* score_dst = nullptr;
-        if (a.score_raw) {
+        if constexpr (SC) {
             const long long so = runs[d.run].score_off;
             if (so >= 0) score_dst = a.score_raw + so + (long long)d.tok0 * SL + g;
         }
@@ -465,9 +469,11 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
                 }
                 s0 = ok0 ? s0 : -INFINITY;
                 s1 = ok1 ? s1 : -INFINITY;
-                if (score_dst) {
-                    if (ok0) __stcs(score_dst + tk * SL + 8 * r, s0);
-                    if (ok1) __stcs(score_dst + (tk + 1) * SL + 8 * r, s1);
+                if constexpr (SC) {
+                    if (score_dst) {
+                        if (ok0) __stcs(score_dst + tk * SL + 8 * r, s0);
+                        if (ok1) __stcs(score_dst + (tk + 1) * SL + 8 * r, s1);
+                    }
                 }
                 sacc[j][2 * r] = s0; sacc[j][2 * r + 1] = s1;
                 tmax[r] = fmaxf(tmax[r], fmaxf(s0, s1));
@@ -691,20 +697,23 @@ template <int D, int BS, int CACHE>
 int occupancy_t(const KernelArgs& a) {
     using Cfg = DecodeCfg<D, BS, CACHE>;
     constexpr int kMaxDevices = 64;
-    static std::atomic<int> cache[2][kMaxDevices];   // 0 = unknown, else per_sm + 1
+    static std::atomic<int> cache[4][kMaxDevices];   // 0 = unknown, else per_sm + 1
     const bool hi = a.g.Hq / a.g.Hkv > 8;
+    const bool sc = a.score_raw != nullptr && a.score_aggregation_window != nullptr;
+    const int slot = (hi ? 2 : 0) + (sc ? 1 : 0);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     const bool cached = dev >= 0 && dev < kMaxDevices;
     if (cached) {
-        const int v = cache[hi][dev].load(std::memory_order_acquire);
+        const int v = cache[slot][dev].load(std::memory_order_acquire);
         if (v > 0) return v - 1;
     }
-    auto kern = hi ? decode_kernel<D, BS, CACHE, true> : decode_kernel<D, BS, CACHE, false>;
+    auto kern = hi ? (sc ? decode_kernel<D, BS, CACHE, true, true> : decode_kernel<D, BS, CACHE, true, false>)
+                   : (sc ? decode_kernel<D, BS, CACHE, false, true> : decode_kernel<D, BS, CACHE, false, false>);
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return 0;
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeWarps * 32, Cfg::SMEM) != cudaSuccess) return 0;
-    if (cached) cache[hi][dev].store(per_sm + 1, std::memory_order_release);
+    if (cached) cache[slot][dev].store(per_sm + 1, std::memory_order_release);
     return per_sm;
 }
 
@@ -713,7 +722,9 @@ cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
     using Cfg = DecodeCfg<D, BS, CACHE>;
     const int G = a.g.Hq / a.g.Hkv;
     const bool hi = G > 8;
-    auto kern = hi ? decode_kernel<D, BS, CACHE, true> : decode_kernel<D, BS, CACHE, false>;
+    const bool sc = a.score_raw != nullptr && a.score_aggregation_window != nullptr;
+    auto kern = hi ? (sc ? decode_kernel<D, BS, CACHE, true, true> : decode_kernel<D, BS, CACHE, true, false>)
+                   : (sc ? decode_kernel<D, BS, CACHE, false, true> : decode_kernel<D, BS, CACHE, false, false>);
     const int per_sm = occupancy_t<D, BS, CACHE>(a);
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
     const long long ctas = decode_ctas(a, per_sm, sm_count);
