@@ -372,7 +372,10 @@ def run_sampler(args):
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
     dev = torch.device("cuda", 0)
     greedy = args.workload == "qwen25_sampler_greedy"
-    logits_h, par, hist = workloads.config_qwen_sampler(greedy=greedy)
+    mode = {"qwen25_sampler_topp": "top_p", "qwen25_sampler_temperature": "temperature"}.get(args.workload)
+    logits_h, par, hist = workloads.config_qwen_sampler(greedy=greedy, mode=mode)
+    sampling = {"top_p": "T 1, top_p 0.95 over the whole vocabulary", "temperature": "T 0.8 over the whole vocabulary"}.get(
+        mode, "greedy + penalties" if greedy else "top_k 50, T 0.7, top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1")
     pristine = torch.from_numpy(logits_h).to(dev)
     work = pristine.clone()
     smp = sampler_mod.SamplerStep(0)
@@ -398,8 +401,7 @@ def run_sampler(args):
     line = {"metric": "sampler_step_us", "value": round(us, 1), "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(us / 1e3, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "rows": int(logits_h.shape[0]), "vocab": int(logits_h.shape[1]),
-                       "sampling": "greedy + penalties" if greedy else "top_k 50, T 0.7, top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1",
-                       "history": "1024 generated ids per row", "l2_policy": "logits rewritten from a pristine copy before every step"},
+                       "sampling": sampling, "history": "none" if hist is None else "1024 generated ids per row", "l2_policy": "logits rewritten from a pristine copy before every step"},
             "min_us": round(min(times), 1),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
                          "kernel": "sampler_kernel", "algorithmic_bytes_per_launch": int(logits_h.nbytes), "peak_source": peak_kind},
@@ -536,7 +538,7 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload in ("qwen25_sampler_topk", "qwen25_sampler_greedy"):
+    elif args.workload in ("qwen25_sampler_topk", "qwen25_sampler_greedy", "qwen25_sampler_topp", "qwen25_sampler_temperature"):
         run_sampler(args)
     elif args.workload == "llama3_70b_u8_step":
         run_engine_step(args)

@@ -339,6 +339,7 @@ struct Shared {
             unsigned long long hist_mass[2048];
             unsigned int hist_piece[3][2048];      // the same masses while they are being added, in pieces
             unsigned long long first_mass[2048];   // first level of the top-p descent, kept for the draw
+            int bin_first[1024];                   // lowest index of every bin of the draw's last level
         };
     };
     int cand_count[2];
@@ -701,14 +702,33 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     // ---- 4. full vocabulary ---------------------------------------------------------------------------
     const float T = p.temperature;
     const float f = 1.0f / T;
+    const bool top_p_on = p.top_p != 1.0f;
     float mx = -CUDART_INF_F;
-    for_row(row, V, tid, [&](float x, long long) { mx = fmaxf(mx, x); });
-    mx = block_reduce(mx, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
+    double dsum = 0.0;
     // single-precision expf here: this path does not reproduce the reference's order of summation
     // anyway, and the double-precision form costs an order of magnitude more over a whole vocabulary
-    auto weight = [&](float x) { return T == 1.0f ? expf(x - mx) : expf((x - mx) * f); };
-    double dsum = 0.0;
-    for_row(row, V, tid, [&](float x, long long) { dsum += (double)weight(x); });
+    auto wexp = [&](float d) { return T == 1.0f ? expf(d) : expf(d * f); };
+    if (top_p_on) {
+        // maximum and sum in one pass over the row (the passes are bound by DRAM: a batch of rows does not
+        // fit in L2): every thread sums against its own running maximum and rescales when that rises
+        float m = -CUDART_INF_F;
+        double sacc = 0.0;
+        for_row(row, V, tid, [&](float x, long long) {
+            if (x > m) {
+                sacc = sacc * (double)wexp(m - x) + 1.0;
+                m = x;
+            } else if (m > -CUDART_INF_F) {
+                sacc += (double)wexp(x - m);
+            }
+        });
+        mx = block_reduce(m, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
+        dsum = sacc != 0.0 ? sacc * (double)wexp(m - mx) : 0.0;
+    } else {
+        for_row(row, V, tid, [&](float x, long long) { mx = fmaxf(mx, x); });
+        mx = block_reduce(mx, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
+    }
+    auto weight = [&](float x) { return wexp(x - mx); };
+    if (!top_p_on) for_row(row, V, tid, [&](float x, long long) { dsum += (double)weight(x); });
     dsum = block_reduce(dsum, 0.0, [](double x, double y) { return x + y; }, sh.red_d);
     const float norm = (float)dsum;
     auto prob = [&](float x) { return __fdiv_rn(weight(x), norm); };
@@ -727,21 +747,23 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     // atomics, which resolve collisions in hardware, instead of 64-bit ones (a compare-and-swap loop).
     // A piece's sum stays below 2^32 for rows of fewer than 2^18 elements; longer rows add 64-bit.
     const bool pieces = V < (1ll << 18);
-    auto build_level = [&](uint32_t prefix, int shift, int bits, bool first, uint32_t lo_key) {
+    auto build_level = [&](uint32_t prefix, int shift, int bits, bool first, uint32_t lo_key, bool want_index) {
         const int nb = 1 << bits;
         for (int i = tid; i < nb; i += kThreads) {
             sh.hist_mass[i] = 0;
+            if (want_index && i < 1024) sh.bin_first[i] = 0x7fffffff;
             sh.hist_piece[0][i] = 0; sh.hist_piece[1][i] = 0; sh.hist_piece[2][i] = 0;
         }
         __syncthreads();
         const uint32_t hi_mask = first ? 0u : (0xffffffffu << (shift + bits));
-        for_row(row, V, tid, [&](float x, long long) {
+        for_row(row, V, tid, [&](float x, long long idx) {
             const uint32_t k = float_key(x);
             if (k < lo_key || (k & hi_mask) != prefix) return;
             const float pr = prob(x);
             if (pr < min_thr) return;
             const int bin = (k >> shift) & (nb - 1);
             const unsigned long long m = fixed(pr);
+            if (want_index) atomicMin(&sh.bin_first[bin], (int)idx);   // last level: a bin is one key, its lowest index is the pick
             if (pieces) {
                 atomicAdd(&sh.hist_piece[0][bin], (unsigned int)(m & 0x3fffu));
                 atomicAdd(&sh.hist_piece[1][bin], (unsigned int)((m >> 14) & 0x3fffu));
@@ -813,7 +835,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         for (int level = 0; level < 3; ++level) {
             const int bits = level == 2 ? 10 : 11;
             shift -= bits;
-            build_level(prefix, shift, bits, level == 0, 0u);
+            build_level(prefix, shift, bits, level == 0, 0u, false);
             if (level == 0)   // the second descent starts from this histogram
                 for (int i = tid; i < 2048; i += kThreads) sh.first_mass[i] = sh.hist_mass[i];
             select_bin(1 << bits, mass_above, target);
@@ -960,6 +982,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         unsigned long long mass_above = 0;
         uint32_t prefix = 0;
         int shift = 32;
+        int pick = 0x7fffffff;
         for (int level = 0; level < 3; ++level) {
             const int bits = level == 2 ? 10 : 11;
             shift -= bits;
@@ -971,7 +994,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
                     sh.hist_mass[i] = i > first_bin ? sh.first_mass[i] : (i == first_bin ? kept - first_above : 0ull);
                 __syncthreads();
             } else {
-                build_level(prefix, shift, bits, false, key_lo);
+                build_level(prefix, shift, bits, false, key_lo, level == 2);
             }
             select_bin(nb, mass_above, rfix);
             const int sel = sh.sel_bin;
@@ -990,13 +1013,15 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
                 break;
             }
             prefix |= (uint32_t)sel << shift;
+            if (level == 2) pick = sh.bin_first[sel];   // recorded while the last level was built
         }
         // all elements with this exact key have the same probability: the lowest index is taken
-        int pick = 0x7fffffff;
-        for_row(row, V, tid, [&](float x, long long i) {
-            if (float_key(x) == prefix) pick = min(pick, (int)i);
-        });
-        pick = block_reduce(pick, 0x7fffffff, [](int x, int y) { return min(x, y); }, sh.red_i);
+        if (pick == 0x7fffffff) {   // only after the fallback above
+            for_row(row, V, tid, [&](float x, long long i) {
+                if (float_key(x) == prefix) pick = min(pick, (int)i);
+            });
+            pick = block_reduce(pick, 0x7fffffff, [](int x, int y) { return min(x, y); }, sh.red_i);
+        }
         if (tid == 0) {
             const float pr = prob(row[pick]);
             a.out_token[r] = pick;

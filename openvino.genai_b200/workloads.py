@@ -229,9 +229,12 @@ def sampler_history(rng: np.random.Generator, rows: int, vocab: int, generated_l
     return np.array(offs, np.int64), np.array(ids, np.int32), np.array(meta, np.uint32)
 
 
-def config_qwen_sampler(rows: int = 256, vocab: int = 151936, greedy: bool = False, history: int = 1024, seed: int = 1004):
+def config_qwen_sampler(rows: int = 256, vocab: int = 151936, greedy: bool = False, history: int = 1024, seed: int = 1004,
+                        mode: Optional[str] = None):
     """Qwen2.5 vocabulary, 256 rows: logits N(0, 4) with 8 spikes of +15 per row, T 0.7, top_k 50,
     top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1 over a 1024-token generated history.
+    `mode` selects the other paths on the same logits: "top_p" (T 1, top_p 0.95 over the whole vocabulary, no
+    penalties - the sampling of BASELINE.json configs[4]) and "temperature" (T 0.8 only).
     Returns (logits f32 [rows, vocab], packed row parameters, history)."""
     from . import _sampler_abi as SA
     rng = np.random.default_rng(seed)
@@ -249,4 +252,12 @@ def config_qwen_sampler(rows: int = 256, vocab: int = 151936, greedy: bool = Fal
     par["presence_penalty"] = 0.2
     par["frequency_penalty"] = 0.1
     par["rand_u"] = np.random.default_rng(seed + 1).random(rows, dtype=np.float32)
+    if mode in ("top_p", "temperature"):
+        par["top_k"] = SA.TOP_K_OFF
+        par["temperature"] = 1.0 if mode == "top_p" else 0.8
+        par["top_p"] = 0.95 if mode == "top_p" else 1.0
+        par["repetition_penalty"] = 1.0
+        par["presence_penalty"] = 0.0
+        par["frequency_penalty"] = 0.0
+        hist = None
     return logits, par, hist
