@@ -427,9 +427,8 @@ int pa_b200_forward_host(pa_handle* h, const pa_forward_args* a) {
         off += align_up(bytes, 256);
         return in[n_in++].off;
     };
-    const size_t o_q = add(a->query, q_bytes);
-    const size_t o_k = add(a->key, kv_bytes);
-    const size_t o_v = add(a->value, kv_bytes);
+    // metadata first (always staged through the handle's pinned buffer), then the activations, which are
+    // copied straight from the caller's buffers when those are page-locked themselves
     const size_t o_past = add(a->past_lens, B * 4);
     const size_t o_sub = add(a->subsequence_begins, (B + 1) * 4);
     const size_t o_bi = add(a->block_indices, (size_t)a->num_block_indices * 4);
@@ -441,6 +440,11 @@ int pa_b200_forward_host(pa_handle* h, const pa_forward_args* a) {
         o_rd = add(a->rotation_deltas, (size_t)a->num_rotated_blocks * 4);
         o_lut = add(a->rotation_trig_lut, (size_t)a->rotation_lut_rows * g.D * 4);
     }
+    const int n_meta = n_in;
+    const size_t meta_bytes = off;
+    const size_t o_q = add(a->query, q_bytes);
+    const size_t o_k = add(a->key, kv_bytes);
+    const size_t o_v = add(a->value, kv_bytes);
     const size_t in_bytes = off;
     const size_t o_out = off;
     off += align_up(q_bytes, 256);
@@ -449,9 +453,19 @@ int pa_b200_forward_host(pa_handle* h, const pa_forward_args* a) {
     rc = ensure_stage(h, off);
     if (rc != PA_OK) return rc;
 
-    for (int i = 0; i < n_in; ++i)
+    auto page_locked = [](const void* p) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+        return at.type == cudaMemoryTypeHost;
+    };
+    const bool direct = page_locked(a->query) && page_locked(a->key) && page_locked(a->value);
+    const int n_staged = direct ? n_meta : n_in;
+    for (int i = 0; i < n_staged; ++i)
         if (in[i].bytes) std::memcpy(h->stage_host + in[i].off, in[i].src, in[i].bytes);
-    PA_CUDA(cudaMemcpyAsync(h->stage_dev, h->stage_host, in_bytes, cudaMemcpyHostToDevice, stream));
+    PA_CUDA(cudaMemcpyAsync(h->stage_dev, h->stage_host, direct ? meta_bytes : in_bytes, cudaMemcpyHostToDevice, stream));
+    if (direct)
+        for (int i = n_meta; i < n_in; ++i)
+            if (in[i].bytes) PA_CUDA(cudaMemcpyAsync(h->stage_dev + in[i].off, in[i].src, in[i].bytes, cudaMemcpyHostToDevice, stream));
 
     pa_forward_args d = *a;
     uint8_t* base = h->stage_dev;
@@ -471,9 +485,11 @@ int pa_b200_forward_host(pa_handle* h, const pa_forward_args* a) {
     if (rc != PA_OK) return rc;
     PA_CUDA(cudaMemcpyAsync(a->output, base + o_out, q_bytes, cudaMemcpyDeviceToHost, stream));
     if (a->scores) PA_CUDA(cudaMemcpyAsync(a->scores, base + o_scores, (size_t)a->scores_len * 4, cudaMemcpyDeviceToHost, stream));
-    uint32_t bits = 0;
-    PA_CUDA(cudaMemcpyAsync(&bits, h->status, 4, cudaMemcpyDeviceToHost, stream));
+    // the status word comes back through the pinned staging buffer (a pageable target would make the copy synchronous)
+    uint32_t* bits_host = reinterpret_cast<uint32_t*>(h->stage_host);
+    PA_CUDA(cudaMemcpyAsync(bits_host, h->status, 4, cudaMemcpyDeviceToHost, stream));
     PA_CUDA(cudaStreamSynchronize(stream));
+    const uint32_t bits = *bits_host;
     if (bits) {
         PA_CUDA(cudaMemsetAsync(h->status, 0, 4, stream));
         return fail(PA_ERR_BAD_INDEX, "device status word 0x" + std::to_string(bits));
