@@ -41,8 +41,6 @@ __device__ void build_decode_plan(const KernelArgs& a) {
     __shared__ int sh_run_p;
     constexpr int kPrefixCap = 2048;           // rows whose prefix sums are also kept in shared memory
     __shared__ int sh_prefix[kPrefixCap + 1];
-    // what a start record needs of its row, kept here so that the records are built without global loads
-    __shared__ int sh_past[kPrefixCap], sh_sub[kPrefixCap], sh_bib[kPrefixCap + 1];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int B = a.num_sequences;
     const int G = a.g.Hq / a.g.Hkv, HK = a.g.Hkv * ((G + 15) / 16);
@@ -72,12 +70,6 @@ __device__ void build_decode_plan(const KernelArgs& a) {
             a.tile_prefix[s] = off + v - n;
             a.ptile_prefix[s] = offp + vp - np;
             if (s <= kPrefixCap) sh_prefix[s] = off + v - n;
-            if (s < kPrefixCap) {
-                sh_past[s] = a.past_lens[s];
-                sh_sub[s] = a.subsequence_begins[s];
-                sh_bib[s] = a.block_indices_begins[s];
-                if (s == B - 1) sh_bib[B] = a.block_indices_begins[B];
-            }
         }
         __syncthreads();
         if (tid == 255) { sh_run = off + v; sh_run_p = offp + vp; }
@@ -102,9 +94,9 @@ __device__ void build_decode_plan(const KernelArgs& a) {
                         const int mid = (lo + hi) >> 1;
                         if (sh_prefix[mid] <= key) lo = mid; else hi = mid;
                     }
-                    const int tb = sh_bib[lo];
-                    ws = WorkerStart{lo, sh_prefix[lo], sh_prefix[lo + 1] - sh_prefix[lo], total_tiles, sh_past[lo] + 1, tb,
-                                     sh_bib[lo + 1] - tb, sh_sub[lo]};
+                    const int tb = a.block_indices_begins[lo];
+                    ws = WorkerStart{lo, sh_prefix[lo], sh_prefix[lo + 1] - sh_prefix[lo], total_tiles, a.past_lens[lo] + 1, tb,
+                                     a.block_indices_begins[lo + 1] - tb, a.subsequence_begins[lo]};
                 } else {
                     ws.s = -2;   // no tiles for this worker
                 }
