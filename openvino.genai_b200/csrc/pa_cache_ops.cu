@@ -152,9 +152,8 @@ __device__ void build_decode_plan(const KernelArgs& a) {
 template <int D, bool PLAN>
 __global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
     constexpr int PER = D / 32;
-    // a decode launch queued as a programmatic dependent may place its CTAs now; it still waits for
-    // this grid to finish before it reads the plan or the cache
-    asm volatile("griddepcontrol.launch_dependents;");
+    // No early griddepcontrol.launch_dependents here: decode CTAs placed while blocks of this grid still hold
+    // shared memory do not all fit, and the decode kernel's static slices then run in two waves.
     if constexpr (PLAN) {
         if (blockIdx.x == gridDim.x - 1) {
             build_decode_plan(a);

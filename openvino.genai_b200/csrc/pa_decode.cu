@@ -729,9 +729,10 @@ cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
     const long long ctas = decode_ctas(a, per_sm, sm_count);
     if (ev0) cudaEventRecord(ev0, stream);
-    // Programmatic dependent launch: the kernel's CTAs may be placed and run their set-up while the
-    // cache-write launch before it drains; they wait (griddepcontrol.wait) before the first read of
-    // anything that launch writes.  An event record in between (kernel timing) serialises as usual.
+    // Programmatic dependent launch: the launch is queued behind the cache-write kernel without a full
+    // stream serialisation; that kernel never triggers early, so the CTAs start when it has finished, and
+    // they still wait (griddepcontrol.wait) before the first read of anything it writes.  An event record
+    // in between (kernel timing) serialises as usual.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kDecodeWarps * 32);
