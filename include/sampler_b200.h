@@ -54,7 +54,8 @@ typedef enum sampler_status {
  * activation rules (logit_processor.hpp:59-104). */
 typedef struct sampler_row_params {
     int64_t logits_row;        /* row of `logits` to sample from (rows are not assumed to be in request order) */
-    int64_t top_k;             /* active iff 0 < top_k < INT64_MAX; >= vocab leaves the full vocabulary   */
+    int64_t top_k;             /* active iff 0 < top_k < INT64_MAX; >= vocab leaves the full vocabulary; an active
+                                  top_k below the vocabulary must be <= 1024 (status bit 3 otherwise)         */
     int32_t do_sample;         /* 0 = greedy, 1 = multinomial; SAMPLER_ROW_* bits                       */
     float temperature;         /* 1.0 = off                                                            */
     float top_p;               /* 1.0 = off                                                            */
@@ -102,10 +103,18 @@ int sampler_b200_step(sampler_handle* h, const sampler_step_args* args);
 int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* args, int copy_logits_back);
 
 /* Reads (and clears) the device status word: bit 0 = out-of-range history id, bit 1 = logits_row out of
- * range, bit 2 = SAMPLER_ROW_RAW_LOG_PROB on a row with history but no hist_raw scratch. */
+ * range, bit 2 = SAMPLER_ROW_RAW_LOG_PROB on a row with history but no hist_raw scratch, bit 3 = a
+ * multinomial row with 1024 < top_k < vocab (the top-k heap lives in shared memory and holds 1024
+ * candidates; such a row gets token -1 and sampler_b200_step_host returns SAMPLER_ERR_UNSUPPORTED),
+ * bit 4 = internal: the sorted walk of a top-p row did not terminate. */
 int sampler_b200_last_device_status(sampler_handle* h, uint32_t* status_bits);
 
 int64_t sampler_b200_launch_count(const sampler_handle* h);
+
+/* Diagnostic: evaluates the device restatement of the host libm's expf (the function every
+ * TemperatureLogitTransform element goes through, logit_transformers.hpp:327-356) on `n` HOST floats.
+ * The full-vocabulary path is exact only where this returns the host's expf bits; the tests compare. */
+int sampler_b200_selftest_expf(sampler_handle* h, const float* in, float* out, int64_t n);
 
 #ifdef __cplusplus
 }

@@ -65,4 +65,5 @@ SAMPLER_SYMBOLS = {
     "sampler_b200_step_host": (C.c_int, [C.c_void_p, C.POINTER(sampler_step_args), C.c_int]),
     "sampler_b200_last_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "sampler_b200_launch_count": (C.c_int64, [C.c_void_p]),
+    "sampler_b200_selftest_expf": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
 }

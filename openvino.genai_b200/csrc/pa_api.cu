@@ -176,6 +176,7 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.key_cache = a->key_cache; k.value_cache = a->value_cache; k.num_blocks = a->num_blocks;
     k.past_lens = a->past_lens; k.subsequence_begins = a->subsequence_begins;
     k.block_indices = a->block_indices; k.block_indices_begins = a->block_indices_begins;
+    k.num_block_indices = a->num_block_indices;
     k.num_sequences = a->num_sequences; k.max_context_len = a->max_context_len;
     k.scale = a->scale;
     k.score_aggregation_window = a->score_aggregation_window;

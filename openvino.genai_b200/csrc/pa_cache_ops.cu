@@ -21,15 +21,9 @@ __device__ __forceinline__ int find_sequence(const int32_t* begins, int num_seq,
 
 // Number of 32-token context tiles of one decode row (0 for rows that are not decode rows).
 __device__ __forceinline__ int seq_tiles(const KernelArgs& a, int s) {
-    const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
-    if (n != 1) return 0;
-    const int past = a.past_lens[s];
-    const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
-    if (past < 0 || nb < 0 || (long long)nb * a.g.bs < (long long)past + 1) {
-        atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
-        return 0;
-    }
-    return (past + 1 + 31) / 32;
+    SeqView v;
+    if (!seq_view(a, s, v) || v.n != 1) return 0;
+    return (v.past + 1 + 31) / 32;
 }
 
 // Builds the decode plan with one block of 256 threads: the exclusive prefix sum of the per-row
@@ -52,9 +46,8 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         // prefill chunks: q tiles of kPrefillItemRows (new token, q head of one group) pairs
         int np = 0;
         if (s < B) {
-            const int n_new = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
-            const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
-            if (n_new > 1 && a.past_lens[s] >= 0 && (long long)nb * a.g.bs >= (long long)a.past_lens[s] + n_new) np = (n_new * G + kPrefillItemRows - 1) / kPrefillItemRows;
+            SeqView sv;
+            if (n == 0 && seq_view(a, s, sv) && sv.n > 1) np = (sv.n * G + kPrefillItemRows - 1) / kPrefillItemRows;
         }
         int v = n, vp = np;
 #pragma unroll
@@ -171,16 +164,14 @@ __global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
     if (warp >= total) return;
     const int t = warp / a.g.Hkv, h = warp % a.g.Hkv;
     const int s = find_sequence(a.subsequence_begins, a.num_sequences, t);
-    const int t0 = a.subsequence_begins[s];
-    const int n = a.subsequence_begins[s + 1] - t0;
-    const int past = a.past_lens[s];
-    const int tb = a.block_indices_begins[s];
-    const int nb = a.block_indices_begins[s + 1] - tb;
-    const int pos = past + (t - t0);
-    if (past < 0 || n <= 0 || pos / a.g.bs >= nb) {
-        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
+    SeqView sv;
+    if (!seq_view(a, s, sv)) return;
+    const int t0 = sv.t0, past = sv.past, tb = sv.tb;
+    if (t < t0 || t >= t0 + sv.n) {   // prefix sums that are not monotone, or that leave tokens uncovered
+        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_BEGINS);
         return;
     }
+    const int pos = past + (t - t0);
     const int block = a.block_indices[tb + pos / a.g.bs];
     if (block < 0 || block >= a.num_blocks) {
         if (lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);

@@ -183,8 +183,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
             // rows whose attention scores are wanted (window > 0) leave their scaled logits behind
             long long score_off = -1;
             if constexpr (SC) {
-                if (a.score_aggregation_window[r_s] > 0)
-                    score_off = ((long long)r_hkp * a.scores_len + a.score_offsets[r_s]) * (RT <= 8 ? 8 : 16);
+                if (a.score_aggregation_window[r_s] > 0) {
+                    // the row's slot must lie inside `scores` (and so inside score_raw, which is sized from
+                    // the same scores_len): a caller's scores_len shorter than the metadata implies is
+                    // reported, and the row leaves no logits behind
+                    const long long off = a.score_offsets[r_s];
+                    if (off >= 0 && off + ctx <= a.scores_len) score_off = ((long long)r_hkp * a.scores_len + off) * (RT <= 8 ? 8 : 16);
+                    else atomicOr(a.status, PA_DEV_BAD_BEGINS);
+                }
             }
             runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, score_off};
         }

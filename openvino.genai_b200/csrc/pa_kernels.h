@@ -58,6 +58,7 @@ struct KernelArgs {
     const int32_t* subsequence_begins;
     const int32_t* block_indices;
     const int32_t* block_indices_begins;
+    int num_block_indices;
     int num_sequences;
     int max_context_len;
     float scale;
@@ -127,6 +128,32 @@ cudaError_t launch_scores(const KernelArgs& a, cudaStream_t stream, int sm_count
 constexpr int kScoreTile = 32;   // keys per tile of the score kernel
 
 #ifdef __CUDACC__
+// One sequence's slice of the scheduler metadata, checked before anything is indexed with it:
+// 0 <= begins[s] <= begins[s + 1] <= the array it indexes, past_len >= 0 and a block table long
+// enough for past_len + new tokens.  A sequence that fails sets PA_DEV_BAD_BEGINS or
+// PA_DEV_BAD_PAST_LEN and is given no work (n = 0): nothing is read or written through its numbers.
+struct SeqView {
+    int t0, n;      // rows of the sequence in query / key / value / output
+    int past;
+    int tb, nb;     // its block table inside block_indices
+};
+__device__ __forceinline__ bool seq_view(const KernelArgs& a, int s, SeqView& v) {
+    const int t0 = a.subsequence_begins[s], t1 = a.subsequence_begins[s + 1];
+    const int tb = a.block_indices_begins[s], te = a.block_indices_begins[s + 1];
+    const int past = a.past_lens[s];
+    v = SeqView{0, 0, 0, 0, 0};
+    if (t0 < 0 || t1 < t0 || t1 > a.num_tokens || tb < 0 || te < tb || te > a.num_block_indices) {
+        atomicOr(a.status, PA_DEV_BAD_BEGINS);
+        return false;
+    }
+    if (past < 0 || (long long)(te - tb) * a.g.bs < (long long)past + (t1 - t0)) {
+        atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
+        return false;
+    }
+    v = SeqView{t0, t1 - t0, past, tb, te - tb};
+    return true;
+}
+
 // Per-sequence offsets into `scores` (prefix sum of past_len + new tokens) and the prefix sum of the
 // score kernel's work (key tiles x row tiles) over the sequences it serves.  Run by one warp of the
 // cache-write launch, because the decode kernel needs the offsets to leave its logits behind.
@@ -139,11 +166,14 @@ __device__ inline void build_score_plan(const KernelArgs& a) {
         long long len = 0;
         int tiles = 0;
         if (s < a.num_sequences) {
-            const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
-            const int past = a.past_lens[s];
-            const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
-            len = (long long)max(past, 0) + max(n, 0);
-            const bool ok = n > 0 && past >= 0 && (long long)nb * a.g.bs >= len;
+            SeqView sv;
+            const bool valid = seq_view(a, s, sv);
+            const int n = sv.n, past = sv.past;
+            // an invalid sequence still takes the slot its raw numbers describe, so that the offsets of the
+            // sequences after it stay where the caller expects them
+            len = valid ? (long long)past + n
+                        : (long long)max(a.past_lens[s], 0) + max(a.subsequence_begins[s + 1] - a.subsequence_begins[s], 0);
+            const bool ok = valid && n > 0;
             // cost of a sequence: key tiles x 16-row tiles of (window row, q head of the group) pairs
             const int W = ok ? min(max(a.score_aggregation_window[s], 0), n) : 0;
             const int G = a.g.Hq / a.g.Hkv;

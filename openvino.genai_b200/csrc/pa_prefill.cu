@@ -27,16 +27,10 @@ __global__ void __launch_bounds__(256) prefill_generic_kernel(KernelArgs a) {
     if (warp >= (long long)a.num_tokens * a.g.Hq) return;
     const int t = (int)(warp / a.g.Hq), hq = (int)(warp % a.g.Hq);
     const int s = find_sequence(a.subsequence_begins, a.num_sequences, t);
-    const int t0 = a.subsequence_begins[s];
-    const int n = a.subsequence_begins[s + 1] - t0;
-    if (n <= 1) return;  // decode rows are handled by the split-K kernel
-    const int past = a.past_lens[s];
-    const int tb = a.block_indices_begins[s];
-    const int nb = a.block_indices_begins[s + 1] - tb;
-    if (past < 0 || (long long)nb * a.g.bs < (long long)past + n) {
-        if (lane == 0) atomicOr(a.status, PA_DEV_BAD_PAST_LEN);
-        return;
-    }
+    SeqView sv;
+    if (!seq_view(a, s, sv)) return;
+    const int t0 = sv.t0, n = sv.n, past = sv.past, tb = sv.tb;
+    if (n <= 1 || t < t0 || t >= t0 + n) return;  // decode rows are handled by the split-K kernel
     const int visible = past + (t - t0) + 1;
     const int hk = hq / (a.g.Hq / a.g.Hkv);
     const float sm_scale = (a.scale != 0.f ? a.scale : rsqrtf((float)D)) * 1.4426950408889634f;

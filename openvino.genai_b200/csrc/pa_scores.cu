@@ -374,19 +374,20 @@ __global__ void __launch_bounds__(kScoreWarps * 32) score_kernel(KernelArgs a) {
 // src/cpp/src/continuous_batching/model_runner.hpp:1536-1537).
 __global__ void __launch_bounds__(256) score_reduce_kernel(KernelArgs a) {
     const int s = blockIdx.y;
-    const int n = a.subsequence_begins[s + 1] - a.subsequence_begins[s];
+    SeqView sv;
+    const bool valid = seq_view(a, s, sv);
     const long long off = a.score_offsets[s], len = a.score_offsets[s + 1] - off;
-    const bool live = a.stile_prefix[s + 1] > a.stile_prefix[s];
-    const int past = a.past_lens[s];
-    const int nb = a.block_indices_begins[s + 1] - a.block_indices_begins[s];
-    const bool from_decode = a.score_raw != nullptr && n == 1 && past >= 0 && (long long)nb * a.g.bs >= len &&
-                             a.score_aggregation_window[s] > 0;
+    // a sequence whose slot does not fit into `scores` gets zeros where the slot is in range (the kernels
+    // that would have produced its numbers skipped it and raised PA_DEV_BAD_BEGINS)
+    const bool fits = off + len <= a.scores_len;
+    const bool live = fits && a.stile_prefix[s + 1] > a.stile_prefix[s];
+    const bool from_decode = a.score_raw != nullptr && valid && fits && sv.n == 1 && a.score_aggregation_window[s] > 0;
     if (from_decode) {
         // probabilities from the decode kernel's scaled logits (base 2) and the row's log-sum-exp, added
         // over the q heads in head order
         const int G = a.g.Hq / a.g.Hkv, gtiles = (G + 15) / 16, HK = a.g.Hkv * gtiles;
         const int SL = a.rows_per_tile <= 8 ? 8 : 16;
-        const float* lse = a.lse + (long long)a.subsequence_begins[s] * a.g.Hq;
+        const float* lse = a.lse + (long long)sv.t0 * a.g.Hq;
         constexpr float kLog2e = 1.4426950408889634f;
         for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (long long)gridDim.x * blockDim.x) {
             if (off + i >= a.scores_len) break;

@@ -12,10 +12,10 @@
 //      pop_heap / push_heap on the few hundred that really enter, while the producers filter the
 //      next chunk.  Softmax, min-p, top-p and the draw then run over <= K elements in one thread,
 //      in the reference's order of operations;
-//   4. multinomial rows over the full vocabulary: max, exp and sums are block reductions
-//      (deterministic, but not the reference's index-order float accumulation), top-p uses a
-//      three-level radix descent over the order-preserving bit pattern of the logits.
-// HBM-bound: the row is read once (plus an L2-resident second pass for the radix descent).
+//   4. multinomial rows over the full vocabulary get their penalties here and are finished by
+//      sampler_exact_kernel (sampler_exact.cu), which reproduces the reference's index-order and
+//      sorted-order float sums exactly.
+// HBM-bound: the row is read once.
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
@@ -333,15 +333,7 @@ __device__ __forceinline__ void for_row(const float* row, long long V, int tid, 
 
 struct Shared {
     Cand heap[kMaxTopK];
-    union {
-        Cand cand[2][kChunk];          // top-k path: survivors of two filter rounds
-        struct {                       // full-vocabulary path: radix histograms
-            unsigned long long hist_mass[2048];
-            unsigned int hist_piece[3][2048];      // the same masses while they are being added, in pieces
-            unsigned long long first_mass[2048];   // first level of the top-p descent, kept for the draw
-            int bin_first[1024];                   // lowest index of every bin of the draw's last level
-        };
-    };
+    Cand cand[2][kChunk];          // survivors of two filter rounds
     int cand_count[2];
     float tau;                 // producers' copy of the heap minimum (may lag, never leads)
     int warp_off[kWarps];
@@ -350,11 +342,6 @@ struct Shared {
     int red_i[kWarps];
     unsigned long long red_u[kWarps];
     ArgMax red_a[kWarps];
-    int sel_bin;
-    unsigned long long sel_mass_above;
-    unsigned int sel_cnt_above;
-    float out_p;
-    long long out_idx;
 };
 
 // ---- phase 1: penalties ---------------------------------------------------------------------------------
@@ -700,384 +687,15 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     }
 
     // ---- 4. full vocabulary ---------------------------------------------------------------------------
-    const float T = p.temperature;
-    const float f = 1.0f / T;
-    const bool top_p_on = p.top_p != 1.0f;
-    float mx = -CUDART_INF_F;
-    double dsum = 0.0;
-    // single-precision expf here: this path does not reproduce the reference's order of summation
-    // anyway, and the double-precision form costs an order of magnitude more over a whole vocabulary
-    auto wexp = [&](float d) { return T == 1.0f ? expf(d) : expf(d * f); };
-    if (top_p_on) {
-        // maximum and sum in one pass over the row (the passes are bound by DRAM: a batch of rows does not
-        // fit in L2): every thread sums against its own running maximum and rescales when that rises
-        float m = -CUDART_INF_F;
-        double sacc = 0.0;
-        for_row(row, V, tid, [&](float x, long long) {
-            if (x > m) {
-                sacc = sacc * (double)wexp(m - x) + 1.0;
-                m = x;
-            } else if (m > -CUDART_INF_F) {
-                sacc += (double)wexp(x - m);
-            }
-        });
-        mx = block_reduce(m, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
-        dsum = sacc != 0.0 ? sacc * (double)wexp(m - mx) : 0.0;
-    } else {
-        for_row(row, V, tid, [&](float x, long long) { mx = fmaxf(mx, x); });
-        mx = block_reduce(mx, -CUDART_INF_F, [](float x, float y) { return fmaxf(x, y); }, sh.red_f);
-    }
-    auto weight = [&](float x) { return wexp(x - mx); };
-    if (!top_p_on) for_row(row, V, tid, [&](float x, long long) { dsum += (double)weight(x); });
-    dsum = block_reduce(dsum, 0.0, [](double x, double y) { return x + y; }, sh.red_d);
-    const float norm = (float)dsum;
-    auto prob = [&](float x) { return __fdiv_rn(weight(x), norm); };
-
-    const bool min_p_active = p.min_p > 0.0f;
-    const bool top_p_active = p.top_p != 1.0f;
-    // probabilities as 2^-40 fixed point so that sums do not depend on the order of addition
-    // (the product with 2^40 is exact in single precision, so this equals the double-precision form)
-    auto fixed = [](float pr) { return __float2ull_rz(pr * 1099511627776.0f); };
-    const float pmax = prob(mx);
-    const float min_thr = min_p_active ? (float)(double)p.min_p * pmax : -1.0f;
-
-    // One histogram level over the elements whose key matches `prefix` above `shift + bits`.
-    // Most of a row falls into a handful of first-level bins, so lanes of a warp collide all the time:
-    // the masses are therefore added as three pieces (14 + 14 + 13 bits) with native 32-bit shared
-    // atomics, which resolve collisions in hardware, instead of 64-bit ones (a compare-and-swap loop).
-    // A piece's sum stays below 2^32 for rows of fewer than 2^18 elements; longer rows add 64-bit.
-    const bool pieces = V < (1ll << 18);
-    auto build_level = [&](uint32_t prefix, int shift, int bits, bool first, uint32_t lo_key, bool want_index) {
-        const int nb = 1 << bits;
-        for (int i = tid; i < nb; i += kThreads) {
-            sh.hist_mass[i] = 0;
-            if (want_index && i < 1024) sh.bin_first[i] = 0x7fffffff;
-            sh.hist_piece[0][i] = 0; sh.hist_piece[1][i] = 0; sh.hist_piece[2][i] = 0;
-        }
-        __syncthreads();
-        const uint32_t hi_mask = first ? 0u : (0xffffffffu << (shift + bits));
-        for_row(row, V, tid, [&](float x, long long idx) {
-            const uint32_t k = float_key(x);
-            if (k < lo_key || (k & hi_mask) != prefix) return;
-            const float pr = prob(x);
-            if (pr < min_thr) return;
-            const int bin = (k >> shift) & (nb - 1);
-            const unsigned long long m = fixed(pr);
-            if (want_index) atomicMin(&sh.bin_first[bin], (int)idx);   // last level: a bin is one key, its lowest index is the pick
-            if (pieces) {
-                atomicAdd(&sh.hist_piece[0][bin], (unsigned int)(m & 0x3fffu));
-                atomicAdd(&sh.hist_piece[1][bin], (unsigned int)((m >> 14) & 0x3fffu));
-                atomicAdd(&sh.hist_piece[2][bin], (unsigned int)(m >> 28));
-            } else {
-                atomicAdd(&sh.hist_mass[bin], m);
-            }
-        });
-        __syncthreads();
-        if (pieces) {
-            for (int i = tid; i < nb; i += kThreads)
-                sh.hist_mass[i] = (unsigned long long)sh.hist_piece[0][i] + ((unsigned long long)sh.hist_piece[1][i] << 14) +
-                                  ((unsigned long long)sh.hist_piece[2][i] << 28);
-            __syncthreads();
-        }
-    };
-    // Walk the bins from the highest down, starting at mass `start`: sel_bin = the first bin at which the
-    // running mass exceeds `thr`, sel_mass_above = the mass before it. When no bin does, sel_bin = -1
-    // and sel_mass_above = the whole mass.
-    auto select_bin = [&](int nb, unsigned long long start, unsigned long long thr) {
-        if (warp == 0) {
-            const int per = nb >> 5;
-            const int top = nb - 1 - lane * per;    // lane 0 owns the highest bins
-            unsigned long long mine = 0;
-            for (int j = 0; j < per; ++j) mine += sh.hist_mass[top - j];
-            unsigned long long incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += u;
-            }
-            const unsigned long long before = start + incl - mine;
-            const uint32_t hit = __ballot_sync(0xffffffffu, before + mine > thr);
-            if (hit) {
-                if (lane == __ffs(hit) - 1) {
-                    unsigned long long acc = before;
-                    int sel = top - per + 1;
-                    for (int j = 0; j < per; ++j) {
-                        const unsigned long long mj = sh.hist_mass[top - j];
-                        if (acc + mj > thr) { sel = top - j; break; }
-                        acc += mj;
-                    }
-                    sh.sel_bin = sel;
-                    sh.sel_mass_above = acc;
-                }
-            } else {
-                const unsigned long long total_mass = __shfl_sync(0xffffffffu, start + incl, 31);
-                if (lane == 0) { sh.sel_bin = -1; sh.sel_mass_above = total_mass; }
-            }
-        }
-        __syncthreads();
-    };
-
-    uint32_t key_lo = 0;  // candidates are the elements with key >= key_lo that pass min-p
-    unsigned long long kept = 0;
-    // without top-p: rows that can be read in 16-byte pieces and have at most 2048 groups of 128 elements
-    const int groups = (int)((V + 127) >> 7);
-    const bool grouped = !top_p_active && (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0 && groups <= 2048;
-    int first_bin = -1;                      // bin of key_lo in the first-level histogram (-1: whole row kept)
-    unsigned long long first_above = 0;      // mass of the first-level bins above it
-    if (top_p_active) {
-        // radix descent (11 + 11 + 10 bits) for the smallest key whose descending cumulative mass
-        // first exceeds top_p: elements above it are in the nucleus, the boundary key itself too.
-        const unsigned long long target = fixed(p.top_p);
-        unsigned long long mass_above = 0;   // mass of keys strictly above the current prefix range
-        uint32_t prefix = 0;
-        int shift = 32;
-        bool found_all = false;
-        for (int level = 0; level < 3; ++level) {
-            const int bits = level == 2 ? 10 : 11;
-            shift -= bits;
-            build_level(prefix, shift, bits, level == 0, 0u, false);
-            if (level == 0)   // the second descent starts from this histogram
-                for (int i = tid; i < 2048; i += kThreads) sh.first_mass[i] = sh.hist_mass[i];
-            select_bin(1 << bits, mass_above, target);
-            mass_above = sh.sel_mass_above;
-            // no bin reaches top_p (only possible on the first level, where the bins hold the whole row)
-            if (sh.sel_bin < 0) { found_all = true; break; }
-            if (level == 0) { first_bin = sh.sel_bin; first_above = mass_above; }
-            prefix |= (uint32_t)sh.sel_bin << shift;
-        }
-        key_lo = found_all ? 0u : prefix;
-        // kept mass = everything above the boundary key plus the boundary key's own bin of the last level
-        kept = found_all ? mass_above : mass_above + sh.hist_mass[sh.sel_bin];
-        if (found_all) first_bin = -1;
-        __syncthreads();
-    } else if (grouped) {
-        // index-order draw, one pass: the mass of every group of 128 consecutive elements (one 16-byte
-        // load per lane, summed over the warp as three 14-bit pieces); the running sums over the groups
-        // then give both the kept mass and, below, the group in which the draw falls
-        const float4* r4 = reinterpret_cast<const float4*>(row);
-        const long long n4 = V >> 2;
-        auto lane_mass = [&](long long i4) {
-            unsigned long long m = 0;
-            if (i4 < n4) {
-                const float4 q = r4[i4];
-                const float pr0 = prob(q.x), pr1 = prob(q.y), pr2 = prob(q.z), pr3 = prob(q.w);
-                if (!(pr0 < min_thr)) m += fixed(pr0);
-                if (!(pr1 < min_thr)) m += fixed(pr1);
-                if (!(pr2 < min_thr)) m += fixed(pr2);
-                if (!(pr3 < min_thr)) m += fixed(pr3);
-            }
-            return m;
-        };
-        for (int g0 = warp; g0 < groups; g0 += 4 * kWarps) {
-            float4 q[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const long long i4 = (long long)(g0 + u * kWarps) * 32 + lane;
-                q[u] = i4 < n4 ? r4[i4] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int g = g0 + u * kWarps;
-                if (g >= groups) break;
-                const long long i4 = (long long)g * 32 + lane;
-                unsigned long long m = 0;
-                if (i4 < n4) {
-                    const float pr0 = prob(q[u].x), pr1 = prob(q[u].y), pr2 = prob(q[u].z), pr3 = prob(q[u].w);
-                    if (!(pr0 < min_thr)) m += fixed(pr0);
-                    if (!(pr1 < min_thr)) m += fixed(pr1);
-                    if (!(pr2 < min_thr)) m += fixed(pr2);
-                    if (!(pr3 < min_thr)) m += fixed(pr3);
-                }
-                const uint32_t lo = __reduce_add_sync(0xffffffffu, (uint32_t)(m & 0x3fffu));
-                const uint32_t mid = __reduce_add_sync(0xffffffffu, (uint32_t)((m >> 14) & 0x3fffu));
-                const uint32_t hi = __reduce_add_sync(0xffffffffu, (uint32_t)(m >> 28));
-                if (lane == 0) sh.hist_mass[g] = (unsigned long long)lo + ((unsigned long long)mid << 14) + ((unsigned long long)hi << 28);
-            }
-        }
-        __syncthreads();
-        // warp 0: lane l owns `per` consecutive groups; kept mass, r, the group where the running sum
-        // first exceeds r, then the lane and the element inside that group
-        if (warp == 0) {
-            const int per = (groups + 31) >> 5;
-            const int g_lo = lane * per, g_hi = min(groups, g_lo + per);
-            unsigned long long mine = 0;
-            for (int g = g_lo; g < g_hi; ++g) mine += sh.hist_mass[g];
-            unsigned long long incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += u;
-            }
-            const unsigned long long kept_all = __shfl_sync(0xffffffffu, incl, 31);
-            const float total_f = (float)((double)kept_all / 1099511627776.0);
-            const unsigned long long rf = fixed(total_f * p.rand_u);
-            const uint32_t hit = __ballot_sync(0xffffffffu, incl > rf);
-            int sel_g = -1;
-            unsigned long long sel_before = 0;
-            if (hit) {
-                const int src = __ffs(hit) - 1;
-                if (lane == src) {
-                    unsigned long long acc = incl - mine;
-                    sel_g = g_lo;
-                    for (int g = g_lo; g < g_hi; ++g) {
-                        const unsigned long long mg = sh.hist_mass[g];
-                        if (acc + mg > rf) { sel_g = g; break; }
-                        acc += mg;
-                    }
-                    sel_before = acc;
-                }
-                sel_g = __shfl_sync(0xffffffffu, sel_g, src);
-                sel_before = __shfl_sync(0xffffffffu, sel_before, src);
-            }
-            int chosen = -1;
-            if (sel_g >= 0) {
-                const long long i4 = (long long)sel_g * 32 + lane;
-                const unsigned long long m = lane_mass(i4);
-                unsigned long long inc2 = m;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const unsigned long long u = __shfl_up_sync(0xffffffffu, inc2, o);
-                    if (lane >= o) inc2 += u;
-                }
-                const uint32_t hit2 = __ballot_sync(0xffffffffu, sel_before + inc2 > rf);
-                if (hit2 && lane == __ffs(hit2) - 1) {
-                    unsigned long long run = sel_before + inc2 - m;
-                    const float4 q = r4[i4];
-                    const float xs[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float pr = prob(xs[e]);
-                        if (pr < min_thr) continue;
-                        run += fixed(pr);
-                        if (run > rf && chosen < 0) chosen = (int)(4 * i4 + e);
-                    }
-                }
-                chosen = __reduce_max_sync(0xffffffffu, chosen);
-            }
-            if (lane == 0) {
-                // rounding left r at or beyond the total: the reference falls back to the last element
-                if (chosen < 0) chosen = (int)V - 1;
-                const float pr = prob(row[chosen]);
-                a.out_token[r] = chosen;
-                a.out_log_prob[r] = raw_lp ? raw_log_prob(chosen) : logf(pr) - logf(total_f);
-            }
-        }
-        return;
-    } else {
-        for_row(row, V, tid, [&](float x, long long) {
-            const float pr = prob(x);
-            if (!(pr < min_thr)) kept += fixed(pr);
-        });
-        kept = block_reduce(kept, 0ull, [](unsigned long long x, unsigned long long y) { return x + y; }, sh.red_u);
-    }
-
-    // the draw: r = total * u, first element (descending by key when top-p sorted the candidates,
-    // ascending by index otherwise) whose running sum exceeds r.
-    const float total = (float)((double)kept / 1099511627776.0);
-    const unsigned long long rfix = fixed(total * p.rand_u);
-
-    if (top_p_active) {
-        // second radix descent, over the kept elements, for the key where the descending
-        // cumulative mass first exceeds r
-        unsigned long long mass_above = 0;
-        uint32_t prefix = 0;
-        int shift = 32;
-        int pick = 0x7fffffff;
-        for (int level = 0; level < 3; ++level) {
-            const int bits = level == 2 ? 10 : 11;
-            shift -= bits;
-            const int nb = 1 << bits;
-            if (level == 0) {
-                // the kept elements' first level: the saved bins above the boundary key's bin, and of
-                // that bin the part at or above the boundary key
-                for (int i = tid; i < nb; i += kThreads)
-                    sh.hist_mass[i] = i > first_bin ? sh.first_mass[i] : (i == first_bin ? kept - first_above : 0ull);
-                __syncthreads();
-            } else {
-                build_level(prefix, shift, bits, false, key_lo, level == 2);
-            }
-            select_bin(nb, mass_above, rfix);
-            const int sel = sh.sel_bin;
-            mass_above = sh.sel_mass_above;
-            __syncthreads();
-            if (sel < 0) {
-                // rounding left r at or beyond the kept mass (only seen on the first level, whose bins
-                // hold all of it): the last element in descending order, the smallest kept key
-                unsigned long long lowest = ~0ull;
-                for_row(row, V, tid, [&](float x, long long) {
-                    const uint32_t k = float_key(x);
-                    if (k >= key_lo && !(prob(x) < min_thr)) lowest = min(lowest, (unsigned long long)k);
-                });
-                lowest = block_reduce(lowest, ~0ull, [](unsigned long long x, unsigned long long y) { return min(x, y); }, sh.red_u);
-                prefix = (uint32_t)lowest;
-                break;
-            }
-            prefix |= (uint32_t)sel << shift;
-            if (level == 2) pick = sh.bin_first[sel];   // recorded while the last level was built
-        }
-        // all elements with this exact key have the same probability: the lowest index is taken
-        if (pick == 0x7fffffff) {   // only after the fallback above
-            for_row(row, V, tid, [&](float x, long long i) {
-                if (float_key(x) == prefix) pick = min(pick, (int)i);
-            });
-            pick = block_reduce(pick, 0x7fffffff, [](int x, int y) { return min(x, y); }, sh.red_i);
-        }
-        if (tid == 0) {
-            const float pr = prob(row[pick]);
-            a.out_token[r] = pick;
-            a.out_log_prob[r] = raw_lp ? raw_log_prob(pick) : logf(pr) - logf(total);
-        }
+    if (top_k_active && p.top_k < V) {
+        // a heap larger than the shared-memory capacity: not supported, and said so (status bit 3, token -1)
+        if (tid == 0) { atomicOr(a.status, 8u); a.out_token[r] = -1; a.out_log_prob[r] = 0.f; }
         return;
     }
-
-    // index-order draw (no top-p) for rows the grouped form above does not take: running sums over
-    // one contiguous chunk of the row per thread
-    {
-        unsigned long long before = 0;
-        int pick = -1;
-        const long long per = (V + kThreads - 1) / kThreads;
-        const long long lo = (long long)tid * per, hi = min(V, lo + per);
-        unsigned long long mine = 0;
-        for (long long i = lo; i < hi; ++i) {
-            const float pr = prob(row[i]);
-            if (pr >= min_thr) mine += fixed(pr);
-        }
-        // exclusive prefix of `mine` over threads
-        unsigned long long incl = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned long long u = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += u;
-        }
-        __syncthreads();
-        if (lane == 31) sh.red_u[warp] = incl;
-        __syncthreads();
-        for (int w = 0; w < warp; ++w) before += sh.red_u[w];
-        before += incl - mine;
-        if (before <= rfix && rfix < before + mine) {
-            unsigned long long run = before;
-            for (long long i = lo; i < hi; ++i) {
-                const float pr = prob(row[i]);
-                if (pr < min_thr) continue;
-                run += fixed(pr);
-                if (run > rfix) { pick = (int)i; break; }
-            }
-        }
-        __syncthreads();
-        if (tid == 0) sh.sel_bin = -1;
-        __syncthreads();
-        if (pick >= 0) atomicMax(&sh.sel_bin, pick);
-        __syncthreads();
-        if (tid == 0) {
-            int chosen = sh.sel_bin;
-            if (chosen < 0) {  // rounding left r at or beyond the total: the reference falls back to the last element
-                chosen = (int)V - 1;
-            }
-            const float pr = prob(row[chosen]);
-            a.out_token[r] = chosen;
-            a.out_log_prob[r] = raw_lp ? raw_log_prob(chosen) : logf(pr) - logf(total);
-        }
-    }
+    // The row is finished by sampler_exact_kernel (sampler_exact.cu), launched right after this one: it
+    // needs the penalised row, which is in place now, and for raw log-probabilities the log-partition
+    // of the raw row, parked in the row's output slot (NaN: no scratch for the raw logits).
+    if (tid == 0) a.out_log_prob[r] = raw_lp ? (raw_ok ? raw_lse : CUDART_NAN_F) : 0.f;
 }
 
 }  // namespace

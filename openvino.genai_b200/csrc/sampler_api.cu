@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdint>
 #include <cstring>
 #include <string>
 
@@ -35,6 +36,9 @@ struct sampler_handle {
     uint8_t* stage_dev = nullptr;
     uint8_t* stage_host = nullptr;  // pinned
     size_t stage_bytes = 0;
+    float* exact_scratch = nullptr;   // one row of probabilities per CTA of the full-vocabulary kernel
+    size_t exact_bytes = 0;
+    int exact_ctas = 0;               // persistent grid of that kernel: two CTAs per SM
     int64_t launches = 0;
 };
 
@@ -51,6 +55,39 @@ int ensure_stage(sampler_handle* h, size_t bytes) {
     S_CUDA(cudaMallocHost((void**)&h->stage_host, want));
     h->stage_bytes = want;
     return SAMPLER_OK;
+}
+
+// Scratch of the full-vocabulary kernel: grows (with a stream synchronisation) when a step has a larger vocabulary.
+int ensure_exact_scratch(sampler_handle* h, int32_t rows, int64_t vocab) {
+    const int ctas = std::min<int64_t>(rows, h->exact_ctas);
+    const size_t need = sampler::sampler_exact_scratch_bytes(ctas, vocab);
+    if (need <= h->exact_bytes) return SAMPLER_OK;
+    S_CUDA(cudaStreamSynchronize(h->stream));
+    S_CUDA(cudaDeviceSynchronize());
+    if (h->exact_scratch) S_CUDA(cudaFree(h->exact_scratch));
+    h->exact_scratch = nullptr; h->exact_bytes = 0;
+    S_CUDA(cudaMalloc((void**)&h->exact_scratch, need));
+    h->exact_bytes = need;
+    return SAMPLER_OK;
+}
+
+// Both launches of a step: penalties / greedy / top-k rows, then the full-vocabulary multinomial rows.
+int launch_step(sampler_handle* h, const sampler::StepArgs& k, cudaStream_t stream, bool any_full_vocab) {
+    S_CUDA(sampler::launch_sampler(k, stream));
+    h->launches += 1;
+    if (any_full_vocab) {
+        int rc = ensure_exact_scratch(h, k.num_rows, k.vocab);
+        if (rc != SAMPLER_OK) return rc;
+        S_CUDA(sampler::launch_sampler_exact(k, h->exact_scratch, h->exact_ctas, stream));
+        h->launches += 1;
+    }
+    return SAMPLER_OK;
+}
+
+bool row_is_full_vocab(const sampler_row_params& p, int64_t vocab) {
+    if (!(p.do_sample & SAMPLER_ROW_MULTINOMIAL)) return false;
+    const bool top_k_active = p.top_k > 0 && p.top_k < INT64_MAX;
+    return !(top_k_active && p.top_k < vocab);
 }
 
 int validate(const sampler_handle* h, const sampler_step_args* a) {
@@ -77,6 +114,7 @@ extern "C" {
 
 const char* sampler_b200_last_error(void) { return g_sampler_error.c_str(); }
 
+int sampler_b200_destroy(sampler_handle* h);
 int sampler_b200_create(int device, int32_t max_rows, int64_t max_vocab, sampler_handle** out) {
     if (!out) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL out pointer");
     int count = 0;
@@ -94,7 +132,11 @@ int sampler_b200_create(int device, int32_t max_rows, int64_t max_vocab, sampler
         delete h;
         return sfail(SAMPLER_ERR_CUDA, std::string("sampler_b200_create: ") + cudaGetErrorString(e));
     }
-    (void)max_rows; (void)max_vocab;  // scratch is sized on first use of the host entry point
+    h->exact_ctas = 2 * prop.multiProcessorCount;
+    if (max_rows > 0 && max_vocab > 0) {   // otherwise sized on first use
+        const int rc = ensure_exact_scratch(h, max_rows, max_vocab);
+        if (rc != SAMPLER_OK) { sampler_b200_destroy(h); return rc; }
+    }
     *out = h;
     return SAMPLER_OK;
 }
@@ -106,6 +148,7 @@ int sampler_b200_destroy(sampler_handle* h) {
     if (h->status) cudaFree(h->status);
     if (h->stage_dev) cudaFree(h->stage_dev);
     if (h->stage_host) cudaFreeHost(h->stage_host);
+    if (h->exact_scratch) cudaFree(h->exact_scratch);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
     return SAMPLER_OK;
@@ -117,9 +160,8 @@ int sampler_b200_step(sampler_handle* h, const sampler_step_args* a) {
     if (a->num_rows == 0) return SAMPLER_OK;
     S_CUDA(cudaSetDevice(h->device));
     cudaStream_t stream = a->stream ? (cudaStream_t)a->stream : h->stream;
-    S_CUDA(sampler::launch_sampler(kernel_args(h, a), stream));
-    h->launches += 1;
-    return SAMPLER_OK;
+    // the row parameters live on the device: the second launch is always made and leaves at once when no row needs it
+    return launch_step(h, kernel_args(h, a), stream, true);
 }
 
 int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int copy_logits_back) {
@@ -160,8 +202,10 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
     d.out_token = (int64_t*)(h->stage_dev + o_tok);
     d.out_log_prob = (float*)(h->stage_dev + o_lp);
     d.hist_raw = (float*)(h->stage_dev + o_hraw);
-    S_CUDA(sampler::launch_sampler(kernel_args(h, &d), stream));
-    h->launches += 1;
+    bool any_full_vocab = false;
+    for (size_t i = 0; i < n && !any_full_vocab; ++i) any_full_vocab = row_is_full_vocab(a->rows[i], a->vocab);
+    rc = launch_step(h, kernel_args(h, &d), stream, any_full_vocab);
+    if (rc != SAMPLER_OK) return rc;
     S_CUDA(cudaMemcpyAsync(a->out_token, d.out_token, n * sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
     S_CUDA(cudaMemcpyAsync(a->out_log_prob, d.out_log_prob, n * sizeof(float), cudaMemcpyDeviceToHost, stream));
     if (copy_logits_back) S_CUDA(cudaMemcpyAsync(a->logits, d.logits, logits_bytes, cudaMemcpyDeviceToHost, stream));
@@ -170,7 +214,8 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
     S_CUDA(cudaStreamSynchronize(stream));
     if (bits) {
         S_CUDA(cudaMemsetAsync(h->status, 0, 4, stream));
-        return sfail((bits & 1u) ? SAMPLER_ERR_BAD_TOKEN_ID : SAMPLER_ERR_INVALID_ARG, "device status word " + std::to_string(bits));
+        const int code = (bits & 1u) ? SAMPLER_ERR_BAD_TOKEN_ID : (bits & 8u) ? SAMPLER_ERR_UNSUPPORTED : (bits & 16u) ? SAMPLER_ERR_CUDA : SAMPLER_ERR_INVALID_ARG;
+        return sfail(code, "device status word " + std::to_string(bits));
     }
     return SAMPLER_OK;
 }
@@ -185,5 +230,20 @@ int sampler_b200_last_device_status(sampler_handle* h, uint32_t* status_bits) {
 }
 
 int64_t sampler_b200_launch_count(const sampler_handle* h) { return h ? h->launches : -1; }
+
+int sampler_b200_selftest_expf(sampler_handle* h, const float* in, float* out, int64_t n) {
+    if (!h || !in || !out || n < 0) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL argument");
+    if (n == 0) return SAMPLER_OK;
+    S_CUDA(cudaSetDevice(h->device));
+    float* d = nullptr;
+    S_CUDA(cudaMalloc((void**)&d, 2 * (size_t)n * sizeof(float)));
+    cudaError_t e = cudaMemcpyAsync(d, in, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess) e = sampler::launch_expf_selftest(d, d + n, n, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, d + n, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    cudaFree(d);
+    if (e != cudaSuccess) return sfail(SAMPLER_ERR_CUDA, std::string("selftest: ") + cudaGetErrorString(e));
+    return SAMPLER_OK;
+}
 
 }  // extern "C"

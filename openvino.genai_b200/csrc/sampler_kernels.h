@@ -20,11 +20,20 @@ struct StepArgs {
     const uint32_t* hist_meta;
     int64_t* out_token;
     float* out_log_prob;
-    uint32_t* status;  // bit 0: history id out of range, bit 1: logits_row out of range, bit 2: raw log-prob without scratch
+    uint32_t* status;  // bit 0: history id out of range, bit 1: logits_row out of range, bit 2: raw log-prob without scratch,
+                       // bit 3: top_k above the heap capacity (and below the vocabulary), bit 4: the sorted walk did not end
     float* hist_raw;   // raw logits of the history entries (rows that report raw log-probabilities), may be null
 };
 
 cudaError_t launch_sampler(const StepArgs& a, cudaStream_t stream);
 size_t sampler_smem_bytes();
+
+// Full-vocabulary multinomial rows (sampler_exact.cu).  `scratch` holds one row of probabilities per
+// CTA of the persistent grid: sampler_exact_scratch_bytes(ctas, vocab) bytes.
+cudaError_t launch_sampler_exact(const StepArgs& a, float* scratch, int ctas, cudaStream_t stream);
+size_t sampler_exact_scratch_bytes(int ctas, long long vocab);
+size_t sampler_exact_smem_bytes();
+cudaError_t launch_expf_selftest(const float* in, float* out, long long n, cudaStream_t stream);
+constexpr int kSamplerMaxTopK = 1024;   // heap capacity of the top-k path
 
 }  // namespace sampler
