@@ -40,6 +40,8 @@ def load_library(build_if_missing: bool = False) -> ctypes.CDLL:
     _abi.bind(lib, _abi.PA_SYMBOLS)
     from . import _sampler_abi
     _abi.bind(lib, _sampler_abi.SAMPLER_SYMBOLS)
+    from . import _exchange_abi
+    _abi.bind(lib, _exchange_abi.EXCHANGE_SYMBOLS)
     _lib = lib
     return lib
 

@@ -43,7 +43,8 @@ def _newest_header_mtime() -> float:
 
 
 def _compile_one(src: Path, obj: Path, log: Path) -> None:
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(REPO_ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    extra = os.environ.get("GENAI_B200_NVCC_EXTRA", "").split()   # e.g. -DSAMPLER_EXACT_PROF for the kernels' own timers
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(REPO_ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     log.write_text(" ".join(cmd) + "\n" + res.stdout + res.stderr)
     if res.returncode != 0:
@@ -73,7 +74,7 @@ def build_all(force: bool = False, verbose: bool = False) -> Path:
             for _, _, log in jobs:
                 sys.stderr.write(log.read_text())
     if jobs or not LIB_PATH.exists():
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart"]
+        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart", "-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

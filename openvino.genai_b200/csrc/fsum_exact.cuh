@@ -47,7 +47,9 @@ namespace fsx {
     0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
 static const uint64_t kExp2TabHost[32] = {FSX_EXP2_TABLE};
 #if defined(__CUDACC__)
-static __device__ __constant__ uint64_t kExp2TabDev[32] = {FSX_EXP2_TABLE};
+// Device copy.  Lanes of a warp index it with different values: kernels copy it to shared memory first
+// (a constant-bank read with divergent addresses is replayed once per address).
+static __device__ const uint64_t kExp2TabDev[32] = {FSX_EXP2_TABLE};
 #endif
 
 FSX_HD double u64_as_double(uint64_t u) {
@@ -109,7 +111,7 @@ FSX_HD float fadd_rn(float a, float b) {
 
 // expf(x) with the host libm's bits.  Inputs at or below -103.972 give 0, -inf gives 0, NaN stays NaN;
 // arguments above 88.7 do not occur here (the callers pass x - max <= 0) and saturate to +inf.
-FSX_HD float expf_libm(float x) {
+FSX_HD float expf_libm(float x, const uint64_t* tab) {
     if (!(x >= -103.972076f)) return x != x ? x : 0.0f;       // underflow to zero (and NaN passthrough)
     if (x > 88.72283f) return bits_float(0x7f800000u);
     const double kInvLn2N = 0x1.71547652b82fep+0 * 32.0;
@@ -120,12 +122,7 @@ FSX_HD float expf_libm(float x) {
     const uint64_t ki = double_as_u64(kd);
     kd = add_rn(kd, -kShift);
     const double r = fma_rn(kInvLn2N, xd, -kd);
-#if defined(__CUDA_ARCH__)
-    const uint64_t t = kExp2TabDev[ki & 31];
-#else
-    const uint64_t t = kExp2TabHost[ki & 31];
-#endif
-    const double s = u64_as_double(t + (ki << 47));
+    const double s = u64_as_double(tab[ki & 31] + (ki << 47));
     const double z = fma_rn(kC0, r, kC1);
     const double r2 = mul_rn(r, r);
     double y = fma_rn(kC2, r, 1.0);
@@ -133,6 +130,10 @@ FSX_HD float expf_libm(float x) {
     y = mul_rn(y, s);
     return (float)y;
 }
+
+#if !defined(__CUDA_ARCH__)
+inline float expf_libm(float x) { return expf_libm(x, kExp2TabHost); }
+#endif
 
 // ---- running float sums -------------------------------------------------------------------------
 constexpr uint32_t kOne24 = 1u << 24;

@@ -124,6 +124,7 @@ extern "C" int pa_b200_decode_step_static(const pa_model_desc* desc, const pa_fo
     k.key_cache = a->key_cache; k.value_cache = a->value_cache; k.num_blocks = a->num_blocks;
     k.past_lens = a->past_lens; k.subsequence_begins = a->subsequence_begins;
     k.block_indices = a->block_indices; k.block_indices_begins = a->block_indices_begins;
+    k.num_block_indices = a->num_block_indices;
     k.num_sequences = a->num_sequences; k.max_context_len = a->max_context_len;
     k.scale = a->scale;
     unsigned char* base = st.scratch;  // device address from cudaGetSymbolAddress, never the symbol's name

@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include "../../include/sampler_b200.h"
 #include "fsum_exact.cuh"
@@ -31,7 +32,6 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kTile = kThreads * 4;
 constexpr int kListCap = 4096;
 constexpr uint32_t kTopCount = 96;
 constexpr double kMargin = 1.0 / 4096;
@@ -58,6 +58,8 @@ struct ExactShared {
     int list_n;
     // block scan / reduce scratch
     fsx::Step scan_step[kWarps];
+    unsigned long long tile_sum[2][kWarps];
+    unsigned long long exp_tab[32];
     RunSum scan_run[kWarps];
     double scan_d[kWarps];
     unsigned long long scan_u[kWarps];
@@ -72,6 +74,7 @@ struct ExactShared {
     uint32_t rest_cnt;
     int ctl;
     int cleared;
+    int prof_passes;
 };
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -156,25 +159,66 @@ struct StepOp {
 };
 
 // ---- index-order sums ---------------------------------------------------------------------------------
-// Adds the values value(i), i = 0 .. V - 1 in index order to the float sum s, exactly as the host
-// loop `s += v[i]` does.  value(i, &keep) may drop an element (keep = false).  With `thr` finite the
-// walk stops at the first element whose running sum exceeds it and returns its index (else -1).
+// Adds the kept values of a row in index order to the float sum s, exactly as the host loop
+// `s += v[i]` does.  A tile is kTile consecutive elements, kPer per thread.  While the sum stays in
+// its binade and no element of the tile is a tie, the tile's amounts are plain integers whose order
+// does not matter: one block reduction per tile.  A tile with a tie, a change of binade or (with
+// `use_thr`) the first running sum above `thr` is redone as a block scan of two-state steps.
+//   load(i, raw, keep)   fetches elements i .. i + kPer - 1 (keep = false beyond the row)
+//   xform(i, raw, keep)  turns them into the values to add (and may drop elements or park results)
+// Returns the index of the first element whose running sum exceeds thr (-1: none, or !use_thr).
 // All threads call this with the same arguments; s is returned to all.
-template <class ValueFn>
-__device__ long long chain_sum(float& s, long long V, ValueFn&& value, float thr, bool use_thr, ExactShared& sh) {
-    const int tid = threadIdx.x;
+constexpr int kPer = 8;
+constexpr int kTile = kThreads * kPer;
+
+template <class LoadFn, class XformFn>
+__device__ long long chain_sum(float& s, long long V, LoadFn&& load, XformFn&& xform, float thr, bool use_thr, ExactShared& sh) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint32_t E = fsx::state_exp(s), S = fsx::state_sig(s);
-    for (long long base = 0; base < V; base += kTile) {
-        float x[4];
-        bool keep[4];
-        value(base + 4 * tid, x, keep);
+    float raw[kPer], nxt[kPer];
+    bool keep[kPer], nkeep[kPer];
+    load((long long)kPer * tid, raw, keep);
+    int parity = 0;
+    for (long long base = 0; base < V; base += kTile, parity ^= 1) {
+        if (base + kTile < V) load(base + kTile + (long long)kPer * tid, nxt, nkeep);   // in flight while this tile is added
+        float x[kPer];
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) x[e] = raw[e];
+        xform(base + (long long)kPer * tid, x, keep);
+        // fast path: the tile as one integer
+        {
+            uint32_t mine = 0;
+            bool tie = false;
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                if (!keep[e]) continue;
+                bool t;
+                const fsx::Step st = fsx::step_of(x[e], E, &t);
+                tie |= t;
+                mine = fsx::sat_add(mine, st.a);
+            }
+            const uint32_t wsum = __reduce_add_sync(0xffffffffu, mine);   // a thread's amounts saturate at 2^26: 32 of them fit
+            if (lane == 0) sh.tile_sum[parity][warp] = wsum;
+            const int any_tie = __syncthreads_or(tie ? 1 : 0);
+            unsigned long long tot = 0;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) tot += sh.tile_sum[parity][w];
+            if (!any_tie && tot < fsx::kOne24 && S + (uint32_t)tot < fsx::kOne24 &&
+                !(use_thr && fsx::state_float(E, S + (uint32_t)tot) > thr)) {
+                S += (uint32_t)tot;
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) { raw[e] = nxt[e]; keep[e] = nkeep[e]; }
+                continue;
+            }
+        }
+        // slow path: scan of steps, one real addition where the binade changes
         int from = 0;   // elements of the tile below `from` are already in the sum
         for (;;) {
-            fsx::Step loc[4];
+            fsx::Step loc[kPer];
             fsx::Step acc = fsx::step_identity();
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (keep[e] && 4 * tid + e >= from) acc = fsx::then(acc, fsx::step_of(x[e], E));
+            for (int e = 0; e < kPer; ++e) {
+                if (keep[e] && kPer * tid + e >= from) acc = fsx::then(acc, fsx::step_of(x[e], E));
                 loc[e] = acc;
             }
             fsx::Step total;
@@ -186,17 +230,22 @@ __device__ long long chain_sum(float& s, long long V, ValueFn&& value, float thr
             // first element at which the sum leaves the binade or exceeds the threshold
             int mine = 0x7fffffff;
 #pragma unroll
-            for (int e = 3; e >= 0; --e) {
-                if (!(keep[e] && 4 * tid + e >= from)) continue;
+            for (int e = kPer - 1; e >= 0; --e) {
+                if (!(keep[e] && kPer * tid + e >= from)) continue;
                 const uint32_t Se = fsx::apply(fsx::then(excl, loc[e]), S);
-                if (Se >= fsx::kOne24 || (use_thr && fsx::state_float(E, Se) > thr)) mine = 4 * tid + e;
+                if (Se >= fsx::kOne24 || (use_thr && fsx::state_float(E, Se) > thr)) mine = kPer * tid + e;
             }
             const int first = block_min_int(mine, sh);
-            if (first >> 2 == tid) {
-                const int e = first & 3;
-                const fsx::Step pre = e ? fsx::then(excl, loc[e - 1]) : excl;   // loc[e - 1] holds identity steps for skipped elements
+            if (first / kPer == tid) {
+                const int e = first % kPer;
+                fsx::Step pre = excl;   // steps of this thread's elements before e (skipped ones are identities)
+#pragma unroll
+                for (int q = 0; q < kPer; ++q) if (q + 1 == e) pre = fsx::then(excl, loc[q]);
+                float xe = 0.f;
+#pragma unroll
+                for (int q = 0; q < kPer; ++q) if (q == e) xe = x[q];
                 const float before = fsx::state_float(E, fsx::apply(pre, S));
-                const float after = __fadd_rn(before, x[e]);
+                const float after = __fadd_rn(before, xe);
                 sh.bc_E = fsx::state_exp(after);
                 sh.bc_S = fsx::state_sig(after);
             }
@@ -206,6 +255,8 @@ __device__ long long chain_sum(float& s, long long V, ValueFn&& value, float thr
             if (use_thr && fsx::state_float(E, S) > thr) { s = fsx::state_float(E, S); return base + first; }
             from = first + 1;
         }
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) { raw[e] = nxt[e]; keep[e] = nkeep[e]; }
     }
     s = fsx::state_float(E, S);
     return -1;
@@ -450,6 +501,7 @@ __device__ void pass_counts(ExactShared& sh, const RowCtx& c) {
 // amounts of the dirty bins, elements of the bins to collect
 __device__ void pass_amounts(ExactShared& sh, const RowCtx& c) {
     const fsx::Level L = sh.level;
+    if (threadIdx.x == 0) ++sh.prof_passes;
     for_candidates(c, L.F, [&](float p, uint32_t key, long long i) {
         const uint32_t j = fsx::bin_of(L, key);
         if (j >= (uint32_t)fsx::kBins) return;
@@ -568,6 +620,14 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
     const int tid = threadIdx.x;
     const long long V = a.vocab;
     float* prob = scratch + (size_t)blockIdx.x * (size_t)((V + 3) & ~3LL);
+    if (tid < 32) sh.exp_tab[tid] = fsx::kExp2TabDev[tid];
+    __syncthreads();
+#ifdef SAMPLER_EXACT_PROF
+    long long prof_t[8];
+#define PROF_MARK(i) prof_t[i] = clock64()
+#else
+#define PROF_MARK(i)
+#endif
     for (int r = blockIdx.x; r < a.num_rows; r += gridDim.x) {
         const sampler_row_params p = a.rows[r];
         if (!(p.do_sample & SAMPLER_ROW_MULTINOMIAL)) continue;
@@ -581,6 +641,8 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
         __syncthreads();
 
         // 1. maximum
+        PROF_MARK(0);
+        if (tid == 0) sh.prof_passes = 0;
         float mx = -CUDART_INF_F;
         if (vec_ok) {
             const float4* r4 = reinterpret_cast<const float4*>(row);
@@ -598,31 +660,44 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
         // 2. exponentials (parked in the scratch row) and their index-order sum
         const float T = p.temperature;
         const float inv_T = __fdiv_rn(1.0f, T);
-        auto load4 = [&](const float* src, long long i, float (&x)[4], bool (&keep)[4]) {
-            if (vec_ok && i + 3 < V) {
-                const float4 q = *reinterpret_cast<const float4*>(src + i);
-                x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
-                keep[0] = keep[1] = keep[2] = keep[3] = true;
+        auto load_from = [&](const float* src) {
+            return [src, V, vec_ok](long long i, float (&x)[kPer], bool (&keep)[kPer]) {
+                if (vec_ok && i + kPer <= V) {
+                    const float4 q0 = *reinterpret_cast<const float4*>(src + i), q1 = *reinterpret_cast<const float4*>(src + i + 4);
+                    x[0] = q0.x; x[1] = q0.y; x[2] = q0.z; x[3] = q0.w; x[4] = q1.x; x[5] = q1.y; x[6] = q1.z; x[7] = q1.w;
+#pragma unroll
+                    for (int e = 0; e < kPer; ++e) keep[e] = true;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < kPer; ++e) {
+                        keep[e] = i + e < V;
+                        x[e] = keep[e] ? src[i + e] : 0.f;
+                    }
+                }
+            };
+        };
+        // stores of kPer results: 16-byte pieces where the row allows (the scratch row is 16-byte aligned)
+        auto store8 = [&](long long i, const float (&x)[kPer], const bool (&keep)[kPer]) {
+            if (i + kPer <= V) {
+                *reinterpret_cast<float4*>(prob + i) = make_float4(x[0], x[1], x[2], x[3]);
+                *reinterpret_cast<float4*>(prob + i + 4) = make_float4(x[4], x[5], x[6], x[7]);
             } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    keep[e] = i + e < V;
-                    x[e] = keep[e] ? src[i + e] : 0.f;
-                }
+                for (int e = 0; e < kPer; ++e) if (keep[e]) prob[i + e] = x[e];
             }
         };
+        PROF_MARK(1);
         float norm = 0.0f;
-        chain_sum(norm, V, [&](long long i, float (&x)[4], bool (&keep)[4]) {
-            load4(row, i, x, keep);
+        chain_sum(norm, V, load_from(row), [&](long long i, float (&x)[kPer], bool (&keep)[kPer]) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (!keep[e]) continue;
+            for (int e = 0; e < kPer; ++e) {
                 const float d = __fsub_rn(x[e], mx);
-                x[e] = fsx::expf_libm(T == 1.0f ? d : __fmul_rn(d, inv_T));
-                prob[i + e] = x[e];
+                x[e] = keep[e] ? fsx::expf_libm(T == 1.0f ? d : __fmul_rn(d, inv_T), reinterpret_cast<const uint64_t*>(sh.exp_tab)) : 0.f;
             }
+            store8(i, x, keep);
         }, 0.f, false, sh);
         __syncthreads();
+        PROF_MARK(2);
 
         // 3. probabilities; the largest one is that of the maximum logit
         const float pmax = __fdiv_rn(1.0f, norm);
@@ -636,14 +711,13 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             // index-order total of the kept probabilities
             long long my_last = -1;
             unsigned long long my_cnt = 0;
-            chain_sum(total, V, [&](long long i, float (&x)[4], bool (&keep)[4]) {
-                load4(prob, i, x, keep);
+            chain_sum(total, V, load_from(prob), [&](long long i, float (&x)[kPer], bool (&keep)[kPer]) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (!keep[e]) continue;
-                    x[e] = __fdiv_rn(x[e], norm);
-                    prob[i + e] = x[e];
-                    keep[e] = x[e] >= min_thr;
+                for (int e = 0; e < kPer; ++e) x[e] = keep[e] ? __fdiv_rn(x[e], norm) : 0.f;
+                store8(i, x, keep);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    keep[e] = keep[e] && x[e] >= min_thr;
                     if (keep[e]) { my_last = i + e; ++my_cnt; }
                 }
             }, 0.f, false, sh);
@@ -651,9 +725,38 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             const int m = block_min_int(my_last < 0 ? 0x7fffffff : -(int)my_last, sh);   // minimum of the negated = the highest index
             last_kept = m == 0x7fffffff ? -1 : -(long long)m;
         } else {
-            for (long long i = tid; i < V; i += kThreads) prob[i] = __fdiv_rn(prob[i], norm);
+            // division, and the counts / approximate masses of the first level's bins in the same pass
+            const uint32_t F_top = __float_as_uint(pmax) + 1u;
+            if (tid == 0) sh.level = fsx::Level{F_top, fsx::kTopSh};
+            for (int j = tid; j < fsx::kBins; j += kThreads) { sh.A[j] = 0; sh.C[j] = 0; sh.R[j] = 0.f; sh.E[j] = 0; sh.flag[j] = 0; }
+            if (tid == 0) sh.list_n = 0;
+            __syncthreads();
+            const fsx::Level L = sh.level;
+            unsigned long long rest = 0;
+            const auto ld = load_from(prob);
+            for (long long base = (long long)kPer * tid; base < V; base += kTile) {
+                float x[kPer];
+                bool keep[kPer];
+                ld(base, x, keep);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) x[e] = keep[e] ? __fdiv_rn(x[e], norm) : 0.f;
+                store8(base, x, keep);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    if (!keep[e] || !(x[e] >= min_thr)) continue;
+                    const uint32_t key = __float_as_uint(x[e]);
+                    if (key >= L.F) continue;
+                    const uint32_t j = fsx::bin_of(L, key);
+                    if (j >= (uint32_t)fsx::kBins) { ++rest; continue; }
+                    atomicAdd(&sh.C[j], 1u);
+                    atomicAdd(&sh.R[j], x[e]);
+                }
+            }
+            rest = block_sum_u64(rest, sh);
+            if (tid == 0) sh.rest_cnt = rest > 0xffffffffull ? 0xffffffffu : (uint32_t)rest;
         }
         __syncthreads();
+        PROF_MARK(3);
 
         long long pick = -1;
         float pick_p = 0.f;
@@ -664,10 +767,9 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             } else {
                 const float rr = __fmul_rn(total, p.rand_u);
                 float run = 0.0f;
-                pick = chain_sum(run, V, [&](long long i, float (&x)[4], bool (&keep)[4]) {
-                    load4(prob, i, x, keep);
+                pick = chain_sum(run, V, load_from(prob), [&](long long, float (&x)[kPer], bool (&keep)[kPer]) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) keep[e] = keep[e] && x[e] >= min_thr;
+                    for (int e = 0; e < kPer; ++e) keep[e] = keep[e] && x[e] >= min_thr;
                 }, rr, true, sh);
                 if (pick < 0) pick = last_kept;   // rounding left r at or beyond the total: the last kept element
             }
@@ -675,8 +777,9 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
         } else {
             // 4. the sorted walk: the kept set, its total, then the draw over the same running sums
             const uint32_t F_top = __float_as_uint(pmax) + 1u;
-            bool have_level = false;
+            bool have_level = true;   // the division pass counted the first level's bins
             sorted_run(sh, ctx, F_top, p.top_p, 0u, (double)p.rand_u * (double)p.top_p, have_level);
+            PROF_MARK(4);
             const uint32_t n_keep = sh.walk.cnt;
             total = sh.walk.s;
             kept_count = n_keep;
@@ -696,6 +799,12 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             }
             __syncthreads();
         }
+        PROF_MARK(5);
+#ifdef SAMPLER_EXACT_PROF
+        if (tid == 0 && blockIdx.x == 0)
+            printf("exact row %d: max %lld  exp+norm %lld  div(+total|+counts) %lld  run1|draw %lld  run2 %lld  (cycles) passes %d\n", r, prof_t[1] - prof_t[0],
+                   prof_t[2] - prof_t[1], prof_t[3] - prof_t[2], (top_p_active ? prof_t[4] : prof_t[5]) - prof_t[3], top_p_active ? prof_t[5] - prof_t[4] : 0LL, sh.prof_passes);
+#endif
         if (tid == 0) {
             float lp;
             if (uniform_fallback) {
@@ -724,7 +833,10 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
 }
 
 __global__ void expf_selftest_kernel(const float* in, float* out, long long n) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) out[i] = fsx::expf_libm(in[i]);
+    __shared__ uint64_t tab[32];
+    if (threadIdx.x < 32) tab[threadIdx.x] = fsx::kExp2TabDev[threadIdx.x];
+    __syncthreads();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) out[i] = fsx::expf_libm(in[i], tab);
 }
 
 }  // namespace

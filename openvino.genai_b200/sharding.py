@@ -55,6 +55,56 @@ def all_gather_token_ids(local_ids: torch.Tensor, local_index: torch.Tensor, tot
     return out
 
 
+class TokenExchange:
+    """The exchange step on GPUs: one in-place ncclAllGather of a fixed [world, cap] int64 buffer, issued by
+    the C++ host layer (include/exchange_b200.h) on the sampler's stream.  The sampler writes this
+    rank's ids straight into `local_row`; after `all_gather(n_local, stream)` every rank holds all
+    rows in `all_rows` (rank-contiguous; slot k of row r is the k-th sequence rank r owns; unused
+    slots are -1).  The communicator id travels through torch.distributed (any backend)."""
+
+    def __init__(self, device: torch.device, cap: int, group: Optional[dist.ProcessGroup] = None):
+        import ctypes as C
+        from . import _exchange_abi as X, load_library
+        self.lib = load_library()
+        self.rank, self.world, self.cap = dist.get_rank(group), dist.get_world_size(group), int(cap)
+        ident = torch.zeros(X.ID_BYTES, dtype=torch.uint8)
+        if self.rank == 0:
+            buf = (C.c_uint8 * X.ID_BYTES)()
+            self._check(self.lib.exchange_b200_unique_id(buf))
+            ident = torch.frombuffer(bytearray(buf), dtype=torch.uint8).clone()
+        ident = ident.to(device) if dist.get_backend(group) == "nccl" else ident
+        dist.broadcast(ident, src=0, group=group)
+        raw = bytes(ident.cpu().numpy().tobytes())
+        self._h = C.c_void_p()
+        self._check(self.lib.exchange_b200_create(C.c_char_p(raw), self.rank, self.world, device.index or 0, self.cap, C.byref(self._h)))
+        n = self.world * self.cap
+        base = self.lib.exchange_b200_all_rows(self._h)
+        self.all_rows = _wrap_device_int64(base, n, device).view(self.world, self.cap)
+        self.local_row = self.all_rows[self.rank]
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise RuntimeError(f"exchange_b200 error {rc}: {self.lib.exchange_b200_last_error().decode()}")
+
+    def all_gather(self, n_local: int, stream: int) -> torch.Tensor:
+        self._check(self.lib.exchange_b200_all_gather_ids(self._h, int(n_local), stream or None))
+        return self.all_rows
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.lib.exchange_b200_destroy(self._h)
+            self._h = None
+
+
+def _wrap_device_int64(ptr: int, n: int, device: torch.device) -> torch.Tensor:
+    """A torch view of device memory the C++ layer owns (no copy, no ownership)."""
+    class _Mem:
+        pass
+    holder = _Mem()
+    holder.__cuda_array_interface__ = {"shape": (n,), "typestr": "<i8", "data": (int(ptr), False), "version": 3, "strides": None}
+    return torch.as_tensor(holder, device=device)
+
+
 def max_over_ranks(value: float, device, group: Optional[dist.ProcessGroup] = None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
