@@ -1,27 +1,35 @@
 #!/usr/bin/env python
 """Benchmark of the paged-attention decode step (the headline metric: KV GB/s of one
-PagedAttention decode step, as a fraction of the measured HBM peak).
+PagedAttention decode step, as a fraction of the measured HBM peak) and, in the same line, of the
+other steps the north star names.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-A "step" is one PagedAttention operator call over the whole decode batch: write the new token's
+Headline step: one PagedAttention operator call over the whole decode batch: write the new token's
 K/V into the paged cache, split-K attention over every sequence's block table, merge.
-Workload (default): Llama-3-8B attention shape, 64 sequences, past_lens U[512, 8192], u8 by-token
-KV cache scattered over a 20k-block pool, bf16 q - seeded synthetic data.  The KV bytes touched
-per step (~600 MB) exceed the 126 MB L2, so consecutive steps cannot be served from L2.
+Workload: Llama-3-8B attention shape, 64 sequences per GPU, past_lens U[512, 8192], u8 by-token KV
+cache scattered over a 20k-block pool, bf16 q - seeded synthetic data.  The KV bytes touched per step
+(~600 MB) exceed the 126 MB L2, so consecutive steps cannot be served from L2.
 
-Prints ONE JSON line.  `value` is whole-job KV GB/s with every input resident in HBM;
-`e2e` is the same metric through the host-tensor entry point (pa_b200_forward_host) with the
-step's q/k/v/metadata copied host->device and the output device->host inside the timed region.
-`--impl reference` times the CPU restatement of the operator (the reference's own operator lives
-in the OpenVINO runtime, which is not available) on the host cores over a bounded sample.
+Prints ONE JSON line.  `value` is whole-job KV GB/s with every input resident in HBM (the K timed
+steps); `repeats` holds the spread of further regions of K steps.  `e2e` is the same metric through
+the host-tensor entry point (pa_b200_forward_host) with the step's q/k/v/metadata copied
+host->device and the output device->host inside the timed region.  `secondary` holds, measured in
+the same process: the sharded engine step (1024 sequences over all ranks: decode, full-vocabulary
+sampler, all-gather of the ids) at every N, and at N = 1 the Sampler steps, the mixed step and the
+tensor-core rate of prefill chunks.  `--workload NAME` prints one of those alone.
+`--impl reference` times the CPU restatement of the operator (the reference's own operator lives in
+the OpenVINO runtime, which is not available) on the host cores over a bounded sample.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes as C
+import hashlib
 import json
+import math
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -36,14 +44,15 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "paged_attn_decode_kv_gbps"
 UNIT = "GB/s"
+SAMPLER_WORKLOADS = ("qwen25_sampler_topk", "qwen25_sampler_greedy", "qwen25_sampler_topp", "qwen25_sampler_temperature")
 
 
-def load_peaks():
+def load_peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return {"hbm": float(d["hbm_gbs"]), "bf16": float(d.get("bf16_tflops_sustained", 1400.0)), "source": "measured"}
+    return {"hbm": 6650.0, "bf16": 1400.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -105,10 +114,53 @@ def config_of(wl, n_gpus: int) -> dict:
             "l2_policy": "KV bytes per step exceed L2 (inputs larger than L2)"}
 
 
+class Env:
+    """Process-wide state of one bench run: ranks, device, process group."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        import __graft_entry__ as entry
+        self.torch, self.dist = torch, dist
+        self.pkg = entry.load_package()
+        self.pkg.load_library()  # fails loudly when the CUDA extension is missing
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.peaks = load_peaks()
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(list(values), dtype=self.torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t.cpu()]
+
+    def sum_over_ranks(self, values):
+        t = self.torch.tensor(list(values), dtype=self.torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return [float(x) for x in t.cpu()]
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------------------------------------
-def cpu_reference_leg(wl_name: str, steps: int, warmup: int, target_mb: float = 300.0):
-    """Times the CPU restatement of the operator (attention only, cache already written) on a
-    bounded sample: the first sequences of the same seeded workload up to ~target_mb of KV."""
+def cpu_sample_workload(wl_name: str, target_mb: float = 300.0):
+    """The first sequences of the seeded workload up to ~target_mb of KV, with host data and a cache the
+    CPU restatement filled: what the CPU legs time and what the parity field compares against."""
     import torch
     import __graft_entry__ as entry
     entry.load_package()
@@ -125,7 +177,8 @@ def cpu_reference_leg(wl_name: str, steps: int, warmup: int, target_mb: float = 
                                  act=full.act_dtype, cache=full.cache_dtype, past=full.past_lens[:take].astype(np.int64),
                                  new=np.ones(take, np.int64), num_blocks=int(((full.past_lens[:take] + 1 + full.block_size - 1) // full.block_size).sum()) + 2,
                                  seed=full.seed, scale=full.scale)
-    q, k, v, fill, pk, pv = H.make_host_data(wl)
+    data = H.make_host_data(wl)
+    q, k, v, fill, pk, pv = data
     desc = H.desc_of(wl)
     n = wl.num_blocks * H.block_bytes(wl)
     kc, vc = np.zeros(n, np.uint8), np.zeros(n, np.uint8)
@@ -134,54 +187,73 @@ def cpu_reference_leg(wl_name: str, steps: int, warmup: int, target_mb: float = 
     out = torch.zeros_like(q)
     args = H.host_args(wl, q, k, v, out, kc, vc)
     assert pa_oracle.write_kv(desc, args) == 0
+    sample = f"first {take} of {full.num_sequences} sequences of the same seeded workload ({wl.decode_kv_bytes() / 1e6:.1f} MB of KV per step), attention only"
+    # `args` holds raw addresses: every buffer it names stays referenced by the returned record
+    return {"wl": wl, "full": full, "data": data, "desc": desc, "args": args, "out": out, "sample": sample, "buffers": (q, k, v, kc, vc, out)}
+
+
+def cpu_reference_leg(wl_name: str, steps: int, warmup: int):
+    """Times the CPU restatement of the operator (attention only, cache already written) on the bounded sample."""
+    from oracle import pa_oracle
+    smp = cpu_sample_workload(wl_name)
     cores = pa_oracle.hardware_threads()
     for _ in range(warmup):
-        pa_oracle.attend(desc, args, cores)
+        pa_oracle.attend(smp["desc"], smp["args"], cores)
     t0 = time.perf_counter()
     for _ in range(steps):
-        assert pa_oracle.attend(desc, args, cores) == 0
+        assert pa_oracle.attend(smp["desc"], smp["args"], cores) == 0
     dt = (time.perf_counter() - t0) / max(steps, 1)
-    gbps = wl.decode_kv_bytes() / dt / 1e9
-    sample = f"first {take} of {full.num_sequences} sequences of the same seeded workload ({wl.decode_kv_bytes() / 1e6:.1f} MB of KV per step), attention only"
-    return gbps, dt * 1e3, cores, sample, full
+    gbps = smp["wl"].decode_kv_bytes() / dt / 1e9
+    return gbps, dt * 1e3, cores, smp
+
+
+def parity_against_oracle(smp) -> float:
+    """The CUDA operator on the CPU leg's sample (same host data, cache filled through the CUDA write path):
+    largest |difference| of the attention output relative to the largest reference magnitude."""
+    from tests import pa_harness as H
+    res = H.run_gpu(smp["wl"], smp["data"])
+    if res["status"]:
+        raise SystemExit(f"device status word {res['status']:#x} in the parity step")
+    return H.rel_err(res["out_gpu"], smp["out"].float().numpy())
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 5)), min(args.warmup, 1)
-    gbps, ms, cores, sample, wl = cpu_reference_leg(args.workload, steps, warmup)
-    line = {"metric": METRIC, "value": round(gbps, 4), "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+    gbps, ms, cores, smp = cpu_reference_leg(args.workload, args.steps, args.warmup)
+    line = {"metric": METRIC, "value": round(gbps, 4), "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config_of(wl, args.gpus),
-            "cpu_baseline": {"value": round(gbps, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "data": "synthetic", "config": config_of(smp["full"], args.gpus),
+            "cpu_baseline": {"value": round(gbps, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": smp["sample"]},
             "e2e": {"value": round(gbps, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "CPU restatement of the operator contract (the reference's operator lives in the OpenVINO runtime, unavailable here)"}
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-    pkg.load_library()  # fails loudly when the CUDA extension is missing
+def stored_traffic(wl_name: str):
+    """DRAM bytes per launch of the decode kernel from the committed ncu summary - a stored capture, not a value of
+    this run: it is only reported while the kernel source still has the hash the summary was made from."""
+    tp = ROOT / "profiles" / "decode_u8_llama3_8b.md"
+    if wl_name != "llama3_8b_u8_decode" or not tp.exists():
+        return None, None
+    text = tp.read_text()
+    m = re.search(r"dram_bytes_per_launch:\s*(\d+)", text)
+    h = re.search(r"kernel_source_sha16:\s*([0-9a-f]{16})", text)
+    src = ROOT / "openvino.genai_b200" / "csrc" / "pa_decode.cu"
+    now = hashlib.sha256(src.read_bytes()).hexdigest()[:16]
+    if not m or not h or h.group(1) != now:
+        return None, "no ncu capture of the current kernel source is committed"
+    return int(m.group(1)), "profiles/decode_u8_llama3_8b.md (stored ncu capture of this kernel source, not of this run)"
+
+
+def measure_headline(env: Env, args) -> dict:
+    torch = env.torch
     from openvino_genai_b200 import workloads
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
+    dev, rank, world = env.dev, env.rank, env.world
     wl = build_workload(args.workload, rank)
-    op = pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, local)
+    op = env.pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, env.local)
     kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
     workloads.fill_cache_on_device(op, wl, kc, vc)
     q, k, v = workloads.random_activations(wl, dev)
@@ -193,33 +265,36 @@ def run_ours(args):
     dargs = op.make_args(q, k, v, out, kc, vc, *meta, wl.scale, wl.max_context_len, stream=stream.cuda_stream)
     op._check(op.lib.pa_b200_reserve(op._h, wl.num_tokens, wl.num_sequences, wl.max_context_len, 0, len(wl.block_indices)))
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
+    def region(steps):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        env.barrier()
+        ev0.record(stream)
+        for _ in range(steps):
+            op.forward_args(dargs)
+        ev1.record(stream)
+        env.barrier()
+        return ev0.elapsed_time(ev1)
 
-    # ---- device-resident steps --------------------------------------------------------------------
+    # ---- device-resident steps: the K timed steps, then more regions of K steps for the spread ----------
     for _ in range(args.warmup):
         op.forward_args(dargs)
-    barrier()
+    env.barrier()
     launches0 = op.launch_count()
-    op._check(op.lib.pa_b200_set_kernel_timing(op._h, 1))
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(env.local)
     if rank == 0:
         sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record(stream)
-    for _ in range(args.steps):
-        op.forward_args(dargs)
-    ev1.record(stream)
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
+    ms_total = region(args.steps)
+    launches = op.launch_count() - launches0
+    repeats = [region(args.steps) / args.steps for _ in range(args.repeats)]
     clocks = sampler.stop() if rank == 0 else None
+    # the decode kernel alone, in a short loop of its own (event pairs around the kernel inside the operator)
+    op._check(op.lib.pa_b200_set_kernel_timing(op._h, 1))
+    for _ in range(20):
+        op.forward_args(dargs)
+    torch.cuda.synchronize(dev)
     op._check(op.lib.pa_b200_set_kernel_timing(op._h, 0))
     ktot, kcnt = C.c_double(0), C.c_int64(0)
     op._check(op.lib.pa_b200_get_kernel_timing(op._h, C.byref(ktot), C.byref(kcnt)))
-    launches = op.launch_count() - launches0
     status = op.device_status()
     if status:
         raise SystemExit(f"device status word {status:#x} after the timed region")
@@ -234,57 +309,50 @@ def run_ours(args):
     d2h = int(hout.numel() * hout.element_size())
     for _ in range(max(args.warmup, 1)):
         op.forward_args(hargs, host=True)
-    barrier()
+    env.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
         op.forward_args(hargs, host=True)
     e1.record(stream)
-    barrier()
+    env.barrier()
     ms_e2e_total = e0.elapsed_time(e1)
     same = torch.equal(hout.to(dev), out)
 
     # ---- reduce over ranks ------------------------------------------------------------------------
     kv_bytes = wl.decode_kv_bytes()
-    stats = torch.tensor([ms_total, ms_e2e_total, ktot.value / max(kcnt.value, 1)], dtype=torch.float64, device=dev)
-    sums = torch.tensor([float(kv_bytes), float(wl.num_sequences), float(launches)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    ms_total, ms_e2e_total, kernel_ms = (float(x) for x in stats.cpu())
-    total_bytes, total_seqs, total_launches = (float(x) for x in sums.cpu())
-
-    if rank == 0:
-        peak, peak_kind = load_peaks()
-        ms_step = ms_total / args.steps
-        value = total_bytes / (ms_step * 1e-3) / 1e9
-        e2e_value = total_bytes / (ms_e2e_total / args.steps * 1e-3) / 1e9
-        achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
-        traffic = None
-        tp = ROOT / "profiles" / "decode_u8_llama3_8b.md"
-        if tp.exists() and wl.name == "llama3_8b_u8_decode":
-            import re
-            m = re.search(r"dram_bytes_per_launch:\s*(\d+)", tp.read_text())   # from the committed ncu summary of this workload
-            traffic = int(m.group(1)) if m else None
-        line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma / f32 accumulate",
-                "data": "synthetic", "config": config_of(wl, world),
-                "tokens_per_s": round(total_seqs / (ms_step * 1e-3), 1),
-                "hbm_peak_frac_step": round(value / world / peak, 4),
-                "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                             "traffic": traffic, "kernel": "decode_kernel (split-K paged decode)", "kernel_ms": round(kernel_ms, 4),
-                             "algorithmic_bytes_per_launch": kv_bytes, "peak_source": peak_kind},
-                "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": round(ms_e2e_total / args.steps, 4), "matches_device_path": bool(same)},
-                "gpu_launches": int(total_launches), "clocks": clocks}
-        if world == 1 and not args.no_cpu_baseline:
-            gbps, ms, cores, sample, _ = cpu_reference_leg(args.workload, 2, 1)
-            line["cpu_baseline"] = {"value": round(gbps, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    ms_total, ms_e2e_total, kernel_ms, *rep = env.max_over_ranks([ms_total, ms_e2e_total, ktot.value / max(kcnt.value, 1)] + repeats)
+    total_bytes, total_seqs, total_launches = env.sum_over_ranks([float(kv_bytes), float(wl.num_sequences), float(launches)])
+    del kc, vc, op
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return {}
+    peak = env.peaks["hbm"]
+    ms_step = ms_total / args.steps
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+    e2e_value = total_bytes / (ms_e2e_total / args.steps * 1e-3) / 1e9
+    achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
+    traffic, traffic_source = stored_traffic(wl.name)
+    line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma / f32 accumulate",
+            "data": "synthetic", "config": config_of(wl, world),
+            "tokens_per_s": round(total_seqs / (ms_step * 1e-3), 1),
+            "hbm_peak_frac_step": round(value / world / peak, 4),
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "traffic": traffic, "traffic_source": traffic_source, "kernel": "decode_kernel (split-K paged decode)", "kernel_ms": round(kernel_ms, 4),
+                         "kernel_timed": "20 launches in a loop of their own, CUDA events around the kernel on its stream",
+                         "algorithmic_bytes_per_launch": kv_bytes, "peak_source": env.peaks["source"]},
+            "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(ms_e2e_total / args.steps, 4), "matches_device_path": bool(same)},
+            "gpu_launches": int(total_launches), "clocks": clocks}
+    if rep:
+        line["repeats"] = {"regions": len(rep), "steps_per_region": args.steps, "ms_per_step_median": round(statistics.median(rep), 4),
+                           "ms_per_step_min": round(min(rep), 4), "ms_per_step_max": round(max(rep), 4),
+                           "value_median": round(total_bytes / (statistics.median(rep) * 1e-3) / 1e9, 2)}
+    return line
 
 
+# ------------------------------------------------------------------------------------------------
 SECONDARY = {
     # name: (constructor keyword arguments of workloads.config_qwen_mixed, keep scores, what it is)
     "qwen25_7b_mixed": (dict(), True, "16 prefill chunks of 256 + 240 decode rows, score output, 10 % of the blocks re-rotated"),
@@ -294,23 +362,18 @@ SECONDARY = {
 }
 
 
-def run_secondary(args):
-    """Secondary workloads (not the headline line): the mixed step of BASELINE.json configs[2] and
-    prefill-only steps that exercise the tcgen05 kernel.  One JSON line: step time, and for the
-    prefill-only workloads the tensor-core rate of the whole step against the measured bf16 peaks."""
-    import torch
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-    pkg.load_library()
+def measure_pa_step(env: Env, name: str, steps: int, warmup: int) -> dict:
+    """The mixed step (prefill chunks + decode rows + score output + rotation) and prefill-only steps that
+    exercise the tcgen05 kernel: step time, and for prefill-only workloads the tensor-core rate of the whole
+    step against the measured sustained bf16 peak."""
+    torch = env.torch
     from openvino_genai_b200 import workloads
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    kw, keep_scores, what = SECONDARY[args.workload]
-    dev = torch.device("cuda", 0)
+    kw, keep_scores, what = SECONDARY[name]
+    dev = env.dev
     wl = workloads.config_qwen_mixed(**kw)
     if not keep_scores:
         wl.score_aggregation_window = None
-    op = pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, 0)
+    op = env.pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, env.local)
     kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
     workloads.fill_cache_on_device(op, wl, kc, vc)
     q, k, v = workloads.random_activations(wl, dev)
@@ -322,127 +385,113 @@ def run_secondary(args):
     dargs = op.make_args(q, k, v, out, kc, vc, t(wl.past_lens), t(wl.subsequence_begins), t(wl.block_indices), t(wl.block_indices_begins),
                          wl.scale, wl.max_context_len, t(wl.score_aggregation_window), scores, t(wl.rotated_block_indices),
                          t(wl.rotation_deltas), t(wl.rotation_trig_lut), stream=stream.cuda_stream)
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         op.forward_args(dargs)
     torch.cuda.synchronize(dev)
     launches0 = op.launch_count()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(env.local)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         op.forward_args(dargs)
     e1.record(stream)
     torch.cuda.synchronize(dev)
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
     status = op.device_status()
     if status:
         raise SystemExit(f"device status word {status:#x} after the timed region")
     flops = wl.prefill_flops()
-    line = {"metric": "pa_step_ms", "value": round(ms, 4), "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 tcgen05 / f32 accumulate", "data": "synthetic",
-            "config": {"workload": args.workload, "what": what, "tokens": int(wl.num_tokens), "sequences": int(wl.num_sequences),
-                       "kv_cache": "u8 by-token asymmetric", "prefill_gflop": round(flops / 1e9, 1),
-                       "decode_kv_mb": round(wl.decode_kv_bytes() / 1e6, 1), "l2_policy": "KV bytes per step exceed L2"},
-            "gpu_launches": int(op.launch_count() - launches0), "clocks": clocks}
+    res = {"metric": "pa_step_ms", "value": round(ms, 4), "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3),
+           "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+           "dtype": "f16 tcgen05 / f32 accumulate", "data": "synthetic",
+           "config": {"workload": name, "what": what, "tokens": int(wl.num_tokens), "sequences": int(wl.num_sequences),
+                      "kv_cache": "u8 by-token asymmetric", "prefill_gflop": round(flops / 1e9, 1),
+                      "decode_kv_mb": round(wl.decode_kv_bytes() / 1e6, 1), "l2_policy": "KV bytes per step exceed L2"},
+           "gpu_launches": int(op.launch_count() - launches0), "clocks": clocks}
     if wl.decode_kv_bytes() == 0 and flops:
-        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
-        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        peak = env.peaks["bf16"]
         achieved = flops / (ms * 1e-3) / 1e12
-        line["roofline"] = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
-                            "traffic": None, "kernel": "prefill_tc_kernel (whole step: cache write + attention)",
-                            "algorithmic_flops_per_launch": int(flops),
-                            "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained" if peaks else "fallback"}
-    print(json.dumps(line), flush=True)
+        res["roofline"] = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
+                           "traffic": None, "kernel": "prefill_tc_kernel (whole step: cache write + attention)",
+                           "algorithmic_flops_per_launch": int(flops), "peak_source": "bf16_tflops_sustained, " + env.peaks["source"]}
+    del kc, vc, op
+    torch.cuda.empty_cache()
+    return res
 
 
-def run_sampler(args):
-    """BASELINE.json configs[3]: one Sampler step over 256 x 151936 f32 logits (top-k path or greedy),
-    logits resident on the device and restored from a pristine copy before every step (the step
-    applies the penalties in place).  Reports microseconds per step and the HBM roofline of one
-    mandatory read of the logits."""
-    import torch
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-    pkg.load_library()
+def measure_sampler(env: Env, name: str, steps: int, warmup: int) -> dict:
+    """One Sampler step over 256 x 151936 f32 logits, resident on the device and restored from a pristine copy
+    before every step (the step applies the penalties in place).  Microseconds per step and the HBM roofline
+    of one mandatory read of the logits."""
+    torch = env.torch
     from openvino_genai_b200 import workloads, sampler as sampler_mod
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    dev = torch.device("cuda", 0)
-    greedy = args.workload == "qwen25_sampler_greedy"
-    mode = {"qwen25_sampler_topp": "top_p", "qwen25_sampler_temperature": "temperature"}.get(args.workload)
+    dev = env.dev
+    greedy = name == "qwen25_sampler_greedy"
+    mode = {"qwen25_sampler_topp": "top_p", "qwen25_sampler_temperature": "temperature"}.get(name)
     logits_h, par, hist = workloads.config_qwen_sampler(greedy=greedy, mode=mode)
     sampling = {"top_p": "T 1, top_p 0.95 over the whole vocabulary", "temperature": "T 0.8 over the whole vocabulary"}.get(
         mode, "greedy + penalties" if greedy else "top_k 50, T 0.7, top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1")
     pristine = torch.from_numpy(logits_h).to(dev)
     work = pristine.clone()
-    smp = sampler_mod.SamplerStep(0)
+    smp = sampler_mod.SamplerStep(env.local)
     staged = smp.stage(par, hist)
     stream = torch.cuda.Stream(dev)
     times = []
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(env.local)
     sampler.start()
+    launches0 = smp.launch_count()
     with torch.cuda.stream(stream):
-        for it in range(max(args.warmup, 3) + args.steps):
+        for it in range(max(warmup, 3) + steps):
             work.copy_(pristine)      # also evicts the previous step's logits from L2 (311 MB moved)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             smp.step(work, staged, stream=stream.cuda_stream)
             e1.record(stream)
             stream.synchronize()
-            if it >= max(args.warmup, 3):
+            if it >= max(warmup, 3):
                 times.append(e0.elapsed_time(e1) * 1e3)
     clocks = sampler.stop()
+    launches = smp.launch_count() - launches0
     us = statistics.median(times)
-    peak, peak_kind = load_peaks()
+    peak = env.peaks["hbm"]
     achieved = logits_h.nbytes / (us * 1e-6) / 1e9
-    line = {"metric": "sampler_step_us", "value": round(us, 1), "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(us / 1e3, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "rows": int(logits_h.shape[0]), "vocab": int(logits_h.shape[1]),
-                       "sampling": sampling, "history": "none" if hist is None else "1024 generated ids per row", "l2_policy": "logits rewritten from a pristine copy before every step"},
-            "min_us": round(min(times), 1),
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
-                         "kernel": "sampler_kernel", "algorithmic_bytes_per_launch": int(logits_h.nbytes), "peak_source": peak_kind},
-            "gpu_launches": args.steps, "clocks": clocks}
-    print(json.dumps(line), flush=True)
+    res = {"metric": "sampler_step_us", "value": round(us, 1), "unit": "us", "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3),
+           "ms_per_step": round(us / 1e3, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": name, "rows": int(logits_h.shape[0]), "vocab": int(logits_h.shape[1]),
+                      "sampling": sampling, "history": "none" if hist is None else "1024 generated ids per row", "l2_policy": "logits rewritten from a pristine copy before every step"},
+           "min_us": round(min(times), 1), "max_us": round(max(times), 1),
+           "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                        "kernel": "sampler_kernel (+ sampler_exact_kernel for full-vocabulary rows)", "algorithmic_bytes_per_launch": int(logits_h.nbytes),
+                        "peak_source": env.peaks["source"]},
+           "gpu_launches": int(launches), "clocks": clocks}
+    smp.close()
+    del pristine, work
+    torch.cuda.empty_cache()
+    return res
 
 
-def run_engine_step(args):
-    """BASELINE.json configs[4]: one engine step of a sharded batch - Llama-3-70B attention shape,
-    1024 sequences with log-uniform contexts over all ranks (balanced by context length), u8 cache
-    with block size 16; paged decode, then the Sampler over [rows, 128256] f32 logits (T = 1,
-    top_p 0.95: the full-vocabulary path), then the all-gather of the sampled ids.  Reports whole-job
-    tokens per second; weak in sequences per rank is not assumed: the 1024 sequences are split."""
-    import math
-    import torch
-    import torch.distributed as dist
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-    pkg.load_library()
+def measure_engine_step(env: Env, steps: int, warmup: int) -> dict:
+    """One engine step of a sharded batch: Llama-3-70B attention shape, 1024 sequences with log-uniform contexts
+    split over all ranks (balanced by context length), u8 cache with block size 16; paged decode, then the
+    Sampler over [rows, 128256] f32 logits (T = 1, top_p 0.95: the full-vocabulary path) writing its ids
+    straight into this rank's row of the exchange buffer, then ONE in-place ncclAllGather issued by the C++
+    host layer on the same stream.  Strong scaling: whole-job tokens per second."""
+    torch, dist = env.torch, env.dist
     from openvino_genai_b200 import workloads, sharding, sampler as sampler_mod, _sampler_abi as SA
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, dev = env.world, env.rank, env.dev
     total_seqs, vocab = 1024, 128256
     rng = np.random.default_rng(1005)
     past_all = np.exp(rng.uniform(math.log(1024), math.log(32768), size=total_seqs)).astype(np.int64)
     shards = sharding.shard_sequences(past_all + 1, world)
     mine = shards[rank]
-    shard_sizes = [len(x) for x in shards]
+    cap = max(len(x) for x in shards)
     past = past_all[mine]
     need = int(((past + 1 + 15) // 16).sum())
     wl = workloads.make_workload("llama3_70b_u8_step", hq=64, hkv=8, d=128, bs=16, act=torch.bfloat16, cache="u8", past=past,
                                  new=np.ones(len(past), np.int64), num_blocks=need + 16, seed=1005 + 97 * rank)
-    op = pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, local)
+    op = env.pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, env.local)
     kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
     workloads.fill_cache_on_device(op, wl, kc, vc)
     q, k, v = workloads.random_activations(wl, dev)
@@ -463,67 +512,83 @@ def run_engine_step(args):
     rows["top_p"] = 0.95
     rows["repetition_penalty"] = 1.0
     rows["rand_u"] = np.random.default_rng(77 + rank).random(n, dtype=np.float32)
-    smp = sampler_mod.SamplerStep(local)
+    smp = sampler_mod.SamplerStep(env.local)
     staged = smp.stage(rows)
-    index = torch.from_numpy(mine).to(dev)
+    exchange = sharding.TokenExchange(dev, cap) if world > 1 else None
+    token_row = exchange.local_row if exchange else None
     torch.cuda.synchronize(dev)
 
-    def step(mid=None):
+    def step(ev=None):
         op.forward_args(dargs)
-        if mid is not None:
-            mid.record(stream)
-        tok, _ = smp.step(logits, staged, stream=stream.cuda_stream)
-        if world > 1:
-            with torch.cuda.stream(stream):
-                return sharding.all_gather_token_ids(tok, index, total_seqs, counts=shard_sizes)
+        if ev:
+            ev[0].record(stream)
+        tok, _ = smp.step(logits, staged, stream=stream.cuda_stream, out_tokens=token_row)
+        if ev:
+            ev[1].record(stream)
+        if exchange:
+            return exchange.all_gather(n, stream.cuda_stream)
         return tok
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         ids = step()
-    barrier()
-    assert int((ids < 0).sum().item()) == 0, "a sampled id is missing after the all-gather"
-    launches0 = op.launch_count()
-    sampler = ClockSampler(local)
+    env.barrier()
+    if exchange:
+        got = ids.cpu().numpy()
+        for r in range(world):
+            assert (got[r, :len(shards[r])] >= 0).all() and (got[r, len(shards[r]):] == -1).all(), "a sampled id is missing after the all-gather"
+    else:
+        assert int((ids < 0).sum().item()) == 0
+    launches0 = op.launch_count() + smp.launch_count()
+    sampler = ClockSampler(env.local)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    env.barrier()
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     e1.record(stream)
-    barrier()
+    env.barrier()
     clocks = sampler.stop() if rank == 0 else None
-    # where the step's time goes: one more step with an event between the operator and the sampler
-    p0, p1, p2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-    p0.record(stream)
-    step(p1)
-    p2.record(stream)
-    barrier()
-    parts = {"attention_ms": round(p0.elapsed_time(p1), 4), "sampler_and_exchange_ms": round(p1.elapsed_time(p2), 4)}
-    stats = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    sums = torch.tensor([float(wl.decode_kv_bytes()), float(op.launch_count() - launches0 + args.steps)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    if rank == 0:
-        ms = float(stats[0]) / args.steps
-        line = {"metric": "engine_step_tokens_per_s", "value": round(total_seqs / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "f16 mma / f32 accumulate; f32 sampler", "data": "synthetic",
-                "config": {"workload": "llama3_70b_u8_step", "sequences_total": total_seqs, "contexts": "log-uniform [1024, 32768]",
-                           "kv_cache": "u8 by-token asymmetric, block 16", "vocab": vocab, "sampler": "T 1, top_p 0.95 (full vocabulary)",
-                           "exchange": "all-gather of sampled ids" if world > 1 else "none (one rank)",
-                           "parallelism": f"sequences balanced by context length over {world} rank(s)", "l2_policy": "KV bytes per step exceed L2"},
-                "kv_gbps": round(float(sums[0]) / (ms * 1e-3) / 1e9, 1), "parts_rank0": parts, "gpu_launches": int(sums[1]), "clocks": clocks}
+    launches = op.launch_count() + smp.launch_count() - launches0 + (steps if exchange else 0)
+    # where the step's time goes: a few more steps with events between the operator, the sampler and the exchange
+    att, sam, exc = [], [], []
+    for _ in range(5):
+        p = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        p[0].record(stream)
+        step((p[1], p[2]))
+        p[3].record(stream)
+        env.barrier()
+        att.append(p[0].elapsed_time(p[1])); sam.append(p[1].elapsed_time(p[2])); exc.append(p[2].elapsed_time(p[3]))
+    ms_total, a_ms, s_ms, x_ms = env.max_over_ranks([e0.elapsed_time(e1), statistics.median(att), statistics.median(sam), statistics.median(exc)])
+    kv_total, launches_total, kv_max, logit_max = env.sum_over_ranks([float(wl.decode_kv_bytes()), float(launches), 0.0, 0.0])
+    kv_slowest, logits_slowest = env.max_over_ranks([float(wl.decode_kv_bytes()), float(n * vocab * 4)])
+    if exchange:
+        exchange.close()
+    smp.close()
+    del kc, vc, op, logits
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return {}
+    ms = ms_total / steps
+    peak = env.peaks["hbm"]
+    return {"metric": "engine_step_tokens_per_s", "value": round(total_seqs / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 mma / f32 accumulate; f32 sampler", "data": "synthetic",
+            "config": {"workload": "llama3_70b_u8_step", "sequences_total": total_seqs, "contexts": "log-uniform [1024, 32768]",
+                       "kv_cache": "u8 by-token asymmetric, block 16", "vocab": vocab, "sampler": "T 1, top_p 0.95 (full vocabulary)",
+                       "exchange": "one in-place ncclAllGather of [world, cap] int64 ids from the C++ host layer, on the sampler's stream" if world > 1 else "none (one rank)",
+                       "parallelism": f"sequences balanced by context length over {world} rank(s)", "l2_policy": "KV bytes per step exceed L2"},
+            "kv_gbps": round(kv_total / (ms * 1e-3) / 1e9, 1),
+            "attention_ms": round(a_ms, 4), "attention_hbm_frac": round(kv_slowest / (a_ms * 1e-3) / 1e9 / peak, 4),
+            "sampler_ms": round(s_ms, 4), "sampler_hbm_frac_one_read": round(logits_slowest / (s_ms * 1e-3) / 1e9 / peak, 4),
+            "allgather_ms": round(x_ms, 4), "parts": "max over ranks of the median of 5 separately timed steps",
+            "gpu_launches": int(launches_total), "clocks": clocks}
+
+
+def print_line(line: dict):
+    if line:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
@@ -531,23 +596,60 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=30, help="further regions of --steps steps, for the spread of the headline")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama3_8b_u8_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="headline only")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload in ("qwen25_sampler_topk", "qwen25_sampler_greedy", "qwen25_sampler_topp", "qwen25_sampler_temperature"):
-        run_sampler(args)
-    elif args.workload == "llama3_70b_u8_step":
-        run_engine_step(args)
-    elif args.workload in SECONDARY:
-        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
-            raise SystemExit("the secondary workloads run on one GPU")
-        run_secondary(args)
-    else:
-        run_ours(args)
+        return
+    args.warmup = max(args.warmup, 3)
+    env = Env()
+    try:
+        if args.workload in SAMPLER_WORKLOADS:
+            if env.world > 1:
+                raise SystemExit("the sampler workloads run on one GPU")
+            print_line(measure_sampler(env, args.workload, args.steps, args.warmup))
+        elif args.workload == "llama3_70b_u8_step":
+            print_line(measure_engine_step(env, args.steps, args.warmup))
+        elif args.workload in SECONDARY:
+            if env.world > 1:
+                raise SystemExit("the secondary workloads run on one GPU")
+            print_line(measure_pa_step(env, args.workload, args.steps, args.warmup))
+        else:
+            line = measure_headline(env, args)
+            if not args.no_secondary and args.workload == "llama3_8b_u8_decode":
+                keep = lambda d, keys: {k: d[k] for k in keys if k in d}
+                sec = {}
+                eng = measure_engine_step(env, 10, 3)
+                if env.rank == 0:
+                    sec["engine_step"] = keep(eng, ("metric", "value", "unit", "ms_per_step", "scaling", "kv_gbps", "attention_ms", "attention_hbm_frac", "sampler_ms",
+                                                    "sampler_hbm_frac_one_read", "allgather_ms", "gpu_launches", "config"))
+                if env.world == 1:
+                    for key, name in (("sampler_topk", "qwen25_sampler_topk"), ("sampler_topp", "qwen25_sampler_topp")):
+                        r = measure_sampler(env, name, 20, 3)
+                        sec[key + "_us"] = r["value"]
+                        sec[key] = {"min_us": r["min_us"], "max_us": r["max_us"], "hbm_frac_one_read": r["roofline"]["frac"], "sampling": r["config"]["sampling"]}
+                    r = measure_pa_step(env, "qwen25_7b_mixed", 20, 3)
+                    sec["mixed_step_ms"] = r["value"]
+                    sec["mixed_step"] = keep(r["config"], ("what", "tokens", "prefill_gflop", "decode_kv_mb"))
+                    r = measure_pa_step(env, "qwen25_7b_prefill_large", 10, 3)
+                    sec["prefill_tensor_frac"] = r["roofline"]["frac"]
+                    sec["prefill"] = {"tflops": r["roofline"]["achieved"], "peak_tflops": r["roofline"]["peak"], "ms_per_step": r["value"], "what": r["config"]["what"]}
+                    r = measure_pa_step(env, "qwen25_7b_prefill", 20, 3)
+                    sec["prefill_tensor_frac_16x256"] = r["roofline"]["frac"]
+                if env.rank == 0:
+                    line["secondary"] = sec
+            if env.rank == 0 and env.world == 1 and not args.no_cpu_baseline:
+                gbps, ms, cores, smp = cpu_reference_leg(args.workload, 2, 1)
+                line["cpu_baseline"] = {"value": round(gbps, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": smp["sample"]}
+                line["parity_max_rel_err"] = round(parity_against_oracle(smp), 6)
+                line["parity"] = "CUDA operator vs the CPU restatement on the cpu_baseline sample, max |diff| / max |reference|; bf16 output; the restatement itself is unpinned (no reference operator source)"
+            print_line(line)
+    finally:
+        env.close()
 
 
 if __name__ == "__main__":

@@ -184,6 +184,46 @@ int pa_b200_rotate_blocks(pa_handle* h, const pa_forward_args* args);
 int pa_b200_copy_blocks(pa_handle* h, void* key_cache, void* value_cache, int32_t num_blocks,
                         const int32_t* src_dst_pairs, int32_t num_pairs, void* stream);
 
+/* Device-side marshalling of the operator's scheduler inputs.
+ *
+ * ModelRunner::forward builds past_lens / subsequence_begins / block_indices / block_indices_begins on the
+ * host every step, walking layers x groups x blocks of std::maps
+ * (src/cpp/src/continuous_batching/model_runner.hpp:802-856, 1316-1380, 1420-1481).  Here the block tables
+ * live on the device ([num_slots][table_stride] physical ids per layer, updated by the cache manager when
+ * a sequence gains, loses or shares a block) and one call turns them plus the step's schedule into the
+ * operator's tensors:
+ *   past_lens[s]         = processed - evicted - skipped_blocks * block_size      (model_runner.hpp:804-818)
+ *   subsequence_begins   = prefix sum of num_scheduled_tokens                     (:599, :820)
+ *   block_indices        = each sequence's table, logical order, skipped blocks left out (:1420-1481)
+ *   block_indices_begins = prefix sum of the used blocks                          (:600, :822)
+ *   totals               = { num_tokens, num_block_indices, max_context_len = max(processed + scheduled) }
+ * A sequence whose numbers do not hold together (more evicted than processed, more skipped blocks than
+ * the cache holds, a table longer than table_stride - the host code asserts these) sets
+ * PA_DEV_BAD_BEGINS and is given no tokens and no blocks.  All pointers are device memory;
+ * asynchronous on the stream.  `totals` may be read back by the caller or handed on as device scalars. */
+typedef struct pa_marshal_args {
+    uint32_t struct_size;
+    const int32_t* block_table;           /* [num_slots][table_stride] */
+    const int32_t* block_table_len;       /* [num_slots] blocks in use, slots of this step's new tokens included */
+    int32_t table_stride;
+    int32_t num_slots;
+    const int32_t* slot;                  /* [num_sequences] table row of each scheduled sequence, NULL = row s */
+    const int32_t* num_processed_tokens;  /* [num_sequences] */
+    const int32_t* num_evicted_tokens;    /* [num_sequences] or NULL */
+    const int32_t* num_scheduled_tokens;  /* [num_sequences] */
+    const uint32_t* skip_mask;            /* [num_sequences][skip_words], bit j = logical block j hidden, or NULL */
+    int32_t skip_words;
+    int32_t num_sequences;
+    int32_t* past_lens;                   /* out [num_sequences] */
+    int32_t* subsequence_begins;          /* out [num_sequences + 1] */
+    int32_t* block_indices;               /* out [block_indices_capacity] */
+    int32_t* block_indices_begins;        /* out [num_sequences + 1] */
+    int32_t* totals;                      /* out [3] */
+    int32_t block_indices_capacity;
+    void* stream;
+} pa_marshal_args;
+int pa_b200_marshal_inputs(pa_handle* h, const pa_marshal_args* args);
+
 /* Allocation-free decode step.  It has no counterpart in the reference.
  *
  * For callers that cannot allocate device memory where they run the operator - code inside an

@@ -11,8 +11,9 @@
  * number the request's own std::mt19937 produced.  The whole batch is one kernel launch.
  *
  * What stays on the host (and is mirrored by the C++ class in csrc/host/sampler_host.hpp): the
- * per-request RNG engine, the token-count maps, stop conditions.  Structured-output masks,
- * beam search and tree search are outside this entry point (SAMPLER_ERR_UNSUPPORTED).
+ * per-request RNG engine, the token-count maps, stop conditions, and the grammar matcher that fills a
+ * request's next-token bitmask (the mask itself is applied here).  Beam search and tree search are
+ * outside this entry point.
  *
  * logprobs > 0 (logit_processor.hpp:36-47): the reference first takes log(sum(exp(raw logits)))
  * over the whole vocabulary (FullVocabLogSumExpTransform, logit_transformers.hpp:264-277), lets the
@@ -84,7 +85,29 @@ typedef struct sampler_step_args {
                                      penalties overwrite.  Needed by sampler_b200_step when a row that has history sets
                                      SAMPLER_ROW_RAW_LOG_PROB (else status bit 2 and a NaN log-probability); may be NULL
                                      otherwise; ignored by sampler_b200_step_host, which stages its own. */
+    /* Further draws from a row's distribution: a request with num_return_sequences = n draws n tokens from the
+     * distribution of its first sampled token, one uniform number each from the same engine, and forks
+     * (sampler.cpp:1539-1549, 1065-1089, 1163-1182).  Row r keeps its own draw (rand_u -> out_token[r]) and makes
+     * extra_offsets[r + 1] - extra_offsets[r] more with the numbers extra_rand_u[extra_offsets[r] ..], written to
+     * extra_out_token / extra_out_log_prob at the same positions.  Greedy rows make none.  All four NULL: no row
+     * draws more than once.  A caller compiled against the struct without these members and the ones below
+     * (struct_size ends at hist_raw) is served as if they were NULL. */
+    const int64_t* extra_offsets;   /* [num_rows + 1] */
+    const float* extra_rand_u;      /* [extra_offsets[num_rows]] */
+    int64_t* extra_out_token;       /* [extra_offsets[num_rows]] */
+    float* extra_out_log_prob;      /* [extra_offsets[num_rows]] */
+    /* Structured output: the grammar's next-token bitmask (sampling/structured_output/xgrammar_backend.cpp:148-165,
+     * 187-207), applied after the stop-token mask and before the penalties (logit_processor.hpp:47-57): token t is
+     * allowed iff bit (t & 31) of word t / 32 is set, every other logit becomes -inf.  Masks are rows of
+     * token_bitmasks, each bitmask_words = ceil(vocab / 32) int32 words; bitmask_index[r] names row r's mask,
+     * -1 for a request without a grammar (or whose matcher has terminated).  Both NULL: no row has one. */
+    const int32_t* token_bitmasks;  /* [num masks][bitmask_words] */
+    const int32_t* bitmask_index;   /* [num_rows] */
+    int64_t bitmask_words;
 } sampler_step_args;
+
+/* struct_size of the layout that ends at hist_raw */
+#define SAMPLER_STEP_ARGS_SIZE_V1 ((uint32_t)offsetof(sampler_step_args, extra_offsets))
 
 typedef struct sampler_handle sampler_handle;
 

@@ -79,6 +79,30 @@ class pa_forward_args(C.Structure):
     ]
 
 
+class pa_marshal_args(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("block_table", C.c_void_p),
+        ("block_table_len", C.c_void_p),
+        ("table_stride", C.c_int32),
+        ("num_slots", C.c_int32),
+        ("slot", C.c_void_p),
+        ("num_processed_tokens", C.c_void_p),
+        ("num_evicted_tokens", C.c_void_p),
+        ("num_scheduled_tokens", C.c_void_p),
+        ("skip_mask", C.c_void_p),
+        ("skip_words", C.c_int32),
+        ("num_sequences", C.c_int32),
+        ("past_lens", C.c_void_p),
+        ("subsequence_begins", C.c_void_p),
+        ("block_indices", C.c_void_p),
+        ("block_indices_begins", C.c_void_p),
+        ("totals", C.c_void_p),
+        ("block_indices_capacity", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
 PA_SYMBOLS = {
     "pa_b200_abi_version": (C.c_int, []),
     "pa_b200_last_error": (C.c_char_p, []),
@@ -96,6 +120,7 @@ PA_SYMBOLS = {
     "pa_b200_write_kv": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
     "pa_b200_rotate_blocks": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
     "pa_b200_decode_step_static": (C.c_int, [C.POINTER(pa_model_desc), C.POINTER(pa_forward_args), C.c_int]),
+    "pa_b200_marshal_inputs": (C.c_int, [C.c_void_p, C.POINTER(pa_marshal_args)]),
     "pa_b200_copy_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
 }
 

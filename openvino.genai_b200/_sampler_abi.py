@@ -50,6 +50,13 @@ class sampler_step_args(C.Structure):
         ("out_log_prob", C.c_void_p),
         ("stream", C.c_void_p),
         ("hist_raw", C.c_void_p),
+        ("extra_offsets", C.c_void_p),
+        ("extra_rand_u", C.c_void_p),
+        ("extra_out_token", C.c_void_p),
+        ("extra_out_log_prob", C.c_void_p),
+        ("token_bitmasks", C.c_void_p),
+        ("bitmask_index", C.c_void_p),
+        ("bitmask_words", C.c_int64),
     ]
 
 

@@ -135,6 +135,29 @@ FSX_HD float expf_libm(float x, const uint64_t* tab) {
 inline float expf_libm(float x) { return expf_libm(x, kExp2TabHost); }
 #endif
 
+// a / b correctly rounded (what the host's `/=` gives, logit_transformers.hpp:357-359) for a whole row
+// that shares the divisor: with y = RN(1 / b), q0 = RN(a y), the remainder a - b q0 is exact in one fused
+// multiply-add and RN(q0 + rem y) is the rounded quotient.  Small numerators, whose remainder would
+// be a denormal, take the plain division.
+FSX_HD float div_shared(float a, float b, float y) {
+    if (!(a >= 0x1p-90f)) {
+#if defined(__CUDA_ARCH__)
+        return __fdiv_rn(a, b);
+#else
+        return a / b;
+#endif
+    }
+#if defined(__CUDA_ARCH__)
+    const float q0 = __fmul_rn(a, y);
+    const float rem = __fmaf_rn(-q0, b, a);
+    return __fmaf_rn(rem, y, q0);
+#else
+    const float q0 = a * y;
+    const float rem = std::fma(-q0, b, a);
+    return std::fma(rem, y, q0);
+#endif
+}
+
 // ---- running float sums -------------------------------------------------------------------------
 constexpr uint32_t kOne24 = 1u << 24;
 constexpr uint32_t kSat = 1u << 26;   // amounts saturate here: any state that meets one has left its binade
@@ -179,6 +202,26 @@ FSX_HD Step step_of(float x, uint32_t E, bool* tie) {
     return Step{c, c};
 }
 FSX_HD Step step_of(float x, uint32_t E) { bool t; return step_of(x, E, &t); }
+
+// The amount of a term that is not a tie, in five float operations, for the passes that add whole spans
+// or bins.  scale = 2^(150 - E) turns x into units of the sum's ulp exactly (a power of two); rintf
+// rounds to nearest, and the distance to the rounded value tells a tie (exactly one half).  `defer` is
+// set for a tie and for a term of 2^24 ulps or more, which the callers add element by element.
+FSX_HD float amount_scale(uint32_t E) {   // 0 where the scale is not a normal float: such sums go element by element
+    return (E >= 24u && E <= 254u) ? bits_float((277u - E) << 23) : 0.0f;
+}
+FSX_HD uint32_t plain_amount(float x, float scale, bool* defer) {
+    const float t = x * scale;
+#if defined(__CUDA_ARCH__)
+    const float r = rintf(t);
+    *defer = fabsf(t - r) == 0.5f || !(t < 16777216.0f);
+    return __float2uint_rz(r);
+#else
+    const float r = std::nearbyint(t);   // round half to even in the default rounding mode
+    *defer = std::fabs(t - r) == 0.5f || !(t < 16777216.0f);
+    return t < 4294967040.0f ? (uint32_t)r : 0xffffffffu;
+#endif
+}
 
 // g after f
 FSX_HD Step then(Step f, Step g) {

@@ -380,6 +380,30 @@ int pa_b200_last_device_status(pa_handle* h, uint32_t* status_bits) {
     return PA_OK;
 }
 
+int pa_b200_marshal_inputs(pa_handle* h, const pa_marshal_args* a) {
+    if (!h) return fail(PA_ERR_INVALID_ARG, "NULL handle");
+    if (!a || a->struct_size != sizeof(pa_marshal_args)) return fail(PA_ERR_INVALID_ARG, "pa_marshal_args: NULL or struct_size mismatch");
+    if (a->num_sequences < 0 || a->table_stride < 0 || a->num_slots < 0 || a->skip_words < 0 || a->block_indices_capacity < 0)
+        return fail(PA_ERR_INVALID_ARG, "negative size");
+    if (a->num_sequences == 0) return PA_OK;
+    if (!a->block_table || !a->block_table_len || !a->num_processed_tokens || !a->num_scheduled_tokens || !a->past_lens || !a->subsequence_begins ||
+        !a->block_indices_begins || !a->totals || (a->block_indices_capacity > 0 && !a->block_indices))
+        return fail(PA_ERR_INVALID_ARG, "NULL pointer");
+    PA_CUDA(cudaSetDevice(h->device));
+    pa::MarshalArgs m{};
+    m.block_table = a->block_table; m.block_table_len = a->block_table_len; m.table_stride = a->table_stride; m.num_slots = a->num_slots;
+    m.slot = a->slot; m.num_processed_tokens = a->num_processed_tokens; m.num_evicted_tokens = a->num_evicted_tokens;
+    m.num_scheduled_tokens = a->num_scheduled_tokens; m.skip_mask = a->skip_mask; m.skip_words = a->skip_mask ? a->skip_words : 0;
+    m.num_sequences = a->num_sequences; m.block_size = h->g.bs;
+    m.past_lens = a->past_lens; m.subsequence_begins = a->subsequence_begins; m.block_indices = a->block_indices;
+    m.block_indices_begins = a->block_indices_begins; m.totals = a->totals; m.block_indices_capacity = a->block_indices_capacity;
+    m.status = h->status;
+    int launches = 0;
+    PA_CUDA(pa::launch_marshal(m, a->stream ? (cudaStream_t)a->stream : h->stream, &launches));
+    h->launches += launches;
+    return PA_OK;
+}
+
 int64_t pa_b200_launch_count(const pa_handle* h) { return h ? h->launches : -1; }
 
 int pa_b200_set_kernel_timing(pa_handle* h, int enabled) {

@@ -95,6 +95,28 @@ struct KernelArgs {
     long long scores_len;
 };
 
+// Device-side marshalling of the operator's inputs (pa_marshal.cu); all pointers are device memory.
+struct MarshalArgs {
+    const int32_t* block_table;          // [num_slots][table_stride] physical ids in logical order
+    const int32_t* block_table_len;      // [num_slots]
+    int table_stride, num_slots;
+    const int32_t* slot;                 // [B] table row of every scheduled sequence (null: row s)
+    const int32_t* num_processed_tokens; // [B]
+    const int32_t* num_evicted_tokens;   // [B] or null
+    const int32_t* num_scheduled_tokens; // [B]
+    const uint32_t* skip_mask;           // [B][skip_words] bit j: logical block j is hidden this step; or null
+    int skip_words;
+    int num_sequences, block_size;
+    int32_t* past_lens;                  // [B]
+    int32_t* subsequence_begins;         // [B + 1]
+    int32_t* block_indices;              // [block_indices_capacity]
+    int32_t* block_indices_begins;       // [B + 1]
+    int32_t* totals;                     // [3] num_tokens, num_block_indices, max_context_len
+    int block_indices_capacity;
+    uint32_t* status;
+};
+cudaError_t launch_marshal(const MarshalArgs& a, cudaStream_t stream, int* launches);
+
 // Writes the chunk's new keys / values into the paged cache and, in the same launch, builds the
 // decode plan (chunk list, zeroed counters) when `with_plan` is set.
 cudaError_t launch_write_kv(const KernelArgs& a, cudaStream_t stream, bool with_plan);

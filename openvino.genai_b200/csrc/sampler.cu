@@ -371,15 +371,24 @@ __device__ void apply_history(float* row, long long V, const sampler_row_params&
     }
 }
 
-// ---- phase 3 tail: softmax / min-p / top-p / draw over the K heap entries, one thread ---------------
+// ---- phase 3 tail: softmax / min-p / top-p over the K heap entries, then the draws, one thread -------
 // Mirrors TemperatureLogitTransform, MinPFilter, TopPFilter (logit_transformers.hpp:90-362) and
-// Sampler::_multinomial_sample (sampler.cpp:979-1095) statement by statement.
-__device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float* out_p, long long* out_idx, bool* uniform_fallback) {
-    *uniform_fallback = false;
+// Sampler::_multinomial_sample (sampler.cpp:979-1095) statement by statement.  The distribution is
+// built once; a request with num_return_sequences > 1 draws from it several times (sampler.cpp:1065).
+struct TopKDist {
+    int n;          // kept candidates, v[0 .. n)
+    bool defer;     // expf deferred into the draw (top-k without top-p / min-p): v holds scaled logits
+    bool uniform;   // non-finite or empty mass: uniform draws
+    float mx, sum;  // deferred form: maximum and float sum of the exponentials
+    float total;    // normal form: float sum of the kept probabilities
+};
+
+__device__ TopKDist build_top_k_dist(Cand* v, int n, const sampler_row_params& p) {
+    TopKDist d{n, false, false, 0.f, 0.f, 0.f};
     const bool min_p_active = p.min_p > 0.0f;
-    const bool defer = p.top_p == 1.0f && !min_p_active;
+    d.defer = p.top_p == 1.0f && !min_p_active;
     const float T = p.temperature;
-    if (defer) {
+    if (d.defer) {
         if (T != 1.0f) {
             const float f = 1.0f / T;
             for (int i = 0; i < n; ++i) v[i].v *= f;
@@ -387,22 +396,11 @@ __device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float*
         float mx = v[0].v;
         for (int i = 1; i < n; ++i) if (v[i].v > mx) mx = v[i].v;
         float sum = 0.0f;
-        // weights overwrite nothing: recompute in the scan (same values, same order)
         for (int i = 0; i < n; ++i) sum += exp_as_float(v[i].v - mx);
-        const bool uniform = !(sum > 0.0f && isfinite(sum));
-        if (uniform) sum = (float)n;
-        const float log_sum = logf(sum) + (uniform ? 0.0f : mx);
-        const float r = sum * p.rand_u;
-        float run = 0.0f;
-        int pick = n - 1;
-        for (int i = 0; i < n; ++i) {
-            run += uniform ? 1.0f : exp_as_float(v[i].v - mx);
-            if (run > r) { pick = i; break; }
-        }
-        *out_p = uniform ? logf(1.0f / (float)n) : v[pick].v - log_sum;
-        *out_idx = v[pick].idx;
-        *uniform_fallback = uniform;
-        return;
+        d.uniform = !(sum > 0.0f && isfinite(sum));
+        if (d.uniform) sum = (float)n;
+        d.mx = mx; d.sum = sum;
+        return d;
     }
     {   // softmax(logits / T) over the heap array, in array order
         float mx = v[0].v;
@@ -454,16 +452,37 @@ __device__ void finish_top_k(Cand* v, int n, const sampler_row_params& p, float*
     }
     float total = 0.0f;
     for (int i = 0; i < n; ++i) total += v[i].v;
-    if (!(total > 0.0f && isfinite(total))) {
-        int pick = (int)(p.rand_u * (float)n);
+    d.n = n;
+    d.total = total;
+    d.uniform = !(total > 0.0f && isfinite(total));
+    return d;
+}
+
+// One draw with the uniform number u: the candidate's vocabulary index and its log-probability.
+__device__ void draw_top_k(const Cand* v, const TopKDist& d, float u, float* out_p, long long* out_idx) {
+    const int n = d.n;
+    if (d.defer) {
+        const float log_sum = logf(d.sum) + (d.uniform ? 0.0f : d.mx);
+        const float r = d.sum * u;
+        float run = 0.0f;
+        int pick = n - 1;
+        for (int i = 0; i < n; ++i) {
+            run += d.uniform ? 1.0f : exp_as_float(v[i].v - d.mx);
+            if (run > r) { pick = i; break; }
+        }
+        *out_p = d.uniform ? logf(1.0f / (float)n) : v[pick].v - log_sum;
+        *out_idx = v[pick].idx;
+        return;
+    }
+    if (d.uniform) {
+        int pick = (int)(u * (float)n);
         if (pick > n - 1) pick = n - 1;
         *out_p = logf(1.0f / (float)n);
         *out_idx = v[pick].idx;
-        *uniform_fallback = true;
         return;
     }
-    const float log_total = logf(total);
-    const float r = total * p.rand_u;
+    const float log_total = logf(d.total);
+    const float r = d.total * u;
     float run = 0.0f;
     int pick = n - 1;
     for (int i = 0; i < n; ++i) {
@@ -517,6 +536,25 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
             if (a.hist_ids[i] == idx) { raw = a.hist_raw[i]; break; }
         return raw - raw_lse;
     };
+
+    // ---- grammar bitmask (logit_processor.hpp:52-57: after the stop-token mask, before the penalties; both only
+    //      write -inf, so their order does not show) ------------------------------------------------
+    if (a.bitmask_index) {
+        const int mi = a.bitmask_index[r];
+        if (mi >= 0) {
+            const uint32_t* mask = reinterpret_cast<const uint32_t*>(a.token_bitmasks) + (long long)mi * a.bitmask_words;
+            for (long long w = tid; w < a.bitmask_words; w += kThreads) {
+                uint32_t denied = ~mask[w];
+                if (w == a.bitmask_words - 1 && (V & 31)) denied &= (1u << (V & 31)) - 1u;   // bits beyond the vocabulary
+                while (denied) {
+                    const int b = __ffs(denied) - 1;
+                    denied &= denied - 1;
+                    row[32 * w + b] = -CUDART_INF_F;
+                }
+            }
+            __syncthreads();
+        }
+    }
 
     // ---- 1. penalties ------------------------------------------------------------------------------
     if (h1 > h0) apply_history(row, V, p, a.hist_ids + h0, a.hist_meta + h0, h1 - h0, a.status, raw_lp && raw_ok ? a.hist_raw + h0 : nullptr);
@@ -676,12 +714,16 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
         }
         __syncthreads();
         if (tid == 0) {
-            float lp;
-            long long idx;
-            bool uniform_fallback;
-            finish_top_k(sh.heap, K, p, &lp, &idx, &uniform_fallback);
-            a.out_token[r] = idx;
-            a.out_log_prob[r] = raw_lp && !uniform_fallback ? raw_log_prob(idx) : lp;   // sampler.cpp:1022-1029, 1076-1081
+            const TopKDist dist = build_top_k_dist(sh.heap, K, p);
+            const long long x0 = a.extra_offsets ? a.extra_offsets[r] : 0, x1 = a.extra_offsets ? a.extra_offsets[r + 1] : 0;
+            for (long long k = -1; k < x1 - x0; ++k) {   // the row's own draw, then the further ones
+                float lp;
+                long long idx;
+                draw_top_k(sh.heap, dist, k < 0 ? p.rand_u : a.extra_rand_u[x0 + k], &lp, &idx);
+                if (raw_lp && !dist.uniform) lp = raw_log_prob(idx);   // sampler.cpp:1022-1029, 1076-1081
+                if (k < 0) { a.out_token[r] = idx; a.out_log_prob[r] = lp; }
+                else { a.extra_out_token[x0 + k] = idx; a.extra_out_log_prob[x0 + k] = lp; }
+            }
         }
         return;
     }
@@ -689,7 +731,11 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_kernel(StepArgs a) {
     // ---- 4. full vocabulary ---------------------------------------------------------------------------
     if (top_k_active && p.top_k < V) {
         // a heap larger than the shared-memory capacity: not supported, and said so (status bit 3, token -1)
-        if (tid == 0) { atomicOr(a.status, 8u); a.out_token[r] = -1; a.out_log_prob[r] = 0.f; }
+        if (tid == 0) {
+            atomicOr(a.status, 8u); a.out_token[r] = -1; a.out_log_prob[r] = 0.f;
+            if (a.extra_offsets)
+                for (long long k = a.extra_offsets[r]; k < a.extra_offsets[r + 1]; ++k) { a.extra_out_token[k] = -1; a.extra_out_log_prob[k] = 0.f; }
+        }
         return;
     }
     // The row is finished by sampler_exact_kernel (sampler_exact.cu), launched right after this one: it

@@ -92,7 +92,12 @@ bool row_is_full_vocab(const sampler_row_params& p, int64_t vocab) {
 
 int validate(const sampler_handle* h, const sampler_step_args* a) {
     if (!h) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL handle");
-    if (!a || a->struct_size != sizeof(sampler_step_args)) return sfail(SAMPLER_ERR_INVALID_ARG, "sampler_step_args: NULL or struct_size mismatch");
+    if (!a || (a->struct_size != sizeof(sampler_step_args) && a->struct_size != SAMPLER_STEP_ARGS_SIZE_V1))
+        return sfail(SAMPLER_ERR_INVALID_ARG, "sampler_step_args: NULL or struct_size mismatch");
+    if (a->struct_size == sizeof(sampler_step_args) && a->extra_offsets && (!a->extra_rand_u || !a->extra_out_token || !a->extra_out_log_prob))
+        return sfail(SAMPLER_ERR_INVALID_ARG, "extra draws: offsets without numbers or outputs");
+    if (a->struct_size == sizeof(sampler_step_args) && a->token_bitmasks && a->bitmask_index && a->bitmask_words != (a->vocab + 31) / 32)
+        return sfail(SAMPLER_ERR_INVALID_ARG, "bitmask_words must be ceil(vocab / 32)");
     if (a->num_rows < 0 || a->vocab <= 0 || a->num_logit_rows < 0) return sfail(SAMPLER_ERR_INVALID_ARG, "bad size");
     if (a->vocab > 0x7fffffffLL) return sfail(SAMPLER_ERR_TOO_LARGE, "vocab above 2^31 - 1");
     if (a->num_rows > 0 && (!a->logits || !a->rows || !a->out_token || !a->out_log_prob)) return sfail(SAMPLER_ERR_INVALID_ARG, "NULL pointer");
@@ -105,6 +110,15 @@ sampler::StepArgs kernel_args(sampler_handle* h, const sampler_step_args* a) {
     k.logits = a->logits; k.num_logit_rows = a->num_logit_rows; k.vocab = a->vocab; k.num_rows = a->num_rows;
     k.rows = a->rows; k.hist_offsets = a->hist_offsets; k.hist_ids = a->hist_ids; k.hist_meta = a->hist_meta;
     k.out_token = a->out_token; k.out_log_prob = a->out_log_prob; k.status = h->status; k.hist_raw = a->hist_raw;
+    const bool extras = a->struct_size == sizeof(sampler_step_args) && a->extra_offsets != nullptr;
+    k.extra_offsets = extras ? a->extra_offsets : nullptr;
+    k.extra_rand_u = extras ? a->extra_rand_u : nullptr;
+    k.extra_out_token = extras ? a->extra_out_token : nullptr;
+    k.extra_out_log_prob = extras ? a->extra_out_log_prob : nullptr;
+    const bool masks = a->struct_size == sizeof(sampler_step_args) && a->token_bitmasks != nullptr && a->bitmask_index != nullptr;
+    k.token_bitmasks = masks ? a->token_bitmasks : nullptr;
+    k.bitmask_index = masks ? a->bitmask_index : nullptr;
+    k.bitmask_words = masks ? a->bitmask_words : 0;
     return k;
 }
 
@@ -182,6 +196,19 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
     const size_t o_tok = off;   off += up(n * sizeof(int64_t));
     const size_t o_lp = off;    off += up(n * sizeof(float));
     const size_t o_hraw = off;  off += up(hist_n * sizeof(float));
+    const bool extras = a->struct_size == sizeof(sampler_step_args) && a->extra_offsets != nullptr;
+    const size_t extra_n = extras ? (size_t)a->extra_offsets[n] : 0;
+    const size_t o_xoff = off;  off += up(extras ? (n + 1) * sizeof(int64_t) : 0);
+    const size_t o_xu = off;    off += up(extra_n * sizeof(float));
+    const size_t o_xtok = off;  off += up(extra_n * sizeof(int64_t));
+    const size_t o_xlp = off;   off += up(extra_n * sizeof(float));
+    const bool masks = a->struct_size == sizeof(sampler_step_args) && a->token_bitmasks && a->bitmask_index;
+    int32_t num_masks = 0;
+    if (masks)
+        for (size_t i = 0; i < n; ++i) num_masks = std::max(num_masks, a->bitmask_index[i] + 1);
+    const size_t mask_bytes = masks ? (size_t)num_masks * (size_t)a->bitmask_words * sizeof(int32_t) : 0;
+    const size_t o_midx = off;  off += up(masks ? n * sizeof(int32_t) : 0);
+    const size_t o_mask = off;  off += up(mask_bytes);
     const size_t o_logits = off; off += up(logits_bytes);
     rc = ensure_stage(h, off);
     if (rc != SAMPLER_OK) return rc;
@@ -192,8 +219,31 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
         std::memcpy(h->stage_host + o_hmeta, a->hist_meta, hist_n * sizeof(uint32_t));
     }
     S_CUDA(cudaMemcpyAsync(h->stage_dev, h->stage_host, small_in, cudaMemcpyHostToDevice, stream));
+    if (extras) {
+        std::memcpy(h->stage_host + o_xoff, a->extra_offsets, (n + 1) * sizeof(int64_t));
+        std::memcpy(h->stage_host + o_xu, a->extra_rand_u, extra_n * sizeof(float));
+        S_CUDA(cudaMemcpyAsync(h->stage_dev + o_xoff, h->stage_host + o_xoff, o_xtok - o_xoff, cudaMemcpyHostToDevice, stream));
+    }
     S_CUDA(cudaMemcpyAsync(h->stage_dev + o_logits, a->logits, logits_bytes, cudaMemcpyHostToDevice, stream));
-    sampler_step_args d = *a;
+    if (masks) {
+        std::memcpy(h->stage_host + o_midx, a->bitmask_index, n * sizeof(int32_t));
+        if (mask_bytes) std::memcpy(h->stage_host + o_mask, a->token_bitmasks, mask_bytes);
+        S_CUDA(cudaMemcpyAsync(h->stage_dev + o_midx, h->stage_host + o_midx, o_mask + up(mask_bytes) - o_midx, cudaMemcpyHostToDevice, stream));
+    }
+    sampler_step_args d;
+    std::memset(&d, 0, sizeof(d));
+    std::memcpy(&d, a, a->struct_size);
+    d.struct_size = sizeof(d);
+    if (extras) {
+        d.extra_offsets = (const int64_t*)(h->stage_dev + o_xoff);
+        d.extra_rand_u = (const float*)(h->stage_dev + o_xu);
+        d.extra_out_token = (int64_t*)(h->stage_dev + o_xtok);
+        d.extra_out_log_prob = (float*)(h->stage_dev + o_xlp);
+    }
+    if (masks) {
+        d.bitmask_index = (const int32_t*)(h->stage_dev + o_midx);
+        d.token_bitmasks = (const int32_t*)(h->stage_dev + o_mask);
+    }
     d.logits = (float*)(h->stage_dev + o_logits);
     d.rows = (const sampler_row_params*)(h->stage_dev + o_rows);
     d.hist_offsets = a->hist_offsets ? (const int64_t*)(h->stage_dev + o_hoff) : nullptr;
@@ -208,6 +258,10 @@ int sampler_b200_step_host(sampler_handle* h, const sampler_step_args* a, int co
     if (rc != SAMPLER_OK) return rc;
     S_CUDA(cudaMemcpyAsync(a->out_token, d.out_token, n * sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
     S_CUDA(cudaMemcpyAsync(a->out_log_prob, d.out_log_prob, n * sizeof(float), cudaMemcpyDeviceToHost, stream));
+    if (extras && extra_n) {
+        S_CUDA(cudaMemcpyAsync(a->extra_out_token, d.extra_out_token, extra_n * sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+        S_CUDA(cudaMemcpyAsync(a->extra_out_log_prob, d.extra_out_log_prob, extra_n * sizeof(float), cudaMemcpyDeviceToHost, stream));
+    }
     if (copy_logits_back) S_CUDA(cudaMemcpyAsync(a->logits, d.logits, logits_bytes, cudaMemcpyDeviceToHost, stream));
     uint32_t bits = 0;
     S_CUDA(cudaMemcpyAsync(&bits, h->status, 4, cudaMemcpyDeviceToHost, stream));

@@ -58,7 +58,6 @@ struct ExactShared {
     int list_n;
     // block scan / reduce scratch
     fsx::Step scan_step[kWarps];
-    unsigned long long tile_sum[2][kWarps];
     unsigned long long exp_tab[32];
     RunSum scan_run[kWarps];
     double scan_d[kWarps];
@@ -159,66 +158,111 @@ struct StepOp {
 };
 
 // ---- index-order sums ---------------------------------------------------------------------------------
-// Adds the kept values of a row in index order to the float sum s, exactly as the host loop
-// `s += v[i]` does.  A tile is kTile consecutive elements, kPer per thread.  While the sum stays in
-// its binade and no element of the tile is a tie, the tile's amounts are plain integers whose order
-// does not matter: one block reduction per tile.  A tile with a tie, a change of binade or (with
-// `use_thr`) the first running sum above `thr` is redone as a block scan of two-state steps.
-//   load(i, raw, keep)   fetches elements i .. i + kPer - 1 (keep = false beyond the row)
-//   xform(i, raw, keep)  turns them into the values to add (and may drop elements or park results)
-// Returns the index of the first element whose running sum exceeds thr (-1: none, or !use_thr).
-// All threads call this with the same arguments; s is returned to all.
-constexpr int kPer = 8;
-constexpr int kTile = kThreads * kPer;
+// `s += v[i]` over a whole row, exactly as the host loop does it, without a barrier per tile.
+// The row is cut into spans of consecutive elements; every warp owns whole spans.  A first pass leaves
+// an approximate mass per span, from which the exponent of the running sum at each span is
+// hypothesised; the exact pass then adds a span's amounts under that hypothesis into one integer
+// A[j] (their order does not matter while no element is a tie and the sum stays in its binade).
+// One thread walks the spans and checks each hypothesis against the exact sum so far; a span that
+// fails (tie, change of binade, wrong guess, or the draw's threshold inside it) is added element by
+// element with a block scan of two-state steps.  Spans share the bin arrays of the sorted walk, which
+// runs later.
+constexpr int kSpanBase = 2048;
 
-template <class LoadFn, class XformFn>
-__device__ long long chain_sum(float& s, long long V, LoadFn&& load, XformFn&& xform, float thr, bool use_thr, ExactShared& sh) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint32_t E = fsx::state_exp(s), S = fsx::state_sig(s);
-    float raw[kPer], nxt[kPer];
-    bool keep[kPer], nkeep[kPer];
-    load((long long)kPer * tid, raw, keep);
-    int parity = 0;
-    for (long long base = 0; base < V; base += kTile, parity ^= 1) {
-        if (base + kTile < V) load(base + kTile + (long long)kPer * tid, nxt, nkeep);   // in flight while this tile is added
-        float x[kPer];
+struct SpanGeom {
+    long long len;   // elements per span
+    int count;       // spans of the row (<= fsx::kBins)
+};
+__device__ __forceinline__ SpanGeom span_geom(long long V) {
+    const long long mult = (V + (long long)kSpanBase * fsx::kBins - 1) / ((long long)kSpanBase * fsx::kBins);
+    const long long len = kSpanBase * (mult < 1 ? 1 : mult);
+    return SpanGeom{len, (int)((V + len - 1) / len)};
+}
+
+// Calls fn(values[4], keep[4], index of values[0]) for every group of four consecutive elements of span j,
+// dealt to the lanes of the calling warp; four 16-byte loads in flight per lane.
+template <class F>
+__device__ __forceinline__ void for_span(const float* src, long long V, bool vec_ok, const SpanGeom& g, int j, F&& fn) {
+    const int lane = threadIdx.x & 31;
+    const long long lo = (long long)j * g.len, hi = min(V, lo + g.len);
+    for (long long base = lo + 4 * lane; base < hi; base += 4 * 32 * 4) {
+        float x[4][4];
+        bool keep[4][4];
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) x[e] = raw[e];
-        xform(base + (long long)kPer * tid, x, keep);
-        // fast path: the tile as one integer
-        {
-            uint32_t mine = 0;
-            bool tie = false;
+        for (int u = 0; u < 4; ++u) {
+            const long long i = base + (long long)u * 128;
+            if (vec_ok && i + 4 <= hi) {
+                const float4 q = *reinterpret_cast<const float4*>(src + i);
+                x[u][0] = q.x; x[u][1] = q.y; x[u][2] = q.z; x[u][3] = q.w;
+                keep[u][0] = keep[u][1] = keep[u][2] = keep[u][3] = true;
+            } else {
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                if (!keep[e]) continue;
-                bool t;
-                const fsx::Step st = fsx::step_of(x[e], E, &t);
-                tie |= t;
-                mine = fsx::sat_add(mine, st.a);
-            }
-            const uint32_t wsum = __reduce_add_sync(0xffffffffu, mine);   // a thread's amounts saturate at 2^26: 32 of them fit
-            if (lane == 0) sh.tile_sum[parity][warp] = wsum;
-            const int any_tie = __syncthreads_or(tie ? 1 : 0);
-            unsigned long long tot = 0;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) tot += sh.tile_sum[parity][w];
-            if (!any_tie && tot < fsx::kOne24 && S + (uint32_t)tot < fsx::kOne24 &&
-                !(use_thr && fsx::state_float(E, S + (uint32_t)tot) > thr)) {
-                S += (uint32_t)tot;
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) { raw[e] = nxt[e]; keep[e] = nkeep[e]; }
-                continue;
+                for (int e = 0; e < 4; ++e) {
+                    keep[u][e] = i + e < hi;
+                    x[u][e] = keep[u][e] ? src[i + e] : 0.f;
+                }
             }
         }
-        // slow path: scan of steps, one real addition where the binade changes
+#pragma unroll
+        for (int u = 0; u < 4; ++u) fn(x[u], keep[u], base + (long long)u * 128);
+    }
+}
+
+// Hypothesised exponent of the running sum at every span, from the approximate masses R[] scaled by
+// `scale` and a sum that starts at zero.  A span whose range (widened by the margin) is not inside one
+// binade gets exponent 0, which no sum has: the walk then adds it element by element.
+__device__ void hypothesise_spans(ExactShared& sh, int spans, float scale) {
+    const int tid = threadIdx.x, j0 = tid * kBinsPerThread;
+    double mass = 0.0;
+#pragma unroll
+    for (int k = 0; k < kBinsPerThread; ++k)
+        if (j0 + k < spans) mass += (double)sh.R[j0 + k] * (double)scale;
+    double cum = block_scan_exclusive(mass, 0.0, [](double a, double c) { return a + c; }, sh.scan_d, (double*)nullptr);
+#pragma unroll
+    for (int k = 0; k < kBinsPerThread; ++k) {
+        const int j = j0 + k;
+        if (j >= spans) break;
+        const double lo = cum, hi = cum + (double)sh.R[j] * (double)scale;
+        cum = hi;
+        uint32_t E;
+        const bool certain = fsx::hyp_exponent(lo, hi, kMargin, &E);
+        sh.E[j] = certain ? (uint8_t)E : (uint8_t)0;
+        sh.A[j] = 0;
+    }
+    for (int i = tid; i < fsx::kBins / 32; i += kThreads) sh.tie_bits[i] = 0;
+    __syncthreads();
+}
+
+// Adds span j element by element (block scan of steps, real additions where the binade changes) to the
+// state (E, S).  Values come from `src` and are kept when >= min_thr.  With use_thr the scan stops at the
+// first running sum above thr and returns that element's index (else -1).
+__device__ long long span_exact(ExactShared& sh, const float* src, long long V, bool vec_ok, const SpanGeom& g, int j, float min_thr, uint32_t& E,
+                                uint32_t& S, float thr, bool use_thr) {
+    const int tid = threadIdx.x;
+    const long long lo = (long long)j * g.len, hi = min(V, lo + g.len);
+    for (long long base = lo; base < hi; base += kThreads * 4) {
+        float x[4];
+        bool keep[4];
+        const long long i0 = base + 4 * tid;
+        if (vec_ok && i0 + 4 <= hi) {
+            const float4 q = *reinterpret_cast<const float4*>(src + i0);
+            x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) keep[e] = x[e] >= min_thr;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                x[e] = i0 + e < hi ? src[i0 + e] : 0.f;
+                keep[e] = i0 + e < hi && x[e] >= min_thr;
+            }
+        }
         int from = 0;   // elements of the tile below `from` are already in the sum
         for (;;) {
-            fsx::Step loc[kPer];
+            fsx::Step loc[4];
             fsx::Step acc = fsx::step_identity();
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                if (keep[e] && kPer * tid + e >= from) acc = fsx::then(acc, fsx::step_of(x[e], E));
+            for (int e = 0; e < 4; ++e) {
+                if (keep[e] && 4 * tid + e >= from) acc = fsx::then(acc, fsx::step_of(x[e], E));
                 loc[e] = acc;
             }
             fsx::Step total;
@@ -227,36 +271,60 @@ __device__ long long chain_sum(float& s, long long V, LoadFn&& load, XformFn&& x
             const bool crossed = S_end >= fsx::kOne24;
             const bool over = use_thr && !crossed && fsx::state_float(E, S_end) > thr;
             if (!crossed && !over) { S = S_end; break; }
-            // first element at which the sum leaves the binade or exceeds the threshold
-            int mine = 0x7fffffff;
+            int mine = 0x7fffffff;   // first element at which the sum leaves the binade or exceeds the threshold
 #pragma unroll
-            for (int e = kPer - 1; e >= 0; --e) {
-                if (!(keep[e] && kPer * tid + e >= from)) continue;
+            for (int e = 3; e >= 0; --e) {
+                if (!(keep[e] && 4 * tid + e >= from)) continue;
                 const uint32_t Se = fsx::apply(fsx::then(excl, loc[e]), S);
-                if (Se >= fsx::kOne24 || (use_thr && fsx::state_float(E, Se) > thr)) mine = kPer * tid + e;
+                if (Se >= fsx::kOne24 || (use_thr && fsx::state_float(E, Se) > thr)) mine = 4 * tid + e;
             }
             const int first = block_min_int(mine, sh);
-            if (first / kPer == tid) {
-                const int e = first % kPer;
-                fsx::Step pre = excl;   // steps of this thread's elements before e (skipped ones are identities)
-#pragma unroll
-                for (int q = 0; q < kPer; ++q) if (q + 1 == e) pre = fsx::then(excl, loc[q]);
-                float xe = 0.f;
-#pragma unroll
-                for (int q = 0; q < kPer; ++q) if (q == e) xe = x[q];
-                const float before = fsx::state_float(E, fsx::apply(pre, S));
-                const float after = __fadd_rn(before, xe);
+            if (first >> 2 == tid) {
+                const int e = first & 3;
+                const fsx::Step pre = e == 0 ? excl : fsx::then(excl, e == 1 ? loc[0] : e == 2 ? loc[1] : loc[2]);   // skipped elements are identities
+                const float xe = e == 0 ? x[0] : e == 1 ? x[1] : e == 2 ? x[2] : x[3];
+                const float after = __fadd_rn(fsx::state_float(E, fsx::apply(pre, S)), xe);
                 sh.bc_E = fsx::state_exp(after);
                 sh.bc_S = fsx::state_sig(after);
             }
             __syncthreads();
             E = sh.bc_E; S = sh.bc_S;
             __syncthreads();
-            if (use_thr && fsx::state_float(E, S) > thr) { s = fsx::state_float(E, S); return base + first; }
+            if (use_thr && fsx::state_float(E, S) > thr) return base + first;
             from = first + 1;
         }
-#pragma unroll
-        for (int e = 0; e < kPer; ++e) { raw[e] = nxt[e]; keep[e] = nkeep[e]; }
+    }
+    return -1;
+}
+
+// Walks the spans from the start of the row: whole spans where the hypothesis holds, span_exact
+// elsewhere.  Returns the final sum in s; with use_thr, the index of the first element whose running
+// sum exceeds thr (-1: none).
+__device__ long long walk_spans(ExactShared& sh, const float* src, long long V, bool vec_ok, const SpanGeom& g, float min_thr, float& s, float thr,
+                                bool use_thr) {
+    uint32_t E = 1u, S = 0u;
+    int j = 0;
+    __syncthreads();
+    for (;;) {
+        if (threadIdx.x == 0) {
+            while (j < g.count) {
+                const uint32_t add = sh.A[j];
+                const bool tie = (sh.tie_bits[j >> 5] >> (j & 31)) & 1u;
+                if (tie || (uint32_t)sh.E[j] != E) break;
+                if (S == 0u || add >= fsx::kOne24 || S + add >= fsx::kOne24) break;
+                if (use_thr && fsx::state_float(E, S + add) > thr) break;
+                S += add;
+                ++j;
+            }
+            sh.bc_E = E; sh.bc_S = S; sh.bc_idx = j;
+        }
+        __syncthreads();
+        E = sh.bc_E; S = sh.bc_S; j = sh.bc_idx;
+        __syncthreads();
+        if (j >= g.count) break;
+        const long long hit = span_exact(sh, src, V, vec_ok, g, j, min_thr, E, S, thr, use_thr);
+        if (hit >= 0) { s = fsx::state_float(E, S); return hit; }
+        ++j;
     }
     s = fsx::state_float(E, S);
     return -1;
@@ -511,10 +579,10 @@ __device__ void pass_amounts(ExactShared& sh, const RowCtx& c) {
             if (pos < kListCap) sh.list[pos] = fsx::make_entry(key, (uint32_t)i);
         } else if (f & fsx::kBinDirty) {
             bool tie;
-            const fsx::Step st = fsx::step_of(p, sh.E[j], &tie);
+            const uint32_t amount = fsx::plain_amount(p, fsx::amount_scale(sh.E[j]), &tie);
             if (!tie) {
-                const uint32_t old = atomicAdd(&sh.A[j], st.a);
-                tie = old + st.a >= 0x80000000u;   // too much for one binade: never taken as a whole
+                const uint32_t old = atomicAdd(&sh.A[j], amount);
+                tie = old + amount >= 0x80000000u;   // too much for one binade: never taken as a whole
             }
             if (tie) atomicOr(&sh.tie_bits[j >> 5], 1u << (j & 31));
         }
@@ -642,12 +710,28 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
 
         // 1. maximum
         PROF_MARK(0);
+#ifdef SAMPLER_EXACT_PROF
+        unsigned long long prof_g0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
+#endif
         if (tid == 0) sh.prof_passes = 0;
+        const SpanGeom sg = span_geom(V);
+        const float T = p.temperature;
+        const float inv_T = __fdiv_rn(1.0f, T);
+        const int lane = tid & 31, warp = tid >> 5;
         float mx = -CUDART_INF_F;
         if (vec_ok) {
             const float4* r4 = reinterpret_cast<const float4*>(row);
             const long long n4 = V >> 2;
-            for (long long i = tid; i < n4; i += kThreads) {
+            long long i = tid;
+            for (; i + 3 * kThreads < n4; i += 4 * kThreads) {
+                float4 q[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) q[u] = r4[i + u * kThreads];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mx = fmaxf(mx, fmaxf(fmaxf(q[u].x, q[u].y), fmaxf(q[u].z, q[u].w)));
+            }
+            for (; i < n4; i += kThreads) {
                 const float4 q = r4[i];
                 mx = fmaxf(mx, fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)));
             }
@@ -656,178 +740,199 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             for (long long i = tid; i < V; i += kThreads) mx = fmaxf(mx, row[i]);
         }
         mx = block_max(mx, sh);
-
-        // 2. exponentials (parked in the scratch row) and their index-order sum
-        const float T = p.temperature;
-        const float inv_T = __fdiv_rn(1.0f, T);
-        auto load_from = [&](const float* src) {
-            return [src, V, vec_ok](long long i, float (&x)[kPer], bool (&keep)[kPer]) {
-                if (vec_ok && i + kPer <= V) {
-                    const float4 q0 = *reinterpret_cast<const float4*>(src + i), q1 = *reinterpret_cast<const float4*>(src + i + 4);
-                    x[0] = q0.x; x[1] = q0.y; x[2] = q0.z; x[3] = q0.w; x[4] = q1.x; x[5] = q1.y; x[6] = q1.z; x[7] = q1.w;
-#pragma unroll
-                    for (int e = 0; e < kPer; ++e) keep[e] = true;
-                } else {
-#pragma unroll
-                    for (int e = 0; e < kPer; ++e) {
-                        keep[e] = i + e < V;
-                        x[e] = keep[e] ? src[i + e] : 0.f;
-                    }
-                }
-            };
-        };
-        // stores of kPer results: 16-byte pieces where the row allows (the scratch row is 16-byte aligned)
-        auto store8 = [&](long long i, const float (&x)[kPer], const bool (&keep)[kPer]) {
-            if (i + kPer <= V) {
-                *reinterpret_cast<float4*>(prob + i) = make_float4(x[0], x[1], x[2], x[3]);
-                *reinterpret_cast<float4*>(prob + i + 4) = make_float4(x[4], x[5], x[6], x[7]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) if (keep[e]) prob[i + e] = x[e];
-            }
-        };
         PROF_MARK(1);
-        float norm = 0.0f;
-        chain_sum(norm, V, load_from(row), [&](long long i, float (&x)[kPer], bool (&keep)[kPer]) {
+
+        // 2. exponentials (parked in the scratch row) with a float sum per span for the hypotheses, the
+        //    spans' amounts under those, and the index-order sum
+        for (int j = warp; j < sg.count; j += kWarps) {
+            float mass = 0.f;
+            for_span(row, V, vec_ok, sg, j, [&](const float (&x)[4], const bool (&keep)[4], long long i) {
+                float y[4];
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                const float d = __fsub_rn(x[e], mx);
-                x[e] = keep[e] ? fsx::expf_libm(T == 1.0f ? d : __fmul_rn(d, inv_T), reinterpret_cast<const uint64_t*>(sh.exp_tab)) : 0.f;
-            }
-            store8(i, x, keep);
-        }, 0.f, false, sh);
+                for (int e = 0; e < 4; ++e) {
+                    const float d = __fsub_rn(x[e], mx);
+                    y[e] = keep[e] ? fsx::expf_libm(T == 1.0f ? d : __fmul_rn(d, inv_T), reinterpret_cast<const uint64_t*>(sh.exp_tab)) : 0.f;
+                    mass += y[e];
+                }
+                if (keep[3]) *reinterpret_cast<float4*>(prob + i) = make_float4(y[0], y[1], y[2], y[3]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < 3; ++e) if (keep[e]) prob[i + e] = y[e];
+                }
+            });
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mass += __shfl_xor_sync(0xffffffffu, mass, o);
+            if (lane == 0) sh.R[j] = mass;
+        }
         __syncthreads();
+        hypothesise_spans(sh, sg.count, 1.0f);
+        // every lane re-reads the elements it wrote itself
+        auto span_amounts = [&](float min_keep, long long* last, unsigned long long* count) {
+            for (int j = warp; j < sg.count; j += kWarps) {
+                const float scale = fsx::amount_scale(sh.E[j]);
+                uint32_t amount = 0;
+                bool tie = false;
+                for_span(prob, V, true, sg, j, [&](const float (&x)[4], const bool (&keep)[4], long long i) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (!(keep[e] && x[e] >= min_keep)) continue;
+                        bool t;
+                        amount += fsx::plain_amount(x[e], scale, &t);   // below 2^24 each unless deferred: a lane's 64 or so cannot overflow
+                        tie |= t;
+                        if (last) { *last = i + e; ++*count; }
+                    }
+                });
+                const unsigned long long whole = (unsigned long long)__reduce_add_sync(0xffffffffu, amount >> 16) * 65536ull + __reduce_add_sync(0xffffffffu, amount & 0xffffu);
+                const bool any_tie = __any_sync(0xffffffffu, tie) || scale == 0.0f;
+                if (lane == 0) {
+                    sh.A[j] = whole >= fsx::kOne24 ? fsx::kOne24 : (uint32_t)whole;
+                    if (any_tie) atomicOr(&sh.tie_bits[j >> 5], 1u << (j & 31));
+                }
+            }
+        };
+        span_amounts(0.0f, nullptr, nullptr);
+        float norm = 0.0f;
+        walk_spans(sh, prob, V, true, sg, 0.0f, norm, 0.f, false);
         PROF_MARK(2);
 
         // 3. probabilities; the largest one is that of the maximum logit
         const float pmax = __fdiv_rn(1.0f, norm);
+        const float inv_norm = pmax;   // RN(1 / norm), the shared reciprocal of the row's divisions
         const bool min_p_active = p.min_p > 0.0f;
         const float min_thr = min_p_active ? __fmul_rn((float)(double)p.min_p, pmax) : 0.0f;
         const bool top_p_active = p.top_p != 1.0f;
         RowCtx ctx{prob, V, min_thr, true};
         float total = 0.0f;
         long long kept_count = 0, last_kept = -1;
-        if (!top_p_active) {
-            // index-order total of the kept probabilities
-            long long my_last = -1;
-            unsigned long long my_cnt = 0;
-            chain_sum(total, V, load_from(prob), [&](long long i, float (&x)[kPer], bool (&keep)[kPer]) {
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) x[e] = keep[e] ? __fdiv_rn(x[e], norm) : 0.f;
-                store8(i, x, keep);
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    keep[e] = keep[e] && x[e] >= min_thr;
-                    if (keep[e]) { my_last = i + e; ++my_cnt; }
-                }
-            }, 0.f, false, sh);
-            kept_count = (long long)block_sum_u64(my_cnt, sh);
-            const int m = block_min_int(my_last < 0 ? 0x7fffffff : -(int)my_last, sh);   // minimum of the negated = the highest index
-            last_kept = m == 0x7fffffff ? -1 : -(long long)m;
-        } else {
-            // division, and the counts / approximate masses of the first level's bins in the same pass
-            const uint32_t F_top = __float_as_uint(pmax) + 1u;
-            if (tid == 0) sh.level = fsx::Level{F_top, fsx::kTopSh};
+        const uint32_t F_level = __float_as_uint(pmax) + 1u;
+        if (top_p_active) {
+            __syncthreads();
+            if (tid == 0) sh.level = fsx::Level{F_level, fsx::kTopSh};
             for (int j = tid; j < fsx::kBins; j += kThreads) { sh.A[j] = 0; sh.C[j] = 0; sh.R[j] = 0.f; sh.E[j] = 0; sh.flag[j] = 0; }
             if (tid == 0) sh.list_n = 0;
             __syncthreads();
-            const fsx::Level L = sh.level;
+        }
+        {
+            // division; with top-p also the counts / approximate masses of the first level's bins
+            const fsx::Level L = fsx::Level{F_level, fsx::kTopSh};
             unsigned long long rest = 0;
-            const auto ld = load_from(prob);
-            for (long long base = (long long)kPer * tid; base < V; base += kTile) {
-                float x[kPer];
-                bool keep[kPer];
-                ld(base, x, keep);
+            for (int j = warp; j < sg.count; j += kWarps) {
+                for_span(prob, V, true, sg, j, [&](const float (&x)[4], const bool (&keep)[4], long long i) {
+                    float y[4];
 #pragma unroll
-                for (int e = 0; e < kPer; ++e) x[e] = keep[e] ? __fdiv_rn(x[e], norm) : 0.f;
-                store8(base, x, keep);
+                    for (int e = 0; e < 4; ++e) y[e] = keep[e] ? fsx::div_shared(x[e], norm, inv_norm) : 0.f;
+                    if (keep[3]) *reinterpret_cast<float4*>(prob + i) = make_float4(y[0], y[1], y[2], y[3]);
+                    else {
 #pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    if (!keep[e] || !(x[e] >= min_thr)) continue;
-                    const uint32_t key = __float_as_uint(x[e]);
-                    if (key >= L.F) continue;
-                    const uint32_t j = fsx::bin_of(L, key);
-                    if (j >= (uint32_t)fsx::kBins) { ++rest; continue; }
-                    atomicAdd(&sh.C[j], 1u);
-                    atomicAdd(&sh.R[j], x[e]);
-                }
+                        for (int e = 0; e < 3; ++e) if (keep[e]) prob[i + e] = y[e];
+                    }
+                    if (!top_p_active) return;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (!keep[e] || !(y[e] >= min_thr)) continue;
+                        const uint32_t key = __float_as_uint(y[e]);
+                        if (key >= L.F) continue;
+                        const uint32_t b = fsx::bin_of(L, key);
+                        if (b >= (uint32_t)fsx::kBins) { ++rest; continue; }
+                        atomicAdd(&sh.C[b], 1u);
+                        atomicAdd(&sh.R[b], y[e]);
+                    }
+                });
             }
-            rest = block_sum_u64(rest, sh);
-            if (tid == 0) sh.rest_cnt = rest > 0xffffffffull ? 0xffffffffu : (uint32_t)rest;
+            if (top_p_active) {
+                rest = block_sum_u64(rest, sh);
+                if (tid == 0) sh.rest_cnt = rest > 0xffffffffull ? 0xffffffffu : (uint32_t)rest;
+            }
+        }
+        if (!top_p_active) {
+            // index-order total of the kept probabilities: the spans' masses are those of the exponentials over the sum
+            // (min-p drops mass: a guess that no longer holds only costs a scan of the span)
+            __syncthreads();
+            hypothesise_spans(sh, sg.count, inv_norm);
+            long long my_last = -1;
+            unsigned long long my_cnt = 0;
+            span_amounts(min_thr, &my_last, &my_cnt);
+            kept_count = (long long)block_sum_u64(my_cnt, sh);
+            const int m = block_min_int(my_last < 0 ? 0x7fffffff : -(int)my_last, sh);   // minimum of the negated = the highest index
+            last_kept = m == 0x7fffffff ? -1 : -(long long)m;
+            walk_spans(sh, prob, V, true, sg, min_thr, total, 0.f, false);
         }
         __syncthreads();
         PROF_MARK(3);
 
-        long long pick = -1;
-        float pick_p = 0.f;
-        bool uniform_fallback = false;
-        if (!top_p_active) {
-            if (!(total > 0.0f && isfinite(total))) {
-                uniform_fallback = true;
-            } else {
-                const float rr = __fmul_rn(total, p.rand_u);
-                float run = 0.0f;
-                pick = chain_sum(run, V, load_from(prob), [&](long long, float (&x)[kPer], bool (&keep)[kPer]) {
-#pragma unroll
-                    for (int e = 0; e < kPer; ++e) keep[e] = keep[e] && x[e] >= min_thr;
-                }, rr, true, sh);
-                if (pick < 0) pick = last_kept;   // rounding left r at or beyond the total: the last kept element
-            }
-            if (pick >= 0) pick_p = prob[pick];
-        } else {
-            // 4. the sorted walk: the kept set, its total, then the draw over the same running sums
-            const uint32_t F_top = __float_as_uint(pmax) + 1u;
-            bool have_level = true;   // the division pass counted the first level's bins
+        // 4. the kept set and its total (top-p: the sorted walk), then the draws over the same running sums
+        const uint32_t F_top = F_level;
+        bool have_level = true;   // top-p: the division pass counted the first level's bins
+        uint32_t n_keep = 0;
+        if (top_p_active) {
             sorted_run(sh, ctx, F_top, p.top_p, 0u, (double)p.rand_u * (double)p.top_p, have_level);
-            PROF_MARK(4);
-            const uint32_t n_keep = sh.walk.cnt;
+            n_keep = sh.walk.cnt;
             total = sh.walk.s;
             kept_count = n_keep;
             __syncthreads();
-            if (!(total > 0.0f && isfinite(total)) || n_keep == 0) {
-                uniform_fallback = true;
-            } else {
-                const float rr = __fmul_rn(total, p.rand_u);
-                sorted_run(sh, ctx, F_top, rr, n_keep, 0.0, have_level);
-                if (sh.walk.status == fsx::kWalkFound) {
-                    pick = sh.walk.hit_idx;
-                    pick_p = __uint_as_float(sh.walk.hit_key);
-                } else {   // cannot happen: the element limit ends the second run
-                    if (tid == 0) atomicOr(a.status, 16u);
-                    pick = 0; pick_p = prob[0];
+        }
+        PROF_MARK(4);
+        const bool uniform_fallback = !(total > 0.0f && isfinite(total)) || (top_p_active && n_keep == 0);
+        const long long x0 = a.extra_offsets ? a.extra_offsets[r] : 0, x1 = a.extra_offsets ? a.extra_offsets[r + 1] : 0;
+        for (long long k = -1; k < x1 - x0; ++k) {   // the row's own draw, then the further ones (sampler.cpp:1065)
+            const float u = k < 0 ? p.rand_u : a.extra_rand_u[x0 + k];
+            long long pick = -1;
+            float pick_p = 0.f;
+            if (!uniform_fallback) {
+                const float rr = __fmul_rn(total, u);
+                if (!top_p_active) {
+                    float run = 0.0f;
+                    pick = walk_spans(sh, prob, V, true, sg, min_thr, run, rr, true);   // the same sums again, up to the draw
+                    if (pick < 0) pick = last_kept;   // rounding left r at or beyond the total: the last kept element
+                    if (pick >= 0) pick_p = prob[pick];
+                } else {
+                    sorted_run(sh, ctx, F_top, rr, n_keep, 0.0, have_level);
+                    if (sh.walk.status == fsx::kWalkFound) {
+                        pick = sh.walk.hit_idx;
+                        pick_p = __uint_as_float(sh.walk.hit_key);
+                    } else {   // cannot happen: the element limit ends the run
+                        if (tid == 0) atomicOr(a.status, 16u);
+                        pick = 0; pick_p = prob[0];
+                    }
+                    __syncthreads();
                 }
             }
-            __syncthreads();
+            if (tid == 0) {
+                float lp;
+                if (uniform_fallback) {
+                    // non-finite or empty mass: the reference draws an index uniformly (sampler.cpp:1047-1059)
+                    const long long n = kept_count > 0 ? kept_count : V;
+                    long long q = (long long)(u * (float)n);
+                    if (q > n - 1) q = n - 1;
+                    pick = q < V ? q : V - 1;
+                    lp = logf(1.0f / (float)n);
+                } else {
+                    lp = logf(pick_p) - logf(total);
+                    if (raw_lp) {
+                        float raw = row[pick];
+                        const long long h0 = a.hist_offsets ? a.hist_offsets[r] : 0, h1 = a.hist_offsets ? a.hist_offsets[r + 1] : 0;
+                        if (a.hist_raw)
+                            for (long long i = h0; i < h1; ++i)
+                                if (a.hist_ids[i] == pick) { raw = a.hist_raw[i]; break; }
+                        lp = raw_lse != raw_lse ? CUDART_NAN_F : raw - raw_lse;
+                    }
+                }
+                if (k < 0) { a.out_token[r] = pick; a.out_log_prob[r] = lp; }
+                else { a.extra_out_token[x0 + k] = pick; a.extra_out_log_prob[x0 + k] = lp; }
+            }
         }
         PROF_MARK(5);
 #ifdef SAMPLER_EXACT_PROF
-        if (tid == 0 && blockIdx.x == 0)
-            printf("exact row %d: max %lld  exp+norm %lld  div(+total|+counts) %lld  run1|draw %lld  run2 %lld  (cycles) passes %d\n", r, prof_t[1] - prof_t[0],
-                   prof_t[2] - prof_t[1], prof_t[3] - prof_t[2], (top_p_active ? prof_t[4] : prof_t[5]) - prof_t[3], top_p_active ? prof_t[5] - prof_t[4] : 0LL, sh.prof_passes);
-#endif
         if (tid == 0) {
-            float lp;
-            if (uniform_fallback) {
-                // non-finite or empty mass: the reference draws an index uniformly (sampler.cpp:1047-1059)
-                const long long n = kept_count > 0 ? kept_count : V;
-                long long k = (long long)(p.rand_u * (float)n);
-                if (k > n - 1) k = n - 1;
-                pick = k < V ? k : V - 1;
-                lp = logf(1.0f / (float)n);
-            } else {
-                lp = logf(pick_p) - logf(total);
-                if (raw_lp) {
-                    float raw = row[pick];
-                    const long long h0 = a.hist_offsets ? a.hist_offsets[r] : 0, h1 = a.hist_offsets ? a.hist_offsets[r + 1] : 0;
-                    if (a.hist_raw)
-                        for (long long i = h0; i < h1; ++i)
-                            if (a.hist_ids[i] == pick) { raw = a.hist_raw[i]; break; }
-                    lp = raw_lse != raw_lse ? CUDART_NAN_F : raw - raw_lse;
-                }
-            }
-            a.out_token[r] = pick;
-            a.out_log_prob[r] = lp;
+            unsigned long long g1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+            const unsigned long long dur = (g1 - prof_g0) / 1000;
+            if (blockIdx.x % 64 == 0 || dur > 450)
+                printf("block %d row %d start %llu us dur %llu us: max %lld  exp+norm %lld  div(+total|+counts) %lld  keep %lld  draws %lld  (cycles) passes %d\n", blockIdx.x, r,
+                       (prof_g0 / 1000) % 100000, dur, prof_t[1] - prof_t[0], prof_t[2] - prof_t[1], prof_t[3] - prof_t[2], prof_t[4] - prof_t[3], prof_t[5] - prof_t[4],
+                       sh.prof_passes);
         }
+#endif
         __syncthreads();
     }
 }

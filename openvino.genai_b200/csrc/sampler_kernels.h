@@ -23,6 +23,15 @@ struct StepArgs {
     uint32_t* status;  // bit 0: history id out of range, bit 1: logits_row out of range, bit 2: raw log-prob without scratch,
                        // bit 3: top_k above the heap capacity (and below the vocabulary), bit 4: the sorted walk did not end
     float* hist_raw;   // raw logits of the history entries (rows that report raw log-probabilities), may be null
+    // further draws of a row (all null: none): CSR offsets, their uniform numbers, their outputs
+    const int64_t* extra_offsets;
+    const float* extra_rand_u;
+    int64_t* extra_out_token;
+    float* extra_out_log_prob;
+    // grammar bitmasks (both null: none)
+    const int32_t* token_bitmasks;
+    const int32_t* bitmask_index;
+    long long bitmask_words;
 };
 
 cudaError_t launch_sampler(const StepArgs& a, cudaStream_t stream);

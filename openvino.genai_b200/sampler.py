@@ -30,6 +30,9 @@ class SamplerStep:
 
     __del__ = close
 
+    def launch_count(self) -> int:
+        return int(self.lib.sampler_b200_launch_count(self._h)) if self._h else 0
+
     def stage(self, rows: np.ndarray, hist: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray]] = None):
         """Copies packed row parameters (dtype _sampler_abi.ROW_DTYPE) and the CSR history to the device."""
         dev = torch.device("cuda", self.device)
@@ -39,9 +42,10 @@ class SamplerStep:
         return {"n": n, "rows": t(rows), "hist": tuple(t(x) for x in hist) if hist is not None else None, "hist_raw": raw,
                 "tokens": torch.full((n,), -1, dtype=torch.int64, device=dev), "log_probs": torch.zeros(n, dtype=torch.float32, device=dev)}
 
-    def step(self, logits: torch.Tensor, staged: dict, stream: int = 0):
+    def step(self, logits: torch.Tensor, staged: dict, stream: int = 0, out_tokens: Optional[torch.Tensor] = None):
         """One step over device logits [rows, vocab] f32 (mutated in place); asynchronous on `stream`
-        (a cudaStream_t handle; 0 = the legacy default stream).  Returns the staged output tensors."""
+        (a cudaStream_t handle; 0 = the legacy default stream).  Returns the output tensors: the staged
+        ones, or `out_tokens` (int64, at least `rows` long - e.g. this rank's row of the exchange buffer)."""
         a = A.sampler_step_args()
         a.struct_size = C.sizeof(A.sampler_step_args)
         a.logits = logits.data_ptr()
@@ -51,10 +55,11 @@ class SamplerStep:
         if staged["hist"] is not None:
             a.hist_offsets, a.hist_ids, a.hist_meta = (x.data_ptr() for x in staged["hist"])
             a.hist_raw = staged["hist_raw"].data_ptr()   # scratch for rows that report raw log-probabilities
-        a.out_token = staged["tokens"].data_ptr()
+        tokens = staged["tokens"] if out_tokens is None else out_tokens
+        a.out_token = tokens.data_ptr()
         a.out_log_prob = staged["log_probs"].data_ptr()
         a.stream = stream if stream else 1   # 1 = cudaStreamLegacy: a null handle would select the handle's own stream
         rc = self.lib.sampler_b200_step(self._h, C.byref(a))
         if rc != 0:
             raise GenaiB200Error(f"sampler_b200_step: {self.lib.sampler_b200_last_error().decode()}")
-        return staged["tokens"], staged["log_probs"]
+        return tokens, staged["log_probs"]

@@ -21,6 +21,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdint>
+#include <cstddef>
 #include <cstring>
 #include <limits>
 #include <random>
@@ -219,6 +220,12 @@ int process_row(const sampler_step_args* a, int r, std::vector<float>& scratch) 
     // stop-token mask while generated_len < min_new_tokens (logit_transformers.hpp:452-463)
     for (int64_t i = h0; i < h1; ++i)
         if (a->hist_meta[i] & SAMPLER_HIST_STOP_MASK) row[a->hist_ids[i]] = -std::numeric_limits<float>::infinity();
+    // grammar bitmask (structured_output/xgrammar_backend.cpp:187-207): a cleared bit makes the logit -inf
+    if (a->struct_size == sizeof(sampler_step_args) && a->token_bitmasks && a->bitmask_index && a->bitmask_index[r] >= 0) {
+        const int32_t* mask = a->token_bitmasks + (int64_t)a->bitmask_index[r] * a->bitmask_words;
+        for (size_t i = 0; i < V; ++i)
+            if (!((uint32_t)mask[i / 32] >> (i % 32) & 1u)) row[i] = -std::numeric_limits<float>::infinity();
+    }
     // repetition: unique prompt ids, then generated ids not in the prompt (403-427)
     if (p.repetition_penalty != 1.0f) {
         const double pen = p.repetition_penalty;
@@ -268,6 +275,16 @@ int process_row(const sampler_step_args* a, int r, std::vector<float>& scratch) 
         if (min_p_active) min_p_filter(st, p.min_p);
         if (p.top_p != 1.0f) top_p_filter(st, p.top_p);
         out = multinomial(st, p.rand_u, &uniform_fallback);
+        // num_return_sequences > 1: further draws from the same distribution, one uniform number each (sampler.cpp:1065-1089)
+        const bool extras = a->struct_size == sizeof(sampler_step_args) && a->extra_offsets;
+        if (extras)
+            for (int64_t k = a->extra_offsets[r]; k < a->extra_offsets[r + 1]; ++k) {
+                bool uf = false;
+                Tok more = multinomial(st, a->extra_rand_u[k], &uf);
+                if (raw_lp && !uf) more.p = raw[(size_t)more.idx] - raw_lse;
+                a->extra_out_token[k] = more.idx;
+                a->extra_out_log_prob[k] = more.p;
+            }
     }
     if (raw_lp && !uniform_fallback) out.p = raw[(size_t)out.idx] - raw_lse;
     a->out_token[r] = out.idx;
@@ -282,7 +299,7 @@ extern "C" {
 // One task per row over `threads` workers, as the reference's ThreadPool does per request
 // (sampler.cpp:1751-1754).
 int sampler_oracle_step(const sampler_step_args* a, int threads) {
-    if (!a || a->struct_size != sizeof(sampler_step_args)) return SAMPLER_ERR_INVALID_ARG;
+    if (!a || (a->struct_size != sizeof(sampler_step_args) && a->struct_size != SAMPLER_STEP_ARGS_SIZE_V1)) return SAMPLER_ERR_INVALID_ARG;
     std::atomic<int> next{0};
     std::atomic<int> status{SAMPLER_OK};
     auto work = [&] {

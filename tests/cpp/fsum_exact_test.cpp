@@ -113,6 +113,30 @@ static void test_scan(std::mt19937_64& rng) {
     }
 }
 
+// plain_amount against step_of, div_shared against the division
+static void test_amount_and_division(std::mt19937_64& rng) {
+    for (int i = 0; i < 4000000; ++i) {
+        const uint32_t E = 24 + (uint32_t)(rng() % 200);
+        const int ex = (int)E - (int)(rng() % 40) + 3;
+        if (ex < 1 || ex > 254) continue;
+        uint32_t m = (uint32_t)(rng() & 0x7fffffu);
+        if (i % 3 == 0) m &= ~((1u << (rng() % 23)) - 1u);   // many ties and exact multiples
+        const float x = fsx::bits_float(((uint32_t)ex << 23) | m);
+        bool tie, defer;
+        const fsx::Step st = fsx::step_of(x, E, &tie);
+        const uint32_t a = fsx::plain_amount(x, fsx::amount_scale(E), &defer);
+        if (st.a >= fsx::kOne24) { CHECK(defer, "amount of %a under E %u: not deferred", x, E); continue; }
+        CHECK(defer == tie, "amount of %a under E %u: tie %d defer %d", x, E, (int)tie, (int)defer);
+        if (!tie) CHECK(a == st.a, "amount of %a under E %u: %u vs %u", x, E, a, st.a);
+    }
+    for (int i = 0; i < 4000000; ++i) {
+        const float b = fsx::bits_float(0x3e000000u + (uint32_t)(rng() % (12u << 23)));
+        const float a = fsx::bits_float((uint32_t)(rng() % 0x40000000u));
+        const float got = fsx::div_shared(a, b, 1.0f / b), want = a / b;
+        CHECK(std::memcmp(&got, &want, 4) == 0, "%a / %a: %a vs %a", a, b, got, want);
+    }
+}
+
 // add_repeated against a loop
 static void test_repeated(std::mt19937_64& rng) {
     std::uniform_real_distribution<double> U(0.0, 1.0);
@@ -210,6 +234,7 @@ int main(int argc, char** argv) {
     test_expf(stride);
     test_scan(rng);
     test_repeated(rng);
+    test_amount_and_division(rng);
     test_walk(rng, rows);
     if (g_fail) { std::printf("%d check(s) failed\n", g_fail); return 1; }
     std::printf("fsum_exact: all checks passed\n");

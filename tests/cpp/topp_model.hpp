@@ -119,12 +119,12 @@ struct Model {
             if (f & fsx::kBinCollect) list.push_back(fsx::make_entry(key, (uint32_t)i));
             else if (f & fsx::kBinDirty) {
                 bool tie;
-                const fsx::Step st = fsx::step_of(p[i], E[j], &tie);
+                const uint32_t amount = fsx::plain_amount(p[i], fsx::amount_scale(E[j]), &tie);
                 if (tie) flag[j] |= fsx::kBinTie;
                 else {
                     const uint32_t old = A[j];
-                    A[j] = old + st.a;
-                    if (old + st.a >= 0x80000000u) flag[j] |= fsx::kBinTie;   // too much for one binade anyway: never taken as a whole
+                    A[j] = old + amount;
+                    if (old + amount >= 0x80000000u) flag[j] |= fsx::kBinTie;   // too much for one binade anyway: never taken as a whole
                 }
             }
         }

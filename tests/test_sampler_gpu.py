@@ -306,3 +306,88 @@ def test_out_of_range_history_id_is_reported(gpu):
     assert rc == A.SAMPLER_ERR_BAD_TOKEN_ID
     rc, tok, *_ = gpu.step_host(x, H.make_rows(1, do_sample=0))   # the handle is still usable
     assert rc == 0 and tok[0] == 0
+
+
+@pytest.mark.parametrize("mode", ["top_k", "top_k_deferred", "top_p_full", "plain_full"])
+def test_several_draws_from_one_distribution(gpu, mode):
+    """num_return_sequences = n: the first sampled token's distribution is drawn from n times with
+    consecutive numbers of the request's engine; every draw must equal the oracle's."""
+    rng = np.random.default_rng(71)
+    n, vocab = 6, 40000
+    x = (rng.standard_normal((n, vocab)) * 2).astype(np.float32)   # no spikes: several tokens share the mass
+    kw = {"top_k": dict(top_k=40, temperature=0.8, top_p=0.9), "top_k_deferred": dict(top_k=40, temperature=0.8),
+          "top_p_full": dict(top_p=0.9, temperature=1.1), "plain_full": dict(temperature=0.9)}[mode]
+    rows = H.make_rows(n, seeds=np.arange(n) + 900, **kw)
+    counts = np.array([3, 0, 1, 7, 0, 2])
+    offs = np.zeros(n + 1, np.int64)
+    offs[1:] = np.cumsum(counts)
+    us = rng.random(int(offs[-1]), dtype=np.float32)
+
+    def run(step):
+        lg = x.copy()
+        tok = np.full(n, -7, np.int64); lp = np.zeros(n, np.float32)
+        xtok = np.full(len(us), -7, np.int64); xlp = np.zeros(len(us), np.float32)
+        a = H.step_args(lg, rows, None, tok, lp)
+        a.extra_offsets, a.extra_rand_u = offs.ctypes.data, us.ctypes.data
+        a.extra_out_token, a.extra_out_log_prob = xtok.ctypes.data, xlp.ctypes.data
+        assert step(a) == 0
+        return tok, lp, xtok, xlp
+
+    tok_o, lp_o, xtok_o, xlp_o = run(lambda a: sampler_oracle.step(a, 0))
+    tok_g, lp_g, xtok_g, xlp_g = run(lambda a: gpu.lib.sampler_b200_step_host(gpu.h, C.byref(a), 1))
+    assert np.array_equal(tok_o, tok_g) and np.array_equal(xtok_o, xtok_g), (xtok_o, xtok_g)
+    assert np.allclose(lp_o, lp_g, atol=2e-6, rtol=1e-6) and np.allclose(xlp_o, xlp_g, atol=2e-6, rtol=1e-6)
+    # the first draw does not depend on the further ones
+    tok_1 = _both(gpu, x, rows)[3]
+    assert np.array_equal(tok_1, tok_g)
+    assert len(set(xtok_g[offs[3]:offs[4]].tolist())) > 1, "seven draws of one row are not all the same token"
+
+
+def test_step_args_without_the_extra_draw_members_are_still_accepted(gpu):
+    rng = np.random.default_rng(72)
+    x = H.synthetic_logits(rng, 3, 5000)
+    rows = H.make_rows(3, top_k=20, temperature=0.8)
+    lg = x.copy()
+    tok = np.full(3, -7, np.int64); lp = np.zeros(3, np.float32)
+    a = H.step_args(lg, rows, None, tok, lp)
+    a.struct_size = A.sampler_step_args.extra_offsets.offset     # the layout that ends at hist_raw
+    a.extra_offsets = 0xdead0000                                   # must not be read
+    assert gpu.lib.sampler_b200_step_host(gpu.h, C.byref(a), 0) == 0
+    assert np.array_equal(tok, _both(gpu, x, rows)[3])
+
+
+@pytest.mark.parametrize("mode", ["greedy", "top_k", "top_p_full"])
+def test_grammar_bitmask_is_applied_before_the_penalties(gpu, mode):
+    """A request's next-token bitmask: disallowed logits become -inf, the logits left behind and the tokens
+    equal the oracle's; rows without a mask (index -1) are untouched by it."""
+    rng = np.random.default_rng(81)
+    n, vocab = 8, 40003    # the last mask word is partial
+    x = H.synthetic_logits(rng, n, vocab)
+    hist = H.make_history(rng, n, vocab, generated_len=200, prompt_len=40)
+    kw = {"greedy": dict(do_sample=0), "top_k": dict(top_k=30, temperature=0.9, top_p=0.95), "top_p_full": dict(top_p=0.9)}[mode]
+    rows = H.make_rows(n, repetition_penalty=1.2, presence_penalty=0.1, seeds=np.arange(n) + 300, **kw)
+    words = (vocab + 31) // 32
+    masks = rng.integers(0, 2 ** 32, size=(3, words), dtype=np.uint64).astype(np.uint32).view(np.int32)
+    masks[1] = 0
+    masks[1, 7] = 1 << 5            # a single allowed token: 7 * 32 + 5
+    masks[2] &= rng.integers(0, 2 ** 32, size=words, dtype=np.uint64).astype(np.uint32).view(np.int32)
+    index = np.array([0, 1, -1, 2, 0, -1, 1, 2], np.int32)
+
+    def run(step):
+        lg = x.copy()
+        tok = np.full(n, -7, np.int64); lp = np.zeros(n, np.float32)
+        a = H.step_args(lg, rows, hist, tok, lp)
+        a.token_bitmasks, a.bitmask_index, a.bitmask_words = masks.ctypes.data, index.ctypes.data, words
+        assert step(a) == 0
+        return tok, lp, lg
+
+    tok_o, lp_o, lg_o = run(lambda a: sampler_oracle.step(a, 0))
+    tok_g, lp_g, lg_g = run(lambda a: gpu.lib.sampler_b200_step_host(gpu.h, C.byref(a), 1))
+    assert np.array_equal(tok_o, tok_g), (tok_o, tok_g)
+    assert np.array_equal(lg_o.view(np.uint32), lg_g.view(np.uint32))
+    assert tok_g[1] == 7 * 32 + 5 and tok_g[6] == 7 * 32 + 5
+    for r in range(n):
+        if index[r] >= 0:
+            t = int(tok_g[r])
+            assert (masks[index[r]].view(np.uint32)[t // 32] >> (t % 32)) & 1, f"row {r} picked a token its grammar does not allow"
+    assert np.isinf(lg_g[0]).sum() > vocab // 3 and np.isinf(lg_g[2]).sum() == 0
