@@ -53,6 +53,11 @@ typedef enum pa_dtype {
 #define PA_DEV_BAD_BEGINS 0x2u        /* subsequence_begins / block_indices_begins invalid  */
 #define PA_DEV_BAD_PAST_LEN 0x4u      /* past_lens < 0 or block table too short             */
 #define PA_DEV_BAD_ROTATION 0x8u      /* rotated block id or LUT row out of range           */
+/* Every wait of a kernel on a copy it issued is bounded.  A wait that runs out sets one of the bits below and
+ * the waiting warps leave (tensor memory freed, nothing left in flight); the step's output is then incomplete. */
+#define PA_DEV_WAIT_TIMEOUT_SCORES 0x20000000u  /* score kernel: a staged key record never arrived             */
+#define PA_DEV_WAIT_TIMEOUT_PREFILL 0x40000000u /* tcgen05 prefill kernel: a barrier wait ran out               */
+#define PA_DEV_WAIT_TIMEOUT_DECODE 0x80000000u  /* decode kernel: a staged (block, head) record never arrived   */
 
 /* Static attributes of one attention layer.  Replaces what KVCacheManager reads from the
  * compiled model's key_cache.N / value_cache.N ports
@@ -184,6 +189,23 @@ int pa_b200_rotate_blocks(pa_handle* h, const pa_forward_args* args);
 int pa_b200_copy_blocks(pa_handle* h, void* key_cache, void* value_cache, int32_t num_blocks,
                         const int32_t* src_dst_pairs, int32_t num_pairs, void* stream);
 
+/* KV cache pool that grows in place.
+ *
+ * KVCacheManager::allocate_cache_if_needed grows a layer's cache by creating a larger tensor and copying all
+ * blocks (src/cpp/src/continuous_batching/cache/kv_cache_manager.hpp:159-262): twice the memory while it
+ * copies, and new tensor addresses to re-bind.  This pool reserves the address range of `max_blocks` once and
+ * maps physical memory into it as it grows: key_cache / value_cache never move, written blocks keep their
+ * bytes, nothing is copied, new blocks read as zeros.  One pool per layer (the layout is the one
+ * pa_b200_query_cache_layout reports).  grow() to a size not above the current one does nothing, as in the
+ * reference; beyond max_blocks it fails with PA_ERR_TOO_LARGE; when the device is out of memory it fails
+ * with the reference's message.  Calls are host-synchronous; grow while no kernel writes the new range. */
+typedef struct pa_cache_pool pa_cache_pool;
+const char* pa_b200_cache_pool_last_error(void);
+int pa_b200_cache_pool_create(const pa_model_desc* desc, int device, int64_t max_blocks, int64_t initial_blocks, pa_cache_pool** out);
+int pa_b200_cache_pool_grow(pa_cache_pool* pool, int64_t num_blocks);
+int pa_b200_cache_pool_get(pa_cache_pool* pool, void** key_cache, void** value_cache, int64_t* num_blocks);
+int pa_b200_cache_pool_destroy(pa_cache_pool* pool);
+
 /* Device-side marshalling of the operator's scheduler inputs.
  *
  * ModelRunner::forward builds past_lens / subsequence_begins / block_indices / block_indices_begins on the
@@ -235,6 +257,9 @@ int pa_b200_marshal_inputs(pa_handle* h, const pa_marshal_args* args);
  * Same results as pa_b200_forward for a step in which every sequence has exactly one new token,
  * without score output and without rotation inputs (PA_ERR_UNSUPPORTED otherwise).  All pointers
  * are device memory; the launches go to args->stream (NULL = the default stream).
+ *  - The host can only check num_tokens == num_sequences; the per-sequence token counts live in
+ *    device memory.  A sequence whose subsequence_begins give it a count other than one is skipped
+ *    on the device: nothing is written to the cache for it and its output rows stay untouched.
  *  - A step whose scratch need exceeds the fixed array is rejected with PA_ERR_TOO_LARGE (the
  *    message gives both sizes).  With G = Hq / Hkv the need is a few KB of counters plus
  *    (num_sequences * Hkv * ceil(G/16) + 16 * SM count) * min(G,16) * (head_size + 2) * 4 bytes:

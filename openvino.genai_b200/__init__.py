@@ -42,6 +42,8 @@ def load_library(build_if_missing: bool = False) -> ctypes.CDLL:
     _abi.bind(lib, _sampler_abi.SAMPLER_SYMBOLS)
     from . import _exchange_abi
     _abi.bind(lib, _exchange_abi.EXCHANGE_SYMBOLS)
+    from . import _eviction_abi
+    _abi.bind(lib, _eviction_abi.EVICTION_SYMBOLS)
     _lib = lib
     return lib
 

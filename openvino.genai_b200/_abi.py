@@ -20,6 +20,9 @@ PA_DEV_BAD_BLOCK_INDEX = 0x1
 PA_DEV_BAD_BEGINS = 0x2
 PA_DEV_BAD_PAST_LEN = 0x4
 PA_DEV_BAD_ROTATION = 0x8
+PA_DEV_WAIT_TIMEOUT_SCORES = 0x20000000
+PA_DEV_WAIT_TIMEOUT_PREFILL = 0x40000000
+PA_DEV_WAIT_TIMEOUT_DECODE = 0x80000000
 
 
 class pa_model_desc(C.Structure):
@@ -120,6 +123,11 @@ PA_SYMBOLS = {
     "pa_b200_write_kv": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
     "pa_b200_rotate_blocks": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
     "pa_b200_decode_step_static": (C.c_int, [C.POINTER(pa_model_desc), C.POINTER(pa_forward_args), C.c_int]),
+    "pa_b200_cache_pool_last_error": (C.c_char_p, []),
+    "pa_b200_cache_pool_create": (C.c_int, [C.POINTER(pa_model_desc), C.c_int, C.c_int64, C.c_int64, C.POINTER(C.c_void_p)]),
+    "pa_b200_cache_pool_grow": (C.c_int, [C.c_void_p, C.c_int64]),
+    "pa_b200_cache_pool_get": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64)]),
+    "pa_b200_cache_pool_destroy": (C.c_int, [C.c_void_p]),
     "pa_b200_marshal_inputs": (C.c_int, [C.c_void_p, C.POINTER(pa_marshal_args)]),
     "pa_b200_copy_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
 }

@@ -35,7 +35,7 @@ struct GenerationConfig {
     bool do_sample = false;
     float temperature = 1.0f;
     float top_p = 1.0f;
-    size_t top_k = std::numeric_limits<size_t>::max();
+    size_t top_k = std::numeric_limits<size_t>::max();   // 0 and SIZE_MAX both mean "off" (logit_processor.hpp:85-86)
     float min_p = 0.0f;
     size_t rng_seed = 0;
 
@@ -65,13 +65,12 @@ struct GenerationConfig {
         if (frequency_penalty < -2.0f || frequency_penalty > 2.0f) fail("'frequency_penalty' must be in [-2.0, 2.0]");
         if (presence_penalty < -2.0f || presence_penalty > 2.0f) fail("'presence_penalty' must be in [-2.0, 2.0]");
         if (do_sample) {
-            if (top_k == 0) fail("When 'do_sample' is true, top_k must be a strictly positive integer");
             if (!(top_p > 0.0f && top_p <= 1.0f)) fail("When 'do_sample' is true, top_p must be in (0.0, 1.0]");
             if (!(temperature > 0.0f)) fail("When 'do_sample' is true, temperature must be a strictly positive float");
             if (!(min_p >= 0.0f && min_p < 1.0f)) fail("When 'do_sample' is true, min_p must be in [0.0, 1.0)");
         }
         if (is_beam_search() || is_tree_search()) fail("beam search and tree search are outside the accelerated Sampler step");
-        if (num_return_sequences != 1) fail("num_return_sequences > 1 is outside the accelerated Sampler step");
+        if (num_return_sequences > 1 && !do_sample) fail("num_return_sequences > 1 needs multinomial sampling (beam search is outside the accelerated Sampler step)");
     }
 };
 

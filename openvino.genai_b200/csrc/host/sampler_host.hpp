@@ -18,8 +18,17 @@
 
 namespace genai_b200 {
 
-// One running sequence as the Sampler sees it (the reference's SequenceGroup with a single
-// Sequence: num_return_sequences == 1 on this path).
+// A sequence a request forked when it drew num_return_sequences tokens from its first distribution
+// (sampler.cpp:1163-1182, 1539-1549): it shares the request's engine, token-count map and penalties.
+struct ForkedSequence {
+    std::vector<int64_t> generated_ids;
+    std::vector<float> generated_log_probs;
+    bool finished = false;
+    int64_t logits_row = 0;   // set by the scheduler for every later step
+};
+
+// One request as the Sampler sees it: the reference's SequenceGroup, whose first Sequence is held
+// inline and whose further sequences (num_return_sequences > 1) appear in `forks` after the first step.
 struct SequenceGroup {
     uint64_t request_id = 0;
     std::vector<int64_t> prompt_ids;
@@ -33,6 +42,15 @@ struct SequenceGroup {
     // which row of the logits tensor (the row of its last scheduled token)
     bool requires_sampling = true;
     int64_t logits_row = 0;
+    std::vector<ForkedSequence> forks;
+    // structured output: the grammar matcher's next-token bitmask for this step, ceil(vocab / 32) int32 words with bit
+    // (t & 31) of word t / 32 set iff token t is allowed (xgrammar_backend.cpp:148-165); null: no grammar, or terminated
+    const int32_t* token_bitmask = nullptr;
+    bool all_finished() const {
+        if (!finished) return false;
+        for (const ForkedSequence& f : forks) if (!f.finished) return false;
+        return true;
+    }
 };
 
 struct SamplerOutput {
@@ -72,9 +90,15 @@ public:
         std::vector<int32_t> hist_ids;
         std::vector<uint32_t> hist_meta;
         std::vector<SequenceGroup*> groups;   // group of each row
+        std::vector<int> sequence;            // -1: the group's first sequence, k: forks[k]
+        std::vector<int64_t> extra_offsets;   // further draws of each row (a request's first sampled token with num_return_sequences > 1)
+        std::vector<float> extra_rand_u;
+        std::vector<int32_t> bitmask_index;   // mask of each row, -1: none
+        std::vector<const int32_t*> bitmasks; // distinct masks of the step
     };
     PackedStep pack(const std::vector<SequenceGroup*>& sequence_groups);
-    SamplerOutput commit(const PackedStep& step, const std::vector<int64_t>& tokens, const std::vector<float>& log_probs);
+    SamplerOutput commit(const PackedStep& step, const std::vector<int64_t>& tokens, const std::vector<float>& log_probs,
+                         const std::vector<int64_t>& extra_tokens = {}, const std::vector<float>& extra_log_probs = {});
     // the reference's LogitProcessor::decrease_generated_token_occurance (logit_processor.hpp:148-151):
     // the entry stays in the map at zero and still receives the repetition penalty
     void decrease_generated_token_occurance(uint64_t request_id, int64_t token_id);
@@ -88,8 +112,8 @@ private:
         explicit RequestSamplerContext(size_t seed) : rng_engine(seed) {}
     };
     RequestSamplerContext& context_of(SequenceGroup& group);
-    void register_new_token(SequenceGroup& group, RequestSamplerContext& ctx, int64_t token, float log_prob);
-    void try_finish_generation(SequenceGroup& group, SamplerOutput& out);
+    void register_new_token(RequestSamplerContext& ctx, std::vector<int64_t>& ids, std::vector<float>& log_probs, int64_t token, float log_prob);
+    bool should_stop(const GenerationConfig& cfg, const std::vector<int64_t>& ids) const;
 
     int m_device;
     sampler_handle* m_handle = nullptr;

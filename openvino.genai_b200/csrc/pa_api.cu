@@ -53,6 +53,7 @@ struct pa_handle {
     size_t stage_host_bytes = 0;
     int64_t launches = 0;
     bool force_generic_prefill = false;        // env PA_B200_GENERIC_PREFILL=1: cross-check path
+    bool test_drop_copy = false;               // env PA_B200_TEST_DROP_FIRST_COPY=1: the decode kernel's bounded wait is made to run out
     bool timing = false;                       // record events around the split-K decode kernel
     std::vector<cudaEvent_t> ev;               // pairs, created on demand
     size_t ev_used = 0;
@@ -210,7 +211,9 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     int rc = ensure_ws(h, p.total);
     if (rc != PA_OK) return rc;
     pa::KernelArgs k = make_kernel_args(h, a, p);
-    k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count);   // the plan step prepares one start record per worker
+    k.decode_tail_div = pa::decode_tail_div();
+    k.test_drop_copy = h->test_drop_copy ? 1 : 0;
+    k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count, &k.decode_first_workers);   // the plan step prepares one start record per worker
     int launches = 0;
     if (a->num_rotated_blocks > 0) { PA_CUDA(pa::launch_rotate(k, stream)); ++launches; }
     PA_CUDA(pa::launch_write_kv(k, stream, /*with_plan=*/true)); ++launches;
@@ -279,6 +282,7 @@ int pa_b200_create(const pa_model_desc* desc, int device, pa_handle** out) {
     h->device = device;
     h->sm_count = prop.multiProcessorCount;
     if (const char* e = std::getenv("PA_B200_GENERIC_PREFILL")) h->force_generic_prefill = std::atoi(e) != 0;
+    if (const char* e = std::getenv("PA_B200_TEST_DROP_FIRST_COPY")) h->test_drop_copy = std::atoi(e) != 0;
     cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc((void**)&h->status, 256);
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);

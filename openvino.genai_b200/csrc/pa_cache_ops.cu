@@ -75,12 +75,11 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         if (B <= kPrefixCap) {
             if (tid == 0) sh_prefix[B] = sh_run;
             __syncthreads();
-            int workers, per_worker;
-            decode_slices(total_tiles, a.decode_all_workers, workers, per_worker);
+            const DecodeSlices sl = decode_slices(total_tiles, a.decode_all_workers, a.decode_first_workers, a.decode_tail_div);
             for (int w = tid; w < a.decode_all_workers; w += 256) {
                 WorkerStart ws{-1, 0, 0, total_tiles, 0, 0, 0, 0};
-                const long long g_tile = (long long)w * per_worker;
-                if (w < workers && g_tile < total_tiles) {
+                const long long g_tile = sl.begin(w);
+                if (w < sl.workers1 + sl.workers2 && g_tile < sl.end(w)) {
                     const int key = (int)(g_tile / HK);
                     int lo = 0, hi = B;   // sh_prefix[lo] <= key < sh_prefix[hi]
                     while (hi - lo > 1) {

@@ -23,6 +23,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 
 #include "pa_common.cuh"
 #include "pa_kernels.h"
@@ -34,12 +35,6 @@ namespace {
 constexpr int kTile = 32;  // context tokens per pipeline stage
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeMaxCtasPerSm = 4;
-#ifndef PA_DECODE_WAVES
-#define PA_DECODE_WAVES 1
-#endif
-// CTAs launched per resident CTA slot: more than one lets the hardware block scheduler hand the
-// later slices to whichever SM finishes first
-constexpr int kDecodeWaves = PA_DECODE_WAVES;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLazyMax = 8.f;  // the running reference may lag the true row maximum by 2^8
@@ -147,10 +142,9 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         ws = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
     }
     const int total_tiles = ws.s != -1 ? ws.total_tiles : a.plan->total_tiles;   // all streams
-    int workers, per_worker;
-    decode_slices(total_tiles, all_workers, workers, per_worker);
-    int g_tile = min(total_tiles, wid * per_worker);               // next global tile to load
-    const int g_end = min(total_tiles, g_tile + per_worker);
+    const DecodeSlices sl = decode_slices(total_tiles, all_workers, a.decode_first_workers, a.decode_tail_div);
+    int g_tile = (int)sl.begin(wid);               // next global tile to load
+    const int g_end = (int)sl.end(wid);
 
     // ---- loader state (warp-uniform registers) -------------------------------------------------------
     int r_s = -1, r_hkp = 0, r_tiles = 0;   // current stream: row, head tile, tiles of the row per head tile
@@ -158,6 +152,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     int r_tb = 0, r_nb = 0, r_seq = 0;       // block table of the row, run counter
     int w_blk0 = 0, tbl = 0;                 // block window: lane j holds block_indices[r_tb + w_blk0 + j]
     bool r_first = false;
+    bool dropped_once = false;
 
     auto load_window = [&](int first_block) {
         w_blk0 = first_block;
@@ -176,7 +171,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         r_tok = tile0 * kTile;
         r_end = min(ctx, (tile0 + ntile) * kTile);
         const int s_begin = p0 * HK + r_hkp * r_tiles;             // global tile range of the stream
-        const int first_w = s_begin / per_worker, last_w = (s_begin + r_tiles - 1) / per_worker;
+        const int first_w = sl.worker_of(s_begin), last_w = sl.worker_of(s_begin + r_tiles - 1);
         const int stream = r_s * HK + r_hkp;
         ++r_seq;
         if (lane == 0) {
@@ -266,9 +261,13 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
 #pragma unroll
                 for (int r = 0; r < Cfg::NREC; ++r) bytes += live[r] ? 2 * Cfg::REC : 0;
                 mbar_expect_tx(&bars[slot], bytes);
+                // Test hook (PA_B200_TEST_DROP_FIRST_COPY): worker 0 arms the barrier of its first tile and issues no copy,
+                // so that the bounded wait below runs out; nothing is in flight for that stage when it does.
+                const bool drop = a.test_drop_copy && wid == 0 && !dropped_once;
+                dropped_once = true;
 #pragma unroll
                 for (int r = 0; r < Cfg::NREC; ++r)
-                    if (live[r]) {
+                    if (live[r] && !drop) {
                         bulk_g2s(st + r * Cfg::REC, kc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, &bars[slot]);
                         bulk_g2s(st + Cfg::HALF_STAGE + r * Cfg::REC, vc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, &bars[slot]);
                     }
@@ -320,8 +319,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         const StageDesc d = descs[slot];
         if (d.flags & kEnd) break;
         if constexpr (U8) {
-            if (!mbar_wait_bounded(&bars[slot], (it / NS) & 1)) {
-                if (lane == 0) atomicOr(a.status, 0x80000000u);
+            if (!mbar_wait_bounded(&bars[slot], (it / NS) & 1, a.test_drop_copy ? (1u << 10) : (1u << 22))) {
+                // the copy never arrived: flag it, let the copies of the other stages land (bounded), and leave
+                if (lane == 0) atomicOr(a.status, PA_DEV_WAIT_TIMEOUT_DECODE);
+#pragma unroll
+                for (int o = 1; o < NS; ++o) {
+                    const int other = (it + o) % NS;
+                    if (!(descs[other].flags & kEnd)) mbar_wait_bounded(&bars[other], ((it + o) / NS) & 1, 1u << 16);
+                }
                 break;
             }
         } else {
@@ -686,15 +691,20 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[3]));
     if (lane == 0 && wid % 61 == 0)
         printf("decode prof wid %d sm-start %llu first-tile +%llu last-tile-ready +%llu end +%llu tiles %d\n", wid, prof_t[0] % 100000000ull,
-               prof_t[1] - prof_t[0], prof_t[2] - prof_t[0], prof_t[3] - prof_t[0], g_end - min(total_tiles, wid * per_worker));
+               prof_t[1] - prof_t[0], prof_t[2] - prof_t[0], prof_t[3] - prof_t[0], g_end - (int)sl.begin(wid));
 #endif
 }
 
-// no more workers than slices could ever exist (upper bound known on the host)
-long long decode_ctas(const KernelArgs& a, int per_sm, int sm_count) {
+// CTAs of the launch: the resident ones, and as many again when a tail wave is wanted; never more workers than
+// slices could exist (upper bound known on the host).  *resident receives the CTAs of the first wave.
+long long decode_ctas(const KernelArgs& a, int per_sm, int sm_count, long long* resident) {
     const long long max_slices = (a.max_tiles + kDecodeMinSlice - 1) / kDecodeMinSlice;
-    long long ctas = (long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count * kDecodeWaves;
-    return std::max(1LL, std::min(ctas, (max_slices + kDecodeWarps - 1) / kDecodeWarps));
+    const long long cap = std::max(1LL, (max_slices + kDecodeWarps - 1) / kDecodeWarps);
+    const long long first = std::min((long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count, cap);
+    long long ctas = first;
+    if (a.decode_tail_div > 0 && first * kDecodeWarps * kDecodeMinSlice * 8 <= a.max_tiles) ctas = std::min(2 * first, cap);
+    if (resident) *resident = first;
+    return std::max(1LL, ctas);
 }
 
 // Resident CTAs per SM of one instantiation on the current device; the shared-memory opt-in and the
@@ -733,7 +743,7 @@ cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
                    : (sc ? decode_kernel<D, BS, CACHE, false, true> : decode_kernel<D, BS, CACHE, false, false>);
     const int per_sm = occupancy_t<D, BS, CACHE>(a);
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
-    const long long ctas = decode_ctas(a, per_sm, sm_count);
+    const long long ctas = decode_ctas(a, per_sm, sm_count, nullptr);
     if (ev0) cudaEventRecord(ev0, stream);
     // Programmatic dependent launch: the launch is queued behind the cache-write kernel without a full
     // stream serialisation; that kernel never triggers early, so the CTAs start when it has finished, and
@@ -768,9 +778,19 @@ cudaError_t launch_decode_c(const KernelArgs& a, cudaStream_t stream, int sm_cou
 
 }  // namespace
 
-int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps * kDecodeWaves; }
+int decode_tail_div() {
+    static const int v = [] {
+        const char* e = std::getenv("PA_B200_DECODE_TAIL");
+        const int n = e ? std::atoi(e) : 0;  // a second wave measured slower than one wave at every setting tried (4, 8, 16)
+        return n < 0 ? 0 : n;
+    }();
+    return v;
+}
 
-int decode_launch_workers(const KernelArgs& a, int sm_count) {
+int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps * 2; }
+
+int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers) {
+    if (first_workers) *first_workers = 0;
     if (a.num_sequences <= 0) return 0;
     int per_sm = 0;
 #define PA_OCC(D_, BS_)                                                                           \
@@ -785,7 +805,10 @@ int decode_launch_workers(const KernelArgs& a, int sm_count) {
     else if (a.g.D == 64 && a.g.bs == 16) { PA_OCC(64, 16) }
 #undef PA_OCC
     if (per_sm < 1) return 0;
-    return (int)decode_ctas(a, per_sm, sm_count) * kDecodeWarps;
+    long long resident = 0;
+    const long long ctas = decode_ctas(a, per_sm, sm_count, &resident);
+    if (first_workers) *first_workers = (int)resident * kDecodeWarps;
+    return (int)ctas * kDecodeWarps;
 }
 
 cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {

@@ -35,12 +35,53 @@ struct __align__(16) WorkerStart {
 
 constexpr int kDecodeMinSlice = 4;   // a worker is given at least this many tiles
 
-// The slice every worker takes: `workers` of the launched `all_workers` get `per_worker` tiles each.
-__host__ __device__ inline void decode_slices(int total_tiles, int all_workers, int& workers, int& per_worker) {
+// The slices of the global tile sequence.  The launch has `all_workers` warps, of which the first
+// `first_workers` are resident at once (the first wave).  With a tail (tail_div > 0) they take equal
+// slices of all but 1 / tail_div of the tiles; that remainder is cut into small slices for the other
+// warps, whose CTAs the hardware hands to whichever SM finishes its first-wave work first: HBM
+// arbitration is not fair, equal slices finish a fifth of the kernel time apart, and the small slices
+// fill those gaps.  Without a tail every worker gets an equal slice.
+struct DecodeSlices {
+    int workers1, per1;   // first class: workers [0, workers1), per1 tiles each
+    int workers2, per2;   // second class: workers [workers1, workers1 + workers2), per2 tiles each
+    int total;
+    __host__ __device__ long long begin(int w) const {
+        const long long b = w < workers1 ? (long long)w * per1 : (long long)workers1 * per1 + (long long)(w - workers1) * per2;
+        return b < total ? b : total;
+    }
+    __host__ __device__ long long end(int w) const {
+        if (w >= workers1 + workers2) return total;
+        const long long e = begin(w) + (w < workers1 ? per1 : per2);
+        return e < total ? e : total;
+    }
+    __host__ __device__ int worker_of(long long tile) const {   // tile < total
+        const long long first = (long long)workers1 * per1;
+        return tile < first ? (int)(tile / per1) : workers1 + (int)((tile - first) / per2);
+    }
+};
+__host__ __device__ inline DecodeSlices decode_slices(int total_tiles, int all_workers, int first_workers, int tail_div) {
+    DecodeSlices d{1, 1, 0, 1, total_tiles};
     const int want = (total_tiles + kDecodeMinSlice - 1) / kDecodeMinSlice;
-    workers = all_workers < want ? all_workers : want;
-    if (workers < 1) workers = 1;
-    per_worker = (total_tiles + workers - 1) / workers;
+    if (first_workers > all_workers || first_workers <= 0) first_workers = all_workers;
+    const int tail_workers = all_workers - first_workers;
+    const long long tail_tiles = tail_div > 0 ? total_tiles / tail_div : 0;
+    if (tail_workers <= 0 || tail_tiles < (long long)kDecodeMinSlice * 8 || want <= first_workers) {
+        d.workers1 = all_workers < want ? all_workers : want;   // one class (small steps use fewer workers: at least kDecodeMinSlice tiles each)
+        if (d.workers1 > first_workers) d.workers1 = first_workers;
+        if (d.workers1 < 1) d.workers1 = 1;
+        d.per1 = (total_tiles + d.workers1 - 1) / d.workers1;
+        if (d.per1 < 1) d.per1 = 1;
+        return d;
+    }
+    d.workers1 = first_workers;
+    d.per1 = (int)((total_tiles - tail_tiles + first_workers - 1) / first_workers);
+    const long long rest = total_tiles - (long long)d.workers1 * d.per1;
+    if (rest <= 0) { d.workers2 = 0; return d; }
+    long long w2 = (rest + kDecodeMinSlice - 1) / kDecodeMinSlice;
+    if (w2 > tail_workers) w2 = tail_workers;
+    d.workers2 = (int)w2;
+    d.per2 = (int)((rest + w2 - 1) / w2);
+    return d;
 }
 
 // Everything a kernel needs, passed by value.  All pointers are device memory.
@@ -80,6 +121,9 @@ struct KernelArgs {
     int* ptile_prefix;     // [num_sequences + 1] exclusive prefix sum of prefill q tiles per row (one kv head)
     int* pitem_order;      // [kPrefillSortCap] q tiles, longest context first (valid when plan->pitems_sorted); may be null
     int decode_all_workers;      // warps the decode launch will have (0: the plan prepares no start records)
+    int decode_first_workers;    // warps resident at once (the first wave)
+    int decode_tail_div;         // 1 / tail_div of the tiles go to the warps after the first wave (0: none)
+    int test_drop_copy;          // test hook: worker 0 issues no copy for its first tile and polls 2^10 times only
     WorkerStart* worker_start;   // [decode_all_workers], may be null
     long long max_tiles;   // upper bound of total_tiles known on the host
     int rows_per_tile;     // q heads per head tile: min(G, 16)
@@ -132,8 +176,10 @@ cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count
 
 // Upper bound of the decode kernel's worker (warp) count, for sizing the partial-result scratch.
 int decode_max_workers(int sm_count);
-// Warps the decode launch of this step will have (the plan step prepares one start record each).
-int decode_launch_workers(const KernelArgs& a, int sm_count);
+// Warps the decode launch of this step will have (the plan step prepares one start record each); *first_workers
+// receives those of the first wave.
+int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers);
+int decode_tail_div();   // the PA_B200_DECODE_TAIL setting (default 0 = single wave)
 
 // Attention over rows with more than one new token (prefill chunks): generic CUDA-core kernel.
 cudaError_t launch_prefill(const KernelArgs& a, cudaStream_t stream, int* launches);

@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         (void)cat;
         if (ok) return true;
         sm.abort = 1;
-        atomicOr(a.status, 0x40000000u);
+        atomicOr(a.status, PA_DEV_WAIT_TIMEOUT_PREFILL);
         return false;
     };
     auto wait_warp = [&](uint64_t* bar, uint32_t parity, int cat) -> bool { return __all_sync(0xffffffffu, wait(bar, parity, cat)) != 0; };
@@ -317,7 +317,28 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 
             // ---- Q -> f16 swizzled A operand; the row's sum goes into the extra dims.  Every S of this
             // half's previous item has completed, so the tile is free. ------------------------------
+            float qs = qscale;   // the row's softmax scale: the kernel's, divided by the row's prescale
             {
+                // large queries (bf16 / f32 beyond the f16 range, or f16 rows whose sum would leave it): an exact power-of-two
+                // prescale keeps the packed row and its sum inside the f16 range (the decode kernel does the same), and the
+                // softmax scale of the row takes it back out
+                float qmul = 1.f;
+                if (row_live) {
+                    float amax = 0.f;
+#pragma unroll 4
+                    for (int c = 0; c < kD / 8; ++c) {
+                        float v[8];
+                        load_act_vec<8>(a.query, grow_off * kD + 8 * c, a.g.act, v);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+                    }
+                    if (amax > 256.f && amax < INFINITY) {   // 128 terms of at most 2^8 each keep the row sum below the f16 maximum too
+                        int ex;
+                        frexpf(amax, &ex);
+                        qmul = ldexpf(1.f, 8 - ex);
+                    }
+                }
+                qs = qscale / qmul;
                 float qsum = 0.f;
 #pragma unroll 4
                 for (int c = 0; c < kD / 8; ++c) {
@@ -325,6 +346,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] = 0.f;
                     if (row_live) load_act_vec<8>(a.query, grow_off * kD + 8 * c, a.g.act, v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] *= qmul;
                     uint4 w;
                     w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
                     const __half2* h = reinterpret_cast<const __half2*>(&w);
@@ -332,7 +355,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
                     *reinterpret_cast<uint4*>(sq + (c / 8) * (kRows * 128) + sw128(r, c % 8)) = w;
                 }
-                // |q| is assumed to stay inside the f16 range (no power-of-two prescale here)
                 const __half qh = f2h(qsum), ql = f2h(qsum - __half2float(qh));
                 const __half zero = __ushort_as_half(0);
                 *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
@@ -347,7 +369,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 if (!wait_warp(&sm.s_full[X], n & 1, 0)) goto done;
                 if ((warp & 3) == 0) PA_TRACE(X, 0, n);
                 tc05::fence_after_thread_sync();
-                float sv[kKv];   // q.k' in units of 1 / qscale
+                float sv[kKv];   // q.k' in units of 1 / qs
                 {
                     uint32_t s0[32], s1[32];
                     tc05::ld_32x32b_x32(tmem_s, s0);
@@ -378,22 +400,22 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 if (j == 0) {
                     m_run = mx;      // finite: column 0 of tile 0 is visible to every row
                 } else {
-                    const bool grow = (mx - m_run) * qscale > kLazy;
+                    const bool grow = (mx - m_run) * qs > kLazy;
                     rescale = __any_sync(0xffffffffu, grow);
-                    if (grow) { alpha = ex2((m_run - mx) * qscale); m_run = mx; }
+                    if (grow) { alpha = ex2((m_run - mx) * qs); m_run = mx; }
                 }
-                // P = 2^(qscale * (s - m)) in f16 pairs: the exponent is rounded to f16 first, which costs
+                // P = 2^(qs * (s - m)) in f16 pairs: the exponent is rounded to f16 first, which costs
                 // at most 2^-12 of the exponent's magnitude in relative error of p
-                const float mq = m_run * qscale;
+                const float mq = m_run * qs;
                 uint32_t pw[kKv / 2];
 #pragma unroll
                 for (int c = 0; c < kKv; c += 2) {
 #if defined(PA_EXP_NOEXP)
-                    pw[c >> 1] = __byte_perm(__float_as_uint(fmaf(sv[c], qscale, -mq)), __float_as_uint(fmaf(sv[c + 1], qscale, -mq)), 0x7632);
+                    pw[c >> 1] = __byte_perm(__float_as_uint(fmaf(sv[c], qs, -mq)), __float_as_uint(fmaf(sv[c + 1], qs, -mq)), 0x7632);
 #elif defined(PA_EXP_NOCVT)
-                    pw[c >> 1] = ex2_h2(__byte_perm(__float_as_uint(fmaf(sv[c], qscale, -mq)), __float_as_uint(fmaf(sv[c + 1], qscale, -mq)), 0x7632));
+                    pw[c >> 1] = ex2_h2(__byte_perm(__float_as_uint(fmaf(sv[c], qs, -mq)), __float_as_uint(fmaf(sv[c + 1], qs, -mq)), 0x7632));
 #else
-                    pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qscale, -mq), fmaf(sv[c + 1], qscale, -mq)));
+                    pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qs, -mq), fmaf(sv[c + 1], qs, -mq)));
 #endif
                 }
 #endif
@@ -453,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                         }
                     }
                 }
-                if (row_live && a.lse) a.lse[grow_off] = (m_run * qscale + log2f(l_run)) * kLn2P;
+                if (row_live && a.lse) a.lse[grow_off] = (m_run * qs + log2f(l_run)) * kLn2P;
             }
             tc05::fence_before_thread_sync();
         }

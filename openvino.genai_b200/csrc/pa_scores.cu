@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(kScoreWarps * 32) score_kernel(KernelArgs a) {
         if (d.s < 0) break;
         if constexpr (U8) {
             if (!mbar_wait_bounded(&bars[slot], (it / NS) & 1)) {
-                if (lane == 0) atomicOr(a.status, 0x20000000u);
+                if (lane == 0) atomicOr(a.status, PA_DEV_WAIT_TIMEOUT_SCORES);
                 break;
             }
         } else {

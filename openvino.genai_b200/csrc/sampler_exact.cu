@@ -58,6 +58,7 @@ struct ExactShared {
     int list_n;
     // block scan / reduce scratch
     fsx::Step scan_step[kWarps];
+    uint32_t scan_u32[kWarps];
     unsigned long long exp_tab[32];
     RunSum scan_run[kWarps];
     double scan_d[kWarps];
@@ -74,6 +75,7 @@ struct ExactShared {
     int ctl;
     int cleared;
     int prof_passes;
+    int prof_slow_spans;
 };
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -133,13 +135,26 @@ __device__ T block_scan_exclusive(T v, T identity, Op op, T* warp_buf, T* total)
     __syncthreads();
     if (lane == 31) warp_buf[w] = incl;
     __syncthreads();
-    T before = identity;
-    T all = identity;
-    for (int i = 0; i < kWarps; ++i) {
-        const T wi = warp_buf[i];
-        if (i < w) before = op(before, wi);
-        all = op(all, wi);
+    // every warp scans the warp totals itself (lane i holds warp i's): four shuffle rounds instead of a walk over all of them
+    T wt = lane < kWarps ? warp_buf[lane] : identity;
+#pragma unroll
+    for (int o = 1; o < kWarps; o <<= 1) {
+        union { T t; uint32_t u[sizeof(T) / 4]; } a, r;
+        a.t = wt;
+#pragma unroll
+        for (int i = 0; i < (int)(sizeof(T) / 4); ++i) r.u[i] = __shfl_up_sync(0xffffffffu, a.u[i], o);
+        if (lane >= o && lane < kWarps) wt = op(r.t, wt);
     }
+    auto pick = [&](int src) {
+        union { T t; uint32_t u[sizeof(T) / 4]; } a, r;
+        a.t = wt;
+#pragma unroll
+        for (int i = 0; i < (int)(sizeof(T) / 4); ++i) r.u[i] = __shfl_sync(0xffffffffu, a.u[i], src);
+        return r.t;
+    };
+    const T all = pick(kWarps - 1);
+    const T before_incl = pick(w > 0 ? w - 1 : 0);
+    const T before = w > 0 ? before_incl : identity;
     if (total) *total = all;
     // exclusive within the warp
     T excl_lane;
@@ -168,6 +183,7 @@ struct StepOp {
 // element with a block scan of two-state steps.  Spans share the bin arrays of the sorted walk, which
 // runs later.
 constexpr int kSpanBase = 2048;
+constexpr int kHead = 256;          // elements at the start of a row that one thread adds with real additions
 
 struct SpanGeom {
     long long len;   // elements per span
@@ -257,7 +273,82 @@ __device__ long long span_exact(ExactShared& sh, const float* src, long long V, 
             }
         }
         int from = 0;   // elements of the tile below `from` are already in the sum
+        if (base == 0) {
+            // The sum starts at zero and changes binade at almost every one of the first additions: one thread
+            // adds the head of the row with real additions (every scan below costs a few barriers per change).
+            float* head = reinterpret_cast<float*>(sh.list);
+            if (tid < kHead / 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) head[4 * tid + e] = keep[e] ? x[e] : -1.0f;   // -1: not in the sum
+            }
+            __syncthreads();
+            if (tid == 0) {
+                float s = fsx::state_float(E, S);
+                int hit = -1;
+                const int n = (int)min((long long)kHead, hi - base);
+                for (int i = 0; i < n; ++i) {
+                    const float v = head[i];
+                    if (v < 0.0f) continue;
+                    s = __fadd_rn(s, v);
+                    if (use_thr && s > thr) { hit = i; break; }
+                }
+                sh.bc_E = fsx::state_exp(s); sh.bc_S = fsx::state_sig(s); sh.bc_idx = hit;
+            }
+            __syncthreads();
+            E = sh.bc_E; S = sh.bc_S;
+            const int hit = sh.bc_idx;
+            __syncthreads();
+            if (hit >= 0) return base + hit;
+            from = kHead;
+        }
         for (;;) {
+            // Without a tie among the remaining elements their amounts are plain integers: an integer scan finds where
+            // the sum leaves the binade or exceeds the threshold.  With one, the scan composes two-state steps.
+            {
+                const float scale = fsx::amount_scale(E);
+                uint32_t amt[4], mine_sum = 0;
+                bool defer = scale == 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    amt[e] = 0;
+                    if (keep[e] && 4 * tid + e >= from) {
+                        bool d;
+                        amt[e] = fsx::plain_amount(x[e], scale, &d);
+                        defer |= d;
+                    }
+                    mine_sum = fsx::sat_add(mine_sum, amt[e] > fsx::kSat ? fsx::kSat : amt[e]);
+                }
+                if (!__syncthreads_or(defer ? 1 : 0)) {
+                    uint32_t total_amt;
+                    const uint32_t before = block_scan_exclusive(mine_sum, 0u, [](uint32_t p, uint32_t q) { return fsx::sat_add(p, q); }, sh.scan_u32, &total_amt);
+                    const bool crossed_i = S + total_amt >= fsx::kOne24;
+                    const bool over_i = use_thr && !crossed_i && fsx::state_float(E, S + total_amt) > thr;
+                    if (!crossed_i && !over_i) { S += total_amt; break; }
+                    int mine_first = 0x7fffffff;
+                    uint32_t run = before, run_before_first = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t prev = run;
+                        run = fsx::sat_add(run, amt[e]);
+                        if (!(keep[e] && 4 * tid + e >= from) || mine_first != 0x7fffffff) continue;
+                        if (S + run >= fsx::kOne24 || (use_thr && fsx::state_float(E, S + run) > thr)) { mine_first = 4 * tid + e; run_before_first = prev; }
+                    }
+                    const int first = block_min_int(mine_first, sh);
+                    if (first >> 2 == tid) {
+                        const int e = first & 3;
+                        const float xe = e == 0 ? x[0] : e == 1 ? x[1] : e == 2 ? x[2] : x[3];
+                        const float after = __fadd_rn(fsx::state_float(E, S + run_before_first), xe);
+                        sh.bc_E = fsx::state_exp(after);
+                        sh.bc_S = fsx::state_sig(after);
+                    }
+                    __syncthreads();
+                    E = sh.bc_E; S = sh.bc_S;
+                    __syncthreads();
+                    if (use_thr && fsx::state_float(E, S) > thr) return base + first;
+                    from = first + 1;
+                    continue;
+                }
+            }
             fsx::Step loc[4];
             fsx::Step acc = fsx::step_identity();
 #pragma unroll
@@ -322,6 +413,9 @@ __device__ long long walk_spans(ExactShared& sh, const float* src, long long V, 
         E = sh.bc_E; S = sh.bc_S; j = sh.bc_idx;
         __syncthreads();
         if (j >= g.count) break;
+#ifdef SAMPLER_EXACT_PROF
+        if (threadIdx.x == 0) ++sh.prof_slow_spans;
+#endif
         const long long hit = span_exact(sh, src, V, vec_ok, g, j, min_thr, E, S, thr, use_thr);
         if (hit >= 0) { s = fsx::state_float(E, S); return hit; }
         ++j;
@@ -714,7 +808,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
         unsigned long long prof_g0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #endif
-        if (tid == 0) sh.prof_passes = 0;
+        if (tid == 0) { sh.prof_passes = 0; sh.prof_slow_spans = 0; }
         const SpanGeom sg = span_geom(V);
         const float T = p.temperature;
         const float inv_T = __fdiv_rn(1.0f, T);
@@ -765,6 +859,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             if (lane == 0) sh.R[j] = mass;
         }
         __syncthreads();
+        PROF_MARK(6);
         hypothesise_spans(sh, sg.count, 1.0f);
         // every lane re-reads the elements it wrote itself
         auto span_amounts = [&](float min_keep, long long* last, unsigned long long* count) {
@@ -791,6 +886,7 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             }
         };
         span_amounts(0.0f, nullptr, nullptr);
+        PROF_MARK(7);
         float norm = 0.0f;
         walk_spans(sh, prob, V, true, sg, 0.0f, norm, 0.f, false);
         PROF_MARK(2);
@@ -928,9 +1024,9 @@ __global__ void __launch_bounds__(kThreads, 2) sampler_exact_kernel(StepArgs a, 
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
             const unsigned long long dur = (g1 - prof_g0) / 1000;
             if (blockIdx.x % 64 == 0 || dur > 450)
-                printf("block %d row %d start %llu us dur %llu us: max %lld  exp+norm %lld  div(+total|+counts) %lld  keep %lld  draws %lld  (cycles) passes %d\n", blockIdx.x, r,
-                       (prof_g0 / 1000) % 100000, dur, prof_t[1] - prof_t[0], prof_t[2] - prof_t[1], prof_t[3] - prof_t[2], prof_t[4] - prof_t[3], prof_t[5] - prof_t[4],
-                       sh.prof_passes);
+                printf("block %d row %d start %llu us dur %llu us: max %lld  exp %lld  hyp+amounts %lld  walk %lld  div(+total|+counts) %lld  keep %lld  draws %lld  (cycles) passes %d slow spans %d of %d\n",
+                       blockIdx.x, r, (prof_g0 / 1000) % 100000, dur, prof_t[1] - prof_t[0], prof_t[6] - prof_t[1], prof_t[7] - prof_t[6], prof_t[2] - prof_t[7], prof_t[3] - prof_t[2],
+                       prof_t[4] - prof_t[3], prof_t[5] - prof_t[4], sh.prof_passes, sh.prof_slow_spans, sg.count);
         }
 #endif
         __syncthreads();

@@ -234,7 +234,7 @@ def config_qwen_sampler(rows: int = 256, vocab: int = 151936, greedy: bool = Fal
     """Qwen2.5 vocabulary, 256 rows: logits N(0, 4) with 8 spikes of +15 per row, T 0.7, top_k 50,
     top_p 0.9, repetition 1.1, presence 0.2, frequency 0.1 over a 1024-token generated history.
     `mode` selects the other paths on the same logits: "top_p" (T 1, top_p 0.95 over the whole vocabulary, no
-    penalties - the sampling of BASELINE.json configs[4]) and "temperature" (T 0.8 only).
+    penalties - the sampling a vLLM-style throughput benchmark uses) and "temperature" (T 0.8 only).
     Returns (logits f32 [rows, vocab], packed row parameters, history)."""
     from . import _sampler_abi as SA
     rng = np.random.default_rng(seed)

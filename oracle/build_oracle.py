@@ -18,7 +18,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 BUILD = HERE / "_build"
 REF_OUT = HERE / "_ref"
-REFERENCE = Path(os.environ.get("GENAI_REFERENCE_ROOT", "/root/reference"))
+# the reference checkout: GENAI_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REFERENCE = Path(os.environ.get("GENAI_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 
 # -ffp-contract=off: the oracle's quantiser / rotation spell out every rounding step.
 CXXFLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-pthread"]

@@ -27,7 +27,44 @@ def lib():
         _lib.ref_snapkv_window.argtypes = [C.c_int] * 4
         _lib.ref_rotation_lut.restype = C.c_int
         _lib.ref_rotation_lut.argtypes = [C.c_int, C.c_int, C.c_int, C.c_double, C.c_void_p, C.c_void_p]
+        if hasattr(_lib, "ref_eviction_new"):
+            _lib.ref_eviction_new.restype = C.c_void_p
+            _lib.ref_eviction_new.argtypes = [C.c_int] * 7
+            _lib.ref_eviction_free.restype = None
+            _lib.ref_eviction_free.argtypes = [C.c_void_p]
+            _lib.ref_eviction_register.restype = C.c_int
+            _lib.ref_eviction_register.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_char_p, C.c_int]
+            _lib.ref_eviction_evict.restype = C.c_int
+            _lib.ref_eviction_evict.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_char_p, C.c_int]
     return _lib
+
+
+class Algorithm:
+    """The reference's CacheEvictionAlgorithm for one sequence and one layer, kept alive over several steps."""
+
+    def __init__(self, *, start_size, recent_size, max_cache_size, block_size, aggregation="NORM_SUM", snapkv_window=0, max_pool_window=7):
+        self._h = lib().ref_eviction_new(start_size, recent_size, max_cache_size, 0 if aggregation == "SUM" else 1, snapkv_window, block_size, max_pool_window)
+        if not self._h:
+            raise RuntimeError("the reference rejected the eviction configuration")
+
+    def register(self, scores, num_snapkv_scores=0):
+        s = np.ascontiguousarray(scores, np.float32)
+        err = C.create_string_buffer(512)
+        if lib().ref_eviction_register(self._h, s.ctypes.data, len(s), int(num_snapkv_scores), err, 512) != 0:
+            raise RuntimeError(err.value.decode())
+
+    def evict(self):
+        out = np.zeros(8192, np.int32)
+        err = C.create_string_buffer(512)
+        n = lib().ref_eviction_evict(self._h, out.ctypes.data, len(out), err, 512)
+        if n < 0:
+            raise RuntimeError(err.value.decode())
+        return sorted(int(b) for b in out[:n])
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().ref_eviction_free(self._h)
+            self._h = None
 
 
 def select_blocks(score_steps, snapkv_counts, *, start_size, recent_size, max_cache_size, block_size, aggregation="NORM_SUM",

@@ -49,6 +49,45 @@ int ref_eviction_select(int start_size, int recent_size, int max_cache_size, int
     }
 }
 
+// The same algorithm kept alive over several steps (one sequence, one layer): register a step's scores,
+// evict, register more ... as the pipeline does (pipeline_impl.cpp:884-959).
+void* ref_eviction_new(int start_size, int recent_size, int max_cache_size, int aggregation, int snapkv_window, int block_size, int max_pool_window) {
+    try {
+        CacheEvictionConfig cfg(start_size, recent_size, max_cache_size, aggregation == 0 ? AggregationMode::SUM : AggregationMode::NORM_SUM,
+                                /*apply_rotation=*/false, snapkv_window);
+        return new CacheEvictionAlgorithm(cfg, block_size, /*num_decoder_layers=*/1, max_pool_window);
+    } catch (const std::exception&) {
+        return nullptr;
+    }
+}
+void ref_eviction_free(void* h) { delete static_cast<CacheEvictionAlgorithm*>(h); }
+int ref_eviction_register(void* h, const float* scores, int64_t len, int snapkv, char* err, int err_cap) {
+    try {
+        ov::Tensor t(ov::element::f32, ov::Shape{(size_t)len});
+        std::memcpy(t.data<float>(), scores, (size_t)len * sizeof(float));
+        AttentionScoresForEachDecoderLayer layers{t};
+        static_cast<CacheEvictionAlgorithm*>(h)->register_new_token_scores(layers, (size_t)snapkv);
+        return 0;
+    } catch (const std::exception& e) {
+        if (err && err_cap > 0) { std::strncpy(err, e.what(), err_cap - 1); err[err_cap - 1] = 0; }
+        return -1;
+    }
+}
+int ref_eviction_evict(void* h, int32_t* out_blocks, int cap, char* err, int err_cap) {
+    try {
+        auto evicted = static_cast<CacheEvictionAlgorithm*>(h)->evict_logical_blocks();
+        int n = 0;
+        for (size_t b : evicted.at(0)) {
+            if (n < cap) out_blocks[n] = (int32_t)b;
+            ++n;
+        }
+        return n;
+    } catch (const std::exception& e) {
+        if (err && err_cap > 0) { std::strncpy(err, e.what(), err_cap - 1); err[err_cap - 1] = 0; }
+        return -1;
+    }
+}
+
 // SnapKVScoreAggregationCalculator::get_num_token_scores_to_aggregate
 int ref_snapkv_window(int snapkv_window_size, int prompt_len, int num_processed, int num_scheduled) {
     SnapKVScoreAggregationCalculator calc(snapkv_window_size);

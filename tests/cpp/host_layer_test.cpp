@@ -50,7 +50,9 @@ static void test_generation_config() {
     CHECK(bad([](GenerationConfig& x) { x.top_p = 0.f; }));
     CHECK(bad([](GenerationConfig& x) { x.top_p = 1.5f; }));
     CHECK(bad([](GenerationConfig& x) { x.temperature = 0.f; }));
-    CHECK(bad([](GenerationConfig& x) { x.top_k = 0; }));
+    CHECK(!bad([](GenerationConfig& x) { x.top_k = 0; }));                         // 0 = top-k off (logit_processor.hpp:85-86)
+    CHECK(!bad([](GenerationConfig& x) { x.num_return_sequences = 3; }));
+    CHECK(bad([](GenerationConfig& x) { x.num_return_sequences = 3; x.do_sample = false; }));
     CHECK(bad([](GenerationConfig& x) { x.min_p = 1.f; }));
     CHECK(bad([](GenerationConfig& x) { x.repetition_penalty = 0.f; }));
     CHECK(bad([](GenerationConfig& x) { x.frequency_penalty = 2.5f; }));
@@ -232,6 +234,12 @@ static std::vector<GenerationConfig> request_configs() {
     GenerationConfig e = greedy;   // greedy with a stop token that the spikes make likely
     e.set_eos_token_id(5); e.repetition_penalty = 1.0f;
     v.push_back(e);
+    GenerationConfig f = b;   // three sequences from one request: three draws from the first distribution, then one row each
+    f.num_return_sequences = 3; f.rng_seed = 15; f.top_k = 0; f.top_p = 0.8f;   // top_k 0 = off: the full-vocabulary path
+    v.push_back(f);
+    GenerationConfig h = a;   // a grammar that only allows multiples of three
+    h.rng_seed = 16;
+    v.push_back(h);
     return v;
 }
 
@@ -243,7 +251,7 @@ static void fill_logits(std::vector<float>& logits, int64_t rows, int64_t vocab,
         for (int s = 0; s < 4; ++s) logits[r * vocab + (gen() % 64)] += 6.f;   // a few likely ids in [0, 64): repeats and stop hits
 }
 
-struct Generation { std::vector<std::vector<int64_t>> ids; std::vector<std::vector<float>> lps; std::vector<int> reasons; };
+struct Generation { std::vector<std::vector<int64_t>> ids; std::vector<std::vector<float>> lps; std::vector<int> reasons; std::vector<std::vector<int64_t>> fork_ids; };
 
 static Generation generate(Sampler& sampler, bool device_logits) {
     const int64_t vocab = 4096;
@@ -252,12 +260,19 @@ static Generation generate(Sampler& sampler, bool device_logits) {
     for (size_t i = 0; i < cfgs.size(); ++i) groups.push_back(make_group(100 + i, cfgs[i], {(int64_t)i, 40, 41, 40}, (int64_t)i));
     std::vector<SequenceGroup*> ptrs;
     for (auto& g : groups) ptrs.push_back(&g);
-    const int64_t rows = (int64_t)groups.size();
+    std::vector<int32_t> grammar((size_t)(vocab + 31) / 32, 0);
+    for (int64_t tkn = 0; tkn < vocab; tkn += 3) grammar[(size_t)tkn / 32] |= (int32_t)(1u << (tkn % 32));
+    groups[7].token_bitmask = grammar.data();
+    const int64_t rows = (int64_t)groups.size() + 2;   // two more rows once the three-sequence request has forked
     std::vector<float> logits(rows * vocab);
     float* dev = nullptr;
     if (device_logits && cudaMalloc(&dev, logits.size() * 4) != cudaSuccess) { CHECK(false); return {}; }
     for (int step = 0; step < 14; ++step) {
         fill_logits(logits, rows, vocab, step);
+        // the scheduler's part: a row of the logits tensor for every running sequence
+        int64_t next_row = (int64_t)groups.size();
+        for (auto& g : groups)
+            for (auto& fk : g.forks) fk.logits_row = next_row++;
         if (device_logits) {
             cudaMemcpy(dev, logits.data(), logits.size() * 4, cudaMemcpyHostToDevice);
             sampler.sample_device(ptrs, dev, rows, vocab, nullptr);
@@ -272,7 +287,10 @@ static Generation generate(Sampler& sampler, bool device_logits) {
     }
     if (dev) cudaFree(dev);
     Generation out;
-    for (auto& g : groups) { out.ids.push_back(g.generated_ids); out.lps.push_back(g.generated_log_probs); out.reasons.push_back((int)g.finish_reason); }
+    for (auto& g : groups) {
+        out.ids.push_back(g.generated_ids); out.lps.push_back(g.generated_log_probs); out.reasons.push_back((int)g.finish_reason);
+        for (auto& fk : g.forks) out.fork_ids.push_back(fk.generated_ids);
+    }
     return out;
 }
 
@@ -287,7 +305,12 @@ static void test_sampler_gpu(const char* oracle_lib) {
     const Generation want = generate(expected_sampler, false);
     const Generation got_host = generate(host_sampler, false);
     const Generation got_dev = generate(device_sampler, true);
-    CHECK(want.ids.size() == 6);
+    CHECK(want.ids.size() == 8);
+    // the three-sequence request forked twice; its sequences differ and every one of them equals the expected stream
+    CHECK(want.fork_ids.size() == 2 && got_host.fork_ids == want.fork_ids && got_dev.fork_ids == want.fork_ids);
+    CHECK(want.fork_ids.size() == 2 && (want.fork_ids[0] != want.ids[6] || want.fork_ids[1] != want.ids[6]));
+    // the grammar's request only produced allowed ids
+    for (int64_t id : got_dev.ids[7]) CHECK(id % 3 == 0);
     for (size_t i = 0; i < want.ids.size(); ++i) {
         CHECK(!want.ids[i].empty());
         CHECK(want.ids[i] == got_host.ids[i]);

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 import json
+import os
 import re
 import sys
 from pathlib import Path
@@ -20,7 +21,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("GENAI_REFERENCE_ROOT") or ROOT.parent / "reference")
 sys.path.insert(0, str(ROOT))
 
 

@@ -102,11 +102,11 @@ def make_op(wl, device=0):
     return pkg.PagedAttentionExtension(wl.num_q_heads, wl.num_kv_heads, wl.head_size, wl.block_size, wl.act_dtype, wl.cache_dtype, device)
 
 
-def run_gpu(wl, data=None, device=0, host_entry=False, op=None):
+def run_gpu(wl, data=None, device=0, host_entry=False, op=None, caches=None):
     q, k, v, fill, pk, pv = data or make_host_data(wl)
     dev = torch.device("cuda", device)
     op = op or make_op(wl, device)
-    kc, vc = op.allocate_cache(wl.num_blocks, fill=0)
+    kc, vc = caches if caches is not None else op.allocate_cache(wl.num_blocks, fill=0)   # caches: flat uint8 device tensors the caller owns
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev) if a is not None else None
     if fill.num_tokens:
         dummy = torch.zeros((fill.num_tokens, 1), dtype=wl.act_dtype, device=dev)
@@ -153,3 +153,12 @@ def rel_err(a: np.ndarray, b: np.ndarray) -> float:
     """max |a - b| relative to the largest reference magnitude."""
     denom = float(np.abs(b).max()) or 1.0
     return float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max() / denom)
+
+
+def wrap_device_bytes(ptr: int, nbytes: int, device=0) -> torch.Tensor:
+    """A flat uint8 torch view of device memory that something else owns (no copy, no ownership)."""
+    class _Mem:
+        pass
+    holder = _Mem()
+    holder.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 3, "strides": None}
+    return torch.as_tensor(holder, device=torch.device("cuda", device))

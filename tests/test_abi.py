@@ -10,7 +10,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 def _declared(header: Path):
     text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b((?:pa|sampler|exchange)_b200_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b((?:pa|sampler|exchange|eviction)_b200_\w+)\s*\(", text)))
 
 
 @pytest.fixture(scope="module")

@@ -16,8 +16,20 @@ if str(ROOT) not in sys.path:
 
 import __graft_entry__ as entry  # noqa: E402
 
-CUDA_INC = Path("/usr/local/cuda/include")
-CUDA_LIB = Path("/usr/local/cuda/lib64")
+
+
+def _cuda_home() -> Path:
+    entry.load_package()
+    """The toolkit the library was built with: CUDA_HOME, else the directory two levels above nvcc."""
+    import os
+    if os.environ.get("CUDA_HOME"):
+        return Path(os.environ["CUDA_HOME"])
+    from openvino_genai_b200 import build
+    return Path(build._nvcc()).resolve().parent.parent
+
+
+CUDA_INC = _cuda_home() / "include"
+CUDA_LIB = _cuda_home() / "lib64"
 
 
 def _build(tmp: Path) -> Path:

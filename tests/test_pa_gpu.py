@@ -245,3 +245,34 @@ def test_empty_step_is_a_no_op():
     args = op.make_args(z, zk, zk, z, kc, vc, zi[:0], zi, zi[:0], zi, wl.scale, 0)
     assert op.lib.pa_b200_forward(op._h, C.byref(args)) == 0
     assert op.launch_count() == before and op.device_status() == 0
+
+
+def test_a_copy_that_never_arrives_ends_with_a_status_bit_not_a_hang(monkeypatch):
+    """Every wait of the decode kernel on a staged record is bounded.  The test hook makes worker 0 arm the
+    barrier of its first tile without issuing the copy (nothing is in flight) and poll 2^10 times only: the
+    step must return with PA_DEV_WAIT_TIMEOUT_DECODE set, and the next step on the same context must be clean."""
+    from openvino_genai_b200 import _abi
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[900, 300, 64], new=[1, 1, 1], seed=113)
+    data = H.make_host_data(wl)
+    good = H.run_gpu(wl, data)
+    assert good["status"] == 0
+    monkeypatch.setenv("PA_B200_TEST_DROP_FIRST_COPY", "1")
+    hooked = H.run_gpu(wl, data)            # a new handle reads the hook
+    assert hooked["status"] & _abi.PA_DEV_WAIT_TIMEOUT_DECODE
+    monkeypatch.delenv("PA_B200_TEST_DROP_FIRST_COPY")
+    again = H.run_gpu(wl, data)
+    assert again["status"] == 0 and np.array_equal(again["out_gpu"], good["out_gpu"])
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+def test_queries_beyond_the_f16_range(act):
+    """|q| around 1e5 (with a softmax scale that brings the logits back to order one): prefill chunks and decode
+    rows rescale such rows by an exact power of two before packing them for the tensor cores."""
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache="u8", past=[300, 40, 0], new=[64, 1, 33], seed=127, scale=1.0 / (1.0e5 * 128 ** 0.5))
+    q, k, v, fill, pk, pv = H.make_host_data(wl)
+    data = ((q.float() * 1.0e5).to(act), k, v, fill, pk, pv)
+    res = H.run_oracle(wl, data)
+    res.update(H.run_gpu(wl, data))
+    assert res["status"] == 0
+    assert np.isfinite(res["out_gpu"]).all()
+    assert H.rel_err(res["out_gpu"], res["out_ref"]) < (1e-2 if act == torch.float32 else 1.2e-2)

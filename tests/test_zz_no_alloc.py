@@ -37,13 +37,19 @@ def _filled_cache(op, wl, data, dev):
     return kc, vc
 
 
-@pytest.mark.parametrize("cache,act", [("u8", torch.bfloat16), ("f16", torch.float16)])
-def test_static_scratch_entry_matches_regular_entry_twice(cache, act):
+@pytest.mark.parametrize("cache,act,hq,hkv,d,bs", [
+    ("u8", torch.bfloat16, 32, 8, 128, 32),
+    ("f16", torch.float16, 32, 8, 128, 32),
+    ("f16", torch.float16, 16, 4, 64, 16),      # the 16-token block / 64-dim instantiation
+    ("u8", torch.bfloat16, 40, 2, 128, 32),     # 20 query heads per KV head: two head tiles, the second ragged
+])
+def test_static_scratch_entry_matches_regular_entry_twice(cache, act, hq, hkv, d, bs):
     dev = torch.device("cuda", 0)
     tol = 1e-2 if cache == "u8" else 2e-3
     # two different steps, the second shorter than the first so stale partials would show
-    steps = [H.small_workload(hq=32, hkv=8, d=128, bs=32, act=act, cache=cache, past=[1500, 700, 33, 0, 4000, 257], new=[1] * 6, seed=301),
-             H.small_workload(hq=32, hkv=8, d=128, bs=32, act=act, cache=cache, past=[90, 2100, 5], new=[1] * 3, seed=302)]
+    geo = dict(hq=hq, hkv=hkv, d=d, bs=bs, act=act, cache=cache)
+    steps = [H.small_workload(**geo, past=[1500, 700, 33, 0, 4000, 257], new=[1] * 6, seed=301),
+             H.small_workload(**geo, past=[90, 2100, 5], new=[1] * 3, seed=302)]
     for wl in steps:
         data = H.make_host_data(wl)
         op = H.make_op(wl)
