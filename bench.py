@@ -317,7 +317,9 @@ def measure_headline(env: Env, args) -> dict:
     e1.record(stream)
     env.barrier()
     ms_e2e_total = e0.elapsed_time(e1)
-    same = torch.equal(hout.to(dev), out)
+    # the decode kernel hands tiles to its warps dynamically, so the order of its partial sums - and with it the last bits of
+    # the output - differs between launches: the host-buffer call is compared with the device call at bf16 resolution
+    same = torch.allclose(hout.to(dev).float(), out.float(), rtol=2e-2, atol=2e-3)
 
     # ---- reduce over ranks ------------------------------------------------------------------------
     kv_bytes = wl.decode_kv_bytes()

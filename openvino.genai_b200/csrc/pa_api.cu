@@ -86,7 +86,7 @@ pa::CacheGeom make_geom(const pa_model_desc& d) {
 // Scratch layout of one forward call.
 struct Plan {
     long long max_tiles;
-    size_t off_hdr, off_prefix, off_pprefix, off_porder, off_wstart, off_done, off_part_o, off_part_ml, off_lse, off_score_off, off_stile, off_score_part, off_score_raw, total;
+    size_t off_hdr, off_prefix, off_pprefix, off_porder, off_wstart, off_done, off_part_o, off_part_ml, off_cta_q, off_lse, off_score_off, off_stile, off_score_part, off_score_raw, total;
     bool has_score_raw;
 };
 
@@ -100,16 +100,17 @@ Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_co
     long long tiles = B * ((std::max(max_context_len, 1) + 31) / 32);
     if (num_block_indices >= 0) tiles = std::min(tiles, (long long)num_block_indices * g.bs / 32 + B);
     p.max_tiles = tiles * HK;
-    const long long slots = B * HK + pa::decode_max_workers(h->sm_count);  // slot = stream + worker
+    const long long slots = B * HK + pa::decode_max_slices(h->sm_count);  // slot = stream + slice
     size_t off = 0;
     p.off_hdr = off;       off += 256;
     p.off_prefix = off;    off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_pprefix = off;   off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_porder = off;    off += align_up((size_t)pa::kPrefillSortCap * sizeof(int), 256);
-    p.off_wstart = off;    off += align_up((size_t)pa::decode_max_workers(h->sm_count) * sizeof(pa::WorkerStart), 256);
+    p.off_wstart = off;    off += align_up((size_t)pa::decode_max_slices(h->sm_count) * sizeof(pa::WorkerStart), 256);
     p.off_done = off;      off += align_up((size_t)std::max(B, 1LL) * HK * sizeof(int), 256);
     p.off_part_o = off;    off += align_up((size_t)slots * RT * g.D * sizeof(float), 256);
     p.off_part_ml = off;   off += align_up((size_t)slots * RT * 2 * sizeof(float), 256);
+    p.off_cta_q = off;     off += pa::decode_shared_supported(g) ? align_up(pa::decode_shared_scratch_bytes(h->sm_count), 256) : 0;
     p.off_lse = off;       off += align_up((size_t)std::max(num_tokens, 1) * g.Hq * sizeof(float), 256);
     p.off_score_off = off; off += align_up((size_t)(B + 1) * sizeof(int64_t), 256);
     p.off_stile = off;     off += align_up((size_t)(B + 1) * sizeof(int), 256);
@@ -188,6 +189,7 @@ pa::KernelArgs make_kernel_args(pa_handle* h, const pa_forward_args* a, const Pl
     k.status = h->status;
     k.part_o = (float*)(h->ws + p.off_part_o);
     k.part_ml = (float*)(h->ws + p.off_part_ml);
+    k.cta_q = (uint8_t*)(h->ws + p.off_cta_q);
     k.lse = (float*)(h->ws + p.off_lse);
     k.score_offsets = (int64_t*)(h->ws + p.off_score_off);
     k.stile_prefix = (int*)(h->ws + p.off_stile);
@@ -213,7 +215,15 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     pa::KernelArgs k = make_kernel_args(h, a, p);
     k.decode_tail_div = pa::decode_tail_div();
     k.test_drop_copy = h->test_drop_copy ? 1 : 0;
-    k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count, &k.decode_first_workers);   // the plan step prepares one start record per worker
+    const bool shared_decode = pa::decode_shared_supported(h->g);
+    if (shared_decode) {   // one CTA per SM is the worker; its warps share the slice
+        k.decode_tail_div = 0;
+        k.decode_phantom = pa::decode_shared_phantom();
+        k.max_tiles += (long long)a->num_sequences * h->g.Hkv * k.decode_phantom;
+        k.decode_all_workers = k.decode_first_workers = pa::decode_shared_ctas(k, h->sm_count);
+    } else {
+        k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count, &k.decode_first_workers);   // the plan step prepares one start record per worker
+    }
     int launches = 0;
     if (a->num_rotated_blocks > 0) { PA_CUDA(pa::launch_rotate(k, stream)); ++launches; }
     PA_CUDA(pa::launch_write_kv(k, stream, /*with_plan=*/true)); ++launches;
@@ -227,7 +237,8 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
         ev0 = h->ev[h->ev_used]; ev1 = h->ev[h->ev_used + 1];
         h->ev_used += 2;
     }
-    PA_CUDA(pa::launch_decode(k, stream, h->sm_count, &launches, ev0, ev1));
+    if (shared_decode) PA_CUDA(pa::launch_decode_shared(k, stream, h->sm_count, &launches, ev0, ev1));
+    else PA_CUDA(pa::launch_decode(k, stream, h->sm_count, &launches, ev0, ev1));
     if (a->num_tokens > a->num_sequences) {
         if (pa::prefill_tc_supported(h->g) && !h->force_generic_prefill) {
             const int G = h->g.Hq / h->g.Hkv;

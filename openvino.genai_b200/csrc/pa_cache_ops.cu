@@ -19,11 +19,12 @@ __device__ __forceinline__ int find_sequence(const int32_t* begins, int num_seq,
     return lo;
 }
 
-// Number of 32-token context tiles of one decode row (0 for rows that are not decode rows).
+// Number of 32-token context tiles of one decode row (0 for rows that are not decode rows), plus the phantom tiles
+// of the slicing sequence where the decode kernel asks for them.
 __device__ __forceinline__ int seq_tiles(const KernelArgs& a, int s) {
     SeqView v;
     if (!seq_view(a, s, v) || v.n != 1) return 0;
-    return (v.past + 1 + 31) / 32;
+    return (v.past + 1 + 31) / 32 + a.decode_phantom;
 }
 
 // Builds the decode plan with one block of 256 threads: the exclusive prefix sum of the per-row
@@ -135,6 +136,7 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         a.ptile_prefix[B] = sh_run_p;
         a.plan->total_ptiles = sh_run_p;
         a.plan->next_pitem = 0;
+        a.plan->next_slice = 0;
         a.plan->pitems_sorted = sort_items ? 1 : 0;
     }
 }

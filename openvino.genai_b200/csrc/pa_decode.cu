@@ -94,6 +94,10 @@ __device__ __forceinline__ void store_pair(void* out, long long idx, int act, fl
     else *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)out + idx) = __floats2bfloat162_rn(v0, v1);
 }
 
+#ifdef PA_DECODE_PROF
+__device__ unsigned long long g_decode_prof[8192 * 8];   // per worker: start, first tile ready, end (ns), tiles, cycles waiting for tiles, cycles in all, cycles in produce
+#endif
+
 // SC: the launch keeps the scaled logits of rows whose scores are wanted (a.score_raw is set); a
 // separate instantiation so that steps without a score output run the same code as before.
 template <int D, int BS, int CACHE, bool HI, bool SC>
@@ -132,19 +136,27 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- this worker's slice of the global tile sequence -----------------------------------------
-    const int all_workers = gridDim.x * kDecodeWarps;
+    // The launch's warps own the first slices; further ("shared") slices are handed out by a counter.
+    const int phys_workers = gridDim.x * kDecodeWarps;
     const int wid = blockIdx.x * kDecodeWarps + warp;
-    WorkerStart ws;
-    ws.s = -1;
-    if (a.worker_start && a.decode_all_workers == all_workers) {
-        const int4 lo4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + wid));
-        const int4 hi4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + wid) + 1);
-        ws = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
-    }
-    const int total_tiles = ws.s != -1 ? ws.total_tiles : a.plan->total_tiles;   // all streams
-    const DecodeSlices sl = decode_slices(total_tiles, all_workers, a.decode_first_workers, a.decode_tail_div);
-    int g_tile = (int)sl.begin(wid);               // next global tile to load
-    const int g_end = (int)sl.end(wid);
+    const bool planned = a.worker_start && a.decode_all_workers >= phys_workers && a.decode_first_workers == phys_workers;   // one start record per slice
+    const int all_workers = planned ? a.decode_all_workers : phys_workers;
+    auto load_start = [&](int id) {
+        WorkerStart w;
+        w.s = -1;
+        if (planned) {
+            const int4 lo4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + id));
+            const int4 hi4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + id) + 1);
+            w = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+        }
+        return w;
+    };
+    const WorkerStart ws0 = load_start(wid);
+    const int total_tiles = ws0.s != -1 ? ws0.total_tiles : a.plan->total_tiles;   // all streams
+    const DecodeSlices sl = decode_slices(total_tiles, all_workers, planned ? a.decode_first_workers : phys_workers, planned ? a.decode_tail_div : 0);
+    int cur = wid;                   // slice in work
+    int g_tile = 0, g_end = 0;       // next global tile to load, end of the slice
+    bool more = planned && sl.workers2 > 0 && ws0.s != -1;   // shared slices (every one has a start record) may be left
 
     // ---- loader state (warp-uniform registers) -------------------------------------------------------
     int r_s = -1, r_hkp = 0, r_tiles = 0;   // current stream: row, head tile, tiles of the row per head tile
@@ -187,33 +199,60 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
                     else atomicOr(a.status, PA_DEV_BAD_BEGINS);
                 }
             }
-            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, score_off};
+            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + cur, score_off};
         }
         g_tile += ntile;
         r_first = true;
         load_window(r_tok / BS);
     };
-    // Later runs start at the first tile of the next stream.
-    auto next_run = [&]() {
-        if (++r_hkp == HK) {
-            r_hkp = 0;
-            do {
-                ++r_s;
-                r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
-            } while (r_tiles == 0);
-        }
-        r_tb = a.block_indices_begins[r_s];
-        r_nb = a.block_indices_begins[r_s + 1] - r_tb;
-        start_run(0, __ldcg(a.tile_prefix + r_s), a.past_lens[r_s] + 1, a.subsequence_begins[r_s]);
-    };
-    // The first run: from the record the plan step prepared, else by binary search in the prefix sums.
-    if (g_tile < g_end) {
-        int p0, ctx, t0row;
-        if (ws.s >= 0) {
+    // Moves the loader to its next run: the first tile of the next stream of the slice in work, else the first
+    // run of the next shared slice from the counter.  False when nothing is left.
+    auto advance = [&]() -> bool {
+        int tile0 = 0, p0, ctx, t0row;
+        if (g_tile < g_end) {
+            if (++r_hkp == HK) {
+                r_hkp = 0;
+                do {
+                    ++r_s;
+                    r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
+                } while (r_tiles == 0);
+            }
+            r_tb = a.block_indices_begins[r_s];
+            r_nb = a.block_indices_begins[r_s + 1] - r_tb;
+            p0 = __ldcg(a.tile_prefix + r_s);
+            ctx = a.past_lens[r_s] + 1;
+            t0row = a.subsequence_begins[r_s];
+        } else {
+            if (!more) return false;
+            int id = 0;
+            if (lane == 0) id = atomicAdd(&a.plan->next_slice, 1);
+            id = sl.workers1 + __shfl_sync(0xffffffffu, id, 0);
+            if (id >= sl.workers1 + sl.workers2) { more = false; return false; }
+            cur = id;
+            g_tile = (int)sl.begin(id);   // shared slices are never empty
+            g_end = (int)sl.end(id);
+            const WorkerStart ws = load_start(id);
             r_s = ws.s;
             p0 = ws.p0;
             r_tiles = ws.r_tiles;
             ctx = ws.ctx; r_tb = ws.tb; r_nb = ws.nb; t0row = ws.t0;
+            const int off = g_tile - p0 * HK;
+            r_hkp = off / r_tiles;
+            tile0 = off % r_tiles;
+        }
+        start_run(tile0, p0, ctx, t0row);
+        return true;
+    };
+    // The worker's own slice: from the record the plan step prepared, else by binary search in the prefix sums.
+    g_tile = (int)sl.begin(wid);
+    g_end = (int)sl.end(wid);
+    if (g_tile < g_end) {
+        int p0, ctx, t0row;
+        if (ws0.s >= 0) {
+            r_s = ws0.s;
+            p0 = ws0.p0;
+            r_tiles = ws0.r_tiles;
+            ctx = ws0.ctx; r_tb = ws0.tb; r_nb = ws0.nb; t0row = ws0.t0;
         } else {
             const int key = g_tile / HK;
             int lo = 0, hi = a.num_sequences;  // tile_prefix[lo] <= key < tile_prefix[hi]
@@ -235,9 +274,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     }
 
     // Issues the next tile of the load stream into ring stage `slot` and records its descriptor.
+#ifdef PA_DECODE_PROF
+    long long prof_adv = 0, prof_tma = 0;
+#endif
     auto produce = [&](int slot) {
-        if (r_tok >= r_end && g_tile < g_end) next_run();
-        if (r_tok >= r_end) {
+#ifdef PA_DECODE_PROF
+        const long long prof_a0 = clock64();
+#endif
+        if (r_tok >= r_end && !advance()) {
             if (lane == 0) descs[slot] = StageDesc{kEnd, 0, 0, 0};
             if constexpr (!U8) cp_async_commit();
             return;
@@ -248,6 +292,9 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)hk * a.g.head_bytes;
         const int bi0 = r_tok / BS;
         if (bi0 + Cfg::NREC - 1 - w_blk0 >= 32) load_window(bi0);
+#ifdef PA_DECODE_PROF
+        prof_adv += clock64() - prof_a0;
+#endif
         int blocks[Cfg::NREC];
         bool live[Cfg::NREC];
 #pragma unroll
@@ -256,22 +303,35 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
             blocks[r] = __shfl_sync(0xffffffffu, tbl, (bi0 + r - w_blk0) & 31);
         }
         if constexpr (U8) {
+            // Test hook (PA_B200_TEST_DROP_FIRST_COPY): worker 0 arms the barrier of its first tile and issues no copy,
+            // so that the bounded wait below runs out; nothing is in flight for that stage when it does.
+            const bool drop = a.test_drop_copy && wid == 0 && !dropped_once;
+            dropped_once = true;
+#ifdef PA_DECODE_PROF
+            const long long prof_b0 = clock64();
+#endif
             if (lane == 0) {
                 uint32_t bytes = 0;
 #pragma unroll
                 for (int r = 0; r < Cfg::NREC; ++r) bytes += live[r] ? 2 * Cfg::REC : 0;
                 mbar_expect_tx(&bars[slot], bytes);
-                // Test hook (PA_B200_TEST_DROP_FIRST_COPY): worker 0 arms the barrier of its first tile and issues no copy,
-                // so that the bounded wait below runs out; nothing is in flight for that stage when it does.
-                const bool drop = a.test_drop_copy && wid == 0 && !dropped_once;
-                dropped_once = true;
-#pragma unroll
-                for (int r = 0; r < Cfg::NREC; ++r)
-                    if (live[r] && !drop) {
-                        bulk_g2s(st + r * Cfg::REC, kc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, &bars[slot]);
-                        bulk_g2s(st + Cfg::HALF_STAGE + r * Cfg::REC, vc + (long long)blocks[r] * a.g.block_bytes, Cfg::REC, &bars[slot]);
-                    }
             }
+            // one copy per lane (key / value record of each block of the tile): the copies of a tile leave as one
+            // warp instruction instead of one after the other
+            if (lane < 2 * Cfg::NREC) {
+                const int r = lane >> 1;
+                const bool is_v = lane & 1;
+                int blk = blocks[0];
+                bool lv = live[0];
+                if constexpr (Cfg::NREC > 1) {
+                    if (r == 1) { blk = blocks[1]; lv = live[1]; }
+                }
+                if (lv && !drop)
+                    bulk_g2s(st + (is_v ? Cfg::HALF_STAGE : 0) + r * Cfg::REC, (is_v ? vc : kc) + (long long)blk * a.g.block_bytes, Cfg::REC, &bars[slot]);
+            }
+#ifdef PA_DECODE_PROF
+            prof_tma += clock64() - prof_b0;
+#endif
         } else {
             constexpr int CPR = D / 8;  // 16-byte chunks per token row
 #pragma unroll
@@ -307,14 +367,23 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
 #ifdef PA_DECODE_PROF
     unsigned long long prof_t[4] = {0, 0, 0, 0};
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[0]));
+    long long prof_wait = 0, prof_prod = 0;
+    const long long prof_c0 = clock64();
 #endif
 #pragma unroll
     for (int p = 0; p < NS - 1; ++p) produce(p);
 
     for (int it = 0;; ++it) {
         __syncwarp();  // every lane is done with the stage that is refilled next
+#ifdef PA_DECODE_PROF
+        const long long prof_p0 = clock64();
+#endif
         produce((it + NS - 1) % NS);
         __syncwarp();
+#ifdef PA_DECODE_PROF
+        const long long prof_w0 = clock64();
+        prof_prod += prof_w0 - prof_p0;
+#endif
         const int slot = it % NS;
         const StageDesc d = descs[slot];
         if (d.flags & kEnd) break;
@@ -335,7 +404,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
         }
 #ifdef PA_DECODE_PROF
         if (it == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[1]));
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[2]));
+        prof_wait += clock64() - prof_w0;
 #endif
         const uint8_t* st = ring + slot * Cfg::STAGE;
         const int valid = d.valid;
@@ -689,22 +758,24 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     if (__any_sync(0xffffffffu, bad_index) && lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
 #ifdef PA_DECODE_PROF
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_t[3]));
-    if (lane == 0 && wid % 61 == 0)
-        printf("decode prof wid %d sm-start %llu first-tile +%llu last-tile-ready +%llu end +%llu tiles %d\n", wid, prof_t[0] % 100000000ull,
-               prof_t[1] - prof_t[0], prof_t[2] - prof_t[0], prof_t[3] - prof_t[0], g_end - (int)sl.begin(wid));
+    if (lane == 0 && wid < 8192) {
+        g_decode_prof[wid * 8 + 0] = prof_t[0];
+        g_decode_prof[wid * 8 + 1] = prof_t[1] - prof_t[0];
+        g_decode_prof[wid * 8 + 2] = prof_t[3] - prof_t[0];
+        g_decode_prof[wid * 8 + 3] = (unsigned long long)(sl.end(wid) - sl.begin(wid));
+        g_decode_prof[wid * 8 + 4] = (unsigned long long)prof_wait;
+        g_decode_prof[wid * 8 + 5] = (unsigned long long)(clock64() - prof_c0);
+        g_decode_prof[wid * 8 + 6] = (unsigned long long)prof_prod;
+        g_decode_prof[wid * 8 + 7] = ((unsigned long long)prof_adv << 32) | (unsigned long long)(prof_tma & 0xffffffffll);
+    }
 #endif
 }
 
-// CTAs of the launch: the resident ones, and as many again when a tail wave is wanted; never more workers than
-// slices could exist (upper bound known on the host).  *resident receives the CTAs of the first wave.
-long long decode_ctas(const KernelArgs& a, int per_sm, int sm_count, long long* resident) {
+// CTAs of the launch: the resident ones; never more workers than slices could exist (upper bound known on the host).
+long long decode_ctas(const KernelArgs& a, int per_sm, int sm_count) {
     const long long max_slices = (a.max_tiles + kDecodeMinSlice - 1) / kDecodeMinSlice;
     const long long cap = std::max(1LL, (max_slices + kDecodeWarps - 1) / kDecodeWarps);
-    const long long first = std::min((long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count, cap);
-    long long ctas = first;
-    if (a.decode_tail_div > 0 && first * kDecodeWarps * kDecodeMinSlice * 8 <= a.max_tiles) ctas = std::min(2 * first, cap);
-    if (resident) *resident = first;
-    return std::max(1LL, ctas);
+    return std::max(1LL, std::min((long long)std::min(per_sm, kDecodeMaxCtasPerSm) * sm_count, cap));
 }
 
 // Resident CTAs per SM of one instantiation on the current device; the shared-memory opt-in and the
@@ -743,7 +814,7 @@ cudaError_t launch_decode_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
                    : (sc ? decode_kernel<D, BS, CACHE, false, true> : decode_kernel<D, BS, CACHE, false, false>);
     const int per_sm = occupancy_t<D, BS, CACHE>(a);
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
-    const long long ctas = decode_ctas(a, per_sm, sm_count, nullptr);
+    const long long ctas = decode_ctas(a, per_sm, sm_count);
     if (ev0) cudaEventRecord(ev0, stream);
     // Programmatic dependent launch: the launch is queued behind the cache-write kernel without a full
     // stream serialisation; that kernel never triggers early, so the CTAs start when it has finished, and
@@ -781,13 +852,14 @@ cudaError_t launch_decode_c(const KernelArgs& a, cudaStream_t stream, int sm_cou
 int decode_tail_div() {
     static const int v = [] {
         const char* e = std::getenv("PA_B200_DECODE_TAIL");
-        const int n = e ? std::atoi(e) : 0;  // a second wave measured slower than one wave at every setting tried (4, 8, 16)
+        const int n = e ? std::atoi(e) : 0;   // shared slices measured slower than equal slices (every slice start is a chain of dependent loads)
         return n < 0 ? 0 : n;
     }();
     return v;
 }
 
-int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps * 2; }
+int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps; }
+int decode_max_slices(int sm_count) { return decode_max_workers(sm_count) * (1 + kDecodeSharedPerWorker); }
 
 int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers) {
     if (first_workers) *first_workers = 0;
@@ -805,10 +877,9 @@ int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers)
     else if (a.g.D == 64 && a.g.bs == 16) { PA_OCC(64, 16) }
 #undef PA_OCC
     if (per_sm < 1) return 0;
-    long long resident = 0;
-    const long long ctas = decode_ctas(a, per_sm, sm_count, &resident);
-    if (first_workers) *first_workers = (int)resident * kDecodeWarps;
-    return (int)ctas * kDecodeWarps;
+    const int launched = (int)decode_ctas(a, per_sm, sm_count) * kDecodeWarps;
+    if (first_workers) *first_workers = launched;
+    return a.decode_tail_div > 0 ? launched * (1 + kDecodeSharedPerWorker) : launched;
 }
 
 cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {
@@ -821,3 +892,9 @@ cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count
 }
 
 }  // namespace pa
+
+#ifdef PA_DECODE_PROF
+extern "C" int pa_b200_debug_read_decode_prof(void* dst, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(dst, pa::g_decode_prof, bytes);
+}
+#endif

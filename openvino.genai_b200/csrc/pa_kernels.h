@@ -17,6 +17,7 @@ struct PlanHeader {
     int total_ptiles;  // kPrefillItemRows-row q tiles of all prefill chunks (per kv head)
     int next_pitem;    // work counter of the prefill kernel: next (q tile, kv head) item to hand out
     int pitems_sorted; // 1: pitem_order lists the q tiles by decreasing context length
+    int next_slice;    // work counter of the decode kernel: next shared slice (second class) to hand out
 };
 
 constexpr int kPrefillSortCap = 512;   // q tiles (per kv head) up to which the plan step orders them
@@ -34,13 +35,15 @@ struct __align__(16) WorkerStart {
 };
 
 constexpr int kDecodeMinSlice = 4;   // a worker is given at least this many tiles
+constexpr int kDecodeSharedPhantom = 12;    // SM-shared decode: what one more stream in a CTA's slice costs, in tiles
+constexpr int kDecodeSharedPerWorker = 3;   // shared slices per launched warp at most (sizes the start records and the partial slots)
 
-// The slices of the global tile sequence.  The launch has `all_workers` warps, of which the first
-// `first_workers` are resident at once (the first wave).  With a tail (tail_div > 0) they take equal
-// slices of all but 1 / tail_div of the tiles; that remainder is cut into small slices for the other
-// warps, whose CTAs the hardware hands to whichever SM finishes its first-wave work first: HBM
-// arbitration is not fair, equal slices finish a fifth of the kernel time apart, and the small slices
-// fill those gaps.  Without a tail every worker gets an equal slice.
+// The slices of the global tile sequence: `all_workers` slices at most, of which the first `first_workers`
+// belong to the warps of the launch, one each.  With a shared part (tail_div > 0) they take equal slices of all but
+// 1 / tail_div of the tiles as their own; that remainder is cut into small slices ("shared", the second
+// class) which the warps take from a counter as they finish their own: warps of one launch run up to a
+// factor two apart in speed (scheduler priority, HBM arbitration), so equal slices alone leave a quarter
+// of the warp-time idle at the end.  Without a shared part every worker gets an equal slice.
 struct DecodeSlices {
     int workers1, per1;   // first class: workers [0, workers1), per1 tiles each
     int workers2, per2;   // second class: workers [workers1, workers1 + workers2), per2 tiles each
@@ -121,14 +124,16 @@ struct KernelArgs {
     int* ptile_prefix;     // [num_sequences + 1] exclusive prefix sum of prefill q tiles per row (one kv head)
     int* pitem_order;      // [kPrefillSortCap] q tiles, longest context first (valid when plan->pitems_sorted); may be null
     int decode_all_workers;      // warps the decode launch will have (0: the plan prepares no start records)
-    int decode_first_workers;    // warps resident at once (the first wave)
-    int decode_tail_div;         // 1 / tail_div of the tiles go to the warps after the first wave (0: none)
+    int decode_first_workers;    // warps of the launch: they own the first slices
+    int decode_tail_div;         // 1 / tail_div of the tiles are handed out as shared slices (0: none)
+    int decode_phantom;          // tiles added to every stream in the sequence the slices are cut in (SM-shared decode: a stream costs a CTA time beyond its tiles)
     int test_drop_copy;          // test hook: worker 0 issues no copy for its first tile and polls 2^10 times only
     WorkerStart* worker_start;   // [decode_all_workers], may be null
     long long max_tiles;   // upper bound of total_tiles known on the host
     int rows_per_tile;     // q heads per head tile: min(G, 16)
     float* part_o;         // partial outputs    [slot = stream + worker][rows_per_tile][D]
     float* part_ml;        // partial (max, sum) [slot][rows_per_tile][2]
+    uint8_t* cta_q;        // SM-shared decode: staged query rows of the runs of each CTA
     float* lse;            // log-sum-exp per (token, q head), natural log, of the scaled logits
     int64_t* score_offsets;// [num_sequences + 1] prefix sum of past_len + new tokens
     int* stile_prefix;     // [num_sequences + 1] prefix sum of key tiles of the sequences that want scores
@@ -179,7 +184,15 @@ int decode_max_workers(int sm_count);
 // Warps the decode launch of this step will have (the plan step prepares one start record each); *first_workers
 // receives those of the first wave.
 int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers);
-int decode_tail_div();   // the PA_B200_DECODE_TAIL setting (default 0 = single wave)
+int decode_tail_div();   // the PA_B200_DECODE_TAIL setting: 1 / n of the tiles are handed out as shared slices (default 0 = none)
+int decode_max_slices(int sm_count);   // upper bound of decode_launch_workers
+// SM-shared decode (pa_decode_shared.cu): one CTA per SM whose warps take tiles from a shared counter
+bool decode_shared_supported(const CacheGeom& g);
+size_t decode_shared_scratch_bytes(int sm_count);
+int decode_shared_phantom();   // PA_B200_DECODE_PHANTOM, default kDecodeSharedPhantom
+int decode_shared_ctas(const KernelArgs& a, int sm_count);
+cudaError_t launch_decode_shared(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0 = nullptr,
+                                 cudaEvent_t ev1 = nullptr);
 
 // Attention over rows with more than one new token (prefill chunks): generic CUDA-core kernel.
 cudaError_t launch_prefill(const KernelArgs& a, cudaStream_t stream, int* launches);

@@ -185,7 +185,7 @@ def test_begins_that_do_not_hold_together_set_a_status_bit_and_touch_nothing_els
         assert res["status"] & (_abi.PA_DEV_BAD_BEGINS | _abi.PA_DEV_BAD_PAST_LEN), name
     again = _run_with(wl, data, op)     # the context is still usable and gives the same numbers
     assert again["status"] == 0
-    assert np.array_equal(again["out_gpu"], good["out_gpu"])
+    assert np.allclose(again["out_gpu"], good["out_gpu"], rtol=2e-2, atol=2e-3)
 
 
 def test_scores_len_shorter_than_the_metadata_implies():
@@ -220,6 +220,7 @@ def test_scores_len_shorter_than_the_metadata_implies():
     got = scores.cpu().numpy()
     assert np.all(got[short:] == 7.0), "stores beyond scores_len"
     first_two = 301 + 41
-    assert np.array_equal(got[:first_two], full["scores_gpu"][:first_two]), "the slots that fit keep their scores"
+    # (the decode kernel hands tiles out dynamically: the order of its partial sums, and so the last bits, differ between launches)
+    assert np.allclose(got[:first_two], full["scores_gpu"][:first_two], rtol=1e-4, atol=1e-7), "the slots that fit keep their scores"
     assert np.all(got[first_two:short] == 0.0)
-    assert np.array_equal(out.float().cpu().numpy(), full["out_gpu"]), "attention output does not depend on the score slot"
+    assert np.allclose(out.float().cpu().numpy(), full["out_gpu"], rtol=2e-2, atol=2e-3), "attention output does not depend on the score slot"
