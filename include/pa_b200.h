@@ -263,14 +263,15 @@ int pa_b200_marshal_inputs(pa_handle* h, const pa_marshal_args* args);
  *  - A step whose scratch need exceeds the fixed array is rejected with PA_ERR_TOO_LARGE (the
  *    message gives both sizes).  With G = Hq / Hkv the need is a few KB of counters plus
  *    (num_sequences * Hkv * ceil(G/16) + 16 * SM count) * min(G,16) * (head_size + 2) * 4 bytes:
- *    about 6 MB for 64 sequences of the 32/8-head, 128-dim shape on a 148-SM GPU.
+ *    about 6 MB for 64 sequences of the 32/8-head, 128-dim shape on a 148-SM GPU, about 20 MB with more than 16 query
+ *    heads per KV head (the array holds 32 MB).
  *  - The first call on a device looks up the array's device address; make that call before any
  *    stream capture.
  *  - All calls on a device share the array: two calls that overlap on the GPU (different streams)
  *    race.  Every call rewrites the parts that must start from a known state.
  *  - Block-index errors are still skipped on the device, but this entry point has no way to
  *    report the device status word; use pa_b200_forward to diagnose inputs. */
-#define PA_B200_STATIC_SCRATCH_BYTES (16u << 20)
+#define PA_B200_STATIC_SCRATCH_BYTES (32u << 20)
 int pa_b200_decode_step_static(const pa_model_desc* desc, const pa_forward_args* args, int device);
 
 #ifdef __cplusplus

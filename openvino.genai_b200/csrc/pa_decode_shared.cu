@@ -284,7 +284,6 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
             ctl->pos = off % r_tiles;
         }
     }
-    __syncthreads();
 
     // ---- consumer state (per warp) -------------------------------------------------------------------
     uint32_t qa[NKK][2];            // live A registers of the query fragments
@@ -415,7 +414,7 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
 
     bool ch_started_before = false;
     for (;;) {   // chapters
-        // ---- thread 0 lists the runs of the chapter ---------------------------------------------------
+        // ---- thread 0 lists the runs of the chapter (walk state in registers while it does) --------------------
         if (tid == 0) {
             const int total_tiles = a.plan->total_tiles;
             const DecodeSlices sl = decode_slices(total_tiles, nctas, nctas, 0);
@@ -423,17 +422,20 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
             int g_tile = ctl->g_tile, seq = ctl->seq;
             int nruns = 0, ntiles = 0, nblk = 0;
             int r_s = ctl->r_s, hk = ctl->hk, r_tiles = ctl->r_tiles, p0 = ctl->p0, pos = ctl->pos;
+            int w_ctx = ctl->ctx, w_tb = ctl->tb, w_nb = ctl->nb, w_t0 = ctl->t0row;
+            bool cont = ctl->cont != 0;
             // a run cut by the previous chapter goes on with its record (and its staged query rows)
-            if (ctl->cont) --seq;
-            ctl->first_seq = seq;
-            ctl->new_first = ctl->cont ? seq + 1 : seq;
+            if (cont) --seq;
+            const int first_seq = seq, new_first = cont ? seq + 1 : seq;
             // The slices are cut in a sequence in which every stream is followed by a.decode_phantom tiles that do not
             // exist: a CTA whose slice holds many streams (each costs it time beyond its tiles) gets fewer tiles.
             const int ph = a.decode_phantom;
+            const unsigned per1 = (unsigned)sl.per1;   // one class of slices: worker of a tile = tile / per1
             while (g_tile < g_end && nruns < kShRuns && ntiles < Cfg::TILES) {
                 ShRun& r = runs[seq % kShRuns];
-                const bool fresh = seq >= ctl->new_first;
+                const bool fresh = seq >= new_first;
                 bool have = true;
+                int total = 0, upto = 0, vtail = 0;
                 if (fresh) {
                     const int v_all = min(r_tiles - pos, g_end - g_tile);              // tiles of the stream in the slice, phantoms included
                     const int n_all = max(0, min(pos + v_all, r_tiles - ph) - pos);   // real ones
@@ -441,29 +443,33 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
                         g_tile += v_all; pos += v_all;
                         have = false;
                     } else {
-                        const int s_begin = p0 * Hkv + hk * r_tiles;   // global tile range of the stream
-                        const int first_w = sl.worker_of(s_begin), last_w = sl.worker_of(s_begin + r_tiles - ph - 1);
+                        const unsigned s_begin = (unsigned)(p0 * Hkv + hk * r_tiles);   // global tile range of the stream
+                        const int first_w = (int)(s_begin / per1), last_w = (int)((s_begin + (unsigned)(r_tiles - ph - 1)) / per1);
                         const int stream = r_s * Hkv + hk;
                         long long score_off = -1;
                         if constexpr (SC) {
                             if (a.score_aggregation_window[r_s] > 0) {
                                 const long long off = a.score_offsets[r_s];
-                                if (off >= 0 && off + ctl->ctx <= a.scores_len) score_off = ((long long)hk * a.scores_len + off) * 8;
+                                if (off >= 0 && off + w_ctx <= a.scores_len) score_off = ((long long)hk * a.scores_len + off) * 8;
                                 else atomicOr(a.status, PA_DEV_BAD_BEGINS);
                             }
                         }
-                        r.t0 = ctl->t0row; r.hk = hk; r.stream = stream; r.nparts = last_w - first_w + 1;
-                        r.first_slot = stream + first_w; r.slot = stream + cta; r.total = n_all; r.upto = 0; r.ctx = ctl->ctx;
-                        r.score_off = score_off; r.tb = ctl->tb; r.nb = ctl->nb; r.vtail = v_all - n_all;
+                        r.t0 = w_t0; r.hk = hk; r.stream = stream; r.nparts = last_w - first_w + 1;
+                        r.first_slot = stream + first_w; r.slot = stream + cta; r.total = n_all; r.ctx = w_ctx;
+                        r.score_off = score_off; r.tb = w_tb; r.nb = w_nb; r.vtail = v_all - n_all;
+                        total = n_all; vtail = v_all - n_all;
                     }
+                } else {
+                    total = r.total; upto = r.upto; vtail = r.vtail;
                 }
                 if (have) {
-                    const int n = min(r.total - r.upto, Cfg::TILES - ntiles);
+                    const int n = min(total - upto, Cfg::TILES - ntiles);
                     r.g_first = ntiles; r.n_ch = n; r.tok_base = pos * kTile; r.blk_base = nblk; r.next = 0;
-                    r.upto += n;
-                    ctl->cont = r.upto < r.total;
+                    upto += n;
+                    r.upto = upto;
+                    cont = upto < total;
                     ntiles += n; nblk += n * NREC; g_tile += n; pos += n;
-                    if (r.upto == r.total) { g_tile += r.vtail; pos += r.vtail; }   // past the stream's phantoms
+                    if (!cont) { g_tile += vtail; pos += vtail; }   // past the stream's phantoms
                     ++seq; ++nruns;
                 }
                 if (pos == r_tiles && g_tile < g_end) {   // next stream
@@ -475,15 +481,17 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
                             p0 = __ldcg(a.tile_prefix + r_s);
                             r_tiles = __ldcg(a.tile_prefix + r_s + 1) - p0;
                         } while (r_tiles == 0);
-                        ctl->ctx = a.past_lens[r_s] + 1;
-                        ctl->tb = a.block_indices_begins[r_s];
-                        ctl->nb = a.block_indices_begins[r_s + 1] - ctl->tb;
-                        ctl->t0row = a.subsequence_begins[r_s];
+                        w_ctx = a.past_lens[r_s] + 1;
+                        w_tb = a.block_indices_begins[r_s];
+                        w_nb = a.block_indices_begins[r_s + 1] - w_tb;
+                        w_t0 = a.subsequence_begins[r_s];
                     }
                 }
             }
             ctl->r_s = r_s; ctl->hk = hk; ctl->r_tiles = r_tiles; ctl->p0 = p0; ctl->pos = pos;
-            ctl->g_tile = g_tile; ctl->seq = seq;
+            ctl->ctx = w_ctx; ctl->tb = w_tb; ctl->nb = w_nb; ctl->t0row = w_t0;
+            ctl->g_tile = g_tile; ctl->seq = seq; ctl->cont = cont ? 1 : 0;
+            ctl->first_seq = first_seq; ctl->new_first = new_first;
             ctl->nruns = nruns; ctl->ntiles = ntiles; ctl->win_lo = 0;
             ctl->more = g_tile < g_end;
         }
@@ -504,40 +512,6 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
                     if (b < 0 || b >= a.num_blocks) { b = 0; ctl->bad = 1; }
                 }
                 blk[r.blk_base + j] = b;
-            }
-        }
-        // Query rows of the chapter's new runs: f16, prescaled, in the register order of the fragments (lane (g, c) of a
-        // consumer reads its 16 registers of row g as four 16-byte loads), with the row's sum and softmax scale.  Staged in
-        // global scratch of the CTA: it is read once per (warp, run) and comes from the L2.
-        {
-            const int npairs = (ch_first + ch_nruns - ch_new) * RT;
-            for (int p = warp; p < npairs; p += nwarps) {
-                const int seq = ch_new + p / RT, hrow = p % RT;
-                const ShRun& r = runs[seq % kShRuns];
-                uint8_t* entry = cta_q + (size_t)(seq % kShRuns) * kShQEntry;
-                const long long qoff = ((long long)r.t0 * a.g.Hq + r.hk * RT + hrow) * D + lane * 4;
-                float q[4];
-                load_act_vec<4>(a.query, qoff, a.g.act, q);
-                float amax = fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3])));
-#pragma unroll
-                for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                float qmul = 1.f;  // exact power-of-two prescale that keeps |q| inside the f16 range
-                if (amax > 32768.f && amax < INFINITY) {
-                    int ex;
-                    frexpf(amax, &ex);
-                    qmul = ldexpf(1.f, 15 - ex);
-                }
-                const uint32_t lo = pack_h2(q[0] * qmul, q[1] * qmul), hi = pack_h2(q[2] * qmul, q[3] * qmul);
-                const __half2 hl = *reinterpret_cast<const __half2*>(&lo), hh = *reinterpret_cast<const __half2*>(&hi);
-                float sum = __low2float(hl) + __high2float(hl) + __low2float(hh) + __high2float(hh);
-#pragma unroll
-                for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                // dims 4*lane .. 4*lane+3 are k-step 4*h + i of consumer lane (hrow, cc): h = lane / 16, cc = (lane % 16) / 4, i = lane % 4
-                const int ks = 4 * (lane >> 4) + (lane & 3), cc = (lane & 15) >> 2;
-                const int reg = 2 * ks;   // registers reg, reg + 1 of that lane
-                uint32_t* dst = reinterpret_cast<uint32_t*>(entry) + ((reg >> 2) * 32 + 4 * hrow + cc) * 4 + (reg & 3);
-                __stcg(reinterpret_cast<uint2*>(dst), make_uint2(lo, hi));
-                if (lane == 0) __stcg(reinterpret_cast<float2*>(entry + 2048) + hrow, make_float2(sum, sm_scale * kLog2e / qmul));
             }
         }
         __syncthreads();
@@ -610,6 +584,43 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
 
 #pragma unroll
         for (int p = 0; p < NS - 1; ++p) produce(p);
+
+        // (staged while the first tiles are on their way)
+        // Query rows of the chapter's new runs: f16, prescaled, in the register order of the fragments (lane (g, c) of a
+        // consumer reads its 16 registers of row g as four 16-byte loads), with the row's sum and softmax scale.  Staged in
+        // global scratch of the CTA: it is read once per (warp, run) and comes from the L2.
+        {
+            const int npairs = (ch_first + ch_nruns - ch_new) * RT;
+            for (int p = warp; p < npairs; p += nwarps) {
+                const int seq = ch_new + p / RT, hrow = p % RT;
+                const ShRun& r = runs[seq % kShRuns];
+                uint8_t* entry = cta_q + (size_t)(seq % kShRuns) * kShQEntry;
+                const long long qoff = ((long long)r.t0 * a.g.Hq + r.hk * RT + hrow) * D + lane * 4;
+                float q[4];
+                load_act_vec<4>(a.query, qoff, a.g.act, q);
+                float amax = fmaxf(fmaxf(fabsf(q[0]), fabsf(q[1])), fmaxf(fabsf(q[2]), fabsf(q[3])));
+#pragma unroll
+                for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                float qmul = 1.f;  // exact power-of-two prescale that keeps |q| inside the f16 range
+                if (amax > 32768.f && amax < INFINITY) {
+                    int ex;
+                    frexpf(amax, &ex);
+                    qmul = ldexpf(1.f, 15 - ex);
+                }
+                const uint32_t lo = pack_h2(q[0] * qmul, q[1] * qmul), hi = pack_h2(q[2] * qmul, q[3] * qmul);
+                const __half2 hl = *reinterpret_cast<const __half2*>(&lo), hh = *reinterpret_cast<const __half2*>(&hi);
+                float sum = __low2float(hl) + __high2float(hl) + __low2float(hh) + __high2float(hh);
+#pragma unroll
+                for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                // dims 4*lane .. 4*lane+3 are k-step 4*h + i of consumer lane (hrow, cc): h = lane / 16, cc = (lane % 16) / 4, i = lane % 4
+                const int ks = 4 * (lane >> 4) + (lane & 3), cc = (lane & 15) >> 2;
+                const int reg = 2 * ks;   // registers reg, reg + 1 of that lane
+                uint32_t* dst = reinterpret_cast<uint32_t*>(entry) + ((reg >> 2) * 32 + 4 * hrow + cc) * 4 + (reg & 3);
+                __stcg(reinterpret_cast<uint2*>(dst), make_uint2(lo, hi));
+                if (lane == 0) __stcg(reinterpret_cast<float2*>(entry + 2048) + hrow, make_float2(sum, sm_scale * kLog2e / qmul));
+            }
+        }
+        __syncthreads();
 
         for (int it = 0; !dead; ++it) {
             __syncwarp();  // every lane is done with the stage that is refilled next
@@ -824,6 +835,8 @@ cudaError_t launch_shared_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
 
 }  // namespace
 
+
+int decode_shared_chapter_tiles(const CacheGeom& g) { return g.bs == 32 ? ShCfg<128, 32>::TILES : ShCfg<128, 16>::TILES; }
 
 int decode_shared_phantom() {
     static const int v = [] {
