@@ -241,7 +241,7 @@ def stored_traffic(wl_name: str):
     text = tp.read_text()
     m = re.search(r"dram_bytes_per_launch:\s*(\d+)", text)
     h = re.search(r"kernel_source_sha16:\s*([0-9a-f]{16})", text)
-    src = ROOT / "openvino.genai_b200" / "csrc" / "pa_decode.cu"
+    src = ROOT / "openvino.genai_b200" / "csrc" / "pa_decode_shared.cu"
     now = hashlib.sha256(src.read_bytes()).hexdigest()[:16]
     if not m or not h or h.group(1) != now:
         return None, "no ncu capture of the current kernel source is committed"
@@ -341,7 +341,7 @@ def measure_headline(env: Env, args) -> dict:
             "tokens_per_s": round(total_seqs / (ms_step * 1e-3), 1),
             "hbm_peak_frac_step": round(value / world / peak, 4),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                         "traffic": traffic, "traffic_source": traffic_source, "kernel": "decode_kernel (split-K paged decode)", "kernel_ms": round(kernel_ms, 4),
+                         "traffic": traffic, "traffic_source": traffic_source, "kernel": "decode_shared_kernel (paged decode, one CTA per SM, tiles handed to its warps from shared-memory counters)", "kernel_ms": round(kernel_ms, 4),
                          "kernel_timed": "20 launches in a loop of their own, CUDA events around the kernel on its stream",
                          "algorithmic_bytes_per_launch": kv_bytes, "peak_source": env.peaks["source"]},
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -1,23 +1,28 @@
-// Paged decode attention for sm_100a, SM-shared variant: u8 cache, up to 8 query heads per KV head.
+// Paged decode attention for sm_100a, SM-shared variant: u8 cache, head size 128, up to 8 query heads per KV head.
 //
-// Same arithmetic as decode_kernel (pa_decode.cu) - mma.sync m16n8k16 with the GQA group on M, bytes
-// as exact f16 (1024 + byte), online softmax with a lazy reference maximum - but the work is handed
-// out differently.  There, every warp owns a fixed slice of the tile sequence; warps of one launch run
-// up to a factor two apart in speed and every stream boundary inside a slice costs a chain of
-// dependent global loads, so the slowest warp decides the kernel time.  Here one CTA per SM owns a
-// slice and its warps take 32-token tiles from a counter in shared memory:
-//   * per "chapter" (up to kShRuns runs, kShTiles tiles) thread 0 walks the slice and lists its runs
-//     (consecutive tiles of one stream); all threads then stage the block ids of every tile and the
-//     query rows of every run (f16, prescaled, with their sums) in shared memory - the only global
-//     metadata reads of the chapter, made once per CTA instead of once per warp;
-//   * a warp's loader takes the next tile index (atomicAdd in shared memory), looks its run and block
-//     up in the tables and issues the bulk copies into its private two-stage ring;
-//   * a warp that leaves a run (its next tile belongs to another run, or none is left) publishes its
-//     partial (m, l, O) to a per-(CTA, run, warp) slot; the warp whose tiles complete the run reduces
-//     the partials of the CTA and then either writes the output (the stream lies in this CTA alone) or
-//     publishes the CTA's partial exactly as a worker of decode_kernel does (slot = stream + CTA).
-// No warp waits for another one except at chapter boundaries (__syncthreads); every mbarrier wait is
-// bounded and a wait that runs out makes the whole CTA stop taking tiles.
+// Same arithmetic as decode_kernel (pa_decode.cu) - mma.sync m16n8k16 with the GQA group on M, bytes as exact f16
+// (1024 + byte), online softmax with a lazy reference maximum - but the work is handed out differently.  There, every
+// warp owns a fixed slice of the tile sequence; warps of one launch run up to a factor two apart in speed and every
+// stream boundary inside a slice costs a chain of dependent global loads, so the slowest warp decides the kernel time.
+// Here one CTA per SM owns a slice and its warps take 32-token tiles from counters in shared memory:
+//   * per "chapter" (up to kShRuns runs and ShCfg::TILES tiles) thread 0 walks the slice and lists its runs (consecutive
+//     tiles of one stream); all threads then stage the block ids of every tile in shared memory and the query rows of
+//     every run - f16, prescaled, in the register order of the fragments, with their sums - in a global scratch of the
+//     CTA: the global metadata reads of the chapter are made once per CTA instead of once per warp;
+//   * the warps spread over a window of kShAcc runs in proportion to the runs' tiles; every run hands its tiles out from
+//     its own counter (atomicAdd in shared memory), a warp stays with a run until the run has no tile left and then moves
+//     on inside the window, which slides as its first runs are used up; the loader of a warp looks run and block up in
+//     the tables and issues the bulk copies into the warp's private two-stage ring;
+//   * a warp that leaves a run adds its partial (m, l, O) to the run's accumulator in shared memory (a ring of kShAcc
+//     accumulators, each behind a lock); the warp whose tiles complete the run takes the result out and either writes the
+//     output (the stream lies in this CTA alone) or publishes the CTA's partial exactly as a worker of decode_kernel does
+//     (slot = stream + CTA), the CTA that completes the stream merging the partials;
+//   * the slices are cut in a sequence in which every stream is followed by a few tiles that do not exist
+//     (KernelArgs::decode_phantom), so that a CTA whose slice holds many streams gets fewer tiles.
+// The order in which partials are added depends on timing, so the last bits of the output differ between launches.
+// No warp waits for another one except at chapter boundaries (__syncthreads) and at an accumulator's lock; every wait
+// on an mbarrier or a lock is bounded, and one that runs out sets a status bit and makes the CTA stop taking tiles.
+// HBM-bound: 2*Hkv*(D+8) bytes per context token.
 #include <algorithm>
 #include <atomic>
 #include <cstdlib>
