@@ -217,7 +217,7 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     k.test_drop_copy = h->test_drop_copy ? 1 : 0;
     // SM-shared kernel while a CTA's slice fits two of its chapters; longer slices go to the warp-per-slice kernel, whose
     // fixed slices cost nothing per chapter and balance well when every warp has hundreds of tiles
-    const bool shared_decode = pa::decode_shared_supported(h->g) && k.max_tiles <= (long long)h->sm_count * pa::decode_shared_chapter_tiles(h->g) * 2;
+    const bool shared_decode = pa::decode_shared_supported(h->g) && k.max_tiles <= (long long)h->sm_count * pa::decode_shared_chapter_tiles(h->g) * pa::decode_shared_max_chapters();
     if (shared_decode) {   // one CTA per SM is the worker; its warps share the slice
         k.decode_tail_div = 0;
         k.decode_phantom = pa::decode_shared_phantom();

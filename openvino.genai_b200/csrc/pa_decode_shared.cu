@@ -534,15 +534,24 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
             pr = 0;
             while (pr + 1 < wn && target >= runs[(ch_first + pr) % kShRuns].g_first + runs[(ch_first + pr) % kShRuns].n_ch) ++pr;
         }
+        int ahead = 0;            // lane 0: index already taken from the counter of run `pr` for the next call
+        bool have_ahead = false;  // (the atomic's latency then falls into the tile's arithmetic, not into the loader)
         auto produce = [&](int slot) {
             int k = -1;
             if (!*reinterpret_cast<volatile int*>(&ctl->abort)) {
                 for (int tries = 0; tries <= ch_nruns; ++tries) {
                     ShRun& rr = runs[(ch_first + pr) % kShRuns];
                     int kk = rr.n_ch;
-                    if (lane == 0 && *reinterpret_cast<volatile int*>(&rr.next) < rr.n_ch) kk = atomicAdd(&rr.next, 1);
+                    if (have_ahead) kk = ahead;
+                    else if (lane == 0 && *reinterpret_cast<volatile int*>(&rr.next) < rr.n_ch) kk = atomicAdd(&rr.next, 1);
+                    have_ahead = false;
                     kk = __shfl_sync(0xffffffffu, kk, 0);
-                    if (kk < rr.n_ch) { k = kk; break; }
+                    if (kk < rr.n_ch) {
+                        k = kk;
+                        if (lane == 0) ahead = *reinterpret_cast<volatile int*>(&rr.next) < rr.n_ch ? atomicAdd(&rr.next, 1) : rr.n_ch;
+                        have_ahead = true;
+                        break;
+                    }
                     // the run is used up: slide the window past used-up runs, go to the next run inside it
                     int lo = 0;
                     if (lane == 0) {
@@ -680,22 +689,28 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
             const uint8_t* st = ring + slot * Cfg::STAGE;
             const int valid = d.valid;
 
-            // ---- S = Q.K^T over four 8-token n-tiles ------------------------------------------------
+            // ---- S = Q.K^T over four 8-token n-tiles: the four accumulator chains advance together -------------------
             float sacc[4][2];
+            {
+                uint4 kw[4][D / 64];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float c0 = 0.f, c1 = 0.f;
-                const int row = 8 * (g >> 1) + 2 * j + (g & 1);
-                const uint8_t* kp = st + (row / BS) * Cfg::REC + (row % BS) * D + 16 * c;
+                for (int j = 0; j < 4; ++j) {
+                    const int row = 8 * (g >> 1) + 2 * j + (g & 1);
+                    const uint8_t* kp = st + (row / BS) * Cfg::REC + (row % BS) * D + 16 * c;
 #pragma unroll
-                for (int h = 0; h < D / 64; ++h) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(kp + 64 * h);
-                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)  // bytes stay offset by 1024; removed with the zero-point
-                        mma_lo(c0, c1, qa[4 * h + i][0], qa[4 * h + i][1], __byte_perm(ww[i], 0x64646464u, 0x4140), __byte_perm(ww[i], 0x64646464u, 0x4342));
+                    for (int h = 0; h < D / 64; ++h) kw[j][h] = *reinterpret_cast<const uint4*>(kp + 64 * h);
                 }
-                sacc[j][0] = c0; sacc[j][1] = c1;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { sacc[j][0] = 0.f; sacc[j][1] = 0.f; }
+#pragma unroll
+                for (int h = 0; h < D / 64; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {   // bytes stay offset by 1024; removed with the zero-point
+                            const uint32_t w = i == 0 ? kw[j][h].x : i == 1 ? kw[j][h].y : i == 2 ? kw[j][h].z : kw[j][h].w;
+                            mma_lo(sacc[j][0], sacc[j][1], qa[4 * h + i][0], qa[4 * h + i][1], __byte_perm(w, 0x64646464u, 0x4140), __byte_perm(w, 0x64646464u, 0x4342));
+                        }
             }
 
             // ---- scale, mask, online softmax -----------------------------------------------------------
@@ -842,6 +857,15 @@ cudaError_t launch_shared_t(const KernelArgs& a, cudaStream_t stream, int sm_cou
 
 
 int decode_shared_chapter_tiles(const CacheGeom& g) { return g.bs == 32 ? ShCfg<128, 32>::TILES : ShCfg<128, 16>::TILES; }
+
+int decode_shared_max_chapters() {
+    static const int v = [] {
+        const char* e = std::getenv("PA_B200_DECODE_SHARED_CHAPTERS");
+        const int n = e ? std::atoi(e) : 4;
+        return n < 1 ? 1 : n;
+    }();
+    return v;
+}
 
 int decode_shared_phantom() {
     static const int v = [] {

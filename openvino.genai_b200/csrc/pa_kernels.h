@@ -190,6 +190,7 @@ int decode_max_slices(int sm_count);   // upper bound of decode_launch_workers
 bool decode_shared_supported(const CacheGeom& g);
 size_t decode_shared_scratch_bytes(int sm_count);
 int decode_shared_chapter_tiles(const CacheGeom& g);   // tiles a CTA stages block ids for at a time
+int decode_shared_max_chapters();   // PA_B200_DECODE_SHARED_CHAPTERS, default 2: longer slices go to the warp-per-slice kernel
 int decode_shared_phantom();   // PA_B200_DECODE_PHANTOM, default kDecodeSharedPhantom
 int decode_shared_ctas(const KernelArgs& a, int sm_count);
 cudaError_t launch_decode_shared(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0 = nullptr,
