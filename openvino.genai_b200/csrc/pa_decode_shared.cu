@@ -79,8 +79,8 @@ static_assert(sizeof(ShRun) % 16 == 0, "run records are copied as a whole");
 // Header of one accumulator of the ring: the reduction of the warps' partials of one run.
 struct __align__(16) ShAcc {
     int lock;    // 0 free, 1 held
-    int owner;   // sequence number of the run that is being reduced here, -1: none
-    int tiles;   // tiles reduced so far
+    int turn;    // sequence number of the run this accumulator serves now: entry e serves the runs e, e + kShAcc, ... in order
+    int tiles;   // tiles of that run reduced so far
     int pad;
 };
 
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
         const DecodeSlices sl = decode_slices(total_tiles, nctas, nctas, 0);
         const int g_tile = (int)sl.begin(cta), g_end = (int)sl.end(cta);
         ctl->abort = 0;
-        for (int i = 0; i < kShAcc; ++i) accs[i] = ShAcc{0, -1, 0, 0};
+        for (int i = 0; i < kShAcc; ++i) accs[i] = ShAcc{0, i, 0, 0};
         ctl->bad = 0;
         ctl->seq = 0;
         ctl->cont = 0;
@@ -311,16 +311,16 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
         l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
         z += __shfl_xor_sync(0xffffffffu, z, 1); z += __shfl_xor_sync(0xffffffffu, z, 2);
         const ShRun fin = runs[seq % kShRuns];
-        // ---- take the lock of the accumulator while it serves this run (or nobody); an older run that still owns it
-        // completes without this warp's help, so the wait ends; it is bounded all the same
+        // ---- take the lock of the accumulator once it is this run's turn.  The runs of an entry are served strictly in
+        // order, so a wait here is always for an older run; a warp holds the partial of one run at a time and needs nothing
+        // from a newer run to add it, so the oldest unfinished run of an entry can always finish and the waits end (they are
+        // bounded all the same).  Serving whichever run comes first instead would deadlock: a warp may already have taken a
+        // tile of the newer run when it comes here with the partial of the older one.
         int state = 0;   // 1: first partial of the run, 2: a later one, 0: not acquired
-        SPROF(const long long pl0 = clock64(); ++pflush;)
         for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
             if (lane == 0) {
                 if (atomicCAS(&hd->lock, 0, 1) == 0) {
-                    const int owner = *reinterpret_cast<volatile int*>(&hd->owner);
-                    if (owner == seq) state = 2;
-                    else if (owner == -1) { hd->owner = seq; hd->tiles = 0; state = 1; }
+                    if (*reinterpret_cast<volatile int*>(&hd->turn) == seq) state = *reinterpret_cast<volatile int*>(&hd->tiles) == 0 ? 1 : 2;
                     else atomicExch(&hd->lock, 0);
                 }
             }
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
             }
         }
         __syncwarp();
-        if (lane == 0) { hd->owner = -1; __threadfence_block(); atomicExch(&hd->lock, 0); }
+        if (lane == 0) { hd->turn = seq + kShAcc; hd->tiles = 0; __threadfence_block(); atomicExch(&hd->lock, 0); }
         if (fin.nparts > 1) {
             // the stream has tiles in other CTAs: publish the CTA's partial; the CTA that completes the stream merges
             float* po = a.part_o + (long long)fin.slot * part_stride;

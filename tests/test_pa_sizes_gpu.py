@@ -224,3 +224,24 @@ def test_scores_len_shorter_than_the_metadata_implies():
     assert np.allclose(got[:first_two], full["scores_gpu"][:first_two], rtol=1e-4, atol=1e-7), "the slots that fit keep their scores"
     assert np.all(got[first_two:short] == 0.0)
     assert np.allclose(out.float().cpu().numpy(), full["out_gpu"], rtol=2e-2, atol=2e-3), "attention output does not depend on the score slot"
+
+
+def test_decode_with_thousands_of_short_streams_per_step():
+    """2000 sequences of 1 to 70 tokens over 4 KV heads: every CTA of the decode kernel meets dozens of streams, more than one
+    run table holds, so its chapters end because of the run count; streams of one tile, contexts that end on a tile boundary."""
+    rng = np.random.default_rng(5)
+    past = rng.integers(0, 70, 2000)
+    past[:8] = [0, 31, 32, 63, 64, 1, 30, 33]
+    wl = H.small_workload(hq=16, hkv=4, d=128, bs=32, act=torch.bfloat16, cache="u8", past=past, new=np.ones(2000, np.int64), seed=131)
+    res = run_step_on_gpu_filled_cache(wl)
+    check(res, "u8", bf16_output=True)
+
+
+def test_decode_slices_longer_than_one_chapter():
+    """24 sequences of about 30 000 tokens over 8 KV heads: a CTA's slice is about 1200 tiles, two chapters, and streams of
+    940 tiles are cut by chapter boundaries (their runs keep their accumulators across the boundary)."""
+    rng = np.random.default_rng(6)
+    past = rng.integers(29000, 31000, 24)
+    wl = H.small_workload(hq=32, hkv=8, d=128, bs=32, act=torch.bfloat16, cache="u8", past=past, new=np.ones(24, np.int64), seed=137)
+    res = run_step_on_gpu_filled_cache(wl)
+    check(res, "u8", bf16_output=True)
