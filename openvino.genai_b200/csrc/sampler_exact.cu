@@ -571,7 +571,7 @@ __device__ void classify_bins(ExactShared& sh, int j_from, float s, uint32_t cnt
             if (wanted_before <= (unsigned long long)room) { sh.flag[j] = fsx::kBinCollect; continue; }
         }
         const bool same_hyp = (sh.flag[j] & fsx::kBinValid) && sh.E[j] == Eh[k];
-        if (!same_hyp) { sh.E[j] = (uint8_t)Eh[k]; sh.flag[j] = fsx::kBinDirty; sh.A[j] = 0; }
+        if (!same_hyp) { sh.E[j] = (uint8_t)Eh[k]; sh.flag[j] = fsx::kBinDirty; sh.A[j] = 0; sh.PA[j] = 0; }
     }
     for (int i = tid; i < fsx::kBins / 32; i += kThreads) sh.tie_bits[i] = 0;
     __syncthreads();
@@ -672,13 +672,17 @@ __device__ void pass_amounts(ExactShared& sh, const RowCtx& c) {
             const int pos = atomicAdd(&sh.list_n, 1);
             if (pos < kListCap) sh.list[pos] = fsx::make_entry(key, (uint32_t)i);
         } else if (f & fsx::kBinDirty) {
+            // the amount (below 2^24) goes in as two 16-bit pieces (A: low, PA: high; PA is rebuilt by prepare_walk afterwards):
+            // neither piece can overflow while the bin has fewer than 2^16 elements, so no result of an atomic is needed and
+            // the additions do not wait for one another
             bool tie;
             const uint32_t amount = fsx::plain_amount(p, fsx::amount_scale(sh.E[j]), &tie);
             if (!tie) {
-                const uint32_t old = atomicAdd(&sh.A[j], amount);
-                tie = old + amount >= 0x80000000u;   // too much for one binade: never taken as a whole
+                atomicAdd(&sh.A[j], amount & 0xffffu);
+                atomicAdd(&sh.PA[j], amount >> 16);
+            } else {
+                atomicOr(&sh.tie_bits[j >> 5], 1u << (j & 31));
             }
-            if (tie) atomicOr(&sh.tie_bits[j >> 5], 1u << (j & 31));
         }
     });
     __syncthreads();
@@ -686,7 +690,10 @@ __device__ void pass_amounts(ExactShared& sh, const RowCtx& c) {
         const uint8_t f = sh.flag[j];
         if (f & fsx::kBinCollect) sh.flag[j] = fsx::kBinListed;
         else if (f & fsx::kBinDirty) {
-            const bool tie = (sh.tie_bits[j >> 5] >> (j & 31)) & 1u;
+            bool tie = (sh.tie_bits[j >> 5] >> (j & 31)) & 1u;
+            const unsigned long long whole = ((unsigned long long)sh.PA[j] << 16) + sh.A[j];
+            if (whole >= 0x80000000ull || sh.C[j] >= 65536u) tie = true;   // too much for one binade: never taken as a whole
+            sh.A[j] = tie ? 0u : (uint32_t)whole;
             sh.flag[j] = (uint8_t)(fsx::kBinValid | (tie ? fsx::kBinTie : 0));
         }
     }
