@@ -100,13 +100,13 @@ Plan make_plan(const pa_handle* h, int num_tokens, int num_sequences, int max_co
     long long tiles = B * ((std::max(max_context_len, 1) + 31) / 32);
     if (num_block_indices >= 0) tiles = std::min(tiles, (long long)num_block_indices * g.bs / 32 + B);
     p.max_tiles = tiles * HK;
-    const long long slots = B * HK + pa::decode_max_slices(h->sm_count);  // slot = stream + slice
+    const long long slots = B * HK + pa::decode_max_workers(h->sm_count);  // slot = stream + slice
     size_t off = 0;
     p.off_hdr = off;       off += 256;
     p.off_prefix = off;    off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_pprefix = off;   off += align_up((size_t)(B + 1) * sizeof(int), 256);
     p.off_porder = off;    off += align_up((size_t)pa::kPrefillSortCap * sizeof(int), 256);
-    p.off_wstart = off;    off += align_up((size_t)pa::decode_max_slices(h->sm_count) * sizeof(pa::WorkerStart), 256);
+    p.off_wstart = off;    off += align_up((size_t)pa::decode_max_workers(h->sm_count) * sizeof(pa::WorkerStart), 256);
     p.off_done = off;      off += align_up((size_t)std::max(B, 1LL) * HK * sizeof(int), 256);
     p.off_part_o = off;    off += align_up((size_t)slots * RT * g.D * sizeof(float), 256);
     p.off_part_ml = off;   off += align_up((size_t)slots * RT * 2 * sizeof(float), 256);
@@ -213,18 +213,16 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     int rc = ensure_ws(h, p.total);
     if (rc != PA_OK) return rc;
     pa::KernelArgs k = make_kernel_args(h, a, p);
-    k.decode_tail_div = pa::decode_tail_div();
     k.test_drop_copy = h->test_drop_copy ? 1 : 0;
     // SM-shared kernel while a CTA's slice fits two of its chapters; longer slices go to the warp-per-slice kernel, whose
     // fixed slices cost nothing per chapter and balance well when every warp has hundreds of tiles
     const bool shared_decode = pa::decode_shared_supported(h->g) && k.max_tiles <= (long long)h->sm_count * pa::decode_shared_chapter_tiles(h->g) * pa::decode_shared_max_chapters();
     if (shared_decode) {   // one CTA per SM is the worker; its warps share the slice
-        k.decode_tail_div = 0;
         k.decode_phantom = pa::decode_shared_phantom();
         k.max_tiles += (long long)a->num_sequences * h->g.Hkv * k.decode_phantom;
-        k.decode_all_workers = k.decode_first_workers = pa::decode_shared_ctas(k, h->sm_count);
+        k.decode_all_workers = pa::decode_shared_ctas(k, h->sm_count);
     } else {
-        k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count, &k.decode_first_workers);   // the plan step prepares one start record per worker
+        k.decode_all_workers = pa::decode_launch_workers(k, h->sm_count);   // the plan step prepares one start record per worker
     }
     int launches = 0;
     if (a->num_rotated_blocks > 0) { PA_CUDA(pa::launch_rotate(k, stream)); ++launches; }

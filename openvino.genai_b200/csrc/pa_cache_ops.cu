@@ -76,11 +76,11 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         if (B <= kPrefixCap) {
             if (tid == 0) sh_prefix[B] = sh_run;
             __syncthreads();
-            const DecodeSlices sl = decode_slices(total_tiles, a.decode_all_workers, a.decode_first_workers, a.decode_tail_div);
+            const DecodeSlices sl = decode_slices(total_tiles, a.decode_all_workers);
             for (int w = tid; w < a.decode_all_workers; w += 256) {
                 WorkerStart ws{-1, 0, 0, total_tiles, 0, 0, 0, 0};
                 const long long g_tile = sl.begin(w);
-                if (w < sl.workers1 + sl.workers2 && g_tile < sl.end(w)) {
+                if (w < sl.workers1 && g_tile < sl.end(w)) {
                     const int key = (int)(g_tile / HK);
                     int lo = 0, hi = B;   // sh_prefix[lo] <= key < sh_prefix[hi]
                     while (hi - lo > 1) {
@@ -136,7 +136,6 @@ __device__ void build_decode_plan(const KernelArgs& a) {
         a.ptile_prefix[B] = sh_run_p;
         a.plan->total_ptiles = sh_run_p;
         a.plan->next_pitem = 0;
-        a.plan->next_slice = 0;
         a.plan->pitems_sorted = sort_items ? 1 : 0;
     }
 }

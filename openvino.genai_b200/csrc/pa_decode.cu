@@ -136,27 +136,18 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- this worker's slice of the global tile sequence -----------------------------------------
-    // The launch's warps own the first slices; further ("shared") slices are handed out by a counter.
-    const int phys_workers = gridDim.x * kDecodeWarps;
+    const int all_workers = gridDim.x * kDecodeWarps;
     const int wid = blockIdx.x * kDecodeWarps + warp;
-    const bool planned = a.worker_start && a.decode_all_workers >= phys_workers && a.decode_first_workers == phys_workers;   // one start record per slice
-    const int all_workers = planned ? a.decode_all_workers : phys_workers;
-    auto load_start = [&](int id) {
-        WorkerStart w;
-        w.s = -1;
-        if (planned) {
-            const int4 lo4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + id));
-            const int4 hi4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + id) + 1);
-            w = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
-        }
-        return w;
-    };
-    const WorkerStart ws0 = load_start(wid);
+    WorkerStart ws0;
+    ws0.s = -1;
+    if (a.worker_start && a.decode_all_workers == all_workers) {   // one start record per worker
+        const int4 lo4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + wid));
+        const int4 hi4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + wid) + 1);
+        ws0 = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+    }
     const int total_tiles = ws0.s != -1 ? ws0.total_tiles : a.plan->total_tiles;   // all streams
-    const DecodeSlices sl = decode_slices(total_tiles, all_workers, planned ? a.decode_first_workers : phys_workers, planned ? a.decode_tail_div : 0);
-    int cur = wid;                   // slice in work
+    const DecodeSlices sl = decode_slices(total_tiles, all_workers);
     int g_tile = 0, g_end = 0;       // next global tile to load, end of the slice
-    bool more = planned && sl.workers2 > 0 && ws0.s != -1;   // shared slices (every one has a start record) may be left
 
     // ---- loader state (warp-uniform registers) -------------------------------------------------------
     int r_s = -1, r_hkp = 0, r_tiles = 0;   // current stream: row, head tile, tiles of the row per head tile
@@ -199,48 +190,25 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, (HI || PA_DECODE_STAGES > 2
                     else atomicOr(a.status, PA_DEV_BAD_BEGINS);
                 }
             }
-            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + cur, score_off};
+            runs[r_seq % kRunRing] = RunRec{t0row, r_hkp, stream, last_w - first_w + 1, stream + first_w, stream + wid, score_off};
         }
         g_tile += ntile;
         r_first = true;
         load_window(r_tok / BS);
     };
-    // Moves the loader to its next run: the first tile of the next stream of the slice in work, else the first
-    // run of the next shared slice from the counter.  False when nothing is left.
+    // Moves the loader to its next run: the first tile of the next stream of the slice.  False when the slice is done.
     auto advance = [&]() -> bool {
-        int tile0 = 0, p0, ctx, t0row;
-        if (g_tile < g_end) {
-            if (++r_hkp == HK) {
-                r_hkp = 0;
-                do {
-                    ++r_s;
-                    r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
-                } while (r_tiles == 0);
-            }
-            r_tb = a.block_indices_begins[r_s];
-            r_nb = a.block_indices_begins[r_s + 1] - r_tb;
-            p0 = __ldcg(a.tile_prefix + r_s);
-            ctx = a.past_lens[r_s] + 1;
-            t0row = a.subsequence_begins[r_s];
-        } else {
-            if (!more) return false;
-            int id = 0;
-            if (lane == 0) id = atomicAdd(&a.plan->next_slice, 1);
-            id = sl.workers1 + __shfl_sync(0xffffffffu, id, 0);
-            if (id >= sl.workers1 + sl.workers2) { more = false; return false; }
-            cur = id;
-            g_tile = (int)sl.begin(id);   // shared slices are never empty
-            g_end = (int)sl.end(id);
-            const WorkerStart ws = load_start(id);
-            r_s = ws.s;
-            p0 = ws.p0;
-            r_tiles = ws.r_tiles;
-            ctx = ws.ctx; r_tb = ws.tb; r_nb = ws.nb; t0row = ws.t0;
-            const int off = g_tile - p0 * HK;
-            r_hkp = off / r_tiles;
-            tile0 = off % r_tiles;
+        if (g_tile >= g_end) return false;
+        if (++r_hkp == HK) {
+            r_hkp = 0;
+            do {
+                ++r_s;
+                r_tiles = __ldcg(a.tile_prefix + r_s + 1) - __ldcg(a.tile_prefix + r_s);
+            } while (r_tiles == 0);
         }
-        start_run(tile0, p0, ctx, t0row);
+        r_tb = a.block_indices_begins[r_s];
+        r_nb = a.block_indices_begins[r_s + 1] - r_tb;
+        start_run(0, __ldcg(a.tile_prefix + r_s), a.past_lens[r_s] + 1, a.subsequence_begins[r_s]);
         return true;
     };
     // The worker's own slice: from the record the plan step prepared, else by binary search in the prefix sums.
@@ -849,20 +817,9 @@ cudaError_t launch_decode_c(const KernelArgs& a, cudaStream_t stream, int sm_cou
 
 }  // namespace
 
-int decode_tail_div() {
-    static const int v = [] {
-        const char* e = std::getenv("PA_B200_DECODE_TAIL");
-        const int n = e ? std::atoi(e) : 0;   // shared slices measured slower than equal slices (every slice start is a chain of dependent loads)
-        return n < 0 ? 0 : n;
-    }();
-    return v;
-}
-
 int decode_max_workers(int sm_count) { return sm_count * kDecodeMaxCtasPerSm * kDecodeWarps; }
-int decode_max_slices(int sm_count) { return decode_max_workers(sm_count) * (1 + kDecodeSharedPerWorker); }
 
-int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers) {
-    if (first_workers) *first_workers = 0;
+int decode_launch_workers(const KernelArgs& a, int sm_count) {
     if (a.num_sequences <= 0) return 0;
     int per_sm = 0;
 #define PA_OCC(D_, BS_)                                                                           \
@@ -877,9 +834,7 @@ int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers)
     else if (a.g.D == 64 && a.g.bs == 16) { PA_OCC(64, 16) }
 #undef PA_OCC
     if (per_sm < 1) return 0;
-    const int launched = (int)decode_ctas(a, per_sm, sm_count) * kDecodeWarps;
-    if (first_workers) *first_workers = launched;
-    return a.decode_tail_div > 0 ? launched * (1 + kDecodeSharedPerWorker) : launched;
+    return (int)decode_ctas(a, per_sm, sm_count) * kDecodeWarps;
 }
 
 cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count, int* launches, cudaEvent_t ev0, cudaEvent_t ev1) {

@@ -247,14 +247,14 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
     if (tid == 0) {
         WorkerStart ws;
         ws.s = -1;
-        const bool planned = a.worker_start && a.decode_all_workers == nctas && a.decode_first_workers == nctas;
+        const bool planned = a.worker_start && a.decode_all_workers == nctas;
         if (planned) {
             const int4 lo4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + cta));
             const int4 hi4 = __ldcg(reinterpret_cast<const int4*>(a.worker_start + cta) + 1);
             ws = WorkerStart{lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
         }
         const int total_tiles = ws.s != -1 ? ws.total_tiles : a.plan->total_tiles;
-        const DecodeSlices sl = decode_slices(total_tiles, nctas, nctas, 0);
+        const DecodeSlices sl = decode_slices(total_tiles, nctas);
         const int g_tile = (int)sl.begin(cta), g_end = (int)sl.end(cta);
         ctl->abort = 0;
         for (int i = 0; i < kShAcc; ++i) accs[i] = ShAcc{0, i, 0, 0};
@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kShMaxWarps * 32, 1) decode_shared_kernel(Kern
         // ---- thread 0 lists the runs of the chapter (walk state in registers while it does) --------------------
         if (tid == 0) {
             const int total_tiles = a.plan->total_tiles;
-            const DecodeSlices sl = decode_slices(total_tiles, nctas, nctas, 0);
+            const DecodeSlices sl = decode_slices(total_tiles, nctas);
             const int g_end = (int)sl.end(cta);
             int g_tile = ctl->g_tile, seq = ctl->seq;
             int nruns = 0, ntiles = 0, nblk = 0;

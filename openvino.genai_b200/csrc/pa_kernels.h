@@ -17,7 +17,6 @@ struct PlanHeader {
     int total_ptiles;  // kPrefillItemRows-row q tiles of all prefill chunks (per kv head)
     int next_pitem;    // work counter of the prefill kernel: next (q tile, kv head) item to hand out
     int pitems_sorted; // 1: pitem_order lists the q tiles by decreasing context length
-    int next_slice;    // work counter of the decode kernel: next shared slice (second class) to hand out
 };
 
 constexpr int kPrefillSortCap = 512;   // q tiles (per kv head) up to which the plan step orders them
@@ -36,54 +35,30 @@ struct __align__(16) WorkerStart {
 
 constexpr int kDecodeMinSlice = 4;   // a worker is given at least this many tiles
 constexpr int kDecodeSharedPhantom = 12;    // SM-shared decode: what one more stream in a CTA's slice costs, in tiles
-constexpr int kDecodeSharedPerWorker = 3;   // shared slices per launched warp at most (sizes the start records and the partial slots)
 
-// The slices of the global tile sequence: `all_workers` slices at most, of which the first `first_workers`
-// belong to the warps of the launch, one each.  With a shared part (tail_div > 0) they take equal slices of all but
-// 1 / tail_div of the tiles as their own; that remainder is cut into small slices ("shared", the second
-// class) which the warps take from a counter as they finish their own: warps of one launch run up to a
-// factor two apart in speed (scheduler priority, HBM arbitration), so equal slices alone leave a quarter
-// of the warp-time idle at the end.  Without a shared part every worker gets an equal slice.
+// The slices of the global tile sequence: worker w (a warp of decode_kernel, a CTA of decode_shared_kernel) takes the
+// w-th of equal slices; small steps use fewer workers, so that every slice has at least kDecodeMinSlice tiles.
 struct DecodeSlices {
-    int workers1, per1;   // first class: workers [0, workers1), per1 tiles each
-    int workers2, per2;   // second class: workers [workers1, workers1 + workers2), per2 tiles each
+    int workers1, per1;   // workers [0, workers1), per1 tiles each
     int total;
     __host__ __device__ long long begin(int w) const {
-        const long long b = w < workers1 ? (long long)w * per1 : (long long)workers1 * per1 + (long long)(w - workers1) * per2;
+        const long long b = (long long)w * per1;
         return b < total ? b : total;
     }
     __host__ __device__ long long end(int w) const {
-        if (w >= workers1 + workers2) return total;
-        const long long e = begin(w) + (w < workers1 ? per1 : per2);
+        if (w >= workers1) return total;
+        const long long e = begin(w) + per1;
         return e < total ? e : total;
     }
-    __host__ __device__ int worker_of(long long tile) const {   // tile < total
-        const long long first = (long long)workers1 * per1;
-        return tile < first ? (int)(tile / per1) : workers1 + (int)((tile - first) / per2);
-    }
+    __host__ __device__ int worker_of(long long tile) const { return (int)(tile / per1); }   // tile < total
 };
-__host__ __device__ inline DecodeSlices decode_slices(int total_tiles, int all_workers, int first_workers, int tail_div) {
-    DecodeSlices d{1, 1, 0, 1, total_tiles};
+__host__ __device__ inline DecodeSlices decode_slices(int total_tiles, int all_workers) {
+    DecodeSlices d{1, 1, total_tiles};
     const int want = (total_tiles + kDecodeMinSlice - 1) / kDecodeMinSlice;
-    if (first_workers > all_workers || first_workers <= 0) first_workers = all_workers;
-    const int tail_workers = all_workers - first_workers;
-    const long long tail_tiles = tail_div > 0 ? total_tiles / tail_div : 0;
-    if (tail_workers <= 0 || tail_tiles < (long long)kDecodeMinSlice * 8 || want <= first_workers) {
-        d.workers1 = all_workers < want ? all_workers : want;   // one class (small steps use fewer workers: at least kDecodeMinSlice tiles each)
-        if (d.workers1 > first_workers) d.workers1 = first_workers;
-        if (d.workers1 < 1) d.workers1 = 1;
-        d.per1 = (total_tiles + d.workers1 - 1) / d.workers1;
-        if (d.per1 < 1) d.per1 = 1;
-        return d;
-    }
-    d.workers1 = first_workers;
-    d.per1 = (int)((total_tiles - tail_tiles + first_workers - 1) / first_workers);
-    const long long rest = total_tiles - (long long)d.workers1 * d.per1;
-    if (rest <= 0) { d.workers2 = 0; return d; }
-    long long w2 = (rest + kDecodeMinSlice - 1) / kDecodeMinSlice;
-    if (w2 > tail_workers) w2 = tail_workers;
-    d.workers2 = (int)w2;
-    d.per2 = (int)((rest + w2 - 1) / w2);
+    d.workers1 = all_workers < want ? all_workers : want;
+    if (d.workers1 < 1) d.workers1 = 1;
+    d.per1 = (total_tiles + d.workers1 - 1) / d.workers1;
+    if (d.per1 < 1) d.per1 = 1;
     return d;
 }
 
@@ -123,9 +98,7 @@ struct KernelArgs {
     int* stream_done;      // [num_sequences * HK] partials of the stream published so far
     int* ptile_prefix;     // [num_sequences + 1] exclusive prefix sum of prefill q tiles per row (one kv head)
     int* pitem_order;      // [kPrefillSortCap] q tiles, longest context first (valid when plan->pitems_sorted); may be null
-    int decode_all_workers;      // warps the decode launch will have (0: the plan prepares no start records)
-    int decode_first_workers;    // warps of the launch: they own the first slices
-    int decode_tail_div;         // 1 / tail_div of the tiles are handed out as shared slices (0: none)
+    int decode_all_workers;      // workers (warps of decode_kernel, CTAs of decode_shared_kernel) the decode launch will have (0: the plan prepares no start records)
     int decode_phantom;          // tiles added to every stream in the sequence the slices are cut in (SM-shared decode: a stream costs a CTA time beyond its tiles)
     int test_drop_copy;          // test hook: worker 0 issues no copy for its first tile and polls 2^10 times only
     WorkerStart* worker_start;   // [decode_all_workers], may be null
@@ -183,9 +156,7 @@ cudaError_t launch_decode(const KernelArgs& a, cudaStream_t stream, int sm_count
 int decode_max_workers(int sm_count);
 // Warps the decode launch of this step will have (the plan step prepares one start record each); *first_workers
 // receives those of the first wave.
-int decode_launch_workers(const KernelArgs& a, int sm_count, int* first_workers);
-int decode_tail_div();   // the PA_B200_DECODE_TAIL setting: 1 / n of the tiles are handed out as shared slices (default 0 = none)
-int decode_max_slices(int sm_count);   // upper bound of decode_launch_workers
+int decode_launch_workers(const KernelArgs& a, int sm_count);
 // SM-shared decode (pa_decode_shared.cu): one CTA per SM whose warps take tiles from a shared counter
 bool decode_shared_supported(const CacheGeom& g);
 size_t decode_shared_scratch_bytes(int sm_count);
