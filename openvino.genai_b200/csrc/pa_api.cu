@@ -240,10 +240,12 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     if (shared_decode) PA_CUDA(pa::launch_decode_shared(k, stream, h->sm_count, &launches, ev0, ev1));
     else PA_CUDA(pa::launch_decode(k, stream, h->sm_count, &launches, ev0, ev1));
     if (a->num_tokens > a->num_sequences) {
+        const int G = h->g.Hq / h->g.Hkv;
+        const long long max_items = ((long long)a->num_tokens * G / pa::kPrefillItemRows + a->num_sequences) * h->g.Hkv;
         if (pa::prefill_tc_supported(h->g) && !h->force_generic_prefill) {
-            const int G = h->g.Hq / h->g.Hkv;
-            const long long max_items = ((long long)a->num_tokens * G / pa::kPrefillItemRows + a->num_sequences) * h->g.Hkv;
             PA_CUDA(pa::launch_prefill_tc(k, stream, h->sm_count, max_items, &launches));
+        } else if (pa::prefill_mma_supported(h->g) && !h->force_generic_prefill) {
+            PA_CUDA(pa::launch_prefill_mma(k, stream, max_items, &launches));
         } else {
             PA_CUDA(pa::launch_prefill(k, stream, &launches));
         }

@@ -173,6 +173,9 @@ cudaError_t launch_prefill(const KernelArgs& a, cudaStream_t stream, int* launch
 // The same on tcgen05 / TMEM for the shapes it supports (u8 cache, head size 128); walks the
 // plan's q-tile list.  `max_items` is the host's upper bound of q tiles x kv heads.
 bool prefill_tc_supported(const CacheGeom& g);
+// f16 / bf16 caches: mma.sync kernel over the same work items (pa_prefill_mma.cu)
+bool prefill_mma_supported(const CacheGeom& g);
+cudaError_t launch_prefill_mma(const KernelArgs& a, cudaStream_t stream, long long max_items, int* launches);
 cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_count, long long max_items, int* launches);
 
 // SnapKV-style score output: scores[pos] = sum over q heads and the last W rows of each chunk of

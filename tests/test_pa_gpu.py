@@ -88,8 +88,10 @@ def test_prefill_tensor_core_shapes(hq, hkv, bs, past, new):
     _check(H.run_both(wl), "u8", torch.bfloat16)
 
 
-def test_prefill_tensor_core_matches_generic_kernel(monkeypatch):
-    wl = H.small_workload(hq=28, hkv=4, d=128, bs=32, act=torch.float16, cache="u8", past=[500, 0], new=[256, 100], seed=71)
+@pytest.mark.parametrize("cache,d,bs,hq,hkv", [("u8", 128, 32, 28, 4), ("f16", 128, 32, 28, 4), ("bf16", 128, 16, 8, 2), ("f16", 64, 16, 12, 4), ("bf16", 64, 32, 40, 2)])
+def test_prefill_tensor_core_matches_generic_kernel(monkeypatch, cache, d, bs, hq, hkv):
+    """The tensor-core chunk kernels (tcgen05 for the u8 cache, mma.sync for the f16 / bf16 caches) against the CUDA-core one."""
+    wl = H.small_workload(hq=hq, hkv=hkv, d=d, bs=bs, act=torch.float16, cache=cache, past=[500, 0, 33], new=[256, 100, 2], seed=71)
     data = H.make_host_data(wl)
     tc = H.run_gpu(wl, data)
     monkeypatch.setenv("PA_B200_GENERIC_PREFILL", "1")
