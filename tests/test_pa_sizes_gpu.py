@@ -226,22 +226,24 @@ def test_scores_len_shorter_than_the_metadata_implies():
     assert np.allclose(out.float().cpu().numpy(), full["out_gpu"], rtol=2e-2, atol=2e-3), "attention output does not depend on the score slot"
 
 
-def test_decode_with_thousands_of_short_streams_per_step():
+@pytest.mark.parametrize("d,bs", [(128, 32), (64, 32), (64, 16)])
+def test_decode_with_thousands_of_short_streams_per_step(d, bs):
     """2000 sequences of 1 to 70 tokens over 4 KV heads: every CTA of the decode kernel meets dozens of streams, more than one
     run table holds, so its chapters end because of the run count; streams of one tile, contexts that end on a tile boundary."""
     rng = np.random.default_rng(5)
     past = rng.integers(0, 70, 2000)
     past[:8] = [0, 31, 32, 63, 64, 1, 30, 33]
-    wl = H.small_workload(hq=16, hkv=4, d=128, bs=32, act=torch.bfloat16, cache="u8", past=past, new=np.ones(2000, np.int64), seed=131)
+    wl = H.small_workload(hq=16, hkv=4, d=d, bs=bs, act=torch.bfloat16, cache="u8", past=past, new=np.ones(2000, np.int64), seed=131)
     res = run_step_on_gpu_filled_cache(wl)
     check(res, "u8", bf16_output=True)
 
 
-def test_decode_slices_longer_than_one_chapter():
+@pytest.mark.parametrize("d", [128, 64])
+def test_decode_slices_longer_than_one_chapter(d):
     """24 sequences of about 30 000 tokens over 8 KV heads: a CTA's slice is about 1200 tiles, two chapters, and streams of
     940 tiles are cut by chapter boundaries (their runs keep their accumulators across the boundary)."""
     rng = np.random.default_rng(6)
     past = rng.integers(29000, 31000, 24)
-    wl = H.small_workload(hq=32, hkv=8, d=128, bs=32, act=torch.bfloat16, cache="u8", past=past, new=np.ones(24, np.int64), seed=137)
+    wl = H.small_workload(hq=32, hkv=8, d=d, bs=32, act=torch.bfloat16, cache="u8", past=past, new=np.ones(24, np.int64), seed=137)
     res = run_step_on_gpu_filled_cache(wl)
     check(res, "u8", bf16_output=True)
