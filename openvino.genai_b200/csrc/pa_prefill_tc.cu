@@ -1,5 +1,5 @@
-// Prefill-chunk attention on the 5th-generation tensor cores (tcgen05 + TMEM) for the u8 cache,
-// head size 128.
+// Prefill-chunk attention on the 5th-generation tensor cores (tcgen05 + TMEM) for the u8 and the f16
+// cache, head size 128.
 //
 // A work item is a q tile of 256 rows = (new token, q head of one GQA group) pairs of one
 // (sequence, kv head), so a K/V byte is read once for the whole group.  The item is split into two
@@ -23,6 +23,12 @@
 // and minus scale * zero-point split into f16 pieces, so S comes out with the offset term already
 // subtracted; V'^T carries extra rows holding scale * zero-point (subtracted from O in the
 // epilogue) and an all-ones row whose P.V column is the softmax denominator.
+// The f16 cache needs no conversion: its four "converter" warps copy the token rows of a tile with
+// 16-byte cp.async straight into the swizzled operand tiles (rows beyond the context are zero-filled).
+// Key and value rows are both token-major there, so K' is a K-major operand and V' an MN-major one
+// with the same shared-memory image; the softmax denominator comes from a second, 16-column P.V
+// product against a constant tile whose first row is all ones.  The raw ring, the extra dims and
+// the loader's copies do not exist in that variant.
 // Every wait is bounded; a wait that runs out raises a flag that all roles poll.
 // Tensor-bound for long contexts: 4 * Hq * D flops per (new token, context token) pair.
 #include <algorithm>
@@ -54,8 +60,11 @@ constexpr int kWarpMma = kSoftmaxWarps + kConvWarps, kWarpLoad = kWarpMma + 1;
 constexpr int kThreads = (kWarpLoad + 1) * 32;
 static_assert(kPrefillItemRows == 2 * kRows, "an item is two UMMA row tiles");
 
+template <int BS, int CT>
+struct PrefillSmem;
+
 template <int BS>
-struct PrefillSmem {
+struct PrefillSmem<BS, PA_DTYPE_U8> {
     static constexpr int REC = BS * (kD + 8);
     static constexpr int NREC = kKv / BS;
     static constexpr int RSTRIDE = REC + 64;       // records 64 bytes out of phase: conflict-free 16-byte reads across records
@@ -83,6 +92,33 @@ struct PrefillSmem {
     uint32_t tmem_base;
     volatile int abort;
 };
+
+// f16 cache: operand tiles only
+template <int BS>
+struct PrefillSmem<BS, PA_DTYPE_F16> {
+    static constexpr int NREC = kKv / BS;
+    alignas(1024) uint8_t q[2][kRows * kD * 2];       // per half: 2 swizzle atoms of [128 rows][64 dims]
+    alignas(1024) uint8_t k[kStages][kKv * kD * 2];   // 2 atoms of [64 tokens][64 dims], K-major
+    alignas(1024) uint8_t vt[kStages][kKv * kD * 2];  // the same image read as an MN-major operand: 2 atoms of 64 dims, 8-token groups 1024 bytes apart
+    alignas(128) uint8_t ones[16 * 16 * 2];           // unswizzled K-major [16 rows][16 tokens]: row 0 all ones
+    alignas(8) uint64_t k_full[kStages];     // copy warps -> mma
+    alignas(8) uint64_t v_full[kStages];
+    alignas(8) uint64_t k_free[kStages];     // mma (commit) -> copy warps
+    alignas(8) uint64_t v_free[kStages];
+    alignas(8) uint64_t q_full[2];
+    alignas(8) uint64_t s_full[2];
+    alignas(8) uint64_t p_full[2];
+    alignas(8) uint64_t o_done[2];
+    alignas(8) uint64_t item_full[kItemSlots];
+    alignas(8) uint64_t item_free[kItemSlots];
+    int item_ring[kItemSlots];
+    uint32_t tmem_base;
+    volatile int abort;
+};
+
+__device__ __forceinline__ void cp_async16_zfill(void* dst_smem, const void* src_gmem, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(src_bytes) : "memory");
+}
 
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
 // unswizzled K-major tile of 16 dims: 8-row groups 256 bytes apart, the two 8-dim halves 128 apart
@@ -207,9 +243,10 @@ __device__ __forceinline__ Item locate_item(const KernelArgs& a, int item, int G
     return it;
 }
 
-template <int BS>
+template <int BS, int CT>
 __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
-    using Smem = PrefillSmem<BS>;
+    using Smem = PrefillSmem<BS, CT>;
+    constexpr bool U8 = CT == PA_DTYPE_U8;
     extern __shared__ uint8_t smem_raw_[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw_) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -221,8 +258,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&sm.raw_full[i], 1);
-            mbar_init(&sm.raw_free[i], kConvWarps);
+            if constexpr (U8) {
+                mbar_init(&sm.raw_full[i], 1);
+                mbar_init(&sm.raw_free[i], kConvWarps);
+            }
             mbar_init(&sm.k_full[i], kConvWarps);
             mbar_init(&sm.v_full[i], kConvWarps);
             mbar_init(&sm.k_free[i], 1);
@@ -243,10 +282,18 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         mbar_fence_init();
         sm.abort = 0;
     }
-    // rows 132..143 of V'^T stay zero for the whole kernel
-    if (tid < kStages * (kNo - kD - 4) * 8) {
-        const int st = tid / ((kNo - kD - 4) * 8), i = tid % ((kNo - kD - 4) * 8);
-        *reinterpret_cast<uint4*>(sm.vt[st] + (kD + 4) * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+    if constexpr (U8) {
+        // rows 132..143 of V'^T stay zero for the whole kernel
+        if (tid < kStages * (kNo - kD - 4) * 8) {
+            const int st = tid / ((kNo - kD - 4) * 8), i = tid % ((kNo - kD - 4) * 8);
+            *reinterpret_cast<uint4*>(sm.vt[st] + (kD + 4) * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+        }
+    } else {
+        // row 0 of the constant tile (16-byte units 0 and 8: its two halves along the tokens) is all ones
+        if (tid < 32) {
+            const uint32_t one2 = tid == 0 || tid == 8 ? 0x3C003C00u : 0u;
+            *reinterpret_cast<uint4*>(sm.ones + tid * 16) = make_uint4(one2, one2, one2, one2);
+        }
     }
     if (warp == 0) tc05::tmem_alloc(&sm.tmem_base, kTmemCols);
     tc05::fence_proxy_async_smem();
@@ -355,10 +402,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
                     *reinterpret_cast<uint4*>(sq + (c / 8) * (kRows * 128) + sw128(r, c % 8)) = w;
                 }
-                const __half qh = f2h(qsum), ql = f2h(qsum - __half2float(qh));
-                const __half zero = __ushort_as_half(0);
-                *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
-                *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                if constexpr (U8) {
+                    const __half qh = f2h(qsum), ql = f2h(qsum - __half2float(qh));
+                    const __half zero = __ushort_as_half(0);
+                    *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 0)) = make_uint4(h2_bits(qh, qh), h2_bits(qh, ql), h2_bits(ql, zero), 0u);
+                    *reinterpret_cast<uint4*>(sm.qx[X] + plain16(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                }
                 tc05::fence_proxy_async_smem();
                 warp_arrive(&sm.q_full[X]);
             }
@@ -415,7 +464,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #elif defined(PA_EXP_NOCVT)
                     pw[c >> 1] = ex2_h2(__byte_perm(__float_as_uint(fmaf(sv[c], qs, -mq)), __float_as_uint(fmaf(sv[c + 1], qs, -mq)), 0x7632));
 #else
-                    pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qs, -mq), fmaf(sv[c + 1], qs, -mq)));
+                    // the packed f16 exponential is good to 2^-9.9 relative: inside the u8 cache's error bound, not inside the
+                    // f16 cache's, whose P goes through the f32 exponential and is rounded once
+                    if constexpr (U8) pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qs, -mq), fmaf(sv[c + 1], qs, -mq)));
+                    else pw[c >> 1] = pack_h2(ex2(fmaf(sv[c], qs, -mq)), ex2(fmaf(sv[c + 1], qs, -mq)));
 #endif
                 }
 #endif
@@ -450,15 +502,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 warp_arrive(&sm.p_full[X]);
                 if ((warp & 3) == 0) PA_TRACE(X, 4, n);
             }
-            // ---- epilogue: out = (O - z) / l; z = the three zero-point columns, l = the all-ones column
+            // ---- epilogue: out = (O - z) / l; z = the three zero-point columns, l = the all-ones column (u8 cache);
+            // the f16 cache has no z and its l is the first column of the 16-column product
             if (!wait_warp(&sm.o_done[X], (n - 1) & 1, 2)) goto done;
             tc05::fence_after_thread_sync();
             {
                 uint32_t zr[16];
                 tc05::ld_32x32b_x16(tmem_o + kD, zr);
                 tc05::wait_ld();
-                const float z = __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]);
-                const float l_run = __uint_as_float(zr[3]);
+                const float z = U8 ? __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]) : 0.f;
+                const float l_run = __uint_as_float(zr[U8 ? 3 : 0]);
                 const float inv = 1.f / l_run;
 #pragma unroll
                 for (int q4 = 0; q4 < kD / 32; ++q4) {
@@ -482,6 +535,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     } else if (warp < kWarpMma) {
         // ======================= converter: raw records -> f16 operand tiles =============================
         const int ctid = tid - kSoftmaxWarps * 32, cwarp = warp - kSoftmaxWarps;
+        if constexpr (U8) {
         uint32_t t = 0;   // tiles so far, over all items
         for (uint32_t ik = 0;; ++ik) {
             const int item = fetch_item(ik);
@@ -594,20 +648,98 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 if (cwarp == 0) PA_TRACE(2, 4, t);
             }
         }
+        } else {
+            // ---- f16 cache: token rows -> operand tiles with cp.async; thread = 16-byte chunk `ch` of the rows trow + 8 u.
+            // The copies of tile t are in flight while tile t - 1 is handed over: K_t is issued, then K_(t-1) is
+            // awaited, fenced for the tensor core's proxy and published, then the same for V.
+            (void)cwarp;
+            const int ch = ctid & 15, trow = ctid >> 4;
+            const uint32_t dst0 = (uint32_t)(ch >> 3) * (kKv * 128);
+            uint32_t t = 0;
+            bool bad_index = false;
+            for (uint32_t ik = 0;; ++ik) {
+                const int item = fetch_item(ik);
+                if (item == -2) goto done;
+                if (item < 0) break;
+                const Item it = locate_item(a, item, G, Hkv);
+                const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
+                const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes + 16 * ch;
+                const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)it.hk * a.g.head_bytes + 16 * ch;
+                for (int j = 0; j < it.ntiles; ++j, ++t) {
+                    const int st = t & 1;
+                    const uint32_t use = t >> 1;
+                    const int live_tokens = min(kKv, ctx_hi - j * kKv);
+                    long long off[8];   // byte offset of this thread's chunk of token trow + 8 u; -1: beyond the context
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int token = trow + 8 * u;
+                        off[u] = -1;
+                        if (token < live_tokens) {
+                            int blk = it.table[j * Smem::NREC + token / BS];
+                            if (blk < 0 || blk >= a.num_blocks) { blk = 0; bad_index = true; }
+                            off[u] = (long long)blk * a.g.block_bytes + (long long)(token % BS) * (kD * 2);
+                        }
+                    }
+                    if (use > 0 && !wait_warp(&sm.k_free[st], (use - 1) & 1, 1)) goto done;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const bool ok = off[u] >= 0;
+                        cp_async16_zfill(sm.k[st] + dst0 + sw128(trow + 8 * u, ch & 7), kc + (ok ? off[u] : 0), ok ? 16u : 0u);
+                    }
+                    cp_async_commit();
+                    if (t > 0) {
+                        cp_async_wait<2>();   // pending at most V_(t-1), K_t
+                        tc05::fence_proxy_async_smem();
+                        warp_arrive(&sm.k_full[st ^ 1]);
+                    }
+                    if (use > 0 && !wait_warp(&sm.v_free[st], (use - 1) & 1, 2)) goto done;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const bool ok = off[u] >= 0;
+                        cp_async16_zfill(sm.vt[st] + dst0 + sw128(trow + 8 * u, ch & 7), vc + (ok ? off[u] : 0), ok ? 16u : 0u);
+                    }
+                    cp_async_commit();
+                    if (t > 0) {
+                        cp_async_wait<2>();   // pending at most K_t, V_t
+                        tc05::fence_proxy_async_smem();
+                        warp_arrive(&sm.v_full[st ^ 1]);
+                    }
+                }
+            }
+            if (t > 0) {
+                cp_async_wait<1>();
+                tc05::fence_proxy_async_smem();
+                warp_arrive(&sm.k_full[(t - 1) & 1]);
+                cp_async_wait<0>();
+                tc05::fence_proxy_async_smem();
+                warp_arrive(&sm.v_full[(t - 1) & 1]);
+            }
+            if (__any_sync(0xffffffffu, bad_index) && lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
+        }
     } else if (warp == kWarpMma) {
         // ======================= mma issue ================================================================
         // The whole warp runs the loop (uniform control flow keeps the descriptors in uniform registers);
         // one elected lane issues the tensor-core instructions.
         {
             constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
-            constexpr uint32_t idesc_o = tc05::instr_desc_f16(kRows, kNo, 0, 0, 0);
+            constexpr uint32_t idesc_o = U8 ? tc05::instr_desc_f16(kRows, kNo, 0, 0, 0) : tc05::instr_desc_f16(kRows, kD, 0, 0, 1);   // f16 cache: V' MN-major
+            constexpr uint32_t idesc_l = tc05::instr_desc_f16(kRows, kDx, 0, 0, 0);   // f16 cache: P . ones
             // operand descriptors are built once; a step along K or to another buffer only moves the
             // start-address field (bits [0,14) of the low word, in 16-byte units, no carry out of it)
             const uint64_t dq = tc05::smem_desc_sw128(smem_u32(sm.q[0]), 1024), dk = tc05::smem_desc_sw128(smem_u32(sm.k[0]), 1024);
-            const uint64_t dv = tc05::smem_desc_sw128(smem_u32(sm.vt[0]), 1024);
-            const uint64_t dqx = tc05::smem_desc_plain(smem_u32(sm.qx[0]), 128, 256), dkx = tc05::smem_desc_plain(smem_u32(sm.kx[0]), 128, 256);
+            // MN-major V' of the f16 cache: 8-token groups 1024 bytes apart, the two 64-dim atoms kKv * 128 bytes apart
+            const uint64_t dv = U8 ? tc05::smem_desc_sw128(smem_u32(sm.vt[0]), 1024) : tc05::smem_desc_sw128(smem_u32(sm.vt[0]), 1024, kKv * 128);
+            uint64_t dqx = 0, dkx = 0, dones = 0;
+            uint32_t qx_step = 0, kx_step = 0;
+            if constexpr (U8) {
+                dqx = tc05::smem_desc_plain(smem_u32(sm.qx[0]), 128, 256);
+                dkx = tc05::smem_desc_plain(smem_u32(sm.kx[0]), 128, 256);
+                qx_step = sizeof(sm.qx[0]) >> 4;
+                kx_step = sizeof(sm.kx[0]) >> 4;
+            } else {
+                dones = tc05::smem_desc_plain(smem_u32(sm.ones), 128, 256);
+            }
             constexpr uint32_t q_step = sizeof(sm.q[0]) >> 4, k_step = sizeof(sm.k[0]) >> 4, v_step = sizeof(sm.vt[0]) >> 4;
-            constexpr uint32_t qx_step = sizeof(sm.qx[0]) >> 4, kx_step = sizeof(sm.kx[0]) >> 4;
             auto issue_s = [&](int X, int st) {
                 const uint64_t da0 = dq + X * q_step, db0 = dk + st * k_step;
                 const uint32_t d = tmem + kKv * X;
@@ -618,7 +750,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     if (kk == 0) tc05::mma_ss<0>(d, da0 + a_off, db0 + b_off, idesc_s);
                     else tc05::mma_ss<1>(d, da0 + a_off, db0 + b_off, idesc_s);
                 }
-                tc05::mma_ss<1>(d, dqx + X * qx_step, dkx + st * kx_step, idesc_s);
+                if constexpr (U8) tc05::mma_ss<1>(d, dqx + X * qx_step, dkx + st * kx_step, idesc_s);
                 tc05::commit(&sm.s_full[X]);
                 }
                 __syncwarp();
@@ -628,10 +760,21 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 const uint64_t db0 = dv + st * v_step;
                 const uint32_t d = tmem + 2 * kKv + kNo * X;
                 if (tc05::elect_one()) {
-                if (acc) tc05::mma_ts<1>(d, pa, db0, idesc_o);
-                else tc05::mma_ts<0>(d, pa, db0, idesc_o);
+                if constexpr (U8) {
+                    if (acc) tc05::mma_ts<1>(d, pa, db0, idesc_o);
+                    else tc05::mma_ts<0>(d, pa, db0, idesc_o);
 #pragma unroll
-                for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 2 * kk, idesc_o);
+                    for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 2 * kk, idesc_o);
+                } else {
+                    // 16 tokens further along K = 16 rows of 128 bytes; the denominators go to the 16 columns after O
+                    if (acc) { tc05::mma_ts<1>(d, pa, db0, idesc_o); tc05::mma_ts<1>(d + kD, pa, dones, idesc_l); }
+                    else { tc05::mma_ts<0>(d, pa, db0, idesc_o); tc05::mma_ts<0>(d + kD, pa, dones, idesc_l); }
+#pragma unroll
+                    for (int kk = 1; kk < kKv / 16; ++kk) {
+                        tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 128 * kk, idesc_o);
+                        tc05::mma_ts<1>(d + kD, pa + 8 * kk, dones, idesc_l);
+                    }
+                }
                 tc05::commit(&sm.o_done[X]);
                 }
                 __syncwarp();
@@ -703,6 +846,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 sm.item_ring[slot] = item;
                 mbar_arrive(&sm.item_full[slot]);
                 if (item < 0) break;
+                if constexpr (U8) {
                 const Item it = locate_item(a, item, G, Hkv);
                 const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
                 const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes;
@@ -736,6 +880,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                             bulk_g2s(sm.raw_v[st] + r * Smem::RSTRIDE, vc + (long long)blocks[r] * a.g.block_bytes, Smem::REC, &sm.raw_full[st]);
                         }
                 }
+                }
             }
             if (bad_index) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
         }
@@ -754,6 +899,7 @@ done:
     if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == kSoftmaxWarps || warp >= kWarpMma))
         printf("prefill prof warp %d total %lld waits %lld %lld %lld %lld %lld\n", warp, clock64() - prof_begin, prof[0], prof[1], prof[2], prof[3], prof[4]);
 #endif
+    if constexpr (!U8) cp_async_wait<0>();   // an aborted copy warp leaves no copy in flight
     tc05::fence_before_thread_sync();
     __syncthreads();
     if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
@@ -762,26 +908,29 @@ done:
 }  // namespace
 
 bool prefill_tc_supported(const CacheGeom& g) {
-    return g.cache == PA_DTYPE_U8 && g.D == kD && (g.bs == 32 || g.bs == 16) && g.Hq % g.Hkv == 0;
+    return (g.cache == PA_DTYPE_U8 || g.cache == PA_DTYPE_F16) && g.D == kD && (g.bs == 32 || g.bs == 16) && g.Hq % g.Hkv == 0;
 }
+
+namespace {
+template <int BS, int CT>
+cudaError_t launch_tc_t(const KernelArgs& a, cudaStream_t stream, int grid) {
+    const int bytes = (int)sizeof(PrefillSmem<BS, CT>) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<BS, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    prefill_tc_kernel<BS, CT><<<grid, kThreads, bytes, stream>>>(a);
+    return cudaGetLastError();
+}
+}  // namespace
 
 cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_count, long long max_items, int* launches) {
     if (max_items <= 0) return cudaSuccess;
     const int grid = (int)std::min<long long>(max_items, sm_count);
     cudaError_t e;
-    if (a.g.bs == 32) {
-        const int bytes = (int)sizeof(PrefillSmem<32>) + 1024;
-        e = cudaFuncSetAttribute(prefill_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        if (e != cudaSuccess) return e;
-        prefill_tc_kernel<32><<<grid, kThreads, bytes, stream>>>(a);
-    } else {
-        const int bytes = (int)sizeof(PrefillSmem<16>) + 1024;
-        e = cudaFuncSetAttribute(prefill_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        if (e != cudaSuccess) return e;
-        prefill_tc_kernel<16><<<grid, kThreads, bytes, stream>>>(a);
-    }
+    if (a.g.cache == PA_DTYPE_U8) e = a.g.bs == 32 ? launch_tc_t<32, PA_DTYPE_U8>(a, stream, grid) : launch_tc_t<16, PA_DTYPE_U8>(a, stream, grid);
+    else e = a.g.bs == 32 ? launch_tc_t<32, PA_DTYPE_F16>(a, stream, grid) : launch_tc_t<16, PA_DTYPE_F16>(a, stream, grid);
+    if (e != cudaSuccess) return e;
     ++*launches;
-    return cudaGetLastError();
+    return cudaSuccess;
 }
 
 }  // namespace pa
