@@ -1,5 +1,5 @@
 // Prefill-chunk attention on the 5th-generation tensor cores (tcgen05 + TMEM) for the u8 and the f16
-// cache, head size 128.
+// cache, head sizes 128 and 64.
 //
 // A work item is a q tile of 256 rows = (new token, q head of one GQA group) pairs of one
 // (sequence, kv head), so a K/V byte is read once for the whole group.  The item is split into two
@@ -43,13 +43,11 @@ namespace pa {
 namespace {
 
 constexpr int kRows = 128;     // rows of one half = UMMA M
-constexpr int kD = 128;        // head size
 constexpr int kDx = 16;        // extra dims / extra V^T rows that carry the zero-point terms
 constexpr int kKv = 64;        // context tokens per KV tile = UMMA N of Q.K^T
-constexpr int kNo = kD + kDx;  // UMMA N of P.V
-constexpr int kTmemCols = 512; // S_A [0,64) S_B [64,128) O_A [128,272) O_B [272,416) P_A [416,448) P_B [448,480)
-constexpr int kTmemP = 2 * kKv + 2 * kNo;
-constexpr int kStages = 2;
+constexpr int kTmemCols = 512; // head size 128: S_A [0,64) S_B [64,128) O_A [128,272) O_B [272,416) P_A [416,448) P_B [448,480)
+constexpr int kStages = 2;     // operand stages of the u8 variant (its raw ring has two more); the f16 variant has kStages16
+constexpr int kStages16 = 4;
 constexpr int kItemSlots = 4;   // depth of the queue that hands work items from the loader to the other roles
 constexpr float kLazy = 4.f;   // log2 of the growth of a row maximum that forces a rescale of O
 constexpr float kLog2eP = 1.4426950408889634f;
@@ -60,17 +58,19 @@ constexpr int kWarpMma = kSoftmaxWarps + kConvWarps, kWarpLoad = kWarpMma + 1;
 constexpr int kThreads = (kWarpLoad + 1) * 32;
 static_assert(kPrefillItemRows == 2 * kRows, "an item is two UMMA row tiles");
 
-template <int BS, int CT>
+template <int BS, int CT, int D>
 struct PrefillSmem;
 
-template <int BS>
-struct PrefillSmem<BS, PA_DTYPE_U8> {
-    static constexpr int REC = BS * (kD + 8);
+template <int BS, int D>
+struct PrefillSmem<BS, PA_DTYPE_U8, D> {
+    static constexpr int NO = D + kDx;   // UMMA N of P.V
+    static constexpr int NST = kStages;
+    static constexpr int REC = BS * (D + 8);
     static constexpr int NREC = kKv / BS;
     static constexpr int RSTRIDE = REC + 64;       // records 64 bytes out of phase: conflict-free 16-byte reads across records
-    alignas(1024) uint8_t q[2][kRows * kD * 2];    // per half: 2 swizzle atoms of [128 rows][64 dims]
-    alignas(1024) uint8_t k[kStages][kKv * kD * 2];   // 2 atoms of [64 tokens][64 dims]
-    alignas(1024) uint8_t vt[kStages][kNo * kKv * 2]; // [144 dims][64 tokens], 18 groups of 8 rows
+    alignas(1024) uint8_t q[2][kRows * D * 2];     // per half: D / 64 swizzle atoms of [128 rows][64 dims]
+    alignas(1024) uint8_t k[kStages][kKv * D * 2];    // D / 64 atoms of [64 tokens][64 dims]
+    alignas(1024) uint8_t vt[kStages][NO * kKv * 2];  // [D + 16 dims][64 tokens], groups of 8 rows
     alignas(128) uint8_t qx[2][kRows * kDx * 2];   // unswizzled [128 rows][16 dims]
     alignas(128) uint8_t kx[kStages][kKv * kDx * 2];  // unswizzled [64 tokens][16 dims]
     alignas(128) uint8_t raw_k[kStages][NREC * RSTRIDE];
@@ -94,17 +94,19 @@ struct PrefillSmem<BS, PA_DTYPE_U8> {
 };
 
 // f16 cache: operand tiles only
-template <int BS>
-struct PrefillSmem<BS, PA_DTYPE_F16> {
+template <int BS, int D>
+struct PrefillSmem<BS, PA_DTYPE_F16, D> {
+    static constexpr int NO = D + kDx;
     static constexpr int NREC = kKv / BS;
-    alignas(1024) uint8_t q[2][kRows * kD * 2];       // per half: 2 swizzle atoms of [128 rows][64 dims]
-    alignas(1024) uint8_t k[kStages][kKv * kD * 2];   // 2 atoms of [64 tokens][64 dims], K-major
-    alignas(1024) uint8_t vt[kStages][kKv * kD * 2];  // the same image read as an MN-major operand: 2 atoms of 64 dims, 8-token groups 1024 bytes apart
+    static constexpr int NST = kStages16;
+    alignas(1024) uint8_t q[2][kRows * D * 2];        // per half: D / 64 swizzle atoms of [128 rows][64 dims]
+    alignas(1024) uint8_t k[NST][kKv * D * 2];    // D / 64 atoms of [64 tokens][64 dims], K-major
+    alignas(1024) uint8_t vt[NST][kKv * D * 2];   // the same image read as an MN-major operand: atoms of 64 dims, 8-token groups 1024 bytes apart
     alignas(128) uint8_t ones[16 * 16 * 2];           // unswizzled K-major [16 rows][16 tokens]: row 0 all ones
-    alignas(8) uint64_t k_full[kStages];     // copy warps -> mma
-    alignas(8) uint64_t v_full[kStages];
-    alignas(8) uint64_t k_free[kStages];     // mma (commit) -> copy warps
-    alignas(8) uint64_t v_free[kStages];
+    alignas(8) uint64_t k_full[NST];     // copy warps -> mma
+    alignas(8) uint64_t v_full[NST];
+    alignas(8) uint64_t k_free[NST];     // mma (commit) -> copy warps
+    alignas(8) uint64_t v_free[NST];
     alignas(8) uint64_t q_full[2];
     alignas(8) uint64_t s_full[2];
     alignas(8) uint64_t p_full[2];
@@ -243,10 +245,13 @@ __device__ __forceinline__ Item locate_item(const KernelArgs& a, int item, int G
     return it;
 }
 
-template <int BS, int CT>
+template <int BS, int CT, int D>
 __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
-    using Smem = PrefillSmem<BS, CT>;
+    using Smem = PrefillSmem<BS, CT, D>;
     constexpr bool U8 = CT == PA_DTYPE_U8;
+    constexpr int kD = D, kNo = Smem::NO, kTmemP = 2 * kKv + 2 * kNo, NST = Smem::NST;
+    static_assert(!U8 || NST == 2, "the converter and the loader of the u8 variant index two stages");
+    static_assert(kTmemP + kKv <= kTmemCols, "S, O and P of both halves fit the tensor memory");
     extern __shared__ uint8_t smem_raw_[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw_) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -257,7 +262,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < NST; ++i) {
             if constexpr (U8) {
                 mbar_init(&sm.raw_full[i], 1);
                 mbar_init(&sm.raw_free[i], kConvWarps);
@@ -284,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     }
     if constexpr (U8) {
         // rows 132..143 of V'^T stay zero for the whole kernel
-        if (tid < kStages * (kNo - kD - 4) * 8) {
+        if (tid < NST * (kNo - kD - 4) * 8) {
             const int st = tid / ((kNo - kD - 4) * 8), i = tid % ((kNo - kD - 4) * 8);
             *reinterpret_cast<uint4*>(sm.vt[st] + (kD + 4) * 128 + i * 16) = make_uint4(0, 0, 0, 0);
         }
@@ -556,9 +561,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 // K' = byte * f16(k scale): unit u = 16 dims of one token
 #ifndef PA_EXP_NOCONV
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < kD / 32; ++i) {
                     const int u = ctid + 128 * i;
-                    const int token = u >> 3, seg = u & 7;
+                    const int token = u / (kD / 16), seg = u % (kD / 16);
                     uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
                     if (token < live_tokens) {
                         const uint8_t* rec = raw_k + (token / BS) * Smem::RSTRIDE;
@@ -612,7 +617,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 constexpr int UPR = BS / 16;   // 16-token units per record
 #ifndef PA_EXP_NOCONV
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < kD / 32; ++i) {
                     const int d = (ctid >> 2) + 32 * i;
                     uint4 lo4, hi4;
                     bytes16_to_h(*reinterpret_cast<const uint4*>(raw_v + (tg / UPR) * Smem::RSTRIDE + d * BS + 16 * (tg % UPR)), lo4, hi4);
@@ -649,11 +654,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             }
         }
         } else {
-            // ---- f16 cache: token rows -> operand tiles with cp.async; thread = 16-byte chunk `ch` of the rows trow + 8 u.
+            // ---- f16 cache: token rows -> operand tiles with cp.async; thread = 16-byte chunk `ch` of the rows trow + TP u.
             // The copies of tile t are in flight while tile t - 1 is handed over: K_t is issued, then K_(t-1) is
             // awaited, fenced for the tensor core's proxy and published, then the same for V.
             (void)cwarp;
-            const int ch = ctid & 15, trow = ctid >> 4;
+            constexpr int CH = kD / 8, TP = kConvWarps * 32 / CH, NU = kKv / TP;   // chunks of a row, tokens per pass, passes
+            const int ch = ctid % CH, trow = ctid / CH;
             const uint32_t dst0 = (uint32_t)(ch >> 3) * (kKv * 128);
             uint32_t t = 0;
             bool bad_index = false;
@@ -666,13 +672,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes + 16 * ch;
                 const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)it.hk * a.g.head_bytes + 16 * ch;
                 for (int j = 0; j < it.ntiles; ++j, ++t) {
-                    const int st = t & 1;
-                    const uint32_t use = t >> 1;
+                    const int st = t % NST, stp = (t + NST - 1) % NST;
+                    const uint32_t use = t / NST;
                     const int live_tokens = min(kKv, ctx_hi - j * kKv);
-                    long long off[8];   // byte offset of this thread's chunk of token trow + 8 u; -1: beyond the context
+                    long long off[NU];   // byte offset of this thread's chunk of token trow + TP u; -1: beyond the context
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int token = trow + 8 * u;
+                    for (int u = 0; u < NU; ++u) {
+                        const int token = trow + TP * u;
                         off[u] = -1;
                         if (token < live_tokens) {
                             int blk = it.table[j * Smem::NREC + token / BS];
@@ -682,37 +688,41 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     }
                     if (use > 0 && !wait_warp(&sm.k_free[st], (use - 1) & 1, 1)) goto done;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < NU; ++u) {
                         const bool ok = off[u] >= 0;
-                        cp_async16_zfill(sm.k[st] + dst0 + sw128(trow + 8 * u, ch & 7), kc + (ok ? off[u] : 0), ok ? 16u : 0u);
+#ifndef PA_EXP_NOCOPY16
+                        cp_async16_zfill(sm.k[st] + dst0 + sw128(trow + TP * u, ch & 7), kc + (ok ? off[u] : 0), ok ? 16u : 0u);
+#endif
                     }
                     cp_async_commit();
                     if (t > 0) {
                         cp_async_wait<2>();   // pending at most V_(t-1), K_t
                         tc05::fence_proxy_async_smem();
-                        warp_arrive(&sm.k_full[st ^ 1]);
+                        warp_arrive(&sm.k_full[stp]);
                     }
                     if (use > 0 && !wait_warp(&sm.v_free[st], (use - 1) & 1, 2)) goto done;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < NU; ++u) {
                         const bool ok = off[u] >= 0;
-                        cp_async16_zfill(sm.vt[st] + dst0 + sw128(trow + 8 * u, ch & 7), vc + (ok ? off[u] : 0), ok ? 16u : 0u);
+#ifndef PA_EXP_NOCOPY16
+                        cp_async16_zfill(sm.vt[st] + dst0 + sw128(trow + TP * u, ch & 7), vc + (ok ? off[u] : 0), ok ? 16u : 0u);
+#endif
                     }
                     cp_async_commit();
                     if (t > 0) {
                         cp_async_wait<2>();   // pending at most K_t, V_t
                         tc05::fence_proxy_async_smem();
-                        warp_arrive(&sm.v_full[st ^ 1]);
+                        warp_arrive(&sm.v_full[stp]);
                     }
                 }
             }
             if (t > 0) {
                 cp_async_wait<1>();
                 tc05::fence_proxy_async_smem();
-                warp_arrive(&sm.k_full[(t - 1) & 1]);
+                warp_arrive(&sm.k_full[(t - 1) % NST]);
                 cp_async_wait<0>();
                 tc05::fence_proxy_async_smem();
-                warp_arrive(&sm.v_full[(t - 1) & 1]);
+                warp_arrive(&sm.v_full[(t - 1) % NST]);
             }
             if (__any_sync(0xffffffffu, bad_index) && lane == 0) atomicOr(a.status, PA_DEV_BAD_BLOCK_INDEX);
         }
@@ -767,6 +777,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 2 * kk, idesc_o);
                 } else {
                     // 16 tokens further along K = 16 rows of 128 bytes; the denominators go to the 16 columns after O
+#ifdef PA_EXP_NOONES
+                    if (acc) { tc05::mma_ts<1>(d, pa, db0, idesc_o); }
+                    else { tc05::mma_ts<0>(d, pa, db0, idesc_o); }
+#pragma unroll
+                    for (int kk = 1; kk < kKv / 16; ++kk) {
+                        tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 128 * kk, idesc_o);
+                    }
+#else
                     if (acc) { tc05::mma_ts<1>(d, pa, db0, idesc_o); tc05::mma_ts<1>(d + kD, pa, dones, idesc_l); }
                     else { tc05::mma_ts<0>(d, pa, db0, idesc_o); tc05::mma_ts<0>(d + kD, pa, dones, idesc_l); }
 #pragma unroll
@@ -774,6 +792,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                         tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 128 * kk, idesc_o);
                         tc05::mma_ts<1>(d + kD, pa + 8 * kk, dones, idesc_l);
                     }
+#endif
                 }
                 tc05::commit(&sm.o_done[X]);
                 }
@@ -793,22 +812,22 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                         if (!wait_warp(&sm.q_full[X], iq[X] & 1, 0)) goto done;
                         ++iq[X];
                     }
-                if (!wait_warp(&sm.k_full[t & 1], (t >> 1) & 1, 1)) goto done;
+                if (!wait_warp(&sm.k_full[t % NST], (t / NST) & 1, 1)) goto done;
                 tc05::fence_after_thread_sync();
 #pragma unroll
                 for (int X = 0; X < 2; ++X)
-                    if (it.nt[X] > 0) issue_s(X, t & 1);
-                if (tc05::elect_one()) tc05::commit(&sm.k_free[t & 1]);
+                    if (it.nt[X] > 0) issue_s(X, t % NST);
+                if (tc05::elect_one()) tc05::commit(&sm.k_free[t % NST]);
                 for (int j = 0; j < it.ntiles; ++j, ++t) {
-                    const int st = t & 1, st1 = (t + 1) & 1;
+                    const int st = t % NST, st1 = (t + 1) % NST;
                     const bool more = j + 1 < it.ntiles;
                     PA_TRACE(3, 0, t);
                     // The converter finishes V' of tile j before K' of tile j + 1, so the latter's barrier
                     // covers both; only the item's last tile waits for its V' directly.
                     if (more) {
-                        if (!wait_warp(&sm.k_full[st1], ((t + 1) >> 1) & 1, 1)) goto done;
+                        if (!wait_warp(&sm.k_full[st1], ((t + 1) / NST) & 1, 1)) goto done;
                     } else {
-                        if (!wait_warp(&sm.v_full[st], (t >> 1) & 1, 3)) goto done;
+                        if (!wait_warp(&sm.v_full[st], (t / NST) & 1, 3)) goto done;
                     }
                     PA_TRACE(3, 3, t);
 #pragma unroll
@@ -831,7 +850,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 n[1] += it.nt[1];
             }
             // every commit has landed before the CTA's shared memory is given up
-            if (t > 0) wait_warp(&sm.v_free[(t - 1) & 1], ((t - 1) >> 1) & 1, 0);
+            if (t > 0) wait_warp(&sm.v_free[(t - 1) % NST], ((t - 1) / NST) & 1, 0);
         }
     } else {
         // ======================= loader: TMA-engine copies of the tiles' records =========================
@@ -908,17 +927,21 @@ done:
 }  // namespace
 
 bool prefill_tc_supported(const CacheGeom& g) {
-    return (g.cache == PA_DTYPE_U8 || g.cache == PA_DTYPE_F16) && g.D == kD && (g.bs == 32 || g.bs == 16) && g.Hq % g.Hkv == 0;
+    return (g.cache == PA_DTYPE_U8 || g.cache == PA_DTYPE_F16) && (g.D == 128 || g.D == 64) && (g.bs == 32 || g.bs == 16) && g.Hq % g.Hkv == 0;
 }
 
 namespace {
-template <int BS, int CT>
+template <int BS, int CT, int D>
 cudaError_t launch_tc_t(const KernelArgs& a, cudaStream_t stream, int grid) {
-    const int bytes = (int)sizeof(PrefillSmem<BS, CT>) + 1024;
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<BS, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    const int bytes = (int)sizeof(PrefillSmem<BS, CT, D>) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<BS, CT, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return e;
-    prefill_tc_kernel<BS, CT><<<grid, kThreads, bytes, stream>>>(a);
+    prefill_tc_kernel<BS, CT, D><<<grid, kThreads, bytes, stream>>>(a);
     return cudaGetLastError();
+}
+template <int CT, int D>
+cudaError_t launch_tc_bs(const KernelArgs& a, cudaStream_t stream, int grid) {
+    return a.g.bs == 32 ? launch_tc_t<32, CT, D>(a, stream, grid) : launch_tc_t<16, CT, D>(a, stream, grid);
 }
 }  // namespace
 
@@ -926,8 +949,8 @@ cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_c
     if (max_items <= 0) return cudaSuccess;
     const int grid = (int)std::min<long long>(max_items, sm_count);
     cudaError_t e;
-    if (a.g.cache == PA_DTYPE_U8) e = a.g.bs == 32 ? launch_tc_t<32, PA_DTYPE_U8>(a, stream, grid) : launch_tc_t<16, PA_DTYPE_U8>(a, stream, grid);
-    else e = a.g.bs == 32 ? launch_tc_t<32, PA_DTYPE_F16>(a, stream, grid) : launch_tc_t<16, PA_DTYPE_F16>(a, stream, grid);
+    if (a.g.cache == PA_DTYPE_U8) e = a.g.D == 128 ? launch_tc_bs<PA_DTYPE_U8, 128>(a, stream, grid) : launch_tc_bs<PA_DTYPE_U8, 64>(a, stream, grid);
+    else e = a.g.D == 128 ? launch_tc_bs<PA_DTYPE_F16, 128>(a, stream, grid) : launch_tc_bs<PA_DTYPE_F16, 64>(a, stream, grid);
     if (e != cudaSuccess) return e;
     ++*launches;
     return cudaSuccess;

@@ -89,10 +89,9 @@ def test_prefill_tensor_core_shapes(hq, hkv, bs, past, new):
 
 
 @pytest.mark.parametrize("cache,d,bs,hq,hkv", [("u8", 128, 32, 28, 4), ("f16", 128, 32, 28, 4), ("f16", 128, 16, 32, 8), ("bf16", 128, 16, 8, 2), ("f16", 64, 16, 12, 4),
-                                               ("bf16", 64, 32, 40, 2)])
+                                               ("f16", 64, 32, 32, 4), ("u8", 64, 32, 32, 4), ("u8", 64, 16, 12, 4), ("bf16", 64, 32, 40, 2)])
 def test_prefill_tensor_core_matches_generic_kernel(monkeypatch, cache, d, bs, hq, hkv):
-    """The tensor-core chunk kernels (tcgen05 for the u8 and f16 caches at head size 128, mma.sync for the bf16 cache and head size 64)
-    against the CUDA-core one."""
+    """The tensor-core chunk kernels (tcgen05 for the u8 and f16 caches, mma.sync for the bf16 cache) against the CUDA-core one."""
     wl = H.small_workload(hq=hq, hkv=hkv, d=d, bs=bs, act=torch.float16, cache=cache, past=[500, 0, 33], new=[256, 100, 2], seed=71)
     data = H.make_host_data(wl)
     tc = H.run_gpu(wl, data)
