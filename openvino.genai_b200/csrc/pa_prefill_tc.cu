@@ -59,6 +59,8 @@ constexpr int kThreads = (kWarpLoad + 1) * 32;
 static_assert(kPrefillItemRows == 2 * kRows, "an item is two UMMA row tiles");
 
 template <int BS, int CT, int D>
+struct PrefillSmem16;
+template <int BS, int CT, int D>
 struct PrefillSmem;
 
 template <int BS, int D>
@@ -93,10 +95,16 @@ struct PrefillSmem<BS, PA_DTYPE_U8, D> {
     volatile int abort;
 };
 
-// f16 cache: operand tiles only
+// f16 / bf16 cache: operand tiles only.  The bf16 variant has no denominator columns (P takes their place in tensor memory
+// as two bf16 pieces, and the rows sum their own probabilities).
 template <int BS, int D>
-struct PrefillSmem<BS, PA_DTYPE_F16, D> {
-    static constexpr int NO = D + kDx;
+struct PrefillSmem<BS, PA_DTYPE_F16, D> : PrefillSmem16<BS, PA_DTYPE_F16, D> {};
+template <int BS, int D>
+struct PrefillSmem<BS, PA_DTYPE_BF16, D> : PrefillSmem16<BS, PA_DTYPE_BF16, D> {};
+
+template <int BS, int CT, int D>
+struct PrefillSmem16 {
+    static constexpr int NO = CT == PA_DTYPE_BF16 ? D : D + kDx;
     static constexpr int NREC = kKv / BS;
     static constexpr int NST = kStages16;
     alignas(1024) uint8_t q[2][kRows * D * 2];        // per half: D / 64 swizzle atoms of [128 rows][64 dims]
@@ -248,10 +256,12 @@ __device__ __forceinline__ Item locate_item(const KernelArgs& a, int item, int G
 template <int BS, int CT, int D>
 __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     using Smem = PrefillSmem<BS, CT, D>;
-    constexpr bool U8 = CT == PA_DTYPE_U8;
+    constexpr bool U8 = CT == PA_DTYPE_U8, BF = CT == PA_DTYPE_BF16;
     constexpr int kD = D, kNo = Smem::NO, kTmemP = 2 * kKv + 2 * kNo, NST = Smem::NST;
+    constexpr int kPCols = BF ? kKv : kKv / 2;   // tensor-memory columns of one half's P: f16, or bf16 high + low pieces
+    constexpr int kFmt = BF ? 1 : 0;
     static_assert(!U8 || NST == 2, "the converter and the loader of the u8 variant index two stages");
-    static_assert(kTmemP + kKv <= kTmemCols, "S, O and P of both halves fit the tensor memory");
+    static_assert(kTmemP + 2 * kPCols <= kTmemCols, "S, O and P of both halves fit the tensor memory");
     extern __shared__ uint8_t smem_raw_[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw_) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -295,7 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         }
     } else {
         // row 0 of the constant tile (16-byte units 0 and 8: its two halves along the tokens) is all ones
-        if (tid < 32) {
+        if (!BF && tid < 32) {
             const uint32_t one2 = tid == 0 || tid == 8 ? 0x3C003C00u : 0u;
             *reinterpret_cast<uint4*>(sm.ones + tid * 16) = make_uint4(one2, one2, one2, one2);
         }
@@ -353,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // this warp's TMEM lanes
         const uint32_t tmem_s = tmem + kKv * X + lane_base, tmem_o = tmem + 2 * kKv + kNo * X + lane_base;
         uint8_t* const sq = sm.q[X];
-        const uint32_t tmem_p = tmem + kTmemP + (kKv / 2) * X + lane_base;
+        const uint32_t tmem_p = tmem + kTmemP + kPCols * X + lane_base;
         uint32_t n = 0;   // tiles of this half so far, over all items
         for (uint32_t ik = 0;; ++ik) {
             const int item = fetch_item(ik);
@@ -375,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 // prescale keeps the packed row and its sum inside the f16 range (the decode kernel does the same), and the
                 // softmax scale of the row takes it back out
                 float qmul = 1.f;
-                if (row_live) {
+                if (!BF && row_live) {   // (the bf16 variant runs on bf16 activations only: its rows go in as they are)
                     float amax = 0.f;
 #pragma unroll 4
                     for (int c = 0; c < kD / 8; ++c) {
@@ -401,10 +411,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] *= qmul;
                     uint4 w;
-                    w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
-                    const __half2* h = reinterpret_cast<const __half2*>(&w);
+                    if constexpr (BF) {
+                        w.x = pack_bf2(v[0], v[1]); w.y = pack_bf2(v[2], v[3]); w.z = pack_bf2(v[4], v[5]); w.w = pack_bf2(v[6], v[7]);
+                    } else {
+                        w.x = pack_h2(v[0], v[1]); w.y = pack_h2(v[2], v[3]); w.z = pack_h2(v[4], v[5]); w.w = pack_h2(v[6], v[7]);
+                    }
+                    if constexpr (U8) {
+                        const __half2* h = reinterpret_cast<const __half2*>(&w);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
+                        for (int e = 0; e < 4; ++e) qsum += __low2float(h[e]) + __high2float(h[e]);
+                    }
                     *reinterpret_cast<uint4*>(sq + (c / 8) * (kRows * 128) + sw128(r, c % 8)) = w;
                 }
                 if constexpr (U8) {
@@ -418,6 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             }
 
             float m_run = -INFINITY;   // running maximum of q.k' (before the softmax scale)
+            float l_own = 0.f;         // bf16 variant: the row's own sum of probabilities
             for (int j = 0; j < it.nt[X]; ++j, ++n) {
                 const int col0 = j * kKv;
                 if (!wait_warp(&sm.s_full[X], n & 1, 0)) goto done;
@@ -458,10 +475,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     rescale = __any_sync(0xffffffffu, grow);
                     if (grow) { alpha = ex2((m_run - mx) * qs); m_run = mx; }
                 }
+                if constexpr (BF) l_own *= alpha;
                 // P = 2^(qs * (s - m)) in f16 pairs: the exponent is rounded to f16 first, which costs
                 // at most 2^-12 of the exponent's magnitude in relative error of p
                 const float mq = m_run * qs;
                 uint32_t pw[kKv / 2];
+                uint32_t pl[BF ? kKv / 2 : 1];   // bf16 variant: the low pieces, p = high + low up to 2^-17 p
 #pragma unroll
                 for (int c = 0; c < kKv; c += 2) {
 #if defined(PA_EXP_NOEXP)
@@ -471,8 +490,17 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
 #else
                     // the packed f16 exponential is good to 2^-9.9 relative: inside the u8 cache's error bound, not inside the
                     // f16 cache's, whose P goes through the f32 exponential and is rounded once
-                    if constexpr (U8) pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qs, -mq), fmaf(sv[c + 1], qs, -mq)));
-                    else pw[c >> 1] = pack_h2(ex2(fmaf(sv[c], qs, -mq)), ex2(fmaf(sv[c + 1], qs, -mq)));
+                    if constexpr (U8) {
+                        pw[c >> 1] = ex2_h2(pack_h2(fmaf(sv[c], qs, -mq), fmaf(sv[c + 1], qs, -mq)));
+                    } else if constexpr (BF) {
+                        const float p0 = ex2(fmaf(sv[c], qs, -mq)), p1 = ex2(fmaf(sv[c + 1], qs, -mq));
+                        l_own += p0 + p1;
+                        const uint32_t hi = pack_bf2(p0, p1);
+                        pw[c >> 1] = hi;
+                        pl[c >> 1] = pack_bf2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
+                    } else {
+                        pw[c >> 1] = pack_h2(ex2(fmaf(sv[c], qs, -mq)), ex2(fmaf(sv[c + 1], qs, -mq)));
+                    }
 #endif
                 }
 #endif
@@ -493,15 +521,18 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                         for (int c = 0; c < 32; ++c) t[c] = __float_as_uint(__uint_as_float(t[c]) * alpha);
                         tc05::st_32x32b_x32(tmem_o + 32 * q4, t);
                     }
-                    uint32_t t[16];
-                    tc05::ld_32x32b_x16(tmem_o + kD, t);
-                    tc05::wait_ld();
+                    if constexpr (!BF) {
+                        uint32_t t[16];
+                        tc05::ld_32x32b_x16(tmem_o + kD, t);
+                        tc05::wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) t[c] = __float_as_uint(__uint_as_float(t[c]) * alpha);
-                    tc05::st_32x32b_x16(tmem_o + kD, t);
+                        for (int c = 0; c < 16; ++c) t[c] = __float_as_uint(__uint_as_float(t[c]) * alpha);
+                        tc05::st_32x32b_x16(tmem_o + kD, t);
+                    }
                     tc05::wait_st();
                 }
                 tc05::st_32x32b_x32(tmem_p, pw);   // row r of the A operand: lane r, two tokens per column
+                if constexpr (BF) tc05::st_32x32b_x32(tmem_p + kKv / 2, pl);
                 tc05::wait_st();
                 tc05::fence_before_thread_sync();
                 warp_arrive(&sm.p_full[X]);
@@ -512,11 +543,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             if (!wait_warp(&sm.o_done[X], (n - 1) & 1, 2)) goto done;
             tc05::fence_after_thread_sync();
             {
-                uint32_t zr[16];
-                tc05::ld_32x32b_x16(tmem_o + kD, zr);
-                tc05::wait_ld();
-                const float z = U8 ? __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]) : 0.f;
-                const float l_run = __uint_as_float(zr[U8 ? 3 : 0]);
+                float z = 0.f, l_run = l_own;
+                if constexpr (!BF) {
+                    uint32_t zr[16];
+                    tc05::ld_32x32b_x16(tmem_o + kD, zr);
+                    tc05::wait_ld();
+                    if constexpr (U8) z = __uint_as_float(zr[0]) + __uint_as_float(zr[1]) + __uint_as_float(zr[2]);
+                    l_run = __uint_as_float(zr[U8 ? 3 : 0]);
+                }
                 const float inv = 1.f / l_run;
 #pragma unroll
                 for (int q4 = 0; q4 < kD / 32; ++q4) {
@@ -731,8 +765,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         // The whole warp runs the loop (uniform control flow keeps the descriptors in uniform registers);
         // one elected lane issues the tensor-core instructions.
         {
-            constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, 0, 0, 0);   // f16, A and B K-major
-            constexpr uint32_t idesc_o = U8 ? tc05::instr_desc_f16(kRows, kNo, 0, 0, 0) : tc05::instr_desc_f16(kRows, kD, 0, 0, 1);   // f16 cache: V' MN-major
+            constexpr uint32_t idesc_s = tc05::instr_desc_f16(kRows, kKv, kFmt, 0, 0);   // A and B K-major
+            constexpr uint32_t idesc_o = U8 ? tc05::instr_desc_f16(kRows, kNo, 0, 0, 0) : tc05::instr_desc_f16(kRows, kD, kFmt, 0, 1);   // f16 / bf16 cache: V' MN-major
             constexpr uint32_t idesc_l = tc05::instr_desc_f16(kRows, kDx, 0, 0, 0);   // f16 cache: P . ones
             // operand descriptors are built once; a step along K or to another buffer only moves the
             // start-address field (bits [0,14) of the low word, in 16-byte units, no carry out of it)
@@ -746,7 +780,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 dkx = tc05::smem_desc_plain(smem_u32(sm.kx[0]), 128, 256);
                 qx_step = sizeof(sm.qx[0]) >> 4;
                 kx_step = sizeof(sm.kx[0]) >> 4;
-            } else {
+            } else if constexpr (!BF) {
                 dones = tc05::smem_desc_plain(smem_u32(sm.ones), 128, 256);
             }
             constexpr uint32_t q_step = sizeof(sm.q[0]) >> 4, k_step = sizeof(sm.k[0]) >> 4, v_step = sizeof(sm.vt[0]) >> 4;
@@ -766,7 +800,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 __syncwarp();
             };
             auto issue_pv = [&](int X, int st, bool acc) {
-                const uint32_t pa = tmem + kTmemP + (kKv / 2) * X;   // 16 tokens of P = 8 columns
+                const uint32_t pa = tmem + kTmemP + kPCols * X;   // 16 tokens of P = 8 columns
                 const uint64_t db0 = dv + st * v_step;
                 const uint32_t d = tmem + 2 * kKv + kNo * X;
                 if (tc05::elect_one()) {
@@ -775,6 +809,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                     else tc05::mma_ts<0>(d, pa, db0, idesc_o);
 #pragma unroll
                     for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 2 * kk, idesc_o);
+                } else if constexpr (BF) {
+                    // high pieces of P, then the low pieces against the same value rows
+                    if (acc) tc05::mma_ts<1>(d, pa, db0, idesc_o);
+                    else tc05::mma_ts<0>(d, pa, db0, idesc_o);
+#pragma unroll
+                    for (int kk = 1; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + 8 * kk, db0 + 128 * kk, idesc_o);
+#pragma unroll
+                    for (int kk = 0; kk < kKv / 16; ++kk) tc05::mma_ts<1>(d, pa + kKv / 2 + 8 * kk, db0 + 128 * kk, idesc_o);
                 } else {
                     // 16 tokens further along K = 16 rows of 128 bytes; the denominators go to the 16 columns after O
 #ifdef PA_EXP_NOONES
@@ -927,7 +969,9 @@ done:
 }  // namespace
 
 bool prefill_tc_supported(const CacheGeom& g) {
-    return (g.cache == PA_DTYPE_U8 || g.cache == PA_DTYPE_F16) && (g.D == 128 || g.D == 64) && (g.bs == 32 || g.bs == 16) && g.Hq % g.Hkv == 0;
+    // the bf16 cache with bf16 activations only: other queries would need a second, low piece of every row
+    const bool cache_ok = g.cache == PA_DTYPE_U8 || g.cache == PA_DTYPE_F16 || (g.cache == PA_DTYPE_BF16 && g.act == PA_DTYPE_BF16);
+    return cache_ok && (g.D == 128 || g.D == 64) && (g.bs == 32 || g.bs == 16) && g.Hq % g.Hkv == 0;
 }
 
 namespace {
@@ -950,7 +994,8 @@ cudaError_t launch_prefill_tc(const KernelArgs& a, cudaStream_t stream, int sm_c
     const int grid = (int)std::min<long long>(max_items, sm_count);
     cudaError_t e;
     if (a.g.cache == PA_DTYPE_U8) e = a.g.D == 128 ? launch_tc_bs<PA_DTYPE_U8, 128>(a, stream, grid) : launch_tc_bs<PA_DTYPE_U8, 64>(a, stream, grid);
-    else e = a.g.D == 128 ? launch_tc_bs<PA_DTYPE_F16, 128>(a, stream, grid) : launch_tc_bs<PA_DTYPE_F16, 64>(a, stream, grid);
+    else if (a.g.cache == PA_DTYPE_F16) e = a.g.D == 128 ? launch_tc_bs<PA_DTYPE_F16, 128>(a, stream, grid) : launch_tc_bs<PA_DTYPE_F16, 64>(a, stream, grid);
+    else e = a.g.D == 128 ? launch_tc_bs<PA_DTYPE_BF16, 128>(a, stream, grid) : launch_tc_bs<PA_DTYPE_BF16, 64>(a, stream, grid);
     if (e != cudaSuccess) return e;
     ++*launches;
     return cudaSuccess;

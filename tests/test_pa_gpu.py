@@ -88,17 +88,22 @@ def test_prefill_tensor_core_shapes(hq, hkv, bs, past, new):
     _check(H.run_both(wl), "u8", torch.bfloat16)
 
 
-@pytest.mark.parametrize("cache,d,bs,hq,hkv", [("u8", 128, 32, 28, 4), ("f16", 128, 32, 28, 4), ("f16", 128, 16, 32, 8), ("bf16", 128, 16, 8, 2), ("f16", 64, 16, 12, 4),
-                                               ("f16", 64, 32, 32, 4), ("u8", 64, 32, 32, 4), ("u8", 64, 16, 12, 4), ("bf16", 64, 32, 40, 2)])
-def test_prefill_tensor_core_matches_generic_kernel(monkeypatch, cache, d, bs, hq, hkv):
-    """The tensor-core chunk kernels (tcgen05 for the u8 and f16 caches, mma.sync for the bf16 cache) against the CUDA-core one."""
-    wl = H.small_workload(hq=hq, hkv=hkv, d=d, bs=bs, act=torch.float16, cache=cache, past=[500, 0, 33], new=[256, 100, 2], seed=71)
+@pytest.mark.parametrize("cache,d,bs,hq,hkv,act", [
+    ("u8", 128, 32, 28, 4, torch.float16), ("f16", 128, 32, 28, 4, torch.float16), ("f16", 128, 16, 32, 8, torch.float16),
+    ("f16", 64, 16, 12, 4, torch.float16), ("f16", 64, 32, 32, 4, torch.float32), ("u8", 64, 32, 32, 4, torch.bfloat16), ("u8", 64, 16, 12, 4, torch.float16),
+    ("bf16", 128, 32, 28, 4, torch.bfloat16), ("bf16", 128, 16, 8, 2, torch.bfloat16), ("bf16", 64, 32, 40, 2, torch.bfloat16), ("bf16", 64, 16, 8, 8, torch.bfloat16),
+    ("bf16", 128, 16, 8, 2, torch.float16), ("bf16", 64, 32, 40, 2, torch.float32)])
+def test_prefill_tensor_core_matches_generic_kernel(monkeypatch, cache, d, bs, hq, hkv, act):
+    """The tensor-core chunk kernels (tcgen05 for the u8 and f16 caches and for the bf16 cache under bf16 activations, mma.sync for
+    the bf16 cache under other activations) against the CUDA-core one."""
+    wl = H.small_workload(hq=hq, hkv=hkv, d=d, bs=bs, act=act, cache=cache, past=[500, 0, 33], new=[256, 100, 2], seed=71)
     data = H.make_host_data(wl)
     tc = H.run_gpu(wl, data)
     monkeypatch.setenv("PA_B200_GENERIC_PREFILL", "1")
     gen = H.run_gpu(wl, data)
     assert tc["status"] == 0 and gen["status"] == 0
-    assert H.rel_err(tc["out_gpu"], gen["out_gpu"]) < 2e-3
+    # both kernels round their output to the activation type: bf16 outputs differ by an ulp where the f32 values straddle a tie
+    assert H.rel_err(tc["out_gpu"], gen["out_gpu"]) < (8e-3 if act == torch.bfloat16 else 2e-3)
 
 
 def test_host_entry_point_matches():
