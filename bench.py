@@ -361,6 +361,10 @@ SECONDARY = {
     "qwen25_7b_prefill": (dict(num_decode=0, rotated_fraction=0.0), False, "16 prefill chunks of 256 tokens, past U[0,4096]"),
     "qwen25_7b_prefill_large": (dict(num_prefill=64, chunk=512, prefill_hi=8192, num_decode=0, rotated_fraction=0.0), False,
                                 "64 prefill chunks of 512 tokens, past U[0,8192]"),
+    "qwen25_7b_prefill_large_f16": (dict(num_prefill=64, chunk=512, prefill_hi=8192, num_decode=0, rotated_fraction=0.0, cache="f16"), False,
+                                    "64 prefill chunks of 512 tokens, past U[0,8192], f16 cache and activations"),
+    "qwen25_7b_prefill_large_bf16": (dict(num_prefill=64, chunk=512, prefill_hi=8192, num_decode=0, rotated_fraction=0.0, cache="bf16"), False,
+                                     "64 prefill chunks of 512 tokens, past U[0,8192], bf16 cache and activations"),
 }
 
 
@@ -407,9 +411,9 @@ def measure_pa_step(env: Env, name: str, steps: int, warmup: int) -> dict:
     flops = wl.prefill_flops()
     res = {"metric": "pa_step_ms", "value": round(ms, 4), "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3),
            "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-           "dtype": "f16 tcgen05 / f32 accumulate", "data": "synthetic",
+           "dtype": ("bf16" if kw.get("cache") == "bf16" else "f16") + " tcgen05 / f32 accumulate", "data": "synthetic",
            "config": {"workload": name, "what": what, "tokens": int(wl.num_tokens), "sequences": int(wl.num_sequences),
-                      "kv_cache": "u8 by-token asymmetric", "prefill_gflop": round(flops / 1e9, 1),
+                      "kv_cache": {"f16": "f16", "bf16": "bf16"}.get(kw.get("cache"), "u8 by-token asymmetric"), "prefill_gflop": round(flops / 1e9, 1),
                       "decode_kv_mb": round(wl.decode_kv_bytes() / 1e6, 1), "l2_policy": "KV bytes per step exceed L2"},
            "gpu_launches": int(op.launch_count() - launches0), "clocks": clocks}
     if wl.decode_kv_bytes() == 0 and flops:

@@ -122,14 +122,14 @@ def config_llama3_8b_decode(num_seqs: int = 64, pool: int = 20000, lo: int = 512
 
 def config_qwen_mixed(num_prefill: int = 16, chunk: int = 256, prefill_hi: int = 4096, num_decode: int = 240,
                       decode_lo: int = 256, decode_hi: int = 16384, pool: Optional[int] = None, rotated_fraction: float = 0.1,
-                      lut_rows: int = 513, theta: float = 1e6, seed: int = 1003) -> AttnWorkload:
-    """Qwen2.5-7B attention shape, one mixed step: prefill chunks + decode rows, u8 cache, score
-    output (window 8 on prefill rows, 1 on decode rows) and 10 % of the blocks re-rotated."""
+                      lut_rows: int = 513, theta: float = 1e6, seed: int = 1003, cache: str = "u8") -> AttnWorkload:
+    """Qwen2.5-7B attention shape, one mixed step: prefill chunks + decode rows, u8 cache (or `cache` = "f16" / "bf16" with
+    activations of the same type), score output (window 8 on prefill rows, 1 on decode rows) and 10 % of the blocks re-rotated."""
     rng = np.random.default_rng(seed)
     past = np.concatenate([rng.integers(0, prefill_hi + 1, size=num_prefill), rng.integers(decode_lo, decode_hi + 1, size=num_decode)])
     new = np.concatenate([np.full(num_prefill, chunk), np.ones(num_decode, np.int64)])
     need = int(((past + new + 31) // 32).sum())
-    wl = make_workload("qwen25_7b_mixed", hq=28, hkv=4, d=128, bs=32, act=torch.bfloat16, cache="u8", past=past, new=new,
+    wl = make_workload("qwen25_7b_mixed", hq=28, hkv=4, d=128, bs=32, act=torch.float16 if cache == "f16" else torch.bfloat16, cache=cache, past=past, new=new,
                        num_blocks=pool or int(need * 1.1) + 1, seed=seed)
     wl.score_aggregation_window = np.concatenate([np.full(num_prefill, 8), np.ones(num_decode, np.int64)]).astype(np.int32)
     # rotate 10 % of every sequence's fully past blocks (blocks the chunk does not write)

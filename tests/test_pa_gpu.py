@@ -70,9 +70,10 @@ def test_decode_f32_activations():
 
 
 @pytest.mark.parametrize("cache", ["f16", "bf16", "u8"])
-def test_prefill_and_mixed_parity(cache):
+@pytest.mark.parametrize("d,bs", [(128, 32), (64, 32), (64, 16)])
+def test_prefill_and_mixed_parity(cache, d, bs):
     act = torch.float16 if cache == "f16" else torch.bfloat16
-    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache=cache, past=[0, 40, 300, 0, 65], new=[37, 1, 64, 1, 130], seed=41)
+    wl = H.small_workload(hq=8, hkv=2, d=d, bs=bs, act=act, cache=cache, past=[0, 40, 300, 0, 65], new=[37, 1, 64, 1, 130], seed=41)
     _check(H.run_both(wl), cache, act)
 
 
