@@ -19,7 +19,7 @@ struct PlanHeader {
     int pitems_sorted; // 1: pitem_order lists the q tiles by decreasing context length
 };
 
-constexpr int kPrefillSortCap = 512;   // q tiles (per kv head) up to which the plan step orders them
+constexpr int kPrefillSortCap = 2048;  // q tiles (per kv head) up to which the plan step orders them
 
 // Where a decode worker's slice of the global tile sequence starts, prepared by the plan step so
 // that the worker's first load is one 32-byte record instead of a binary search.
