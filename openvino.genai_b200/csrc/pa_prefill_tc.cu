@@ -902,6 +902,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             for (uint32_t ik = 0;; ++ik) {
                 const int slot = ik & (kItemSlots - 1);
                 if (ik >= kItemSlots && !wait(&sm.item_free[slot], ((ik / kItemSlots) - 1) & 1, 1)) goto done;
+                if constexpr (!U8) {
+                    // Nothing throttles this loader (it copies no tiles), and an item drawn early is an item another CTA cannot
+                    // take: the next one is drawn when every role has started the previous one, which is still several tiles
+                    // before the copy warps need it.
+                    if (ik >= 1 && !wait(&sm.item_free[(ik - 1) & (kItemSlots - 1)], ((ik - 1) / kItemSlots) & 1, 1)) goto done;
+                }
                 int item = atomicAdd(&a.plan->next_pitem, 1);
                 if (item >= total_items) item = -1;
                 sm.item_ring[slot] = item;
