@@ -12,8 +12,8 @@
 //                          f16(v scale) as [128 dims][64 tokens] (the cache keeps value bytes
 //                          token-minor, so both are K-major operands), two stages each;
 //   mma       (1 warp, one elected lane issues) tcgen05.mma: S_X = Q_X.K'^T into TMEM, O_X += P_X.V' in
-//                          TMEM, for X = A, B; as soon as half X has published P of tile j its P.V and
-//                          the S of tile j + 1 are queued, so the tensor core works on one half while the
+//                          TMEM, for X = A, B; as soon as half X has published P of tile j the S of tile
+//                          j + 1 and then its P.V are queued, so the tensor core works on one half while the
 //                          other half's softmax runs;
 //   softmax   (2 x 4 warps) thread r owns row r of its half: reads S from TMEM, masks (diagonal
 //                          tiles only), keeps a lazy running maximum, writes P = 2^(scale*(s-m)) as
@@ -879,8 +879,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                             if (!wait_warp(&sm.p_full[X], (n[X] + j) & 1, 4)) goto done;
                             PA_TRACE(3, 4 + 2 * X, t);
                             tc05::fence_after_thread_sync();
-                            issue_pv(X, st, j > 0);
+                            // the next logits first: the half's softmax warps wait for them, nobody waits for this P.V yet
                             if (j + 1 < it.nt[X]) issue_s(X, st1);
+                            issue_pv(X, st, j > 0);
                             PA_TRACE(3, 5 + 2 * X, t);
                         }
                     if (tc05::elect_one()) {
