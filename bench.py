@@ -646,6 +646,9 @@ def main():
                     sec["prefill"] = {"tflops": r["roofline"]["achieved"], "peak_tflops": r["roofline"]["peak"], "ms_per_step": r["value"], "what": r["config"]["what"]}
                     r = measure_pa_step(env, "qwen25_7b_prefill", 20, 3)
                     sec["prefill_tensor_frac_16x256"] = r["roofline"]["frac"]
+                    for cache in ("f16", "bf16"):   # the same 64 chunks over the 16-bit caches (activations of the cache's type)
+                        r = measure_pa_step(env, "qwen25_7b_prefill_large_" + cache, 10, 3)
+                        sec["prefill_tensor_frac_" + cache] = r["roofline"]["frac"]
                 if env.rank == 0:
                     line["secondary"] = sec
             if env.rank == 0 and env.world == 1 and not args.no_cpu_baseline:
