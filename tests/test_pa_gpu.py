@@ -273,11 +273,11 @@ def test_a_copy_that_never_arrives_ends_with_a_status_bit_not_a_hang(monkeypatch
     assert again["status"] == 0 and np.allclose(again["out_gpu"], good["out_gpu"], rtol=2e-2, atol=2e-3)
 
 
-@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
-def test_queries_beyond_the_f16_range(act):
+@pytest.mark.parametrize("act,cache", [(torch.float32, "u8"), (torch.bfloat16, "u8"), (torch.float32, "f16"), (torch.bfloat16, "f16"), (torch.bfloat16, "bf16")])
+def test_queries_beyond_the_f16_range(act, cache):
     """|q| around 1e5 (with a softmax scale that brings the logits back to order one): prefill chunks and decode
     rows rescale such rows by an exact power of two before packing them for the tensor cores."""
-    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache="u8", past=[300, 40, 0], new=[64, 1, 33], seed=127, scale=1.0 / (1.0e5 * 128 ** 0.5))
+    wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=act, cache=cache, past=[300, 40, 0], new=[64, 1, 33], seed=127, scale=1.0 / (1.0e5 * 128 ** 0.5))
     q, k, v, fill, pk, pv = H.make_host_data(wl)
     data = ((q.float() * 1.0e5).to(act), k, v, fill, pk, pv)
     res = H.run_oracle(wl, data)
