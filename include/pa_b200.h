@@ -173,6 +173,15 @@ int pa_b200_last_device_status(pa_handle* h, uint32_t* status_bits);
 /* Number of kernels this handle has launched since creation (for launch accounting). */
 int64_t pa_b200_launch_count(const pa_handle* h);
 
+/* Which kernel served the prefill chunks of the handle's last forward call (for tests and launch accounting): */
+enum pa_prefill_kernel {
+    PA_PREFILL_NONE = 0,     /* the step had no row with more than one new token */
+    PA_PREFILL_GENERIC = 1,  /* CUDA cores, one warp per (token, q head) */
+    PA_PREFILL_MMA_SYNC = 2, /* mma.sync m16n8k16 */
+    PA_PREFILL_TCGEN05 = 3   /* tcgen05.mma with accumulators in tensor memory */
+};
+int pa_b200_last_prefill_kernel(const pa_handle* h);
+
 /* Measurement support: while enabled, every forward call records a CUDA event pair around its
  * split-K decode kernel on the stream it launches on.  get_kernel_timing waits for the recorded
  * pairs, returns their summed duration and count, and clears them (at most 4096 pairs are kept). */

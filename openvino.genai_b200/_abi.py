@@ -118,6 +118,7 @@ PA_SYMBOLS = {
     "pa_b200_forward_host": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),
     "pa_b200_last_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "pa_b200_launch_count": (C.c_int64, [C.c_void_p]),
+    "pa_b200_last_prefill_kernel": (C.c_int, [C.c_void_p]),
     "pa_b200_set_kernel_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "pa_b200_get_kernel_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "pa_b200_write_kv": (C.c_int, [C.c_void_p, C.POINTER(pa_forward_args)]),

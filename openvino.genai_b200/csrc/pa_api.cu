@@ -52,6 +52,7 @@ struct pa_handle {
     uint8_t* stage_host = nullptr;  // pinned
     size_t stage_host_bytes = 0;
     int64_t launches = 0;
+    int last_prefill_kernel = PA_PREFILL_NONE;
     bool force_generic_prefill = false;        // env PA_B200_GENERIC_PREFILL=1: cross-check path
     bool test_drop_copy = false;               // env PA_B200_TEST_DROP_FIRST_COPY=1: the decode kernel's bounded wait is made to run out
     bool timing = false;                       // record events around the split-K decode kernel
@@ -239,15 +240,19 @@ int run_forward(pa_handle* h, const pa_forward_args* a, cudaStream_t stream) {
     }
     if (shared_decode) PA_CUDA(pa::launch_decode_shared(k, stream, h->sm_count, &launches, ev0, ev1));
     else PA_CUDA(pa::launch_decode(k, stream, h->sm_count, &launches, ev0, ev1));
+    h->last_prefill_kernel = PA_PREFILL_NONE;
     if (a->num_tokens > a->num_sequences) {
         const int G = h->g.Hq / h->g.Hkv;
         const long long max_items = ((long long)a->num_tokens * G / pa::kPrefillItemRows + a->num_sequences) * h->g.Hkv;
         if (pa::prefill_tc_supported(h->g) && !h->force_generic_prefill) {
             PA_CUDA(pa::launch_prefill_tc(k, stream, h->sm_count, max_items, &launches));
+            h->last_prefill_kernel = PA_PREFILL_TCGEN05;
         } else if (pa::prefill_mma_supported(h->g) && !h->force_generic_prefill) {
             PA_CUDA(pa::launch_prefill_mma(k, stream, max_items, &launches));
+            h->last_prefill_kernel = PA_PREFILL_MMA_SYNC;
         } else {
             PA_CUDA(pa::launch_prefill(k, stream, &launches));
+            h->last_prefill_kernel = PA_PREFILL_GENERIC;
         }
     }
     if (a->scores) PA_CUDA(pa::launch_scores(k, stream, h->sm_count, &launches));
@@ -422,6 +427,7 @@ int pa_b200_marshal_inputs(pa_handle* h, const pa_marshal_args* a) {
 }
 
 int64_t pa_b200_launch_count(const pa_handle* h) { return h ? h->launches : -1; }
+int pa_b200_last_prefill_kernel(const pa_handle* h) { return h ? h->last_prefill_kernel : -1; }
 
 int pa_b200_set_kernel_timing(pa_handle* h, int enabled) {
     if (!h) return fail(PA_ERR_INVALID_ARG, "NULL handle");

@@ -139,6 +139,10 @@ class PagedAttentionExtension:
     def launch_count(self) -> int:
         return int(self.lib.pa_b200_launch_count(self._h))
 
+    def last_prefill_kernel(self) -> str:
+        """Which kernel served the prefill chunks of the last forward call: "none", "generic", "mma_sync" or "tcgen05"."""
+        return ("none", "generic", "mma_sync", "tcgen05")[int(self.lib.pa_b200_last_prefill_kernel(self._h))]
+
     def copy_blocks(self, key_cache, value_cache, pairs, stream=None) -> None:
         lay = self.cache_layout()
         self._check(self.lib.pa_b200_copy_blocks(self._h, _ptr(key_cache), _ptr(value_cache),

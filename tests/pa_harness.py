@@ -139,7 +139,7 @@ def run_gpu(wl, data=None, device=0, host_entry=False, op=None, caches=None):
         scores_np = scores.cpu().numpy() if want_scores else None
     status = op.device_status()
     return {"out_gpu": out_np, "kc_gpu": kc.cpu().numpy(), "vc_gpu": vc.cpu().numpy(), "scores_gpu": scores_np,
-            "status": status, "launches": op.launch_count(), "op": op}
+            "status": status, "launches": op.launch_count(), "prefill_kernel": op.last_prefill_kernel(), "op": op}
 
 
 def run_both(wl, device=0, host_entry=False):

@@ -74,7 +74,9 @@ def test_decode_f32_activations():
 def test_prefill_and_mixed_parity(cache, d, bs):
     act = torch.float16 if cache == "f16" else torch.bfloat16
     wl = H.small_workload(hq=8, hkv=2, d=d, bs=bs, act=act, cache=cache, past=[0, 40, 300, 0, 65], new=[37, 1, 64, 1, 130], seed=41)
-    _check(H.run_both(wl), cache, act)
+    res = H.run_both(wl)
+    _check(res, cache, act)
+    assert res["prefill_kernel"] == "tcgen05"   # every cache type, both head sizes
 
 
 @pytest.mark.parametrize("hq,hkv,bs,past,new", [
@@ -103,6 +105,8 @@ def test_prefill_tensor_core_matches_generic_kernel(monkeypatch, cache, d, bs, h
     monkeypatch.setenv("PA_B200_GENERIC_PREFILL", "1")
     gen = H.run_gpu(wl, data)
     assert tc["status"] == 0 and gen["status"] == 0
+    assert gen["prefill_kernel"] == "generic"
+    assert tc["prefill_kernel"] == ("mma_sync" if cache == "bf16" and act != torch.bfloat16 else "tcgen05")
     # both kernels round their output to the activation type: bf16 outputs differ by an ulp where the f32 values straddle a tie
     assert H.rel_err(tc["out_gpu"], gen["out_gpu"]) < (8e-3 if act == torch.bfloat16 else 2e-3)
 
