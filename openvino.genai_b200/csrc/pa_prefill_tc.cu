@@ -58,6 +58,16 @@ constexpr int kWarpMma = kSoftmaxWarps + kConvWarps, kWarpLoad = kWarpMma + 1;
 constexpr int kThreads = (kWarpLoad + 1) * 32;
 static_assert(kPrefillItemRows == 2 * kRows, "an item is two UMMA row tiles");
 
+// One work item as every role sees it.
+struct Item {
+    int s, hk, t0, n_new, past;
+    int row0;            // first (token, head) pair of half A
+    int ctx_hi[2];       // context the last row of each half sees (0: the half has no rows)
+    int nt[2];           // 64-token tiles of each half
+    int ntiles;          // max of the two
+    const int32_t* table;
+};
+
 template <int BS, int CT, int D>
 struct PrefillSmem16;
 template <int BS, int CT, int D>
@@ -91,6 +101,7 @@ struct PrefillSmem<BS, PA_DTYPE_U8, D> {
     alignas(8) uint64_t item_full[kItemSlots];   // loader -> every other warp
     alignas(8) uint64_t item_free[kItemSlots];   // every other warp -> loader: the slot has been read
     int item_ring[kItemSlots];
+    Item item_desc[kItemSlots];   // the loader locates an item once for every role
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -122,6 +133,7 @@ struct PrefillSmem16 {
     alignas(8) uint64_t item_full[kItemSlots];
     alignas(8) uint64_t item_free[kItemSlots];
     int item_ring[kItemSlots];
+    Item item_desc[kItemSlots];   // the loader locates an item once for every role
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -209,15 +221,6 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
     if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
 
-// One work item as every role sees it.
-struct Item {
-    int s, hk, t0, n_new, past;
-    int row0;            // first (token, head) pair of half A
-    int ctx_hi[2];       // context the last row of each half sees (0: the half has no rows)
-    int nt[2];           // 64-token tiles of each half
-    int ntiles;          // max of the two
-    const int32_t* table;
-};
 
 __device__ __forceinline__ Item locate_item(const KernelArgs& a, int item, int G, int Hkv) {
     Item it;
@@ -349,10 +352,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
     // Work items come from a global counter: the loader draws them and publishes each through a
     // small ring, so that all roles of the CTA walk the same sequence.  -1 ends the sequence, -2
     // reports a wait that ran out.
-    auto fetch_item = [&](uint32_t k) -> int {
+    auto fetch_item = [&](uint32_t k, Item& it) -> int {
         const int slot = k & (kItemSlots - 1);
         if (!wait_warp(&sm.item_full[slot], (k / kItemSlots) & 1, 0)) return -2;
         const int item = sm.item_ring[slot];
+        if (item >= 0) it = sm.item_desc[slot];
         warp_arrive(&sm.item_free[slot]);
         return item;
     };
@@ -366,10 +370,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         const uint32_t tmem_p = tmem + kTmemP + kPCols * X + lane_base;
         uint32_t n = 0;   // tiles of this half so far, over all items
         for (uint32_t ik = 0;; ++ik) {
-            const int item = fetch_item(ik);
+            Item it;
+            const int item = fetch_item(ik, it);
             if (item == -2) goto done;
             if (item < 0) break;
-            const Item it = locate_item(a, item, G, Hkv);
             if (it.nt[X] == 0) continue;
             const int flat = it.row0 + X * kRows + r;
             const int tok = flat / G, hq = it.hk * G + flat % G;
@@ -577,10 +581,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         if constexpr (U8) {
         uint32_t t = 0;   // tiles so far, over all items
         for (uint32_t ik = 0;; ++ik) {
-            const int item = fetch_item(ik);
+            Item it;
+            const int item = fetch_item(ik, it);
             if (item == -2) goto done;
             if (item < 0) break;
-            const Item it = locate_item(a, item, G, Hkv);
             const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
             for (int j = 0; j < it.ntiles; ++j, ++t) {
                 const int st = t & 1;
@@ -698,10 +702,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             uint32_t t = 0;
             bool bad_index = false;
             for (uint32_t ik = 0;; ++ik) {
-                const int item = fetch_item(ik);
+                Item it;
+                const int item = fetch_item(ik, it);
                 if (item == -2) goto done;
                 if (item < 0) break;
-                const Item it = locate_item(a, item, G, Hkv);
                 const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
                 const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes + 16 * ch;
                 const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)it.hk * a.g.head_bytes + 16 * ch;
@@ -842,10 +846,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             };
             uint32_t t = 0, n[2] = {0, 0}, iq[2] = {0, 0};
             for (uint32_t ik = 0;; ++ik) {
-                const int item = fetch_item(ik);
+                Item it;
+                const int item = fetch_item(ik, it);
                 if (item == -2) goto done;
                 if (item < 0) break;
-                const Item it = locate_item(a, item, G, Hkv);
                 // first S of the item.  The S region of a half is free: its softmax published the last P of
                 // the previous item (waited below) after reading that tile's S.
 #pragma unroll
@@ -911,11 +915,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
                 }
                 int item = atomicAdd(&a.plan->next_pitem, 1);
                 if (item >= total_items) item = -1;
+                Item it{};
+                if (item >= 0) {
+                    it = locate_item(a, item, G, Hkv);
+                    sm.item_desc[slot] = it;
+                }
                 sm.item_ring[slot] = item;
                 mbar_arrive(&sm.item_full[slot]);
                 if (item < 0) break;
                 if constexpr (U8) {
-                const Item it = locate_item(a, item, G, Hkv);
                 const int ctx_hi = max(it.ctx_hi[0], it.ctx_hi[1]);
                 const uint8_t* kc = (const uint8_t*)a.key_cache + (long long)it.hk * a.g.head_bytes;
                 const uint8_t* vc = (const uint8_t*)a.value_cache + (long long)it.hk * a.g.head_bytes;
