@@ -29,6 +29,9 @@
 // with the same shared-memory image; the softmax denominator comes from a second, 16-column P.V
 // product against a constant tile whose first row is all ones.  The raw ring, the extra dims and
 // the loader's copies do not exist in that variant.
+// The CTA has four warpgroups (softmax A, softmax B, converter / copy, {mma, loader, two idle warps}) that re-divide the
+// register file with setmaxnreg once their roles start: 160 registers per softmax thread, 104 per converter thread, 88 for
+// the rest (one warp of each warpgroup shares a scheduler's 16 K registers).
 // Every wait is bounded; a wait that runs out raises a flag that all roles poll.
 // Tensor-bound for long contexts: 4 * Hq * D flops per (new token, context token) pair.
 #include <algorithm>
@@ -55,7 +58,16 @@ constexpr float kLn2P = 0.6931471805599453f;
 
 constexpr int kSoftmaxWarps = 8, kConvWarps = 4;
 constexpr int kWarpMma = kSoftmaxWarps + kConvWarps, kWarpLoad = kWarpMma + 1;
-constexpr int kThreads = (kWarpLoad + 1) * 32;
+constexpr int kThreads = 512;   // four warpgroups: softmax A, softmax B, converter / copy warps, {mma, loader, two idle warps}
+// Registers per thread after the roles have re-divided the register file among the warpgroups (one warp of each shares a
+// scheduler's 16 K registers: 160 + 160 + 104 + 88 = 512 x 32)
+#ifndef PA_TC_REG_SOFTMAX
+#define PA_TC_REG_SOFTMAX 160
+#define PA_TC_REG_CONV 104
+#define PA_TC_REG_MISC 88
+#endif
+template <int R> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R)); }
+template <int R> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R)); }
 static_assert(kPrefillItemRows == 2 * kRows, "an item is two UMMA row tiles");
 
 // One work item as every role sees it.
@@ -361,8 +373,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         return item;
     };
 
+    if (warp >= kWarpMma) reg_dec<PA_TC_REG_MISC>();   // the fourth warpgroup: mma, loader and two warps that only keep it whole
     if (warp < kSoftmaxWarps) {
         // ======================= softmax + epilogue of half X ==========================================
+        reg_inc<PA_TC_REG_SOFTMAX>();
         const int X = warp >> 2, r = tid & (kRows - 1);
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // this warp's TMEM lanes
         const uint32_t tmem_s = tmem + kKv * X + lane_base, tmem_o = tmem + 2 * kKv + kNo * X + lane_base;
@@ -577,6 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
         }
     } else if (warp < kWarpMma) {
         // ======================= converter: raw records -> f16 operand tiles =============================
+        reg_dec<PA_TC_REG_CONV>();
         const int ctid = tid - kSoftmaxWarps * 32, cwarp = warp - kSoftmaxWarps;
         if constexpr (U8) {
         uint32_t t = 0;   // tiles so far, over all items
@@ -899,7 +914,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(KernelArgs a) {
             // every commit has landed before the CTA's shared memory is given up
             if (t > 0) wait_warp(&sm.v_free[(t - 1) % NST], ((t - 1) / NST) & 1, 0);
         }
-    } else {
+    } else if (warp == kWarpLoad) {
         // ======================= loader: TMA-engine copies of the tiles' records =========================
         if (lane == 0) {
             uint32_t t = 0;
