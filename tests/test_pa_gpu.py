@@ -111,6 +111,33 @@ def test_prefill_tensor_core_matches_generic_kernel(monkeypatch, cache, d, bs, h
     assert H.rel_err(tc["out_gpu"], gen["out_gpu"]) < (8e-3 if act == torch.bfloat16 else 2e-3)
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_mixed_steps_against_the_oracle(seed):
+    """Seeded random geometry (cache type, head size, block size, GQA group) and ragged sequences (past 0 ... 1500, 1 ... 300 new
+    tokens, decode rows mixed in): every kernel choice the dispatcher makes is compared with the oracle."""
+    rng = np.random.default_rng(1000 + seed)
+    cache = ["u8", "f16", "bf16"][seed % 3]
+    d = int(rng.choice([64, 128]))
+    bs = int(rng.choice([16, 32]))
+    hkv = int(rng.choice([1, 2, 4]))
+    g = int(rng.choice([1, 2, 3, 4, 7, 8]))
+    act = {"u8": [torch.float16, torch.bfloat16, torch.float32], "f16": [torch.float16, torch.float32], "bf16": [torch.bfloat16, torch.float16]}[cache][seed // 3 % 2]
+    nseq = int(rng.integers(2, 7))
+    past = [int(x) for x in rng.integers(0, 1500, nseq)]
+    new = [int(x) if rng.random() < 0.7 else 1 for x in rng.integers(1, 300, nseq)]
+    past[0] = 0                                   # a first chunk without context
+    wl = H.small_workload(hq=hkv * g, hkv=hkv, d=d, bs=bs, act=act, cache=cache, past=past, new=new, seed=500 + seed)
+    res = H.run_both(wl)
+    assert res["status"] == 0
+    assert np.array_equal(res["kc_gpu"], res["kc_ref"]) and np.array_equal(res["vc_gpu"], res["vc_ref"])
+    tol = 1e-2 if cache == "u8" else 2e-3
+    if act == torch.bfloat16:
+        tol = max(tol, 8e-3)                      # one bf16 ulp of the largest output
+    elif act == torch.float16:
+        tol = max(tol, 2.5e-3)
+    assert H.rel_err(res["out_gpu"], res["out_ref"]) < tol, (cache, d, bs, hkv, g, act, past, new)
+
+
 def test_host_entry_point_matches():
     wl = H.small_workload(hq=8, hkv=2, d=128, bs=32, act=torch.bfloat16, cache="u8", past=[0, 40, 300], new=[20, 1, 1], seed=43)
     _check(H.run_both(wl, host_entry=True), "u8", torch.bfloat16)
