@@ -228,15 +228,15 @@ __global__ void __launch_bounds__(256) write_kv_kernel(KernelArgs a) {
     }
 }
 
-// D/8 lanes per (rotated block, kv head, token).  Lane l owns the pairs (j, j + D/2) for
-// j in 4*l .. 4*l+3.  k'[j] = fma(-k[j+D/2], s, k[j]*c);  k'[j+D/2] = fma(k[j], s, k[j+D/2]*c)
-// with c = lut[row][j], s = lut[row][D/2 + j].
+// HALF / EL lanes per (rotated block, kv head, token).  Lane l owns the pairs (j, j + D/2) for
+// j in EL*l .. EL*l + EL-1.  k'[j] = fma(-k[j+D/2], s, k[j]*c);  k'[j+D/2] = fma(k[j], s, k[j+D/2]*c)
+// with c = lut[row][j], s = lut[row][D/2 + j].  EL = 8: the three divisions of a token's new scale and
+// zero-point (every lane of the token computes them) are spread over sixteen elements per lane.
 template <int D>
 __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
-    // HALF / 4 lanes per token: a lane owns dims 4*l .. 4*l+3 of the first half and their partners
-    // in the second half, so every access is a 4-byte (u8) or 8-byte (f16 / bf16) vector.
     constexpr int HALF = D / 2;
-    constexpr int LPT = HALF / 4;          // lanes per token: 16 (D = 128) or 8 (D = 64)
+    constexpr int EL = 8;                  // pairs per lane: an 8-byte (u8) or 16-byte (f16 / bf16) vector per half
+    constexpr int LPT = HALF / EL;         // lanes per token: 8 (D = 128) or 4 (D = 64)
     // One CTA per rotated block; its sub-warps walk the block's (kv head, token) units.
     const int l = threadIdx.x % LPT;
     const int r = blockIdx.x;
@@ -245,32 +245,42 @@ __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
     const int row = a.rotation_deltas[r];
     const bool bad = block < 0 || block >= a.num_blocks || row < 0 || row >= a.rotation_lut_rows;
     if (bad && threadIdx.x == 0) atomicOr(a.status, PA_DEV_BAD_ROTATION);
+    const float* lut = a.rotation_trig_lut + (long long)(bad ? 0 : row) * D;
+    float cv[EL], sv[EL];
+#pragma unroll
+    for (int i = 0; i < EL; i += 4) {
+        const float4 c4 = *reinterpret_cast<const float4*>(lut + EL * l + i), s4 = *reinterpret_cast<const float4*>(lut + HALF + EL * l + i);
+        cv[i] = c4.x; cv[i + 1] = c4.y; cv[i + 2] = c4.z; cv[i + 3] = c4.w;
+        sv[i] = s4.x; sv[i + 1] = s4.y; sv[i + 2] = s4.z; sv[i + 3] = s4.w;
+    }
     for (int base = 0; base < units; base += blockDim.x / LPT) {   // warp-uniform trip count
     const int unit = base + threadIdx.x / LPT;
     const bool live = unit < units;
     const int uu = live ? unit : units - 1;
     const int tok = uu % a.g.bs, h = uu / a.g.bs;
     const bool work = live && !bad;
-    const float* lut = a.rotation_trig_lut + (long long)(bad ? 0 : row) * D;
     uint8_t* rec = (uint8_t*)a.key_cache + (long long)(bad ? 0 : block) * a.g.block_bytes + (long long)h * a.g.head_bytes;
     float* params = (float*)(rec + (long long)a.g.bs * D);
-    float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+    float lo[EL], hi[EL];
+#pragma unroll
+    for (int i = 0; i < EL; ++i) { lo[i] = 0.f; hi[i] = 0.f; }
     if (work) {
         if (a.g.cache == PA_DTYPE_U8) {
             const float sc = params[tok], zp = params[a.g.bs + tok];
-            const uint32_t wl = *reinterpret_cast<const uint32_t*>(rec + (long long)tok * D + 4 * l);
-            const uint32_t wh = *reinterpret_cast<const uint32_t*>(rec + (long long)tok * D + HALF + 4 * l);
+            const uint2 wl = *reinterpret_cast<const uint2*>(rec + (long long)tok * D + EL * l);
+            const uint2 wh = *reinterpret_cast<const uint2*>(rec + (long long)tok * D + HALF + EL * l);
+            const uint32_t wlv[2] = {wl.x, wl.y}, whv[2] = {wh.x, wh.y};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                lo[i] = dequant_one((wl >> (8 * i)) & 0xffu, sc, zp);
-                hi[i] = dequant_one((wh >> (8 * i)) & 0xffu, sc, zp);
+            for (int i = 0; i < EL; ++i) {
+                lo[i] = dequant_one((wlv[i >> 2] >> (8 * (i & 3))) & 0xffu, sc, zp);
+                hi[i] = dequant_one((whv[i >> 2] >> (8 * (i & 3))) & 0xffu, sc, zp);
             }
         } else {
             const uint16_t* p = (const uint16_t*)rec + (long long)tok * D;
-            const uint2 wl = *reinterpret_cast<const uint2*>(p + 4 * l), wh = *reinterpret_cast<const uint2*>(p + HALF + 4 * l);
-            const uint32_t wlv[2] = {wl.x, wl.y}, whv[2] = {wh.x, wh.y};
+            const uint4 wl = *reinterpret_cast<const uint4*>(p + EL * l), wh = *reinterpret_cast<const uint4*>(p + HALF + EL * l);
+            const uint32_t wlv[4] = {wl.x, wl.y, wl.z, wl.w}, whv[4] = {wh.x, wh.y, wh.z, wh.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < EL; ++i) {
                 const unsigned short el = (unsigned short)(wlv[i >> 1] >> (16 * (i & 1))), eh = (unsigned short)(whv[i >> 1] >> (16 * (i & 1)));
                 if (a.g.cache == PA_DTYPE_F16) {
                     lo[i] = __half2float(__ushort_as_half(el));
@@ -282,18 +292,16 @@ __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
             }
         }
     }
-    const float4 c4 = *reinterpret_cast<const float4*>(lut + 4 * l), s4 = *reinterpret_cast<const float4*>(lut + HALF + 4 * l);
-    const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
-    float nlo[4], nhi[4];
+    float nlo[EL], nhi[EL];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < EL; ++i) {
         nlo[i] = __fmaf_rn(-hi[i], sv[i], __fmul_rn(lo[i], cv[i]));
         nhi[i] = __fmaf_rn(lo[i], sv[i], __fmul_rn(hi[i], cv[i]));
     }
     if (a.g.cache == PA_DTYPE_U8) {
         float mn = fminf(nlo[0], nhi[0]), mx = fmaxf(nlo[0], nhi[0]);
 #pragma unroll
-        for (int i = 1; i < 4; ++i) {
+        for (int i = 1; i < EL; ++i) {
             mn = fminf(mn, fminf(nlo[i], nhi[i]));
             mx = fmaxf(mx, fmaxf(nlo[i], nhi[i]));
         }
@@ -307,20 +315,20 @@ __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
         __syncwarp();   // every lane has read the old parameters
         if (work) {
             if (l == 0) { params[tok] = sc; params[a.g.bs + tok] = zp; }
-            uint32_t wl = 0, wh = 0;
+            uint32_t wlv[2] = {0, 0}, whv[2] = {0, 0};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                wl |= quant_one(nlo[i], inv, zp) << (8 * i);
-                wh |= quant_one(nhi[i], inv, zp) << (8 * i);
+            for (int i = 0; i < EL; ++i) {
+                wlv[i >> 2] |= quant_one(nlo[i], inv, zp) << (8 * (i & 3));
+                whv[i >> 2] |= quant_one(nhi[i], inv, zp) << (8 * (i & 3));
             }
-            *reinterpret_cast<uint32_t*>(rec + (long long)tok * D + 4 * l) = wl;
-            *reinterpret_cast<uint32_t*>(rec + (long long)tok * D + HALF + 4 * l) = wh;
+            *reinterpret_cast<uint2*>(rec + (long long)tok * D + EL * l) = make_uint2(wlv[0], wlv[1]);
+            *reinterpret_cast<uint2*>(rec + (long long)tok * D + HALF + EL * l) = make_uint2(whv[0], whv[1]);
         }
     } else if (work) {
         uint16_t* p = (uint16_t*)rec + (long long)tok * D;
-        uint32_t wlv[2] = {0, 0}, whv[2] = {0, 0};
+        uint32_t wlv[4] = {0, 0, 0, 0}, whv[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < EL; ++i) {
             unsigned short el, eh;
             if (a.g.cache == PA_DTYPE_F16) {
                 el = __half_as_ushort(__float2half_rn(nlo[i]));
@@ -332,8 +340,8 @@ __global__ void __launch_bounds__(256) rotate_kernel(KernelArgs a) {
             wlv[i >> 1] |= (uint32_t)el << (16 * (i & 1));
             whv[i >> 1] |= (uint32_t)eh << (16 * (i & 1));
         }
-        *reinterpret_cast<uint2*>(p + 4 * l) = make_uint2(wlv[0], wlv[1]);
-        *reinterpret_cast<uint2*>(p + HALF + 4 * l) = make_uint2(whv[0], whv[1]);
+        *reinterpret_cast<uint4*>(p + EL * l) = make_uint4(wlv[0], wlv[1], wlv[2], wlv[3]);
+        *reinterpret_cast<uint4*>(p + HALF + EL * l) = make_uint4(whv[0], whv[1], whv[2], whv[3]);
     }
     }
 }
