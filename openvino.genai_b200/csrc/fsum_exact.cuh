@@ -302,13 +302,26 @@ FSX_HD uint32_t entry_key(uint64_t e) { return (uint32_t)(e >> 32); }
 FSX_HD uint32_t entry_idx(uint64_t e) { return 0xffffffffu - (uint32_t)e; }
 FSX_HD uint64_t make_entry(uint32_t key, uint32_t idx) { return ((uint64_t)key << 32) | (0xffffffffu - idx); }
 
+// Where a walk stood when it came to a bin: the exact sum and count of everything before the bin, and its place in the list.
+// A later walk of the same row with a lower threshold may start from the last such record that is still below its threshold
+// instead of from the top (the sums are the same additions in the same order).
+// One record per group of kCkGroup bins (the last bin of the group the walk came to).
+constexpr int kCkGroup = 4;
+struct Checkpoints {
+    float* s;
+    uint32_t* cnt;
+    uint16_t* j;
+    uint16_t* li;
+};
+
 // Continues the walk from (w.s, w.cnt, w.j, w.li) until the running sum exceeds `thr`, `limit`
 // elements have been added (limit 0: no limit), a bin cannot be taken, or the level ends.
 // `list` is sorted in descending order (key, then ascending index).  One thread runs this.
-FSX_HD void walk_level(Walk& w, Level L, const Bins& b, const uint64_t* list, int list_n, float thr, uint32_t limit) {
+FSX_HD void walk_level(Walk& w, Level L, const Bins& b, const uint64_t* list, int list_n, float thr, uint32_t limit, const Checkpoints* ck = nullptr) {
     for (;;) {
         if (w.j >= kBins) { w.status = kWalkEnd; return; }
         const int j = w.j;
+        if (ck) { const int g = j / kCkGroup; ck->s[g] = w.s; ck->cnt[g] = w.cnt; ck->j[g] = (uint16_t)j; ck->li[g] = (uint16_t)w.li; }
         if (b.C[j] == 0) { w.j = (int)b.next[j]; continue; }     // only empty bins up to the next stop
         const uint8_t f = b.flag[j];
         if (f & kBinListed) {

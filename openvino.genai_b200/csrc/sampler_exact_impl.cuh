@@ -27,6 +27,13 @@ struct ExactShared {
     uint32_t tie_bits[fsx::kBins / 32];
     unsigned long long list[kListCap];
     int list_n;
+    // checkpoints of the top-p run's walk over the first level's bins (fsx::Checkpoints), for the draws of the same row
+    float ck_s[fsx::kBins / fsx::kCkGroup];
+    uint32_t ck_cnt[fsx::kBins / fsx::kCkGroup];   // 0xffffffff: the walk never stood at a bin of this group
+    uint16_t ck_j[fsx::kBins / fsx::kCkGroup];
+    uint16_t ck_li[fsx::kBins / fsx::kCkGroup];
+    int ck_on;         // the checkpoints belong to this row
+    int ck_li_stale;   // the list was emptied after some were taken: their list positions are void
     // block scan / reduce scratch
     fsx::Step scan_step[kWarps];
     uint32_t scan_u32[kWarps];
@@ -485,7 +492,7 @@ __device__ void classify_bins(ExactShared& sh, int j_from, float s, uint32_t cnt
     __syncthreads();
     if (tid == 0) {
         sh.cleared = 0;
-        if ((int)sh.C[j_from] > kListCap - sh.list_n) { sh.cleared = 1; sh.list_n = 0; }
+        if ((int)sh.C[j_from] > kListCap - sh.list_n) { sh.cleared = 1; sh.list_n = 0; sh.ck_li_stale = 1; }
     }
     __syncthreads();
     if (sh.cleared) {
@@ -690,6 +697,21 @@ __device__ void sorted_run(ExactShared& sh, const RowCtx& c, uint32_t F_top, flo
         have_level = false;
     }
     __syncthreads();
+    const bool record = limit == 0 && sh.ck_on != 0;   // the top-p run of a row leaves checkpoints, its draws use them
+    if (limit != 0 && have_level && sh.ck_on != 0) {
+        // the last bin at which the top-p run stood with a sum and a count that this run has not passed either
+        int best = -1;
+        for (int g = tid; g < fsx::kBins / fsx::kCkGroup; g += kThreads) {
+            const uint32_t cn = sh.ck_cnt[g];
+            if (cn != 0xffffffffu && cn < limit && sh.ck_s[g] <= thr) best = g;
+        }
+        best = -block_min_int(-best, sh);
+        if (tid == 0 && best >= 0 && sh.ck_j[best] > 0) {
+            sh.walk.s = sh.ck_s[best]; sh.walk.cnt = sh.ck_cnt[best]; sh.walk.j = (int)sh.ck_j[best];
+            sh.walk.li = sh.ck_li_stale ? 0 : (int)sh.ck_li[best];
+        }
+        __syncthreads();
+    }
     for (;;) {
         if (!have_level) { pass_counts(sh, c); have_level = true; }
         prepare_walk(sh);
@@ -697,7 +719,9 @@ __device__ void sorted_run(ExactShared& sh, const RowCtx& c, uint32_t F_top, flo
             fsx::Walk w = sh.walk;
             const fsx::Bins b = bins_of(sh);
             const fsx::Level L = sh.level;
-            fsx::walk_level(w, L, b, reinterpret_cast<const uint64_t*>(sh.list), sh.list_n, thr, limit);
+            const fsx::Checkpoints ck{sh.ck_s, sh.ck_cnt, sh.ck_j, sh.ck_li};
+            const bool top_level = L.F == F_top && L.sh == fsx::kTopSh;
+            fsx::walk_level(w, L, b, reinterpret_cast<const uint64_t*>(sh.list), sh.list_n, thr, limit, record && top_level ? &ck : nullptr);
             int ctl = kCtlDone;
             if (w.status == fsx::kWalkEnd) {
                 const unsigned long long span = (unsigned long long)fsx::kBins << L.sh;
@@ -939,6 +963,9 @@ __global__ void __launch_bounds__(kThreads, SX_CTAS_PER_SM) sampler_exact_kernel
         bool have_level = true;   // top-p: the division pass counted the first level's bins
         uint32_t n_keep = 0;
         if (top_p_active) {
+            for (int j = tid; j < fsx::kBins / fsx::kCkGroup; j += kThreads) sh.ck_cnt[j] = 0xffffffffu;
+            if (tid == 0) { sh.ck_on = 1; sh.ck_li_stale = 0; }
+            __syncthreads();
             sorted_run(sh, ctx, F_top, p.top_p, 0u, (double)p.rand_u * (double)p.top_p, have_level);
             n_keep = sh.walk.cnt;
             total = sh.walk.s;
