@@ -558,12 +558,34 @@ __device__ void classify_bins(ExactShared& sh, int j_from, float s, uint32_t cnt
 // Descending bitonic sort of the list (padded with zeros, which sort last).
 __device__ void sort_list(ExactShared& sh) {
     const int n = sh.list_n;
-    int m = 1;
+    int m = 64;   // at least one warp's block of 64 entries
     while (m < n) m <<= 1;
     for (int i = n + threadIdx.x; i < m; i += kThreads) sh.list[i] = 0ull;
     __syncthreads();
-    for (int k = 2; k <= m; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // compare-exchange steps whose partners lie inside one block of 64 entries (j <= 32) are done by the block's warp with
+    // warp-level synchronisation only; the whole CTA meets only around the steps that reach across blocks
+    auto local_steps = [&](int k, int j_first) {   // the steps j_first, j_first / 2, ..., 1 of merge size k
+        for (int b0 = warp * 64; b0 < m; b0 += kWarps * 64) {
+            for (int j = j_first; j > 0; j >>= 1) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int i = b0 + lane + 32 * h;
+                    const int l = i ^ j;
+                    if (l > i) {
+                        const unsigned long long a = sh.list[i], c = sh.list[l];
+                        const bool desc = (i & k) == 0;
+                        if (desc ? a < c : a > c) { sh.list[i] = c; sh.list[l] = a; }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    };
+    for (int k = 2; k <= 64 && k <= m; k <<= 1) local_steps(k, k >> 1);
+    __syncthreads();
+    for (int k = 128; k <= m; k <<= 1) {
+        for (int j = k >> 1; j >= 64; j >>= 1) {
             for (int i = threadIdx.x; i < m; i += kThreads) {
                 const int l = i ^ j;
                 if (l > i) {
@@ -574,6 +596,8 @@ __device__ void sort_list(ExactShared& sh) {
             }
             __syncthreads();
         }
+        local_steps(k, 32);
+        __syncthreads();
     }
 }
 
