@@ -252,6 +252,7 @@ enum : uint8_t {
     kBinValid = 4,     // A[j] holds the sum of amounts under E[j]
     kBinDirty = 8,     // A[j] is to be accumulated by the next pass
     kBinCollect = 16,  // the next pass appends the bin's elements to the list
+    kBinStep = 32,     // listed bin: A[j] holds the composition of its elements' steps under E[j], in list order (pack_step)
 };
 
 struct Level {
@@ -272,6 +273,17 @@ struct Bins {
     uint8_t* E;       // [kBins] hypothesised exponent
     uint8_t* flag;    // [kBins]
 };
+
+// A step whose even-state amount is below 2^24 and whose two amounts differ by less than 128, in one word.
+FSX_HD bool step_packs(Step st) {
+    const long long d = (long long)st.b - (long long)st.a;
+    return st.a < kOne24 && st.b < kSat && d >= -128 && d <= 127;
+}
+FSX_HD uint32_t pack_step(Step st) { return st.a | ((uint32_t)(uint8_t)(int8_t)((int)st.b - (int)st.a) << 24); }
+FSX_HD Step unpack_step(uint32_t w) {
+    const uint32_t a = w & 0xffffffu;
+    return Step{a, (uint32_t)((int)a + (int)(int8_t)(uint8_t)(w >> 24))};
+}
 
 // plain: non-empty, summed as a whole
 FSX_HD bool bin_plain(const Bins& b, int j) {
@@ -325,6 +337,25 @@ FSX_HD void walk_level(Walk& w, Level L, const Bins& b, const uint64_t* list, in
         if (b.C[j] == 0) { w.j = (int)b.next[j]; continue; }     // only empty bins up to the next stop
         const uint8_t f = b.flag[j];
         if (f & kBinListed) {
+            if ((f & kBinStep) && w.s != 0.0f && (uint32_t)b.E[j] == state_exp(w.s)) {
+                // The bin's elements as one step: while the sum stays in the binade of the hypothesis (it only grows, so the end
+                // tells), below the threshold and short of the element limit, the composition of the elements' two-state steps
+                // in list order is what adding them one by one gives.
+                const uint32_t E = state_exp(w.s), S = state_sig(w.s);
+                const Step st = unpack_step(b.A[j]);
+                const uint32_t S2 = apply(st, S), n = b.C[j];
+                if (S2 < kOne24 && !(state_float(E, S2) > thr) && !(limit && w.cnt + n >= limit)) {
+                    while (w.li < list_n) {   // entries added earlier
+                        const uint32_t key = entry_key(list[w.li]);
+                        if (key >= L.F || bin_of(L, key) < (uint32_t)j) ++w.li; else break;
+                    }
+                    w.li += (int)n;
+                    w.s = state_float(E, S2);
+                    w.cnt += n;
+                    ++w.j;
+                    continue;
+                }
+            }
             while (w.li < list_n) {   // entries of this bin, one real addition each
                 const uint64_t e = list[w.li];
                 const uint32_t key = entry_key(e);

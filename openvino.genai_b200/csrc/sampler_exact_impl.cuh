@@ -516,11 +516,12 @@ __device__ void classify_bins(ExactShared& sh, int j_from, float s, uint32_t cnt
     bool want[kBinsPerThread];
     uint32_t Eh[kBinsPerThread];
     bool reach[kBinsPerThread];
+    bool cert[kBinsPerThread];
     unsigned long long wanted = 0;
 #pragma unroll
     for (int k = 0; k < kBinsPerThread; ++k) {
         const int j = j0 + k;
-        want[k] = false; reach[k] = false; Eh[k] = 0;
+        want[k] = false; reach[k] = false; Eh[k] = 0; cert[k] = false;
         if (j < j_from || sh.C[j] == 0) continue;
         const double lo = cum, hi = cum + (double)sh.R[j];
         const unsigned long long cbefore = cc;
@@ -529,6 +530,7 @@ __device__ void classify_bins(ExactShared& sh, int j_from, float s, uint32_t cnt
         reach[k] = true;
         if (sh.flag[j] & fsx::kBinListed) continue;
         const bool certain = fsx::hyp_exponent(lo, hi, kMargin, &Eh[k]);
+        cert[k] = certain;
         bool w = j == j_from || !certain || cbefore < kTopCount;
         if (lo * (1.0 - kMargin) <= (double)thr && (double)thr <= hi * (1.0 + kMargin)) w = true;
         if (thr2 > 0.0 && lo * (1.0 - kDrawMargin) <= thr2 && thr2 <= hi * (1.0 + kDrawMargin)) w = true;
@@ -546,7 +548,11 @@ __device__ void classify_bins(ExactShared& sh, int j_from, float s, uint32_t cnt
         if (!reach[k] || (sh.flag[j] & fsx::kBinListed)) continue;
         if (want[k]) {
             wanted_before += sh.C[j];
-            if (wanted_before <= (unsigned long long)room) { sh.flag[j] = fsx::kBinCollect; continue; }
+            if (wanted_before <= (unsigned long long)room) {
+                sh.E[j] = (uint8_t)(cert[k] ? Eh[k] : 0u);   // the exponent under which its elements may later be taken as one step, or none
+                sh.flag[j] = fsx::kBinCollect;
+                continue;
+            }
         }
         const bool same_hyp = (sh.flag[j] & fsx::kBinValid) && sh.E[j] == Eh[k];
         if (!same_hyp) { sh.E[j] = (uint8_t)Eh[k]; sh.flag[j] = fsx::kBinDirty; sh.A[j] = 0; sh.PA[j] = 0; }
@@ -702,6 +708,40 @@ __device__ void pass_amounts(ExactShared& sh, const RowCtx& c) {
     if (threadIdx.x == 0 && sh.list_n > kListCap) sh.list_n = kListCap;   // cannot happen: marks are granted within the room
     __syncthreads();
     sort_list(sh);
+    // Every listed bin with a hypothesis: the composition of its elements' steps in list order (one thread per bin: a bin holds
+    // a handful of elements; its entries are the run of keys of the bin's range in the sorted list).
+    if (sh.list_n > kTopCount + 64) {   // (a list of little more than the row's first elements has no bin worth a step)
+        const int n = sh.list_n;
+        const unsigned long long* list = sh.list;
+        for (int j = threadIdx.x; j < fsx::kBins; j += kThreads) {
+            const uint8_t f = sh.flag[j];
+            if (!(f & fsx::kBinListed)) continue;
+            sh.flag[j] = (uint8_t)(f & ~fsx::kBinStep);
+            const uint32_t E = sh.E[j];
+            if (E < 24u || E > 254u) continue;
+            const uint32_t hi_key = L.F - 1u - ((uint32_t)j << L.sh);
+            const long long lo_ll = (long long)L.F - ((long long)(j + 1) << L.sh);
+            const uint32_t lo_key = lo_ll > 0 ? (uint32_t)lo_ll : 0u;
+            int a = 0, z = n;   // first entry with key <= hi_key
+            while (a < z) {
+                const int mid = (a + z) >> 1;
+                if (fsx::entry_key(list[mid]) > hi_key) a = mid + 1; else z = mid;
+            }
+            fsx::Step st = fsx::step_identity();
+            uint32_t cnt = 0;
+            for (int i = a; i < n; ++i) {
+                const uint32_t key = fsx::entry_key(list[i]);
+                if (key < lo_key) break;
+                st = fsx::then(st, fsx::step_of(__uint_as_float(key), E));
+                ++cnt;
+            }
+            if (cnt == sh.C[j] && fsx::step_packs(st)) {
+                sh.A[j] = fsx::pack_step(st);
+                sh.flag[j] = (uint8_t)(f | fsx::kBinStep);
+            }
+        }
+        __syncthreads();
+    }
 }
 
 enum { kCtlDone = 0, kCtlNewLevel = 1, kCtlClassify = 2, kCtlRepeat = 3 };
