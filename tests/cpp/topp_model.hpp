@@ -37,6 +37,7 @@ struct Model {
     uint32_t rest_cnt = 0;
     bool have_level = false;
     long long passes = 0;
+    long long steps_made = 0;   // listed bins whose elements were composed into one step
 
     Model(const float* p_, int V_, float min_thr_) : p(p_), V(V_), min_thr(min_thr_) {
         A.assign(fsx::kBins, 0); C.assign(fsx::kBins, 0); PA.assign(fsx::kBins, 0); PC.assign(fsx::kBins, 0);
@@ -100,7 +101,11 @@ struct Model {
             if (same_hyp && (flag[j] & fsx::kBinTie)) want = true;
             if (want) {
                 wanted += C[j];
-                if (wanted <= room) { flag[j] = fsx::kBinCollect; continue; }
+                if (wanted <= room) {
+                    E[j] = (uint8_t)(certain ? Eh : 0u);   // the exponent under which the bin may later be taken as one step, or none
+                    flag[j] = fsx::kBinCollect;
+                    continue;
+                }
             }
             if (!same_hyp) { E[j] = (uint8_t)Eh; flag[j] = fsx::kBinDirty; A[j] = 0; }
         }
@@ -133,6 +138,27 @@ struct Model {
             else if (flag[j] & fsx::kBinDirty) flag[j] = (uint8_t)((flag[j] & ~fsx::kBinDirty) | fsx::kBinValid);
         }
         std::sort(list.begin(), list.end(), std::greater<uint64_t>());
+        // listed bins with a hypothesis: the composition of their elements' steps in list order (fsx::kBinStep)
+        if (list.size() > kTopCount + 64) {
+            for (int j = 0; j < fsx::kBins; ++j) {
+                if (!(flag[j] & fsx::kBinListed)) continue;
+                flag[j] = (uint8_t)(flag[j] & ~fsx::kBinStep);
+                if (E[j] < 24u || E[j] > 254u) continue;
+                fsx::Step st = fsx::step_identity();
+                uint32_t cnt = 0;
+                for (const uint64_t e : list) {
+                    const uint32_t key = fsx::entry_key(e);
+                    if (key >= L.F || fsx::bin_of(L, key) != (uint32_t)j) continue;
+                    st = fsx::then(st, fsx::step_of(fsx::bits_float(key), E[j]));
+                    ++cnt;
+                }
+                if (cnt == C[j] && fsx::step_packs(st)) {
+                    A[j] = fsx::pack_step(st);
+                    flag[j] = (uint8_t)(flag[j] | fsx::kBinStep);
+                    ++steps_made;
+                }
+            }
+        }
     }
 
     // prefix sums over plain bins and the next-stop table
