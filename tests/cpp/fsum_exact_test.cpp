@@ -202,7 +202,7 @@ static std::vector<float> softmax_row(std::mt19937_64& rng, int V, int kind) {
 
 static void test_walk(std::mt19937_64& rng, int rows) {
     std::uniform_real_distribution<float> U(0.0f, 1.0f);
-    long long passes = 0, steps = 0;
+    long long passes = 0, steps = 0, resumed = 0;
     int runs = 0;
     for (int t = 0; t < rows; ++t) {
         const int kind = t % 8;
@@ -217,13 +217,15 @@ static void test_walk(std::mt19937_64& rng, int rows) {
         const Ref want = reference_top_p(p, top_p, u, min_thr);
         topp_model::Model m(p.data(), V, min_thr);
         const topp_model::Result got = m.solve(top_p, u);
-        passes += m.passes; steps += m.steps_made; ++runs;
+        passes += m.passes; steps += m.steps_made; resumed += m.resumed; ++runs;
         CHECK(got.n_keep == want.n_keep && std::memcmp(&got.total, &want.total, 4) == 0 && got.pick_key == want.pick_key,
               "row %d kind %d V %d top_p %g u %g: n %u/%u total %a/%a pick key %08x/%08x", t, kind, V, top_p, u, got.n_keep, want.n_keep,
               got.total, want.total, got.pick_key, want.pick_key);
         if (got.pick_key == want.pick_key) CHECK(fsx::float_bits(p[got.pick_idx]) == got.pick_key, "row %d: picked index does not hold the picked key", t);
     }
-    std::printf("walk: %d rows, %.2f passes over the row on average, %lld listed bins composed into steps\n", runs, (double)passes / runs, steps);
+    std::printf("walk: %d rows, %.2f passes over the row on average, %lld listed bins composed into steps, %lld draws started from a checkpoint\n", runs,
+                (double)passes / runs, steps, resumed);
+    CHECK(resumed > 0, "no draw ever started from a checkpoint: that path went untested");
     CHECK(steps > 0, "no listed bin was ever composed into a step: that path of walk_level went untested");
 }
 

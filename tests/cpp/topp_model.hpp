@@ -38,6 +38,13 @@ struct Model {
     bool have_level = false;
     long long passes = 0;
     long long steps_made = 0;   // listed bins whose elements were composed into one step
+    long long resumed = 0;      // draws that started from a checkpoint of the top-p run
+    // checkpoints of the top-p run's walk over the first level (fsx::Checkpoints), as the kernel keeps them
+    std::vector<float> ck_s = std::vector<float>(fsx::kBins / fsx::kCkGroup, 0.0f);
+    std::vector<uint32_t> ck_cnt = std::vector<uint32_t>(fsx::kBins / fsx::kCkGroup, 0xffffffffu);
+    std::vector<uint16_t> ck_j = std::vector<uint16_t>(fsx::kBins / fsx::kCkGroup, 0);
+    std::vector<uint16_t> ck_li = std::vector<uint16_t>(fsx::kBins / fsx::kCkGroup, 0);
+    bool ck_li_stale = false;
 
     Model(const float* p_, int V_, float min_thr_) : p(p_), V(V_), min_thr(min_thr_) {
         A.assign(fsx::kBins, 0); C.assign(fsx::kBins, 0); PA.assign(fsx::kBins, 0); PC.assign(fsx::kBins, 0);
@@ -192,10 +199,21 @@ struct Model {
         fsx::Walk w{};
         w.s = 0.0f; w.cnt = 0; w.j = 0; w.li = 0;
         if (!have_level || L.F != F_top || L.sh != fsx::kTopSh) { L = fsx::Level{F_top, fsx::kTopSh}; have_level = false; }
+        const bool record = limit == 0;   // the top-p run leaves checkpoints, the draw uses them
+        if (limit != 0 && have_level) {
+            int best = -1;
+            for (int g = 0; g < fsx::kBins / fsx::kCkGroup; ++g)
+                if (ck_cnt[g] != 0xffffffffu && ck_cnt[g] < limit && ck_s[g] <= thr) best = g;
+            if (best >= 0 && ck_j[best] > 0) {
+                w.s = ck_s[best]; w.cnt = ck_cnt[best]; w.j = ck_j[best]; w.li = ck_li_stale ? 0 : (int)ck_li[best];
+                ++resumed;
+            }
+        }
+        const fsx::Checkpoints ck{ck_s.data(), ck_cnt.data(), ck_j.data(), ck_li.data()};
         for (;;) {
             if (!have_level) { pass_counts(); have_level = true; }
             prepare();
-            fsx::walk_level(w, L, b, list.data(), (int)list.size(), thr, limit);
+            fsx::walk_level(w, L, b, list.data(), (int)list.size(), thr, limit, record && L.F == F_top && L.sh == fsx::kTopSh ? &ck : nullptr);
 #ifdef TOPP_TRACE
             std::printf("walk: F %08x sh %d status %d j %d C %u s %a cnt %u list %zu rest %u\n", L.F, L.sh, w.status, w.j, w.j < fsx::kBins ? C[w.j] : 0u, w.s, w.cnt, list.size(), rest_cnt);
 #endif
@@ -227,7 +245,7 @@ struct Model {
                 w.j = 0; w.li = 0; have_level = false;
                 continue;
             }
-            if (classify(j, w.s, w.cnt, thr, limit, thr2)) w.li = 0;
+            if (classify(j, w.s, w.cnt, thr, limit, thr2)) { w.li = 0; ck_li_stale = true; }
             pass_amounts();
         }
     }
